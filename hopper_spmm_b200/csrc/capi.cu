@@ -1,0 +1,402 @@
+// C ABI of the library (include/b200_spmm.h): format handles, device plans, launches.
+// Replaces the host side of the reference's operator, fp16_spmm (src/fp16.cu:221-281).
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/b200_spmm.h"
+#include "common.hpp"
+#include "format.hpp"
+#include "spmm_kernel.cuh"
+#include "tensormap.hpp"
+
+namespace b200spmm {
+
+namespace {
+thread_local std::string g_last_cuda_error;
+}
+
+void record_cuda_error(cudaError_t e, const char *what) {
+    g_last_cuda_error = std::string(what) + ": " + cudaGetErrorString(e);
+    cudaGetLastError();  // clear the sticky-free error so later calls start clean
+}
+
+}  // namespace b200spmm
+
+using namespace b200spmm;
+
+struct b200spmm_btcf {
+    Btcf f;
+};
+
+struct b200spmm_plan {
+    b200spmm_btcf_info_t info{};
+    int device = 0;
+    int n_ctas = 0;
+    bool owns_format = false;
+    uint32_t *d_rowOffset = nullptr, *d_tcA2B = nullptr, *d_rowIdx = nullptr;
+    void *d_data = nullptr;
+    uint32_t *d_cta_window = nullptr;
+    uint32_t *d_status = nullptr;
+    CUtensorMap tmap_a{};
+    // buffers of the host-pointer entry point, grown on demand
+    void *d_B = nullptr, *d_C = nullptr;
+    size_t d_B_bytes = 0, d_C_bytes = 0;
+    b200spmm_launch_info_t last{};
+};
+
+namespace {
+
+template <bool kTf32, int kNs>
+int launch_one(b200spmm_plan *p, const SpmmParams &prm, cudaStream_t stream) {
+    using Cfg = SpmmCfg<kTf32, kNs>;
+    auto kernel = spmm_sm100_kernel<kTf32, kNs>;
+    static thread_local int configured_device = -1;
+    if (configured_device != p->device) {
+        B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes));
+        configured_device = p->device;
+    }
+    kernel<<<p->n_ctas, kThreads, Cfg::kSmemBytes, stream>>>(p->tmap_a, prm);
+    B200_CUDA_TRY(cudaGetLastError());
+    p->last.n_ctas = p->n_ctas;
+    p->last.threads = kThreads;
+    p->last.stages = Cfg::kStages;
+    p->last.feature_slab = kNs;
+    p->last.n_slabs = (int)prm.n_slabs;
+    p->last.smem_bytes = (int64_t)Cfg::kSmemBytes;
+    p->last.kernel_launches = 1;
+    return B200SPMM_OK;
+}
+
+template <bool kTf32>
+int launch_dtype(b200spmm_plan *p, SpmmParams &prm, cudaStream_t stream) {
+    const uint32_t n64 = (prm.n + 63u) / 64u * 64u;
+    const uint32_t ns = std::min(256u, n64);
+    prm.n_slabs = (prm.n + ns - 1) / ns;
+    switch (ns) {
+        case 64: return launch_one<kTf32, 64>(p, prm, stream);
+        case 128: return launch_one<kTf32, 128>(p, prm, stream);
+        case 192: return launch_one<kTf32, 192>(p, prm, stream);
+        default: return launch_one<kTf32, 256>(p, prm, stream);
+    }
+}
+
+int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, int n_ctas) {
+    const auto &info = p->info;
+    if (info.row_window != kRowWindow) return B200SPMM_ERR_UNSUPPORTED;
+    const int cw = info.dtype == B200SPMM_F16 ? 16 : 8;
+    if (info.col_window != cw) return B200SPMM_ERR_UNSUPPORTED;
+    if (info.total_tiles * (uint64_t)kRowWindow >= 0x7FFFFFFFull) return B200SPMM_ERR_UNSUPPORTED;  // TMA row coordinate
+    cudaDeviceProp prop;
+    B200_CUDA_TRY(cudaGetDeviceProperties(&prop, p->device));
+    if (prop.major != 10) return B200SPMM_ERR_NO_DEVICE;
+    if (n_ctas <= 0) n_ctas = prop.multiProcessorCount;
+    p->n_ctas = n_ctas;
+    std::vector<uint32_t> cta_window;
+    build_cta_schedule(h_rowOffset, info.eff_row_windows, n_ctas, &cta_window);
+    B200_CUDA_TRY(cudaMalloc(&p->d_cta_window, cta_window.size() * sizeof(uint32_t)));
+    B200_CUDA_TRY(cudaMemcpy(p->d_cta_window, cta_window.data(), cta_window.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
+    B200_CUDA_TRY(cudaMalloc(&p->d_status, sizeof(uint32_t)));
+    B200_CUDA_TRY(cudaMemset(p->d_status, 0, sizeof(uint32_t)));
+    if (info.total_tiles) {
+        // `data` seen as rows of 32 bytes: one tile is 16 consecutive rows.
+        const bool f16 = info.dtype == B200SPMM_F16;
+        if (!encode_2d(&p->tmap_a, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p->d_data,
+                       f16 ? 16 : 8, info.total_tiles * kRowWindow, 32, f16 ? 16 : 8, kRowWindow,
+                       CU_TENSOR_MAP_SWIZZLE_32B)) {
+            g_last_cuda_error = "cuTensorMapEncodeTiled failed for the tile array";
+            return B200SPMM_ERR_CUDA;
+        }
+    }
+    return B200SPMM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *b200spmm_status_string(int status) {
+    switch (status) {
+        case B200SPMM_OK: return "ok";
+        case B200SPMM_ERR_INVALID_ARG: return "invalid argument";
+        case B200SPMM_ERR_BAD_CSR: return "malformed CSR (row_ptr not monotone, wrong nnz, or column out of range)";
+        case B200SPMM_ERR_UNSUPPORTED: return "shape, size or alignment not supported";
+        case B200SPMM_ERR_NO_MEMORY: return "host allocation failed";
+        case B200SPMM_ERR_CUDA: return "CUDA call failed (see b200spmm_last_cuda_error)";
+        case B200SPMM_ERR_NO_DEVICE: return "no sm_100 device available";
+        case B200SPMM_ERR_DEVICE_TIMEOUT: return "a bounded wait inside the kernel ran out";
+        default: return "unknown status";
+    }
+}
+
+const char *b200spmm_last_cuda_error(void) { return g_last_cuda_error.c_str(); }
+
+int b200spmm_version(void) { return 100; }
+
+int b200spmm_csr2btcf_nobitmap(uint64_t rows, uint64_t cols, uint64_t nnz, const uint32_t *row_ptr,
+                               const uint32_t *col_idx, const void *values, int dtype, int row_window,
+                               int col_window, int n_threads, b200spmm_btcf_t **out) {
+    if (!out) return B200SPMM_ERR_INVALID_ARG;
+    *out = nullptr;
+    b200spmm_btcf *h = new (std::nothrow) b200spmm_btcf();
+    if (!h) return B200SPMM_ERR_NO_MEMORY;
+    int st = convert_csr_to_btcf(rows, cols, nnz, row_ptr, col_idx, values, dtype, row_window, col_window, n_threads, &h->f);
+    if (st != B200SPMM_OK) {
+        delete h;
+        return st;
+    }
+    *out = h;
+    return B200SPMM_OK;
+}
+
+int b200spmm_btcf_info(const b200spmm_btcf_t *h, b200spmm_btcf_info_t *info) {
+    if (!h || !info) return B200SPMM_ERR_INVALID_ARG;
+    const Btcf &f = h->f;
+    info->rows = f.rows;
+    info->cols = f.cols;
+    info->nnzs = f.nnzs;
+    info->total_row_windows = f.total_row_windows;
+    info->eff_row_windows = f.eff_row_windows;
+    info->total_tiles = f.total_tiles;
+    info->row_window = f.row_window;
+    info->col_window = f.col_window;
+    info->dtype = f.dtype;
+    info->elt_size = f.elt_size;
+    return B200SPMM_OK;
+}
+
+const uint32_t *b200spmm_btcf_rowOffset(const b200spmm_btcf_t *h) { return h ? h->f.rowOffset.data() : nullptr; }
+const uint32_t *b200spmm_btcf_tcA2B(const b200spmm_btcf_t *h) { return h ? h->f.tcA2B.data() : nullptr; }
+const void *b200spmm_btcf_data(const b200spmm_btcf_t *h) { return h ? h->f.data.data() : nullptr; }
+const uint32_t *b200spmm_btcf_rowIdx(const b200spmm_btcf_t *h) { return h ? h->f.rowIdx.data() : nullptr; }
+void b200spmm_btcf_destroy(b200spmm_btcf_t *h) { delete h; }
+
+int b200spmm_shard_rows(uint64_t rows, const uint32_t *row_ptr, int row_window, int parts, uint64_t *row_begin) {
+    return shard_rows(rows, row_ptr, row_window, parts, row_begin);
+}
+
+int b200spmm_build_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_ctas, uint32_t *cta_window) {
+    if (!rowOffset || !cta_window || n_ctas < 1) return B200SPMM_ERR_INVALID_ARG;
+    std::vector<uint32_t> cuts;
+    build_cta_schedule(rowOffset, eff_row_windows, n_ctas, &cuts);
+    std::memcpy(cta_window, cuts.data(), cuts.size() * sizeof(uint32_t));
+    return B200SPMM_OK;
+}
+
+void b200spmm_plan_destroy(b200spmm_plan_t *p) {
+    if (!p) return;
+    cudaSetDevice(p->device);
+    if (p->owns_format) {
+        cudaFree(p->d_rowOffset);
+        cudaFree(p->d_tcA2B);
+        cudaFree(p->d_rowIdx);
+        cudaFree(p->d_data);
+    }
+    cudaFree(p->d_cta_window);
+    cudaFree(p->d_status);
+    cudaFree(p->d_B);
+    cudaFree(p->d_C);
+    delete p;
+}
+
+int b200spmm_plan_create(const b200spmm_btcf_t *h, int device, int n_ctas, b200spmm_plan_t **out) {
+    if (!h || !out) return B200SPMM_ERR_INVALID_ARG;
+    *out = nullptr;
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || device < 0 || device >= n_dev) {
+        cudaGetLastError();
+        return B200SPMM_ERR_NO_DEVICE;
+    }
+    B200_CUDA_TRY(cudaSetDevice(device));
+    b200spmm_plan *p = new (std::nothrow) b200spmm_plan();
+    if (!p) return B200SPMM_ERR_NO_MEMORY;
+    p->device = device;
+    p->owns_format = true;
+    b200spmm_btcf_info(h, &p->info);
+    const Btcf &f = h->f;
+    auto upload = [&](void **dst, const void *src, size_t bytes) -> int {
+        B200_CUDA_TRY(cudaMalloc(dst, std::max<size_t>(bytes, 16)));
+        if (bytes) B200_CUDA_TRY(cudaMemcpy(*dst, src, bytes, cudaMemcpyHostToDevice));
+        return B200SPMM_OK;
+    };
+    int st = upload((void **)&p->d_rowOffset, f.rowOffset.data(), f.rowOffset.size() * 4);
+    if (st == B200SPMM_OK) st = upload((void **)&p->d_tcA2B, f.tcA2B.data(), f.tcA2B.size() * 4);
+    if (st == B200SPMM_OK) st = upload((void **)&p->d_rowIdx, f.rowIdx.data(), f.rowIdx.size() * 4);
+    if (st == B200SPMM_OK) st = upload(&p->d_data, f.data.data(), f.data.size());
+    if (st == B200SPMM_OK) st = plan_finish(p, f.rowOffset.data(), n_ctas);
+    if (st != B200SPMM_OK) {
+        b200spmm_plan_destroy(p);
+        return st;
+    }
+    *out = p;
+    return B200SPMM_OK;
+}
+
+int b200spmm_plan_create_device(const b200spmm_btcf_info_t *info, const uint32_t *d_rowOffset, const uint32_t *d_tcA2B,
+                                const void *d_data, const uint32_t *d_rowIdx, int device, int n_ctas,
+                                b200spmm_plan_t **out) {
+    if (!info || !out || !d_rowOffset) return B200SPMM_ERR_INVALID_ARG;
+    if (info->total_tiles && (!d_tcA2B || !d_data || !d_rowIdx)) return B200SPMM_ERR_INVALID_ARG;
+    if ((reinterpret_cast<uintptr_t>(d_data) & 15u) != 0) return B200SPMM_ERR_UNSUPPORTED;
+    *out = nullptr;
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || device < 0 || device >= n_dev) {
+        cudaGetLastError();
+        return B200SPMM_ERR_NO_DEVICE;
+    }
+    B200_CUDA_TRY(cudaSetDevice(device));
+    b200spmm_plan *p = new (std::nothrow) b200spmm_plan();
+    if (!p) return B200SPMM_ERR_NO_MEMORY;
+    p->device = device;
+    p->owns_format = false;
+    p->info = *info;
+    p->d_rowOffset = const_cast<uint32_t *>(d_rowOffset);
+    p->d_tcA2B = const_cast<uint32_t *>(d_tcA2B);
+    p->d_rowIdx = const_cast<uint32_t *>(d_rowIdx);
+    p->d_data = const_cast<void *>(d_data);
+    std::vector<uint32_t> h_rowOffset(info->eff_row_windows + 1);
+    int st = B200SPMM_OK;
+    if (cudaMemcpy(h_rowOffset.data(), d_rowOffset, h_rowOffset.size() * 4, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        record_cuda_error(cudaGetLastError(), "cudaMemcpy(rowOffset)");
+        st = B200SPMM_ERR_CUDA;
+    }
+    if (st == B200SPMM_OK && h_rowOffset[info->eff_row_windows] != info->total_tiles) st = B200SPMM_ERR_INVALID_ARG;
+    if (st == B200SPMM_OK) st = plan_finish(p, h_rowOffset.data(), n_ctas);
+    if (st != B200SPMM_OK) {
+        b200spmm_plan_destroy(p);
+        return st;
+    }
+    *out = p;
+    return B200SPMM_OK;
+}
+
+int b200spmm_plan_info(const b200spmm_plan_t *p, b200spmm_btcf_info_t *info) {
+    if (!p || !info) return B200SPMM_ERR_INVALID_ARG;
+    *info = p->info;
+    return B200SPMM_OK;
+}
+
+int b200spmm_plan_launch_info(const b200spmm_plan_t *p, b200spmm_launch_info_t *info) {
+    if (!p || !info) return B200SPMM_ERR_INVALID_ARG;
+    *info = p->last;
+    return B200SPMM_OK;
+}
+
+int b200spmm_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, void *d_C, int64_t ldc, int c_dtype,
+                  void *stream_v) {
+    if (!p || !d_B || !d_C || n <= 0 || ldb < n || ldc < n) return B200SPMM_ERR_INVALID_ARG;
+    if (c_dtype != B200SPMM_C_F32 && c_dtype != B200SPMM_C_F16) return B200SPMM_ERR_INVALID_ARG;
+    const int esz = p->info.elt_size, csz = c_dtype == B200SPMM_C_F32 ? 4 : 2;
+    if (n % 8 || n > 0x7FFFFFFF) return B200SPMM_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(d_B) & 15u) || (reinterpret_cast<uintptr_t>(d_C) & 15u)) return B200SPMM_ERR_UNSUPPORTED;
+    if ((ldb * esz) % 16 || (ldc * csz) % 16) return B200SPMM_ERR_UNSUPPORTED;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    B200_CUDA_TRY(cudaSetDevice(p->device));
+    p->last = b200spmm_launch_info_t{};
+    if (p->info.eff_row_windows == 0) {  // nothing stored: C is all zeros
+        B200_CUDA_TRY(cudaMemset2DAsync(d_C, (size_t)ldc * csz, 0, (size_t)n * csz, p->info.rows, stream));
+        return B200SPMM_OK;
+    }
+    SpmmParams prm{};
+    prm.rowOffset = p->d_rowOffset;
+    prm.tcA2B = p->d_tcA2B;
+    prm.rowIdx = p->d_rowIdx;
+    prm.cta_window = p->d_cta_window;
+    prm.B = d_B;
+    prm.C = d_C;
+    prm.ldb = ldb;
+    prm.ldc = ldc;
+    prm.rows = (uint32_t)p->info.rows;
+    prm.cols = (uint32_t)p->info.cols;
+    prm.n = (uint32_t)n;
+    prm.eff_row_windows = (uint32_t)p->info.eff_row_windows;
+    prm.c_is_half = c_dtype == B200SPMM_C_F16;
+    prm.status = p->d_status;
+    prm.wait_limit_ns = kDeviceWaitLimitNs;
+    return p->info.dtype == B200SPMM_F16 ? launch_dtype<false>(p, prm, stream) : launch_dtype<true>(p, prm, stream);
+}
+
+int b200spmm_fp16_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, void *d_C, int64_t ldc, int c_dtype,
+                       void *stream) {
+    if (!p) return B200SPMM_ERR_INVALID_ARG;
+    if (p->info.dtype != B200SPMM_F16) return B200SPMM_ERR_INVALID_ARG;
+    return b200spmm_spmm(p, d_B, ldb, n, d_C, ldc, c_dtype, stream);
+}
+
+int b200spmm_tf32_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, void *d_C, int64_t ldc, int c_dtype,
+                       void *stream) {
+    if (!p) return B200SPMM_ERR_INVALID_ARG;
+    if (p->info.dtype != B200SPMM_TF32) return B200SPMM_ERR_INVALID_ARG;
+    return b200spmm_spmm(p, d_B, ldb, n, d_C, ldc, c_dtype, stream);
+}
+
+int b200spmm_plan_sync(b200spmm_plan_t *p, void *stream_v) {
+    if (!p) return B200SPMM_ERR_INVALID_ARG;
+    B200_CUDA_TRY(cudaSetDevice(p->device));
+    B200_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream_v)));
+    uint32_t status = 0;
+    B200_CUDA_TRY(cudaMemcpy(&status, p->d_status, sizeof(status), cudaMemcpyDeviceToHost));
+    if (status) {
+        B200_CUDA_TRY(cudaMemset(p->d_status, 0, sizeof(status)));
+        return B200SPMM_ERR_DEVICE_TIMEOUT;
+    }
+    return B200SPMM_OK;
+}
+
+int b200spmm_spmm_host(b200spmm_plan_t *p, const void *h_B, int64_t n, void *h_C, int c_dtype) {
+    if (!p || !h_B || !h_C || n <= 0) return B200SPMM_ERR_INVALID_ARG;
+    if (c_dtype != B200SPMM_C_F32 && c_dtype != B200SPMM_C_F16) return B200SPMM_ERR_INVALID_ARG;
+    B200_CUDA_TRY(cudaSetDevice(p->device));
+    const size_t b_bytes = (size_t)p->info.cols * n * p->info.elt_size;
+    const size_t c_bytes = (size_t)p->info.rows * n * (c_dtype == B200SPMM_C_F32 ? 4 : 2);
+    if (b_bytes > p->d_B_bytes) {
+        cudaFree(p->d_B);
+        p->d_B = nullptr;
+        p->d_B_bytes = 0;
+        B200_CUDA_TRY(cudaMalloc(&p->d_B, b_bytes));
+        p->d_B_bytes = b_bytes;
+    }
+    if (c_bytes > p->d_C_bytes) {
+        cudaFree(p->d_C);
+        p->d_C = nullptr;
+        p->d_C_bytes = 0;
+        B200_CUDA_TRY(cudaMalloc(&p->d_C, c_bytes));
+        p->d_C_bytes = c_bytes;
+    }
+    B200_CUDA_TRY(cudaMemcpyAsync(p->d_B, h_B, b_bytes, cudaMemcpyHostToDevice, nullptr));
+    int st = b200spmm_spmm(p, p->d_B, n, n, p->d_C, n, c_dtype, nullptr);
+    if (st != B200SPMM_OK) return st;
+    B200_CUDA_TRY(cudaMemcpyAsync(h_C, p->d_C, c_bytes, cudaMemcpyDeviceToHost, nullptr));
+    return b200spmm_plan_sync(p, nullptr);
+}
+
+int b200spmm_bench(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, void *d_C, int64_t ldc, int c_dtype,
+                   int warmup, int runs, void *stream_v, float *total_ms) {
+    if (!p || !total_ms || warmup < 0 || runs < 1) return B200SPMM_ERR_INVALID_ARG;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    B200_CUDA_TRY(cudaSetDevice(p->device));
+    for (int i = 0; i < warmup; ++i) {
+        int st = b200spmm_spmm(p, d_B, ldb, n, d_C, ldc, c_dtype, stream_v);
+        if (st != B200SPMM_OK) return st;
+    }
+    cudaEvent_t e0, e1;
+    B200_CUDA_TRY(cudaEventCreate(&e0));
+    B200_CUDA_TRY(cudaEventCreate(&e1));
+    int st = B200SPMM_OK;
+    cudaEventRecord(e0, stream);
+    for (int i = 0; i < runs && st == B200SPMM_OK; ++i) st = b200spmm_spmm(p, d_B, ldb, n, d_C, ldc, c_dtype, stream_v);
+    cudaEventRecord(e1, stream);
+    if (st == B200SPMM_OK) st = b200spmm_plan_sync(p, stream_v);
+    if (st == B200SPMM_OK && cudaEventElapsedTime(total_ms, e0, e1) != cudaSuccess) {
+        record_cuda_error(cudaGetLastError(), "cudaEventElapsedTime");
+        st = B200SPMM_ERR_CUDA;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return st;
+}
+
+}  // extern "C"

@@ -1,0 +1,205 @@
+// CSR -> condensed row-window tiles, multi-threaded.  Same output, bit for bit, as the
+// reference's single-threaded CSR2BTCFNOBITMAP (src/utils/convert.h:146-225) at the same
+// window shape; row windows are independent, so each is converted by one thread.
+#include "format.hpp"
+
+#include <algorithm>
+#include <atomic>
+#include <cstring>
+#include <thread>
+
+#include "../../include/b200_spmm.h"
+
+namespace b200spmm {
+
+namespace {
+
+template <class Fn>
+void parallel_chunks(uint64_t n_items, uint64_t chunk, int n_threads, Fn fn) {
+    if (n_threads <= 0) n_threads = (int)std::thread::hardware_concurrency();
+    if (n_threads <= 0) n_threads = 1;
+    uint64_t n_chunks = (n_items + chunk - 1) / chunk;
+    if ((uint64_t)n_threads > n_chunks) n_threads = (int)std::max<uint64_t>(1, n_chunks);
+    std::atomic<uint64_t> next{0};
+    auto worker = [&]() {
+        for (;;) {
+            uint64_t c = next.fetch_add(1);
+            if (c >= n_chunks) break;
+            fn(c * chunk, std::min(n_items, (c + 1) * chunk));
+        }
+    };
+    if (n_threads == 1) {
+        worker();
+        return;
+    }
+    std::vector<std::thread> pool;
+    pool.reserve(n_threads);
+    for (int t = 0; t < n_threads; ++t) pool.emplace_back(worker);
+    for (auto &t : pool) t.join();
+}
+
+// Sorted distinct columns of rows [first, last).
+void window_columns(const uint32_t *row_ptr, const uint32_t *col_idx, uint64_t first, uint64_t last,
+                    std::vector<uint32_t> *cols) {
+    cols->assign(col_idx + row_ptr[first], col_idx + row_ptr[last]);
+    std::sort(cols->begin(), cols->end());
+    cols->erase(std::unique(cols->begin(), cols->end()), cols->end());
+}
+
+}  // namespace
+
+int validate_csr(uint64_t rows, uint64_t cols, uint64_t nnz, const uint32_t *row_ptr, const uint32_t *col_idx) {
+    if (!row_ptr || (nnz && !col_idx)) return B200SPMM_ERR_INVALID_ARG;
+    if (rows >= 0xFFFFFFFFull || cols > 0xFFFFFFFFull || nnz > 0xFFFFFFFFull) return B200SPMM_ERR_UNSUPPORTED;
+    if (row_ptr[0] != 0 || row_ptr[rows] != nnz) return B200SPMM_ERR_BAD_CSR;
+    std::atomic<int> bad{0};
+    parallel_chunks(rows, 1 << 16, 0, [&](uint64_t lo, uint64_t hi) {
+        for (uint64_t r = lo; r < hi; ++r) {
+            if (row_ptr[r + 1] < row_ptr[r] || row_ptr[r + 1] > nnz) {
+                bad = 1;
+                return;
+            }
+            for (uint64_t p = row_ptr[r]; p < row_ptr[r + 1]; ++p)
+                if (col_idx[p] >= cols) {
+                    bad = 1;
+                    return;
+                }
+        }
+    });
+    return bad ? B200SPMM_ERR_BAD_CSR : B200SPMM_OK;
+}
+
+int convert_csr_to_btcf(uint64_t rows, uint64_t cols, uint64_t nnz, const uint32_t *row_ptr,
+                        const uint32_t *col_idx, const void *values, int dtype, int row_window, int col_window,
+                        int n_threads, Btcf *out) {
+    if (!out || (nnz && !values)) return B200SPMM_ERR_INVALID_ARG;
+    if (dtype != B200SPMM_F16 && dtype != B200SPMM_TF32) return B200SPMM_ERR_INVALID_ARG;
+    if (row_window != 8 && row_window != 16) return B200SPMM_ERR_INVALID_ARG;
+    if (col_window == 0) col_window = dtype == B200SPMM_F16 ? 16 : 8;  // src/common.h:18,41
+    if (col_window != 4 && col_window != 8 && col_window != 16) return B200SPMM_ERR_INVALID_ARG;
+    int st = validate_csr(rows, cols, nnz, row_ptr, col_idx);
+    if (st != B200SPMM_OK) return st;
+
+    const uint64_t RW = (uint64_t)row_window, CW = (uint64_t)col_window;
+    const int esz = dtype == B200SPMM_F16 ? 2 : 4;
+    const uint64_t n_windows = (rows + RW - 1) / RW;
+
+    // Pass 1: tiles per window (0 marks an empty window, which the format omits, convert.h:162).
+    std::vector<uint32_t> window_tiles(n_windows);
+    parallel_chunks(n_windows, 256, n_threads, [&](uint64_t lo, uint64_t hi) {
+        std::vector<uint32_t> cols_w;
+        for (uint64_t w = lo; w < hi; ++w) {
+            uint64_t first = w * RW, last = std::min(rows, first + RW);
+            if (row_ptr[first] == row_ptr[last]) {
+                window_tiles[w] = 0;
+                continue;
+            }
+            window_columns(row_ptr, col_idx, first, last, &cols_w);
+            window_tiles[w] = (uint32_t)((cols_w.size() + CW - 1) / CW);
+        }
+    });
+
+    // Running sums over the non-empty windows.
+    std::vector<uint64_t> tile_base(n_windows + 1), eff_base(n_windows + 1);
+    uint64_t tiles = 0, eff = 0;
+    for (uint64_t w = 0; w < n_windows; ++w) {
+        tile_base[w] = tiles;
+        eff_base[w] = eff;
+        tiles += window_tiles[w];
+        eff += window_tiles[w] ? 1 : 0;
+    }
+    tile_base[n_windows] = tiles;
+    eff_base[n_windows] = eff;
+    if (tiles > 0xFFFFFFFFull) return B200SPMM_ERR_UNSUPPORTED;  // rowOffset is 32-bit (src/common.h:11)
+
+    Btcf &f = *out;
+    f = Btcf();
+    f.rows = rows;
+    f.cols = cols;
+    f.nnzs = nnz;
+    f.row_window = row_window;
+    f.col_window = col_window;
+    f.dtype = dtype;
+    f.elt_size = esz;
+    f.total_row_windows = n_windows;
+    f.eff_row_windows = eff;
+    f.total_tiles = tiles;
+    try {
+        f.rowOffset.assign(eff + 1, 0);
+        f.rowIdx.assign(eff, 0);
+        f.tcA2B.assign(tiles * CW, kIdxMax);
+        f.data.assign(tiles * RW * CW * esz, 0);
+    } catch (const std::bad_alloc &) {
+        return B200SPMM_ERR_NO_MEMORY;
+    }
+
+    // Pass 2: column lists and tile values.
+    const uint8_t *vals = static_cast<const uint8_t *>(values);
+    parallel_chunks(n_windows, 256, n_threads, [&](uint64_t lo, uint64_t hi) {
+        std::vector<uint32_t> cols_w;
+        for (uint64_t w = lo; w < hi; ++w) {
+            if (!window_tiles[w]) continue;
+            uint64_t first = w * RW, last = std::min(rows, first + RW);
+            window_columns(row_ptr, col_idx, first, last, &cols_w);
+            uint64_t e = eff_base[w], t0 = tile_base[w];
+            f.rowOffset[e + 1] = (uint32_t)(t0 + window_tiles[w]);
+            f.rowIdx[e] = (uint32_t)first;
+            std::memcpy(&f.tcA2B[t0 * CW], cols_w.data(), cols_w.size() * sizeof(uint32_t));
+            uint8_t *wdata = f.data.data() + t0 * RW * CW * esz;
+            for (uint64_t r = first; r < last; ++r) {
+                const uint64_t lr = r % RW;
+                for (uint64_t p = row_ptr[r]; p < row_ptr[r + 1]; ++p) {
+                    uint64_t slot = std::lower_bound(cols_w.begin(), cols_w.end(), col_idx[p]) - cols_w.begin();
+                    uint64_t off = (slot / CW) * RW * CW + lr * CW + slot % CW;  // row-major tile
+                    std::memcpy(wdata + off * esz, vals + p * esz, esz);  // repeated (r,c): last one stays
+                }
+            }
+        }
+    });
+    return B200SPMM_OK;
+}
+
+int shard_rows(uint64_t rows, const uint32_t *row_ptr, int row_window, int parts, uint64_t *row_begin) {
+    if (!row_ptr || !row_begin || parts < 1 || row_window < 1) return B200SPMM_ERR_INVALID_ARG;
+    const uint64_t RW = (uint64_t)row_window;
+    const uint64_t n_windows = (rows + RW - 1) / RW;
+    const uint64_t nnz = row_ptr[rows];
+    row_begin[0] = 0;
+    uint64_t w = 0;
+    for (int p = 1; p < parts; ++p) {
+        // first window whose starting nnz offset reaches p/parts of the total
+        const uint64_t target = (nnz * (uint64_t)p + parts - 1) / parts;
+        uint64_t lo = w, hi = n_windows;
+        while (lo < hi) {
+            uint64_t mid = (lo + hi) / 2;
+            if (row_ptr[std::min(rows, mid * RW)] < target) lo = mid + 1; else hi = mid;
+        }
+        w = lo;
+        row_begin[p] = std::min(rows, w * RW);
+    }
+    row_begin[parts] = rows;
+    return B200SPMM_OK;
+}
+
+void build_cta_schedule(const uint32_t *rowOffset, uint64_t eff, int n_ctas, std::vector<uint32_t> *cta_window) {
+    cta_window->assign((size_t)n_ctas + 1, (uint32_t)eff);
+    (*cta_window)[0] = 0;
+    // Cost of windows [0, w): their tiles plus one tile-equivalent per window for its epilogue,
+    // so matrices made of one-tile windows are still split evenly.
+    auto cost = [&](uint64_t w) { return (uint64_t)rowOffset[w] + w; };
+    const uint64_t total = eff ? cost(eff) : 0;
+    uint64_t w = 0;
+    for (int c = 1; c < n_ctas; ++c) {
+        const uint64_t target = (total * (uint64_t)c) / (uint64_t)n_ctas;
+        uint64_t lo = w, hi = eff;
+        while (lo < hi) {
+            uint64_t mid = (lo + hi) / 2;
+            if (cost(mid) < target) lo = mid + 1; else hi = mid;
+        }
+        w = lo;
+        (*cta_window)[c] = (uint32_t)w;
+    }
+    (*cta_window)[n_ctas] = (uint32_t)eff;
+}
+
+}  // namespace b200spmm

@@ -1,0 +1,39 @@
+// Host-side condensed row-window format (the reference's BTCF_MTX_NO_BITMAP,
+// src/utils/class.h:74-85) and its converter (src/utils/convert.h:146-225), with the
+// window shape as a run-time parameter and 64-bit element offsets.
+#pragma once
+
+#include <cstdint>
+#include <vector>
+
+namespace b200spmm {
+
+constexpr uint32_t kIdxMax = 0xFFFFFFFFu;  // IDX_MAX, src/common.h:47
+
+struct Btcf {
+    uint64_t rows = 0, cols = 0, nnzs = 0;
+    uint64_t total_row_windows = 0, eff_row_windows = 0, total_tiles = 0;
+    int row_window = 16, col_window = 16;
+    int dtype = 0;     // B200SPMM_F16 / B200SPMM_TF32
+    int elt_size = 2;  // bytes per value
+    std::vector<uint32_t> rowOffset;  // [eff+1], in tiles
+    std::vector<uint32_t> tcA2B;      // [tiles*CW], padded with kIdxMax
+    std::vector<uint8_t> data;        // [tiles*RW*CW*elt_size]
+    std::vector<uint32_t> rowIdx;     // [eff], first row of each non-empty window
+};
+
+// Returns a B200SPMM_* status.
+int validate_csr(uint64_t rows, uint64_t cols, uint64_t nnz, const uint32_t *row_ptr, const uint32_t *col_idx);
+
+int convert_csr_to_btcf(uint64_t rows, uint64_t cols, uint64_t nnz, const uint32_t *row_ptr,
+                        const uint32_t *col_idx, const void *values, int dtype, int row_window, int col_window,
+                        int n_threads, Btcf *out);
+
+int shard_rows(uint64_t rows, const uint32_t *row_ptr, int row_window, int parts, uint64_t *row_begin);
+
+// Persistent schedule: CTA c owns effective windows [cta_window[c], cta_window[c+1]); the cuts
+// follow the running tile count so every CTA streams about total_tiles / n_ctas tiles.
+void build_cta_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_ctas,
+                        std::vector<uint32_t> *cta_window);
+
+}  // namespace b200spmm

@@ -1,0 +1,232 @@
+// Inline-PTX layer for sm_100a: mbarrier (bounded waits), TMA tiled / gather4 loads,
+// cp.async row gathers, tcgen05 (TMEM allocation, MMA, commit, load) and the shared-memory /
+// instruction descriptors they consume.  Takes the place of the reference's sm_90a wrappers
+// (src/ptx/barrier.h, src/ptx/tma.h, src/ptx/wgmma.h, src/ptx/ptx_utils.h).
+//
+// Unlike the reference's mbarrier_wait (src/ptx/barrier.h:29-41), every wait here gives up
+// after a time limit and reports it, so a broken pipeline ends the kernel instead of hanging
+// the device.
+#pragma once
+
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace b200spmm {
+namespace ptx {
+
+#define B200_DEVICE __device__ __forceinline__
+
+B200_DEVICE uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+B200_DEVICE uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+B200_DEVICE bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "elect.sync _|p, 0xffffffff;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
+}
+
+// ------------------------------------------------------------------ mbarrier
+
+B200_DEVICE void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+B200_DEVICE void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+B200_DEVICE void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Adds `bytes` to the transaction count the current phase waits for, without arriving.
+B200_DEVICE void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+B200_DEVICE void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+B200_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Wait for the phase with the given parity to complete.  Returns false when `*abort_flag`
+// (shared memory) is raised by another role or when `limit_ns` elapses, in which case this
+// thread raises the flag itself.  The caller must then leave its loop.
+B200_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, uint64_t limit_ns) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > limit_ns) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ proxies and fences
+
+// Orders this thread's generic-proxy shared-memory accesses with async-proxy accesses
+// (TMA, tcgen05.mma operand reads).
+B200_DEVICE void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+B200_DEVICE void tcgen05_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+B200_DEVICE void tcgen05_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+B200_DEVICE void named_barrier_sync(uint32_t id, uint32_t n_threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n_threads) : "memory");
+}
+
+// ------------------------------------------------------------------ TMA loads (own HBM only)
+
+B200_DEVICE void prefetch_tensormap(const void *tmap) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+// 2-D tiled load: box at (x, y) -> smem, completion as bytes on `bar`.
+// x * element size must be a multiple of 16 bytes.
+B200_DEVICE void tma_load_2d(uint32_t dst, const void *tmap, int32_t x, int32_t y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+// Gather of four rows y0..y3 of a 2-D tensor, box width taken from the tensor map, starting at
+// column x.  The four rows land one after another in shared memory.
+B200_DEVICE void tma_gather4_2d(uint32_t dst, const void *tmap, int32_t x, int32_t y0, int32_t y1, int32_t y2,
+                                int32_t y3, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, "
+        "%4, %5, %6}], [%7];"
+        ::"r"(dst), "l"(tmap), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3), "r"(bar)
+        : "memory");
+}
+
+// ------------------------------------------------------------------ cp.async (16-byte gathers)
+
+// Copies 16 bytes global -> shared, bypassing L1; src_bytes < 16 zero-fills the rest
+// (src_bytes == 0 reads nothing and writes 16 zero bytes).
+B200_DEVICE void cp_async_16(uint32_t dst, const void *src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+B200_DEVICE void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+B200_DEVICE void cp_async_wait_group() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// ------------------------------------------------------------------ tensor memory
+
+// Whole-warp calls.  `n_cols` is a power of two in [32, 512]; the base address is written to
+// shared memory at `dst_smem`.
+B200_DEVICE void tmem_alloc(uint32_t dst_smem, uint32_t n_cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(n_cols)
+                 : "memory");
+}
+B200_DEVICE void tmem_relinquish_alloc_permit() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+B200_DEVICE void tmem_dealloc(uint32_t taddr, uint32_t n_cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(n_cols) : "memory");
+}
+
+// 32 lanes x 16 consecutive 32-bit columns: thread i of the warp receives lane
+// (taddr.lane + i), columns taddr.col .. +15.  A warp may only touch the 32 lanes of its own
+// quarter: lanes 32*(warp_id % 4) .. +31.
+B200_DEVICE void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
+        "%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+B200_DEVICE void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ------------------------------------------------------------------ tcgen05.mma
+
+// Shared-memory matrix descriptor (64 bit):
+//   [0,14)  start address >> 4          [16,30) leading-dimension byte offset >> 4
+//   [32,46) stride-dimension byte offset >> 4     [46,48) version = 1
+//   [49,52) base offset = 0             [61,64) swizzle: 0 none, 2 128B, 4 64B, 6 32B
+enum : uint32_t { kSwizzleNone = 0, kSwizzle128B = 2, kSwizzle64B = 4, kSwizzle32B = 6 };
+
+B200_DEVICE uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t swizzle) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)(swizzle & 7u) << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::f16 / kind::tf32 with fp32 accumulation:
+//   [4,6) D format (1 = f32)   [7,10) A format   [10,13) B format  (0 f16, 1 bf16, 2 tf32)
+//   [15] A is MN-major   [16] B is MN-major   [17,23) N >> 3   [24,29) M >> 4
+enum : uint32_t { kFmtF16 = 0, kFmtBF16 = 1, kFmtTF32 = 2 };
+
+__host__ __device__ constexpr uint32_t make_instr_desc(uint32_t fmt, uint32_t m, uint32_t n, bool a_mn_major,
+                                                       bool b_mn_major) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+           ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.  accumulate == 0 overwrites D.
+B200_DEVICE void umma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+B200_DEVICE void umma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Makes `bar` receive one arrival when every tcgen05.mma this thread issued so far has
+// finished (implies tcgen05.fence::before_thread_sync).
+B200_DEVICE void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+}  // namespace ptx
+}  // namespace b200spmm

@@ -1,0 +1,370 @@
+// Warp-specialised persistent SpMM kernel for sm_100a over the condensed row-window format.
+//
+// Takes the place of the reference's fp16_spmm_kernel (src/fp16.cu:36-175), which is an
+// sm_90a wgmma kernel with a two-stage ring, and supplies the tf32 kernel the reference
+// never wrote (src/tf32.cu holds only a CPU check).
+//
+// Mapping (same transposition the reference uses, src/fp16.cu:147): for a 16-row window and a
+// tile of CW condensed columns,
+//     Dt[features x 16 rows] += Bgather[features x CW] * Atile^T[CW x 16]
+// so the gathered rows of B are the UMMA "A" operand (M = 128 or 64 features, MN-major,
+// 128-byte swizzle: exactly how B's rows lie in memory) and the 16 x CW tile of the sparse
+// matrix is the UMMA "B" operand (N = 16, K-major, 32-byte swizzle: exactly how the tile lies
+// in `data`).  K per tile is 32 bytes for both element types (16 fp16 / 8 tf32), one
+// tcgen05.mma per tile and 128-feature chunk.  The accumulator lives in TMEM (16 columns per
+// chunk), double-buffered so a window's epilogue overlaps the next window's MMAs.
+//
+// Roles in a CTA of 288 threads:
+//   warps 0-3  epilogue: tcgen05.ld -> shared staging -> 16-byte coalesced row-major C stores,
+//              plus zero-fill of rows that belong to windows without entries
+//   warps 4-7  producers: warp p owns every 4th tile of the CTA's tile stream; lane 0 issues the
+//              TMA load of the 512-byte A tile, all lanes gather the tile's CW rows of B with
+//              16-byte cp.async copies straight into the swizzled operand layout
+//   warp  8    lane 0 issues tcgen05.mma / tcgen05.commit; the warp owns the TMEM allocation
+//
+// Every wait is bounded; on a timeout the roles drain and the kernel raises a status bit.
+#pragma once
+
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "common.hpp"
+#include "ptx_sm100.cuh"
+
+namespace b200spmm {
+
+constexpr int kRowWindow = 16;       // rows per window the kernels consume
+constexpr int kThreads = 288;        // 9 warps
+constexpr int kProducerWarps = 4;
+constexpr int kATileBytes = 512;     // 16 rows x 32 bytes
+constexpr uint32_t kAccCols = 32;    // TMEM columns per accumulator buffer (2 chunks x 16)
+constexpr uint32_t kTmemCols = 64;   // two accumulator buffers
+constexpr uint32_t kEpilogueBarrier = 1;  // named barrier id of the four epilogue warps
+
+struct SpmmParams {
+    const uint32_t *rowOffset;   // [eff+1] tiles
+    const uint32_t *tcA2B;       // [tiles*CW]
+    const uint32_t *rowIdx;      // [eff]
+    const uint32_t *cta_window;  // [gridDim.x+1] schedule: windows owned by each CTA
+    const void *B;               // [cols, n] row-major
+    void *C;                     // [rows, n] row-major
+    int64_t ldb, ldc;            // elements
+    uint32_t rows, cols, n;
+    uint32_t eff_row_windows;
+    uint32_t n_slabs;            // ceil(n / kNs)
+    uint32_t c_is_half;          // 0: fp32 C, 1: fp16 C
+    uint32_t *status;            // device status word
+    unsigned long long wait_limit_ns;
+};
+
+template <bool kTf32, int kNs>
+struct SpmmCfg {
+    static_assert(kNs == 64 || kNs == 128 || kNs == 192 || kNs == 256, "feature slab");
+    static constexpr int kCW = kTf32 ? 8 : 16;           // condensed columns per tile
+    static constexpr int kEsz = kTf32 ? 4 : 2;           // bytes per element of A and B
+    static constexpr int kGatherBytes = 32 * kNs;        // CW rows x kNs features
+    static constexpr int kStageBytes = kGatherBytes + kATileBytes;
+    static constexpr int kFullChunks = kNs / 128;        // M = 128 MMAs per tile
+    static constexpr bool kHalfChunk = (kNs % 128) != 0; // plus one M = 64 MMA
+    static constexpr int kChunks = kFullChunks + (kHalfChunk ? 1 : 0);
+    // cp.async groups each producer warp keeps in flight, and ring depth (multiple of 4).
+    static constexpr int kLag = kNs == 64 ? 11 : kNs == 128 ? 7 : kNs == 192 ? 5 : 3;
+    static constexpr int kStages = kNs == 64 ? 64 : kNs == 128 ? 40 : kNs == 192 ? 28 : 20;
+    static_assert(kStages % kProducerWarps == 0 && kStages / kProducerWarps > kLag, "ring too shallow");
+    static constexpr int kChunksPerRow = kNs * kEsz / 16;           // 16-byte pieces per gathered row
+    static constexpr int kCopiesPerLane = kCW * kChunksPerRow / 32;  // == kNs / 16
+    static constexpr int kStagingBytes = kRowWindow * kNs * 4;
+    static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
+    static constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + kStagingBytes + kBarrierBytes;
+};
+
+template <bool kTf32, int kNs>
+__global__ void __launch_bounds__(kThreads, 1)
+spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p) {
+    using Cfg = SpmmCfg<kTf32, kNs>;
+    constexpr int kStages = Cfg::kStages;
+    extern __shared__ uint8_t smem_raw[];
+
+    // ---- shared memory carve-up (1024-byte aligned: swizzle patterns follow address bits)
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t *base = smem_raw + pad;
+    const uint32_t gather_addr = raw_addr + pad;                               // kStages x kGatherBytes
+    const uint32_t atile_addr = gather_addr + kStages * Cfg::kGatherBytes;      // kStages x 512
+    float *staging = reinterpret_cast<float *>(base + kStages * Cfg::kStageBytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(base + kStages * Cfg::kStageBytes + Cfg::kStagingBytes);
+    const uint32_t bars_addr = atile_addr + kStages * kATileBytes + Cfg::kStagingBytes;
+    auto full_bar = [&](int s) { return bars_addr + 8u * (uint32_t)s; };
+    auto empty_bar = [&](int s) { return bars_addr + 8u * (uint32_t)(kStages + s); };
+    auto acc_full_bar = [&](int a) { return bars_addr + 8u * (uint32_t)(2 * kStages + a); };
+    auto acc_empty_bar = [&](int a) { return bars_addr + 8u * (uint32_t)(2 * kStages + 2 + a); };
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(bars + 2 * kStages + 4);
+    uint32_t *tmem_slot = const_cast<uint32_t *>(abort_flag) + 1;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint64_t limit = p.wait_limit_ns;
+
+    // ---- this CTA's share of the schedule
+    const uint32_t w_begin = p.cta_window[blockIdx.x], w_end = p.cta_window[blockIdx.x + 1];
+    const uint32_t tile_begin = p.rowOffset[w_begin], tile_end = p.rowOffset[w_end];
+    const uint32_t n_tiles = tile_end - tile_begin;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(full_bar(s), 1);
+            ptx::mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(acc_full_bar(a), 1);
+            ptx::mbar_init(acc_empty_bar(a), 4);
+        }
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tmap_a);
+    }
+    if (warp == 8) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
+        ptx::tmem_relinquish_alloc_permit();
+    }
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    ptx::tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 4) {
+        // =========================================================== epilogue warps
+        const int et = tid;  // 0..127
+        uint32_t acc_it = 0;
+        bool failed = false;
+        for (uint32_t slab = 0; slab < p.n_slabs && !failed; ++slab) {
+            const uint32_t f0 = slab * kNs;  // first feature of the slab
+            for (uint32_t w = w_begin; w < w_end; ++w, ++acc_it) {
+                const uint32_t a = acc_it & 1u;
+                bool ok = ptx::mbar_wait(acc_full_bar(a), (acc_it >> 1) & 1u, abort_flag, limit);
+                ptx::tcgen05_fence_after_sync();
+                if (ok) {
+#pragma unroll
+                    for (int c = 0; c < Cfg::kChunks; ++c) {
+                        uint32_t r[16];
+                        ptx::tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(warp * 32) << 16) + a * kAccCols + c * 16, r);
+                        ptx::tmem_ld_wait();
+                        const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
+                        // M = 128: lane l of warp q holds feature 32q + l.  M = 64: lanes 0-15 of warp q
+                        // hold features 16q + l.
+                        const int f = half_chunk ? c * 128 + warp * 16 + lane : c * 128 + warp * 32 + lane;
+                        if (!half_chunk || lane < 16) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) staging[j * kNs + f] = __uint_as_float(r[j]);
+                        }
+                    }
+                    ptx::tcgen05_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(acc_empty_bar(a));
+                }
+                // staging complete for all four warps (also agrees on failure)
+                uint32_t any_fail;
+                asm volatile(
+                    "{\n"
+                    ".reg .pred q, r;\n"
+                    "setp.ne.u32 q, %1, 0;\n"
+                    "barrier.cta.red.or.pred r, %2, %3, q;\n"
+                    "selp.u32 %0, 1, 0, r;\n"
+                    "}\n"
+                    : "=r"(any_fail)
+                    : "r"((uint32_t)(ok ? 0 : 1)), "r"(kEpilogueBarrier), "r"(128u)
+                    : "memory");
+                if (any_fail) {
+                    failed = true;
+                    break;
+                }
+                const uint32_t row0 = p.rowIdx[w];
+                constexpr int kVecPerRow = kNs / 4;
+#pragma unroll
+                for (int it = 0; it < kRowWindow * kVecPerRow / 128; ++it) {
+                    const int idx = it * 128 + et;
+                    const int r = idx / kVecPerRow, c4 = idx % kVecPerRow;
+                    const uint32_t row = row0 + r, feat = f0 + c4 * 4;
+                    if (row < p.rows && feat < p.n) {
+                        const float4 v = *reinterpret_cast<const float4 *>(staging + r * kNs + c4 * 4);
+                        if (p.c_is_half) {
+                            __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+                            uint2 packed;
+                            packed.x = *reinterpret_cast<uint32_t *>(&lo);
+                            packed.y = *reinterpret_cast<uint32_t *>(&hi);
+                            *reinterpret_cast<uint2 *>(static_cast<__half *>(p.C) + (int64_t)row * p.ldc + feat) = packed;
+                        } else {
+                            *reinterpret_cast<float4 *>(static_cast<float *>(p.C) + (int64_t)row * p.ldc + feat) = v;
+                        }
+                    }
+                }
+                // Rows of windows that hold no entries are absent from the format: clear the gap
+                // that follows this window (and the one before the very first window).
+                {
+                    uint32_t gap_lo = row0 + kRowWindow;
+                    const uint32_t gap_hi = (w + 1 < p.eff_row_windows) ? p.rowIdx[w + 1] : p.rows;
+                    uint32_t lead_hi = 0;
+                    if (w == 0) lead_hi = row0;
+                    const uint32_t slab_feats = min((uint32_t)kNs, p.n - f0);
+                    const uint32_t vec_per_row = slab_feats / 4;
+                    for (int pass = 0; pass < 2; ++pass) {
+                        const uint32_t lo = pass == 0 ? gap_lo : 0u, hi = pass == 0 ? gap_hi : lead_hi;
+                        if (hi <= lo || lo >= p.rows) continue;
+                        const uint64_t total = (uint64_t)(hi - lo) * vec_per_row;
+                        for (uint64_t i = et; i < total; i += 128) {
+                            const uint32_t row = lo + (uint32_t)(i / vec_per_row), feat = f0 + (uint32_t)(i % vec_per_row) * 4;
+                            if (p.c_is_half)
+                                *reinterpret_cast<uint2 *>(static_cast<__half *>(p.C) + (int64_t)row * p.ldc + feat) = make_uint2(0, 0);
+                            else
+                                *reinterpret_cast<float4 *>(static_cast<float *>(p.C) + (int64_t)row * p.ldc + feat) = make_float4(0, 0, 0, 0);
+                        }
+                    }
+                }
+                // staging may be overwritten by the next window
+                ptx::named_barrier_sync(kEpilogueBarrier, 128);
+            }
+        }
+    } else if (warp < 8) {
+        // =========================================================== producer warps
+        const int pw = warp - 4;
+        const uint8_t *Bbytes = static_cast<const uint8_t *>(p.B);
+        const uint64_t row_pitch = (uint64_t)p.ldb * Cfg::kEsz;
+        // Per-lane constants of the gather: copy i moves 16-byte piece (i*32 + lane) of the tile.
+        uint32_t dst_off[Cfg::kCopiesPerLane];   // byte offset inside the stage, swizzled
+        uint32_t src_off[Cfg::kCopiesPerLane];   // byte offset inside the slab's part of a B row
+        uint32_t k_of[Cfg::kCopiesPerLane];      // which of the tile's CW rows
+#pragma unroll
+        for (int i = 0; i < Cfg::kCopiesPerLane; ++i) {
+            const uint32_t q = i * 32 + lane;
+            const uint32_t k = q / Cfg::kChunksPerRow, piece = q % Cfg::kChunksPerRow;
+            const uint32_t h = piece >> 3, cc = piece & 7u;  // 128-byte column block, piece inside it
+            uint32_t atom, kr;
+            if (kTf32) { atom = h; kr = k; } else { atom = h * 2 + (k >> 3); kr = k & 7u; }
+            dst_off[i] = atom * 1024u + kr * 128u + ((cc ^ kr) << 4);
+            src_off[i] = piece * 16u;
+            k_of[i] = k;
+        }
+        bool failed = false;
+        uint64_t it = 0;  // iterations this warp has issued
+        // Position of this warp's next tile in the CTA's stream: (slab, tile inside the slab pass),
+        // ring stage and how often that stage has been used.  The warp advances 4 tiles a time.
+        uint32_t slab = 0, tpos = (uint32_t)pw, s = (uint32_t)pw, use = 0, s_arrive = (uint32_t)pw;
+        auto normalise = [&](uint32_t &sl, uint32_t &tp) {
+            while (tp >= n_tiles && sl < p.n_slabs) { tp -= n_tiles; ++sl; }
+        };
+        if (n_tiles == 0) slab = p.n_slabs; else normalise(slab, tpos);
+        uint32_t idx_next = 0;
+        if (slab < p.n_slabs) idx_next = p.tcA2B[(uint64_t)(tile_begin + tpos) * Cfg::kCW + (lane % Cfg::kCW)];
+        const uint32_t n_bytes = p.n * Cfg::kEsz;
+        while (slab < p.n_slabs) {
+            const uint32_t tile = tile_begin + tpos;
+            const uint32_t slab_byte0 = slab * kNs * Cfg::kEsz;
+            const uint32_t idx_cur = idx_next;
+            // column indices of this warp's next tile, fetched a whole iteration early
+            uint32_t slab_n = slab, tpos_n = tpos + kProducerWarps;
+            normalise(slab_n, tpos_n);
+            if (slab_n < p.n_slabs) idx_next = p.tcA2B[(uint64_t)(tile_begin + tpos_n) * Cfg::kCW + (lane % Cfg::kCW)];
+
+            bool ok = ptx::mbar_wait(empty_bar(s), (use & 1u) ^ 1u, abort_flag, limit);
+            if (__any_sync(0xffffffffu, !ok)) { failed = true; break; }
+            if (lane == 0) {
+                ptx::mbar_expect_tx(full_bar(s), kATileBytes);
+                ptx::tma_load_2d(atile_addr + s * kATileBytes, &tmap_a, 0, (int32_t)(tile * kRowWindow), full_bar(s));
+            }
+            const uint32_t stage_addr = gather_addr + s * Cfg::kGatherBytes;
+#pragma unroll
+            for (int i = 0; i < Cfg::kCopiesPerLane; ++i) {
+                const uint32_t col = __shfl_sync(0xffffffffu, idx_cur, k_of[i]);
+                const uint32_t in_row = slab_byte0 + src_off[i];
+                const bool live = col < p.cols && in_row < n_bytes;  // padded slots hold 0xFFFFFFFF
+                const uint8_t *src = live ? Bbytes + (uint64_t)col * row_pitch + in_row : Bbytes;
+                ptx::cp_async_16(stage_addr + dst_off[i], src, live ? 16u : 0u);
+            }
+            ptx::cp_async_commit();
+            if (it >= (uint64_t)Cfg::kLag) {  // the copies issued kLag iterations ago have landed
+                ptx::cp_async_wait_group<Cfg::kLag>();
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(full_bar(s_arrive));
+                s_arrive += kProducerWarps;
+                if (s_arrive >= (uint32_t)kStages) s_arrive -= kStages;
+            }
+            ++it;
+            slab = slab_n;
+            tpos = tpos_n;
+            s += kProducerWarps;
+            if (s >= (uint32_t)kStages) { s -= kStages; ++use; }
+        }
+        // drain: everything this warp issued has to land before the CTA may exit
+        ptx::cp_async_wait_group<0>();
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (!failed && lane == 0) {
+            const uint64_t pending = it < (uint64_t)Cfg::kLag ? it : (uint64_t)Cfg::kLag;
+            for (uint64_t i = 0; i < pending; ++i) {
+                ptx::mbar_arrive(full_bar(s_arrive));
+                s_arrive += kProducerWarps;
+                if (s_arrive >= (uint32_t)kStages) s_arrive -= kStages;
+            }
+        }
+    } else {
+        // =========================================================== MMA issuer (warp 8, lane 0)
+        if (lane == 0) {
+            constexpr uint32_t fmt = kTf32 ? ptx::kFmtTF32 : ptx::kFmtF16;
+            constexpr uint32_t idesc_full = ptx::make_instr_desc(fmt, 128, kRowWindow, true, false);
+            constexpr uint32_t idesc_half = ptx::make_instr_desc(fmt, 64, kRowWindow, true, false);
+            // gathered-B operand: MN-major, 128-byte swizzle.  fp16: 64-feature blocks 2 KiB apart,
+            // 8-row groups 1 KiB apart.  tf32: 32-feature blocks 1 KiB apart, one 8-row group.
+            constexpr uint32_t a_lbo = kTf32 ? 1024u : 2048u, a_sbo = 1024u;
+            const uint64_t a_hi = ptx::make_smem_desc(0, a_lbo, a_sbo, ptx::kSwizzle128B) & ~0x3FFFull;
+            // A-tile operand: K-major, 32-byte swizzle, 8-row groups 256 bytes apart.
+            const uint64_t b_hi = ptx::make_smem_desc(0, 16, 256, ptx::kSwizzle32B) & ~0x3FFFull;
+            uint32_t s = 0, phase = 0;  // ring stage and the parity of its current use
+            uint32_t acc_it = 0;
+            bool ok = true;
+            for (uint32_t slab = 0; slab < p.n_slabs && ok; ++slab) {
+                uint32_t off_lo = p.rowOffset[w_begin];
+                for (uint32_t w = w_begin; w < w_end && ok; ++w, ++acc_it) {
+                    const uint32_t off_hi = p.rowOffset[w + 1];
+                    const uint32_t nt = off_hi - off_lo;
+                    off_lo = off_hi;
+                    const uint32_t a = acc_it & 1u;
+                    ok = ptx::mbar_wait(acc_empty_bar(a), ((acc_it >> 1) & 1u) ^ 1u, abort_flag, limit);
+                    if (!ok) break;
+                    ptx::tcgen05_fence_after_sync();
+                    for (uint32_t t = 0; t < nt; ++t) {
+                        ok = ptx::mbar_wait(full_bar(s), phase, abort_flag, limit);
+                        if (!ok) break;
+                        ptx::tcgen05_fence_after_sync();
+                        const uint64_t bd = b_hi | (uint64_t)(((atile_addr + s * kATileBytes) >> 4) & 0x3FFFu);
+                        const uint32_t g = gather_addr + s * Cfg::kGatherBytes;
+#pragma unroll
+                        for (int c = 0; c < Cfg::kChunks; ++c) {
+                            const uint64_t ad = a_hi | (uint64_t)(((g + c * 4096u) >> 4) & 0x3FFFu);
+                            const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
+                            const uint32_t d = tmem_base + a * kAccCols + c * 16;
+                            if (kTf32) ptx::umma_tf32_ss(d, ad, bd, half_chunk ? idesc_half : idesc_full, t != 0);
+                            else ptx::umma_f16_ss(d, ad, bd, half_chunk ? idesc_half : idesc_full, t != 0);
+                        }
+                        ptx::umma_commit(empty_bar(s));
+                        if (++s == (uint32_t)kStages) { s = 0; phase ^= 1u; }
+                    }
+                    if (ok) ptx::umma_commit(acc_full_bar(a));
+                }
+            }
+        }
+        __syncwarp();
+    }
+
+    // ---- teardown: every role ends up here, on success and on timeout alike
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    if (warp == 8) {
+        ptx::tcgen05_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (tid == 0 && *abort_flag) atomicOr(p.status, kDevStatusTimeout);
+}
+
+}  // namespace b200spmm

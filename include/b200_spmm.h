@@ -1,0 +1,188 @@
+/*
+ * b200_spmm.h - C ABI of the B200 (sm_100a) condensed row-window SpMM.
+ *
+ * The library replaces the host-side operator path of Ritt2020/hopper_spmm
+ *
+ *     CSR_MTX --CSR2BTCFNOBITMAP--> BTCF_MTX_NO_BITMAP --fp16_spmm / tf32--> dense C
+ *
+ * behind plain C entry points: pointers, sizes, integer status codes.  Nothing here
+ * exits the process or prints; every call returns B200SPMM_OK (0) or a negative code
+ * that b200spmm_status_string() explains.  Each declaration cites the reference
+ * interface it stands in for (paths are inside the reference project).
+ *
+ * Threading: handles are immutable once created and may be shared between threads.
+ * One launch per plan may be in flight at a time (the plan owns one status word and
+ * one persistent-schedule table on the device).
+ */
+#ifndef B200_SPMM_H_
+#define B200_SPMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ status codes */
+/* The reference reports errors by printing and exit(1) (src/utils/utils.h:9-21). */
+enum {
+    B200SPMM_OK = 0,
+    B200SPMM_ERR_INVALID_ARG = -1,   /* null pointer, bad enum, negative size            */
+    B200SPMM_ERR_BAD_CSR = -2,       /* row_ptr not monotone / ends != nnz / col >= cols */
+    B200SPMM_ERR_UNSUPPORTED = -3,   /* shape or alignment the kernels do not handle     */
+    B200SPMM_ERR_NO_MEMORY = -4,     /* host allocation failed                           */
+    B200SPMM_ERR_CUDA = -5,          /* a CUDA runtime / driver call failed              */
+    B200SPMM_ERR_NO_DEVICE = -6,     /* no sm_100 device, or the driver is missing       */
+    B200SPMM_ERR_DEVICE_TIMEOUT = -7 /* a bounded wait inside a kernel ran out           */
+};
+
+/* Element type of A's values and of B.  Mirrors -DUSE_FP16 / -DUSE_TF32 (src/common.h:14-43). */
+enum { B200SPMM_F16 = 0, B200SPMM_TF32 = 1 };
+/* Element type C is stored in.  The reference's DENSE_MTX is MAT_VAL_TYPE (src/utils/class.h:44-48). */
+enum { B200SPMM_C_F32 = 0, B200SPMM_C_F16 = 1 };
+
+const char *b200spmm_status_string(int status);
+/* Text of the last CUDA error seen by the calling thread ("" if none). */
+const char *b200spmm_last_cuda_error(void);
+int b200spmm_version(void);
+
+/* ------------------------------------------------------------------ format (host) */
+
+/* Opaque host-side BTCF_MTX_NO_BITMAP (src/utils/class.h:74-85). */
+typedef struct b200spmm_btcf b200spmm_btcf_t;
+
+/* Scalar fields of BTCF_MTX_NO_BITMAP plus the window shape, which the reference fixes at
+ * compile time (ROW_WINDOW / COL_WINDOW, src/common.h:17-18,40-41). */
+typedef struct {
+    uint64_t rows, cols, nnzs;
+    uint64_t total_row_windows; /* ceil(rows / row_window)             */
+    uint64_t eff_row_windows;   /* windows holding at least one entry  */
+    uint64_t total_tiles;       /* rowOffset[eff_row_windows]          */
+    int32_t row_window, col_window;
+    int32_t dtype;    /* B200SPMM_F16 / B200SPMM_TF32 */
+    int32_t elt_size; /* bytes per value in `data`    */
+} b200spmm_btcf_info_t;
+
+/*
+ * Replaces  void CSR2BTCFNOBITMAP(const CSR_MTX&, BTCF_MTX_NO_BITMAP&)   src/utils/convert.h:146-225
+ * with CSR_MTX (src/utils/class.h:30-37) passed as its fields.  Output is bit-identical to
+ * the reference algorithm for the same window shape: per non-empty row window the sorted
+ * distinct columns padded with 0xFFFFFFFF to a multiple of col_window, zero-filled
+ * row-major row_window x col_window tiles, rowOffset in tiles, rowIdx = first row.
+ *   dtype       B200SPMM_F16 (values are IEEE binary16) or B200SPMM_TF32 (values are fp32)
+ *   row_window  8 or 16 (the reference uses 8; the sm_100a kernels consume 16)
+ *   col_window  0 = the reference's choice for dtype (16 for f16, 8 for tf32), or 4/8/16
+ *   n_threads   host threads for the conversion, 0 = all
+ * Validates the CSR (the reference does not) and fails with B200SPMM_ERR_BAD_CSR.
+ */
+int b200spmm_csr2btcf_nobitmap(uint64_t rows, uint64_t cols, uint64_t nnz, const uint32_t *row_ptr,
+                               const uint32_t *col_idx, const void *values, int dtype, int row_window,
+                               int col_window, int n_threads, b200spmm_btcf_t **out);
+
+/* Field access of BTCF_MTX_NO_BITMAP (src/utils/class.h:74-85). Pointers stay valid until destroy. */
+int b200spmm_btcf_info(const b200spmm_btcf_t *f, b200spmm_btcf_info_t *info);
+const uint32_t *b200spmm_btcf_rowOffset(const b200spmm_btcf_t *f); /* [eff_row_windows + 1]              */
+const uint32_t *b200spmm_btcf_tcA2B(const b200spmm_btcf_t *f);     /* [total_tiles * col_window]         */
+const void *b200spmm_btcf_data(const b200spmm_btcf_t *f);          /* [total_tiles * row_window * col_window] */
+const uint32_t *b200spmm_btcf_rowIdx(const b200spmm_btcf_t *f);    /* [eff_row_windows]                  */
+/* The reference's structs are freed by going out of scope (std::vector members). */
+void b200spmm_btcf_destroy(b200spmm_btcf_t *f);
+
+/* ------------------------------------------------------------------ row-window sharding */
+
+/*
+ * nnz-balanced contiguous row ranges for `parts` GPUs, cut on row-window boundaries
+ * (the reference has no multi-GPU path; its only decomposition is row windows over CTAs,
+ * src/fp16.cu:86,138).  row_begin[parts+1] receives the cuts: part p owns rows
+ * [row_begin[p], row_begin[p+1]); every cut is a multiple of row_window or equals rows.
+ */
+int b200spmm_shard_rows(uint64_t rows, const uint32_t *row_ptr, int row_window, int parts, uint64_t *row_begin);
+
+/*
+ * Persistent schedule: cta_window[n_ctas+1] receives the cuts of the effective row windows
+ * over n_ctas persistent CTAs; CTA c streams windows [cta_window[c], cta_window[c+1]).  Cuts
+ * follow the running tile count (rowOffset), so every CTA gets about the same number of tiles
+ * however skewed the rows are.  Stands in for the reference's static `row += gridDim.x`
+ * round-robin (src/fp16.cu:86,138) and its unused Scheduler singleton (src/scheduler.h:5-42).
+ */
+int b200spmm_build_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_ctas, uint32_t *cta_window);
+
+/* ------------------------------------------------------------------ device plan */
+
+/* Device-resident format + persistent schedule. Replaces the cudaMalloc/cudaMemcpy block and
+ * create_tma_desc_A of fp16_spmm (src/fp16.cu:236-252, 177-219) and the unused Scheduler
+ * (src/scheduler.h:5-42). */
+typedef struct b200spmm_plan b200spmm_plan_t;
+
+/*
+ * Uploads a converted matrix to `device` and builds the schedule: contiguous runs of row
+ * windows per persistent CTA, balanced on tile count.  row_window must be 16.
+ * n_ctas = 0 selects one CTA per SM.
+ */
+int b200spmm_plan_create(const b200spmm_btcf_t *f, int device, int n_ctas, b200spmm_plan_t **out);
+
+/*
+ * Same, from format arrays that already live on `device` (for a GPU-side converter or a
+ * caller that keeps the format resident).  The plan borrows the four arrays; they must
+ * outlive it.  rowOffset is read back once to build the schedule.
+ */
+int b200spmm_plan_create_device(const b200spmm_btcf_info_t *info, const uint32_t *d_rowOffset,
+                                const uint32_t *d_tcA2B, const void *d_data, const uint32_t *d_rowIdx,
+                                int device, int n_ctas, b200spmm_plan_t **out);
+void b200spmm_plan_destroy(b200spmm_plan_t *p);
+int b200spmm_plan_info(const b200spmm_plan_t *p, b200spmm_btcf_info_t *info);
+
+/*
+ * C[rows, n] = A * B[cols, n] on the plan's device; B and C are device pointers, row-major
+ * with leading dimensions ldb / ldc in elements.  Asynchronous on `stream` (a cudaStream_t).
+ * Replaces the launch of fp16_spmm_kernel inside fp16_spmm (src/fp16.cu:36-175, 255-264)
+ * for both element types (the reference's tf32.cu has no kernel).
+ * Rows of windows with no entries are written as zeros, so C needs no prior clearing.
+ *   B, C 16-byte aligned; ldb*sizeof(b) and ldc*sizeof(c) multiples of 16; n a multiple of 8.
+ */
+int b200spmm_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, void *d_C, int64_t ldc,
+                  int c_dtype, void *stream);
+/* Named like the reference's operators (src/fp16.cu:221, src/tf32.cu); check the plan's dtype. */
+int b200spmm_fp16_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, void *d_C, int64_t ldc,
+                       int c_dtype, void *stream);
+int b200spmm_tf32_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, void *d_C, int64_t ldc,
+                       int c_dtype, void *stream);
+
+/*
+ * Blocks until `stream` is idle, then returns the kernel-side status of the plan's last
+ * launch (B200SPMM_ERR_DEVICE_TIMEOUT if a bounded wait gave up).
+ */
+int b200spmm_plan_sync(b200spmm_plan_t *p, void *stream);
+
+/*
+ * Host-buffer form of  PERF_RESULT fp16_spmm(BTCF_MTX_NO_BITMAP&, DENSE_MTX& B, DENSE_MTX& C)
+ * (src/fp16.cu:221-281): B [cols, n] and C [rows, n] are host arrays (dense, ld = n).  Copies B
+ * to the device, runs the product and - unlike the reference, which never reads C back -
+ * copies C to the host.  Device buffers for B and C are kept in the plan between calls.
+ * Synchronous.
+ */
+int b200spmm_spmm_host(b200spmm_plan_t *p, const void *h_B, int64_t n, void *h_C, int c_dtype);
+
+/*
+ * The reference's timing protocol (WARMUP_RUNS = 3, RUNS = 5, src/common.h:48-49; cudaEvent
+ * bracket, src/fp16.cu:255-268): `warmup` untimed launches, then `runs` back-to-back launches
+ * between two events on `stream`.  *total_ms receives the bracket time (PERF_RESULT.time).
+ */
+int b200spmm_bench(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, void *d_C, int64_t ldc,
+                   int c_dtype, int warmup, int runs, void *stream, float *total_ms);
+
+/* Per-launch facts of the most recent b200spmm_spmm on this plan. */
+typedef struct {
+    int32_t n_ctas, threads, stages;
+    int32_t feature_slab; /* features one CTA pass covers */
+    int32_t n_slabs;
+    int64_t smem_bytes;
+    int64_t kernel_launches; /* launches issued by that call */
+} b200spmm_launch_info_t;
+int b200spmm_plan_launch_info(const b200spmm_plan_t *p, b200spmm_launch_info_t *info);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_SPMM_H_ */

@@ -1,0 +1,59 @@
+/*
+ * b200_spmm_kat.h - single-tile known-answer entry points for the sm_100a primitives the
+ * SpMM kernels are built from.  They take the place of the reference's stand-alone bring-up
+ * programs: src/test_fp16.cu (one fp16 MMA tile), test/02.tma_and_wgmma/tma_wgmma.cu (one tf32
+ * MMA tile), test/01.tma_copy_matrix/copy.cu (a TMA box landing in shared memory) and
+ * test/03.warp_specialized/main.cu (tiles accumulated through a ring).
+ *
+ * Each call runs one CTA on `device`, is synchronous, takes HOST pointers and returns a
+ * B200SPMM_* status (b200_spmm.h).  Waits inside the kernels are bounded: a pipeline that never
+ * completes yields B200SPMM_ERR_DEVICE_TIMEOUT, not a hang.
+ */
+#ifndef B200_SPMM_KAT_H_
+#define B200_SPMM_KAT_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* One tcgen05.mma: operands described relative to the start of the shared-memory image. */
+typedef struct {
+    uint32_t a_off, a_lbo, a_sbo, a_swizzle; /* byte offset / leading / stride / swizzle code (0,2,4,6) */
+    uint32_t b_off, b_lbo, b_sbo, b_swizzle;
+    uint32_t idesc;      /* instruction descriptor                         */
+    uint32_t d_col;      /* first TMEM column of the accumulator           */
+    uint32_t accumulate; /* 0 = overwrite D, 1 = add to D                  */
+    uint32_t kind;       /* 0 = kind::f16, 1 = kind::tf32                  */
+} b200spmm_kat_mma_t;
+
+/*
+ * Copies `image` (image_bytes <= 96 KiB) into 1024-byte-aligned shared memory, issues the listed
+ * MMAs in order from one thread, then dumps TMEM lanes 0..127 x columns 0..n_cols-1 as fp32 into
+ * out[128 * n_cols].  n_cols is a multiple of 16, at most 128.
+ * Replaces tma_wgmma_kernel + test_result_cpu (src/test_fp16.cu:238-315).
+ */
+int b200spmm_kat_umma(const void *image, uint32_t image_bytes, const b200spmm_kat_mma_t *mmas, int n_mmas,
+                      int n_cols, float *out, int device);
+
+/* Builds an instruction descriptor: fmt 0 = f16, 1 = bf16, 2 = tf32; fp32 accumulate. */
+uint32_t b200spmm_kat_instr_desc(int fmt, int m, int n, int a_mn_major, int b_mn_major);
+
+/*
+ * Uploads a 2-D row-major tensor (rows x inner_elems, pitch_bytes between rows), encodes a tiled
+ * tensor map over it (box_inner x box_rows elements, swizzle 0 none / 1 32B / 2 64B / 3 128B),
+ * issues `n_loads` TMA loads and dumps dump_bytes of shared memory (from its 1024-byte-aligned
+ * start) to `dump`.  loads[i] = {mode, smem_off, x, y0, y1, y2, y3}: mode 0 is a tiled load of the
+ * box at (x, y0); mode 1 is a four-row gather (tile::gather4) of rows y0..y3 starting at column x.
+ * expect_bytes is the total byte count the loads must deliver.
+ * Replaces copy_and_verify_kernel (test/01.tma_copy_matrix/copy.cu:77-171).
+ */
+int b200spmm_kat_tma(const void *tensor, uint64_t inner_elems, uint64_t rows, uint64_t pitch_bytes, int elt_size,
+                     uint32_t box_inner, uint32_t box_rows, int swizzle, const int32_t *loads, int n_loads,
+                     uint32_t expect_bytes, void *dump, uint32_t dump_bytes, int device);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_SPMM_KAT_H_ */

@@ -1,0 +1,140 @@
+"""The shipped converter (through the C ABI) against the oracle and the reference's golden
+vectors, bit for bit, plus the host-side planners."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+import hopper_spmm_b200 as hs
+import oracle
+from cases import FORMAT_FIELDS, random_csr, same_format
+from hopper_spmm_b200 import _capi as capi
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def convert(rows, cols, rp, ci, v, rw=16, cw=0, threads=0):
+    return hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v), row_window=rw, col_window=cw, n_threads=threads)
+
+
+@pytest.mark.parametrize("flavour", ["fp16", "tf32"])
+@pytest.mark.parametrize("case", ["hand", "rand_a", "rand_b"])
+def test_library_matches_reference_golden(flavour, case):
+    g = np.load(os.path.join(GOLDEN, f"format_ref_{flavour}.npz"))
+    rows, cols = (int(x) for x in g[f"{case}_shape"])
+    f = convert(rows, cols, g[f"{case}_row_ptr"], g[f"{case}_col_idx"], g[f"{case}_values"], rw=8)
+    for k in FORMAT_FIELDS:
+        assert np.array_equal(np.asarray(getattr(f, k)).view(np.uint8), g[f"{case}_{k}"].view(np.uint8)), k
+    assert f.total_row_windows == (rows + 7) // 8
+
+
+@pytest.mark.parametrize("dt,cw", [(np.float16, 16), (np.float32, 8), (np.float32, 4), (np.float16, 8)])
+@pytest.mark.parametrize("rw", [8, 16])
+def test_library_matches_oracle(dt, cw, rw):
+    shapes = [(1, 1, 1.0), (16, 16, 0.5), (17, 33, 0.2), (203, 517, 0.03), (500, 70000, 0.0005), (96, 7, 0.6)]
+    for seed, (rows, cols, dens) in enumerate(shapes):
+        rows, cols, rp, ci, v = random_csr(rows, cols, dens, seed, dt, empty_rows=[(16, 48)] if rows > 64 else (),
+                                           dense_rows=[3] if cols < 1000 and rows > 3 else ())
+        a = convert(rows, cols, rp, ci, v, rw, cw, threads=seed % 3)
+        b = oracle.csr2btcf_nobitmap(rows, cols, rp, ci, v, rw, cw)
+        assert same_format(a, b)
+        assert a.rowOffset[-1] == a.total_tiles and len(a.tcA2B) == a.total_tiles * cw
+
+
+def test_empty_matrix_and_empty_windows():
+    rp = np.zeros(41, np.uint32)
+    f = convert(40, 10, rp, np.zeros(0, np.uint32), np.zeros(0, np.float16))
+    assert (f.eff_row_windows, f.total_tiles, f.total_row_windows) == (0, 0, 3)
+    assert f.rowOffset.tolist() == [0]
+    rows, cols, rp, ci, v = random_csr(80, 50, 0.1, 9, empty_rows=[(0, 16), (32, 64)])
+    f = convert(rows, cols, rp, ci, v)
+    assert f.rowIdx.tolist() == [16, 64]
+
+
+def test_duplicates_last_wins_and_unsorted_rows():
+    # one row holding column 5 twice and columns out of order (convert.h:215 keeps the last write)
+    rp = np.array([0, 4], np.uint32)
+    ci = np.array([9, 5, 2, 5], np.uint32)
+    v = np.array([1, 2, 3, 4], np.float16)
+    f = convert(1, 16, rp, ci, v)
+    g = oracle.csr2btcf_nobitmap(1, 16, rp, ci, v, 16, 16)
+    assert same_format(f, g)
+    assert f.tcA2B[:3].tolist() == [2, 5, 9] and f.data[:3].tolist() == [3.0, 4.0, 1.0]
+
+
+def test_padding_and_zero_fill():
+    rows, cols, rp, ci, v = random_csr(37, 100, 0.1, 4)
+    f = convert(rows, cols, rp, ci, v)
+    a2b = f.tcA2B.reshape(-1, 16)
+    for w in range(f.eff_row_windows):
+        lst = a2b[f.rowOffset[w]:f.rowOffset[w + 1]].ravel()
+        real = lst[lst != hs.IDX_MAX]
+        assert np.all(np.diff(real.astype(np.int64)) > 0)            # ascending, distinct
+        assert np.all(lst[len(real):] == hs.IDX_MAX)                 # padding only at the end
+    # the last window has 5 real rows: rows 5..15 of its tiles are zero
+    last = f.data.reshape(-1, 16, 16)[f.rowOffset[-2]:]
+    assert np.all(last[:, 5:, :] == 0)
+    assert np.count_nonzero(f.data) == np.count_nonzero(v)
+
+
+def test_bad_csr_is_rejected():
+    rows, cols, rp, ci, v = random_csr(20, 20, 0.3, 1)
+    for mutate in ("nonmonotone", "col", "nnz"):
+        rp2, ci2 = rp.copy(), ci.copy()
+        if mutate == "nonmonotone":
+            rp2[5], rp2[6] = rp2[6] + 1, rp2[5]
+        elif mutate == "col":
+            ci2[3] = 20
+        else:
+            rp2[-1] += 1
+        with pytest.raises(capi.SpmmError) as e:
+            convert(rows, cols, rp2, ci2, v)
+        assert e.value.status == capi.ERR_BAD_CSR
+    with pytest.raises(capi.SpmmError) as e:
+        convert(rows, cols, rp, ci, v, rw=12)
+    assert e.value.status == capi.ERR_INVALID_ARG
+
+
+def test_shard_rows_is_nnz_balanced():
+    rows, cols, rp, ci, v = random_csr(1000, 300, 0.05, 2, dense_rows=list(range(0, 40)))
+    for parts in (1, 2, 4, 8):
+        cuts = hs.shard_rows(rows, rp, parts)
+        assert cuts[0] == 0 and cuts[-1] == rows and np.all(np.diff(cuts.astype(np.int64)) >= 0)
+        assert all(c % 16 == 0 or c == rows for c in cuts)
+        nnz = np.diff(rp[cuts.astype(np.int64)].astype(np.int64))
+        window_max = max(int(rp[min(rows, r + 16)]) - int(rp[r]) for r in range(0, rows, 16))
+        assert nnz.sum() == len(ci) and nnz.max() - len(ci) / parts <= window_max
+
+
+def test_sharded_conversion_concatenates():
+    rows, cols, rp, ci, v = random_csr(400, 200, 0.04, 7, empty_rows=[(64, 96)])
+    whole = convert(rows, cols, rp, ci, v)
+    cuts = hs.shard_rows(rows, rp, 4).astype(np.int64)
+    per_window, a2b, data, ridx = [], [], [], []
+    for p in range(4):
+        r0, r1 = cuts[p], cuts[p + 1]
+        lo, hi = int(rp[r0]), int(rp[r1])
+        part = convert(r1 - r0, cols, rp[r0:r1 + 1] - lo, ci[lo:hi], v[lo:hi])
+        per_window += np.diff(part.rowOffset.astype(np.int64)).tolist()
+        a2b.append(np.array(part.tcA2B)); data.append(np.array(part.data)); ridx.append(np.array(part.rowIdx) + r0)
+    assert per_window == np.diff(whole.rowOffset.astype(np.int64)).tolist()
+    assert np.array_equal(np.concatenate(a2b), whole.tcA2B)
+    assert np.array_equal(np.concatenate(data).view(np.uint16), np.array(whole.data).view(np.uint16))
+    assert np.array_equal(np.concatenate(ridx), whole.rowIdx)
+
+
+def test_schedule_covers_every_window_once_and_balances_tiles():
+    rng = np.random.default_rng(0)
+    for eff, n_ctas in ((0, 4), (1, 148), (50, 148), (5000, 148), (5000, 7)):
+        tiles = rng.integers(1, 40, eff)
+        if eff > 10:
+            tiles[:3] = 2000  # hub windows
+        row_offset = np.concatenate([[0], np.cumsum(tiles)]).astype(np.uint32)
+        cuts = np.zeros(n_ctas + 1, np.uint32)
+        st = capi.lib().b200spmm_build_schedule(row_offset.ctypes.data, eff, n_ctas, cuts.ctypes.data)
+        assert st == capi.OK
+        assert cuts[0] == 0 and cuts[-1] == eff and np.all(np.diff(cuts.astype(np.int64)) >= 0)
+        if eff >= n_ctas * 4:
+            load = np.diff(row_offset[cuts].astype(np.int64)) + np.diff(cuts.astype(np.int64))
+            assert load.max() <= (row_offset[-1] + eff) / n_ctas + tiles.max() + 1

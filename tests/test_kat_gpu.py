@@ -1,0 +1,98 @@
+"""Single-tile known answers on the device: the tcgen05.mma operand layouts, the M = 64 TMEM
+layout, accumulation over tiles, and the TMA loads.  Counterparts of the reference's bring-up
+programs src/test_fp16.cu (KAT-1), test/02.tma_and_wgmma (KAT-2), test/03.warp_specialized
+(accumulation) and test/01.tma_copy_matrix (TMA box layout)."""
+import numpy as np
+import pytest
+
+import kat_util as ku
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _image(gathered: bytes, tile: bytes):
+    img = gathered + bytes((-len(gathered)) % 4096)
+    b_off = len(img)
+    return img + tile + bytes(8192), b_off
+
+
+@pytest.mark.parametrize("tf32", [False, True])
+@pytest.mark.parametrize("m", [128, 64])
+def test_single_tile_product(tf32, m):
+    dt, cw = (np.float32, 8) if tf32 else (np.float16, 16)
+    rng = np.random.default_rng(m + tf32)
+    feats = rng.integers(-8, 9, (m, cw)).astype(dt)   # gathered rows of B, [feature][k]
+    tile = rng.integers(-8, 9, (16, cw)).astype(dt)   # 16 window rows x CW
+    img, b_off = _image(ku.pack_gathered(feats), ku.pack_tile(tile))
+    st, d = ku.run_umma(img, [ku.spmm_tile_mma(tf32, m, 0, b_off)])
+    assert st == 0
+    got = d if m == 128 else ku.m64_rows(d)
+    assert np.array_equal(got, feats.astype(np.float32) @ tile.astype(np.float32).T)  # small integers: exact
+
+
+def test_kat1_fp16_values():
+    # src/test_fp16.cu:407-415 re-expressed for the transposed mapping: the 64x16 operand
+    # A[i] = half(i+1) plays the feature side (M = 64), the all-ones operand the window side.
+    A = np.arange(1, 64 * 16 + 1, dtype=np.float32).astype(np.float16).reshape(64, 16)
+    ones = np.ones((16, 16), np.float16)
+    img, b_off = _image(ku.pack_gathered(A), ku.pack_tile(ones))
+    st, d = ku.run_umma(img, [ku.spmm_tile_mma(False, 64, 0, b_off)])
+    assert st == 0
+    expect = oracle.tile_accumulate(A.astype(np.float32), ones.astype(np.float32), 64, 16, 16, 1)
+    bad, _, _ = oracle.compare(ku.m64_rows(d), expect, 0.01)  # the reference's tolerance, test_fp16.cu:306
+    assert bad == 0
+    assert np.array_equal(expect[:, 0], A.astype(np.float32).sum(1))
+
+
+def test_kat2_tf32_values():
+    # test/02.tma_and_wgmma/tma_wgmma.cu:340-348: A[i] = i+1 (64x8), B[i] = 1 + 0.01 i
+    A = np.arange(1, 64 * 8 + 1, dtype=np.float32).reshape(64, 8)
+    Bm = np.zeros((16, 8), np.float32)
+    Bm[:8] = (1.0 + 0.01 * np.arange(64, dtype=np.float32)).reshape(8, 8)
+    img, b_off = _image(ku.pack_gathered(A), ku.pack_tile(Bm))
+    st, d = ku.run_umma(img, [ku.spmm_tile_mma(True, 64, 0, b_off)])
+    assert st == 0
+    expect = oracle.tile_accumulate(A, Bm, 64, 16, 8, 1)
+    bad, _, _ = oracle.compare(ku.m64_rows(d), expect, 0.01)
+    assert bad == 0
+
+
+@pytest.mark.parametrize("tf32", [False, True])
+def test_tiles_accumulate_in_tmem(tf32):
+    # test/03.warp_specialized/main.cu: T tiles into one accumulator, inputs rand()/RAND_MAX after srand(42)
+    dt, cw, T = (np.float32, 8, 6) if tf32 else (np.float16, 16, 6)
+    stream = oracle.rand_fill(42, 128 * cw * T + 16 * cw * T)
+    A = stream[:128 * cw * T].reshape(128, cw * T).astype(dt)
+    Bm = stream[128 * cw * T:].reshape(16, cw * T).astype(dt)
+    img, mmas = b"", []
+    for t in range(T):
+        a_off = len(img)
+        img += ku.pack_gathered(np.ascontiguousarray(A[:, t * cw:(t + 1) * cw]))
+        img += bytes((-len(img)) % 4096)
+        b_off = len(img)
+        img += ku.pack_tile(np.ascontiguousarray(Bm[:, t * cw:(t + 1) * cw])) + bytes(512)
+        mmas.append(ku.spmm_tile_mma(tf32, 128, a_off, b_off, d_col=16, accumulate=int(t > 0)))
+    st, d = ku.run_umma(img + bytes(8192), mmas, n_cols=32)
+    assert st == 0
+    expect = oracle.tile_accumulate(A.astype(np.float32), Bm.astype(np.float32), 128, 16, cw, T)
+    bad, max_rel, _ = oracle.compare(d[:, 16:32], expect, 0.01)  # utils.h:61-85
+    assert bad == 0 and max_rel < (2e-3 if tf32 else 1e-5)
+
+
+def test_tma_tile_load_lands_in_operand_layout():
+    data = np.arange(64 * 16, dtype=np.uint16).reshape(64, 16)  # four 16x16 fp16 tiles, 32-byte rows
+    loads = [[0, 0, 0, 16, 0, 0, 0], [0, 512, 0, 48, 0, 0, 0]]
+    st, dump = ku.run_tma(data, 16, 16, 1, loads, 1024, 1024)
+    assert st == 0
+    expect = ku.pack_tile(data[16:32].view(np.float16)) + ku.pack_tile(data[48:64].view(np.float16))
+    assert dump.tobytes() == expect
+
+
+def test_tma_tile_load_past_the_end_reads_zero():
+    data = np.arange(1, 32 * 16 + 1, dtype=np.uint16).reshape(32, 16)
+    st, dump = ku.run_tma(data, 16, 16, 1, [[0, 0, 0, 24, 0, 0, 0]], 512, 512)
+    assert st == 0
+    tile = np.zeros((16, 16), np.uint16)
+    tile[:8] = data[24:32]
+    assert dump.tobytes() == ku.pack_tile(tile.view(np.float16))

@@ -1,0 +1,158 @@
+"""End-to-end parity on the device, through the C ABI: the converted matrix goes to the GPU,
+the sm_100a kernel computes C, and C is compared with the CPU oracle."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import hopper_spmm_b200 as hs
+import parity
+from cases import dense_b, random_csr
+from hopper_spmm_b200 import _capi as capi
+from hopper_spmm_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def run_host(rows, cols, rp, ci, v, B, c_half=False, n_ctas=0):
+    f = hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v))
+    plan = hs.SpmmPlan(f, n_ctas=n_ctas)
+    try:
+        out = plan.spmm_host(B, c_half=c_half)
+        return out, plan.launch_info()
+    finally:
+        plan.close()
+
+
+@pytest.mark.parametrize("dt", [np.float16, np.float32])
+@pytest.mark.parametrize("n", [8, 64, 128, 192, 256, 320, 520])
+def test_ragged_matrix_every_slab_width(dt, n):
+    rows, cols, rp, ci, v = random_csr(203, 517, 0.03, 11, dt, empty_rows=[(48, 96)], dense_rows=[7])
+    B = dense_b(cols, n, 3, dt)
+    C_out, info = run_host(rows, cols, rp, ci, v, B)
+    parity.check(C_out, rows, rp, ci, v, B)
+    assert np.all(C_out[48:96] == 0)
+    assert info.kernel_launches == 1 and info.feature_slab == min(256, (n + 63) // 64 * 64)
+
+
+@pytest.mark.parametrize("dt", [np.float16, np.float32])
+def test_single_entry_and_single_tile(dt):
+    rp = np.zeros(17, np.uint32)
+    rp[6:] = 1
+    ci, v = np.array([3], np.uint32), np.array([2.0], dt)
+    B = dense_b(9, 128, 0, dt)
+    C_out, _ = run_host(16, 9, rp, ci, v, B)
+    expect = np.zeros((16, 128), np.float32)
+    expect[5] = 2.0 * B[3].astype(np.float32)
+    assert np.array_equal(C_out, expect)
+
+
+def test_empty_matrix_gives_zeros():
+    rp = np.zeros(41, np.uint32)
+    C_out, _ = run_host(40, 10, rp, np.zeros(0, np.uint32), np.zeros(0, np.float16), dense_b(10, 64, 0))
+    assert C_out.shape == (40, 64) and np.all(C_out == 0)
+
+
+def test_leading_and_trailing_empty_windows_are_cleared():
+    rows, cols, rp, ci, v = random_csr(400, 64, 0.2, 5, empty_rows=[(0, 64), (350, 400)])
+    B = dense_b(cols, 128, 1)
+    f = hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v))
+    import torch
+    plan = hs.SpmmPlan(f)
+    dB = torch.from_numpy(B).cuda()
+    dC = torch.full((rows, 128), float("nan"), device="cuda")  # poison: every row must be written
+    plan.spmm(dB, dC)
+    parity.check(dC.cpu().numpy(), rows, rp, ci, v, B)
+    plan.close()
+
+
+def test_long_windows_wrap_the_ring_many_times():
+    # 5000 distinct columns in one window = 313 tiles through a 40-stage ring
+    rows, cols, rp, ci, v = random_csr(64, 5000, 0.4, 6, dense_rows=[0, 17, 40])
+    B = dense_b(cols, 128, 2)
+    C_out, _ = run_host(rows, cols, rp, ci, v, B)
+    parity.check(C_out, rows, rp, ci, v, B)
+
+
+def test_more_ctas_than_windows_and_one_cta():
+    rows, cols, rp, ci, v = random_csr(96, 300, 0.1, 8)
+    B = dense_b(cols, 64, 4)
+    for n_ctas in (1, 3, 148, 500):
+        C_out, info = run_host(rows, cols, rp, ci, v, B, n_ctas=n_ctas)
+        parity.check(C_out, rows, rp, ci, v, B)
+        assert info.n_ctas == n_ctas
+
+
+def test_fp16_output():
+    rows, cols, rp, ci, v = random_csr(130, 200, 0.1, 9)
+    B = dense_b(cols, 128, 5)
+    c32, _ = run_host(rows, cols, rp, ci, v, B)
+    c16, _ = run_host(rows, cols, rp, ci, v, B, c_half=True)
+    assert c16.dtype == np.float16 and np.array_equal(c16, c32.astype(np.float16))
+
+
+def test_strided_device_tensors_and_reference_protocol():
+    import torch
+    rows, cols, rp, ci, v = random_csr(300, 256, 0.05, 10)
+    f = hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v))
+    plan = hs.SpmmPlan(f)
+    Bfull = torch.from_numpy(dense_b(cols, 256, 6)).cuda()
+    Cfull = torch.zeros((rows, 512), device="cuda")
+    Bv, Cv = Bfull[:, 64:192], Cfull[:, 128:256]          # ldb = 256, ldc = 512, 16-byte aligned views
+    plan.spmm(Bv, Cv)
+    parity.check(Cv.cpu().numpy(), rows, rp, ci, v, Bv.cpu().numpy())
+    assert float(Cfull[:, :128].abs().sum()) == 0 and float(Cfull[:, 256:].abs().sum()) == 0
+    perf = plan.bench(Bv.contiguous(), torch.empty((rows, 128), device="cuda"))
+    assert perf.runs == hs.RUNS and perf.time > 0
+    plan.close()
+
+
+def test_unsupported_shapes_are_refused():
+    import torch
+    rows, cols, rp, ci, v = random_csr(32, 32, 0.2, 1)
+    plan = hs.SpmmPlan(hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v)))
+    B = torch.zeros((cols, 12), dtype=torch.float16, device="cuda")
+    with pytest.raises(capi.SpmmError) as e:
+        plan.spmm(B)
+    assert e.value.status == capi.ERR_UNSUPPORTED
+    with pytest.raises(capi.SpmmError):
+        hs.SpmmPlan(hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v), row_window=8))
+    plan.close()
+
+
+def test_reference_operator_names():
+    rows, cols, rp, ci, v = random_csr(100, 80, 0.1, 2)
+    B = dense_b(cols, 128, 7)
+    btcf = hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v))
+    Cm = hs.DENSE_MTX(rows, 128)
+    perf = hs.fp16_spmm(btcf, hs.DENSE_MTX(cols, 128, B), Cm)
+    assert perf.runs == 5
+    parity.check(Cm.values, rows, rp, ci, v, B)
+    with pytest.raises(TypeError):
+        hs.tf32_spmm(btcf, hs.DENSE_MTX(cols, 128, B), Cm)
+
+
+@pytest.mark.parametrize("name,k", [("uniform_4096_fp16", 0), ("blocks_16384_tf32", 1), ("rmat20_gnn_fp16", 4),
+                                    ("pruned_llm_fp16", 3), ("rmat24_sharded_fp16", 8)])
+def test_benchmark_configurations(name, k):
+    csr, B = synth.make_config(name, 0, "cpu", k)
+    rp, ci, v = csr.numpy()
+    C_out, _ = run_host(csr.rows, csr.cols, rp, ci, v, B.numpy())
+    stats = parity.check(C_out, csr.rows, rp, ci, v, B.numpy())
+    print(name, stats)
+
+
+def test_rmat_rows_sum_to_one_at_scale():
+    # size-independent property: with values 1/deg(row) and B = ones, every non-empty row of C is 1
+    import torch
+    csr, _ = synth.make_config("rmat24_sharded_fp16", 0, "cuda", 4)  # 2^20 nodes, ~30M entries
+    rp, ci, v = csr.numpy()
+    f = hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(csr.rows, csr.cols, rp, ci, v))
+    plan = hs.SpmmPlan(f)
+    B = torch.ones((csr.cols, 128), dtype=torch.float16, device="cuda")
+    Cd = plan.spmm(B)
+    deg = (csr.row_ptr[1:] - csr.row_ptr[:-1])
+    want = (deg > 0).to(torch.float32)[:, None].expand(-1, 128)
+    err = (Cd - want).abs().max().item()
+    assert err < 2e-3, err  # 1/deg is rounded to fp16: relative 2^-11 per term
+    plan.close()
