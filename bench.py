@@ -1,0 +1,308 @@
+#!/usr/bin/env python
+"""Benchmark of the SpMM hot path: effective GFLOP/s (2*nnz*N) on seeded synthetic inputs.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload NAME] [--scale-down k]
+
+One "step" is one SpMM of the whole matrix.  With N > 1 (launched by torch.distributed.run, one
+rank per GPU) the matrix is cut into N nnz-balanced row-window ranges, B is replicated and every
+rank multiplies its own range; there is no data-path collective, total work is fixed (strong
+scaling).  Rank 0 prints ONE JSON line.
+
+  value       whole-job GFLOP/s with operands resident in HBM, CUDA-event timed, max over ranks
+  e2e         the same through the host-buffer call: B copied from pinned host memory and C
+              copied back inside the timed region (the converted matrix stays resident, like
+              weights)
+  roofline    algorithmic bytes of one launch / its duration against the measured HBM peak
+  cpu_baseline  the CPU oracle's CSR SpMM on a bounded row sample, all host threads
+
+--impl reference times that CPU path alone (the reference project has no CSR-level SpMM and
+its GPU kernel is sm_90a-only and unfinished, so its own verifier arithmetic, restated in
+oracle/, is what can run on the host cores).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+DEFAULT_WORKLOAD = "rmat24_sharded_fp16"
+
+
+def log(*a):
+    print("[bench]", *a, file=sys.stderr, flush=True)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def algorithmic_bytes(nnz, rows, cols, n, a_size, b_size, c_size):
+    """CSR-equivalent A once, B once, C written once."""
+    return nnz * (a_size + 4) + 4 * (rows + 1) + cols * n * b_size + rows * n * c_size
+
+
+def cpu_sample_rows(row_ptr_host: np.ndarray, target_nnz: int):
+    """A contiguous block of rows from the middle of the matrix holding about target_nnz entries."""
+    rows = len(row_ptr_host) - 1
+    nnz = int(row_ptr_host[-1])
+    if target_nnz >= nnz:
+        return 0, rows
+    mid = int(np.searchsorted(row_ptr_host, nnz // 2))
+    lo = int(np.searchsorted(row_ptr_host, max(0, int(row_ptr_host[mid]) - target_nnz // 2)))
+    hi = int(np.searchsorted(row_ptr_host, min(nnz, int(row_ptr_host[lo]) + target_nnz)))
+    return lo, max(hi, lo + 1)
+
+
+def time_cpu_oracle(rp, ci, v, B_host, steps, warmup, budget_s=12.0):
+    """GFLOP/s of the oracle's CSR SpMM (all host threads) on a row sample sized to the budget."""
+    import oracle
+    rows = len(rp) - 1
+    n = B_host.shape[1]
+    threads = oracle.max_threads()
+    lo, hi = cpu_sample_rows(rp, 1 << 20)  # probe
+    t0 = time.perf_counter()
+    oracle.spmm_csr(rows, rp, ci, v, B_host, n_threads=threads, row_begin=lo, row_end=hi)
+    probe = max(time.perf_counter() - t0, 1e-4)
+    probe_nnz = int(rp[hi]) - int(rp[lo])
+    per_step = budget_s / max(1, steps + warmup)
+    target = int(min(int(rp[-1]), max(1 << 20, probe_nnz * per_step / probe)))
+    lo, hi = cpu_sample_rows(rp, target)
+    nnz_s = int(rp[hi]) - int(rp[lo])
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        oracle.spmm_csr(rows, rp, ci, v, B_host, n_threads=threads, row_begin=lo, row_end=hi)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    t = float(np.mean(times))
+    return {"value": 2.0 * nnz_s * n / t / 1e9, "unit": "GFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"rows [{lo}, {hi}) of {rows}: {nnz_s} of {int(rp[-1])} nnz, {len(times)} passes, "
+                      f"{t * 1e3:.1f} ms each"}, t
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
+    ap.add_argument("--scale-down", type=int, default=0)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    import torch
+    from hopper_spmm_b200 import synth
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dtype_name, n_feat, desc = synth.CONFIGS[args.workload]
+    config = {"workload": args.workload, "description": desc, "scale_down": args.scale_down, "features": n_feat,
+              "row_window": 16, "c_dtype": "f32", "parallelism": f"row-window shards x{world}, B replicated",
+              "l2": "operands larger than L2 (no flush needed)"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        dev = "cuda" if torch.cuda.is_available() else "cpu"
+        csr, B = synth.make_config(args.workload, 0, dev, args.scale_down)
+        rp, ci, v = csr.numpy()
+        base, t = time_cpu_oracle(rp, ci, v, B.cpu().numpy(), args.steps, args.warmup, budget_s=60.0)
+        config.update(rows=csr.rows, cols=csr.cols, nnz=csr.nnz)
+        line = {"impl": "reference", "metric": "SpMM effective GFLOP/s (2*nnz*N)", "value": base["value"],
+                "unit": "GFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f16" if dtype_name == "f16" else "f32", "data": "synthetic", "config": config,
+                "cpu_baseline": base, "gpu_launches": 0,
+                "e2e": {"value": base["value"], "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line), flush=True)
+        return
+
+    import torch.distributed as dist
+    import hopper_spmm_b200 as hs
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- inputs: every rank generates the same matrix and keeps its own row range
+    t0 = time.perf_counter()
+    csr, B = synth.make_config(args.workload, 0, dev, args.scale_down)
+    torch.cuda.synchronize()
+    log(f"rank {rank}: generated {csr.rows}x{csr.cols}, nnz={csr.nnz} in {time.perf_counter() - t0:.1f}s")
+    rp_full = csr.row_ptr.cpu().numpy().astype(np.uint32)
+    cuts = hs.shard_rows(csr.rows, rp_full, world).astype(np.int64)
+    r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
+    part = csr.row_slice(r0, r1)
+    rp, ci, v = part.numpy()
+    total_nnz = csr.nnz
+    del csr, part
+    torch.cuda.empty_cache()
+    t0 = time.perf_counter()
+    btcf = hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(r1 - r0, B.shape[0], rp, ci, v))
+    t_conv = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    plan = hs.SpmmPlan(btcf, device=local_rank)
+    log(f"rank {rank}: rows [{r0},{r1}) nnz={len(ci)} tiles={btcf.total_tiles} convert {t_conv:.1f}s "
+        f"upload {time.perf_counter() - t0:.1f}s")
+    tiles_local, nnz_local, rows_local = btcf.total_tiles, len(ci), r1 - r0
+    fill = nnz_local / max(1, tiles_local * 16 * btcf.col_window)
+    del btcf
+    C_dev = torch.empty((rows_local, n_feat), dtype=torch.float32, device=dev)
+
+    # ---- device-resident timing
+    for _ in range(args.warmup):
+        plan.spmm(B, C_dev, sync=False)
+    plan.sync()
+    barrier()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    with ClockSampler(local_rank) as clocks:
+        ev[0].record()
+        for i in range(args.steps):
+            plan.spmm(B, C_dev, sync=False)
+            ev[i + 1].record()
+        plan.sync()
+        barrier()
+    step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    total_ms = ev[0].elapsed_time(ev[-1])
+    info = plan.launch_info()
+    t_all = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t_all, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t_all.item()) / args.steps
+    flops = 2.0 * total_nnz * n_feat
+    value = flops / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end: B from pinned host memory in, C out to pinned host memory, every step
+    e2e = None
+    if not args.no_e2e:
+        hB = torch.empty(B.shape, dtype=B.dtype, pin_memory=True)
+        hB.copy_(B)
+        hC = torch.empty(C_dev.shape, dtype=C_dev.dtype, pin_memory=True)
+        torch.cuda.synchronize()
+        hBn, hCn = hB.numpy(), hC.numpy()
+        plan.spmm_host(hBn, hCn)  # warm-up: allocates the plan's device buffers
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            plan.spmm_host(hBn, hCn)
+        e1.record()
+        barrier()
+        t_e = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
+        e_ms = float(t_e.item()) / args.steps
+        e2e = {"value": flops / (e_ms * 1e-3) / 1e9, "unit": "GFLOP/s", "ms_per_step": e_ms,
+               "h2d_bytes_per_step": int(hB.numel() * hB.element_size()),
+               "d2h_bytes_per_step": int(hC.numel() * hC.element_size())}
+        assert bool(torch.isfinite(hC[:: max(1, hC.shape[0] // 4096)]).all())
+
+    # ---- roofline of the SpMM kernel on this rank's launch
+    peak, peak_kind = measured_peaks()
+    esz = 2 if dtype_name == "f16" else 4
+    alg = algorithmic_bytes(nnz_local, rows_local, B.shape[0], n_feat, esz, esz, 4)
+    kernel_ms = float(np.mean(step_ms))
+    achieved = alg / (kernel_ms * 1e-3) / 1e9
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if os.path.exists(tpath):
+        per_tile = json.load(open(tpath)).get(args.workload, {}).get("dram_bytes_per_tile")
+        if per_tile:
+            traffic = float(per_tile) * tiles_local * info.n_slabs
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": traffic, "peak_source": f"of {peak_kind}", "kernel": "spmm_sm100_kernel",
+                "kernel_ms": kernel_ms, "algorithmic_bytes": alg}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu, _ = time_cpu_oracle(rp, ci, v, B.cpu().numpy(), 2, 1, budget_s=15.0)
+
+    if rank == 0:
+        config.update(rows=int(cuts[-1]), cols=int(B.shape[0]), nnz=int(total_nnz), tiles_rank0=int(tiles_local),
+                      fill_rank0=fill, n_ctas=info.n_ctas, feature_slab=info.feature_slab, stages=info.stages,
+                      convert_s_rank0=t_conv)
+        line = {"metric": "SpMM effective GFLOP/s (2*nnz*N)", "value": value, "unit": "GFLOP/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "f16" if dtype_name == "f16" else "tf32",
+                "data": "synthetic", "config": config, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+                "gpu_launches": int(args.steps * info.kernel_launches), "clocks": clocks.summary()}
+        print(json.dumps(line), flush=True)
+    plan.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

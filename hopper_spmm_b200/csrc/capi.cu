@@ -2,6 +2,7 @@
 // Replaces the host side of the reference's operator, fp16_spmm (src/fp16.cu:221-281).
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -316,6 +317,7 @@ int b200spmm_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, v
     prm.c_is_half = c_dtype == B200SPMM_C_F16;
     prm.status = p->d_status;
     prm.wait_limit_ns = kDeviceWaitLimitNs;
+    if (const char *dbg = std::getenv("B200SPMM_DEBUG")) prm.debug = (uint32_t)std::atoi(dbg);  // measurement aid, results invalid
     return p->info.dtype == B200SPMM_F16 ? launch_dtype<false>(p, prm, stream) : launch_dtype<true>(p, prm, stream);
 }
 

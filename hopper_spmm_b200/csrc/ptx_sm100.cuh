@@ -176,8 +176,9 @@ B200_DEVICE void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" 
 // Shared-memory matrix descriptor (64 bit):
 //   [0,14)  start address >> 4          [16,30) leading-dimension byte offset >> 4
 //   [32,46) stride-dimension byte offset >> 4     [46,48) version = 1
-//   [49,52) base offset = 0             [61,64) swizzle: 0 none, 2 128B, 4 64B, 6 32B
-enum : uint32_t { kSwizzleNone = 0, kSwizzle128B = 2, kSwizzle64B = 4, kSwizzle32B = 6 };
+//   [49,52) base offset = 0             [61,64) swizzle: 0 none, 1 128B over 32-byte units,
+//                                               2 128B, 4 64B, 6 32B (16-byte units)
+enum : uint32_t { kSwizzleNone = 0, kSwizzle128BBase32B = 1, kSwizzle128B = 2, kSwizzle64B = 4, kSwizzle32B = 6 };
 
 B200_DEVICE uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t swizzle) {
     uint64_t d = 0;

@@ -8,7 +8,7 @@
 // tile of CW condensed columns,
 //     Dt[features x 16 rows] += Bgather[features x CW] * Atile^T[CW x 16]
 // so the gathered rows of B are the UMMA "A" operand (M = 128 or 64 features, MN-major,
-// 128-byte swizzle: exactly how B's rows lie in memory) and the 16 x CW tile of the sparse
+// 128-byte swizzle - 16-byte units for fp16, 32-byte units for tf32: how B's rows lie in memory) and the 16 x CW tile of the sparse
 // matrix is the UMMA "B" operand (N = 16, K-major, 32-byte swizzle: exactly how the tile lies
 // in `data`).  K per tile is 32 bytes for both element types (16 fp16 / 8 tf32), one
 // tcgen05.mma per tile and 128-feature chunk.  The accumulator lives in TMEM (16 columns per
@@ -19,7 +19,9 @@
 //              plus zero-fill of rows that belong to windows without entries
 //   warps 4-7  producers: warp p owns every 4th tile of the CTA's tile stream; lane 0 issues the
 //              TMA load of the 512-byte A tile, all lanes gather the tile's CW rows of B with
-//              16-byte cp.async copies straight into the swizzled operand layout
+//              16-byte cp.async copies straight into the swizzled operand layout.  The column
+//              lists themselves are fetched 24 tiles ahead into a per-warp ring, so no role ever
+//              waits on a dependent global load inside its per-tile loop
 //   warp  8    lane 0 issues tcgen05.mma / tcgen05.commit; the warp owns the TMEM allocation
 //
 // Every wait is bounded; on a timeout the roles drain and the kernel raises a status bit.
@@ -56,6 +58,7 @@ struct SpmmParams {
     uint32_t n_slabs;            // ceil(n / kNs)
     uint32_t c_is_half;          // 0: fp32 C, 1: fp16 C
     uint32_t *status;            // device status word
+    uint32_t debug;              // measurement aid: bit 0 skips the B gathers, bit 1 skips the MMAs
     unsigned long long wait_limit_ns;
 };
 
@@ -76,8 +79,15 @@ struct SpmmCfg {
     static constexpr int kChunksPerRow = kNs * kEsz / 16;           // 16-byte pieces per gathered row
     static constexpr int kCopiesPerLane = kCW * kChunksPerRow / 32;  // == kNs / 16
     static constexpr int kStagingBytes = kRowWindow * kNs * 4;
+    // Each producer warp keeps the column lists of its next kIdxAhead tiles in a private ring of
+    // kIdxSlots entries, fetched with the same cp.async groups as the rows they will select.
+    static constexpr int kIdxSlots = 32;
+    static constexpr int kIdxAhead = 24;
+    static_assert(kIdxAhead > kLag && kIdxAhead < kIdxSlots, "column lists must land before they are needed");
+    static constexpr int kIdxBytes = kProducerWarps * kIdxSlots * kCW * 4;
     static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
-    static constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + kStagingBytes + kBarrierBytes;
+    static constexpr size_t kSmemBytes =
+        1024 + (size_t)kStages * kStageBytes + kStagingBytes + kIdxBytes + kBarrierBytes;
 };
 
 template <bool kTf32, int kNs>
@@ -94,8 +104,10 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
     const uint32_t gather_addr = raw_addr + pad;                               // kStages x kGatherBytes
     const uint32_t atile_addr = gather_addr + kStages * Cfg::kGatherBytes;      // kStages x 512
     float *staging = reinterpret_cast<float *>(base + kStages * Cfg::kStageBytes);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(base + kStages * Cfg::kStageBytes + Cfg::kStagingBytes);
-    const uint32_t bars_addr = atile_addr + kStages * kATileBytes + Cfg::kStagingBytes;
+    uint32_t *idx_ring = reinterpret_cast<uint32_t *>(base + kStages * Cfg::kStageBytes + Cfg::kStagingBytes);
+    const uint32_t idx_ring_addr = atile_addr + kStages * kATileBytes + Cfg::kStagingBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(base + kStages * Cfg::kStageBytes + Cfg::kStagingBytes + Cfg::kIdxBytes);
+    const uint32_t bars_addr = idx_ring_addr + Cfg::kIdxBytes;
     auto full_bar = [&](int s) { return bars_addr + 8u * (uint32_t)s; };
     auto empty_bar = [&](int s) { return bars_addr + 8u * (uint32_t)(kStages + s); };
     auto acc_full_bar = [&](int a) { return bars_addr + 8u * (uint32_t)(2 * kStages + a); };
@@ -140,89 +152,103 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
         bool failed = false;
         for (uint32_t slab = 0; slab < p.n_slabs && !failed; ++slab) {
             const uint32_t f0 = slab * kNs;  // first feature of the slab
-            for (uint32_t w = w_begin; w < w_end; ++w, ++acc_it) {
-                const uint32_t a = acc_it & 1u;
-                bool ok = ptx::mbar_wait(acc_full_bar(a), (acc_it >> 1) & 1u, abort_flag, limit);
-                ptx::tcgen05_fence_after_sync();
-                if (ok) {
+            // First rows of 32 windows at a time, one per lane, the next block fetched while this one
+            // is worked on: row_here = first row of window wb + lane, row_after = first row of the
+            // window that follows it (or the row count).
+            auto load_rows = [&](uint32_t wb, uint32_t &here, uint32_t &after) {
+                const uint32_t w = wb + lane;
+                here = w < w_end ? p.rowIdx[w] : 0u;
+                after = (w < w_end && w + 1 < p.eff_row_windows) ? p.rowIdx[w + 1] : p.rows;
+            };
+            uint32_t here_n = 0, after_n = 0;
+            load_rows(w_begin, here_n, after_n);
+            for (uint32_t wb = w_begin; wb < w_end && !failed; wb += 32) {
+                const uint32_t here_c = here_n, after_c = after_n;
+                if (wb + 32 < w_end) load_rows(wb + 32, here_n, after_n);
+                const uint32_t in_block = min(32u, w_end - wb);
+                for (uint32_t i = 0; i < in_block; ++i, ++acc_it) {
+                    const uint32_t w = wb + i;
+                    const uint32_t row0 = __shfl_sync(0xffffffffu, here_c, i);
+                    const uint32_t gap_hi = __shfl_sync(0xffffffffu, after_c, i);
+                    const uint32_t a = acc_it & 1u;
+                    bool ok = ptx::mbar_wait(acc_full_bar(a), (acc_it >> 1) & 1u, abort_flag, limit);
+                    ptx::tcgen05_fence_after_sync();
+                    if (ok) {
 #pragma unroll
-                    for (int c = 0; c < Cfg::kChunks; ++c) {
-                        uint32_t r[16];
-                        ptx::tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(warp * 32) << 16) + a * kAccCols + c * 16, r);
-                        ptx::tmem_ld_wait();
-                        const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
-                        // M = 128: lane l of warp q holds feature 32q + l.  M = 64: lanes 0-15 of warp q
-                        // hold features 16q + l.
-                        const int f = half_chunk ? c * 128 + warp * 16 + lane : c * 128 + warp * 32 + lane;
-                        if (!half_chunk || lane < 16) {
+                        for (int c = 0; c < Cfg::kChunks; ++c) {
+                            uint32_t r[16];
+                            ptx::tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(warp * 32) << 16) + a * kAccCols + c * 16, r);
+                            ptx::tmem_ld_wait();
+                            const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
+                            // M = 128: lane l of warp q holds feature 32q + l.  M = 64: lanes 0-15 of
+                            // warp q hold features 16q + l.
+                            const int f = half_chunk ? c * 128 + warp * 16 + lane : c * 128 + warp * 32 + lane;
+                            if (!half_chunk || lane < 16) {
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) staging[j * kNs + f] = __uint_as_float(r[j]);
+                                for (int j = 0; j < 16; ++j) staging[j * kNs + f] = __uint_as_float(r[j]);
+                            }
+                        }
+                        ptx::tcgen05_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(acc_empty_bar(a));
+                    }
+                    // staging complete for all four warps (also agrees on failure)
+                    uint32_t any_fail;
+                    asm volatile(
+                        "{\n"
+                        ".reg .pred q, r;\n"
+                        "setp.ne.u32 q, %1, 0;\n"
+                        "barrier.cta.red.or.pred r, %2, %3, q;\n"
+                        "selp.u32 %0, 1, 0, r;\n"
+                        "}\n"
+                        : "=r"(any_fail)
+                        : "r"((uint32_t)(ok ? 0 : 1)), "r"(kEpilogueBarrier), "r"(128u)
+                        : "memory");
+                    if (any_fail) {
+                        failed = true;
+                        break;
+                    }
+                    constexpr int kVecPerRow = kNs / 4;
+#pragma unroll
+                    for (int it = 0; it < kRowWindow * kVecPerRow / 128; ++it) {
+                        const int idx = it * 128 + et;
+                        const int r = idx / kVecPerRow, c4 = idx % kVecPerRow;
+                        const uint32_t row = row0 + r, feat = f0 + c4 * 4;
+                        if (row < p.rows && feat < p.n) {
+                            const float4 v = *reinterpret_cast<const float4 *>(staging + r * kNs + c4 * 4);
+                            if (p.c_is_half) {
+                                __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+                                uint2 packed;
+                                packed.x = *reinterpret_cast<uint32_t *>(&lo);
+                                packed.y = *reinterpret_cast<uint32_t *>(&hi);
+                                *reinterpret_cast<uint2 *>(static_cast<__half *>(p.C) + (int64_t)row * p.ldc + feat) = packed;
+                            } else {
+                                *reinterpret_cast<float4 *>(static_cast<float *>(p.C) + (int64_t)row * p.ldc + feat) = v;
+                            }
                         }
                     }
-                    ptx::tcgen05_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(acc_empty_bar(a));
-                }
-                // staging complete for all four warps (also agrees on failure)
-                uint32_t any_fail;
-                asm volatile(
-                    "{\n"
-                    ".reg .pred q, r;\n"
-                    "setp.ne.u32 q, %1, 0;\n"
-                    "barrier.cta.red.or.pred r, %2, %3, q;\n"
-                    "selp.u32 %0, 1, 0, r;\n"
-                    "}\n"
-                    : "=r"(any_fail)
-                    : "r"((uint32_t)(ok ? 0 : 1)), "r"(kEpilogueBarrier), "r"(128u)
-                    : "memory");
-                if (any_fail) {
-                    failed = true;
-                    break;
-                }
-                const uint32_t row0 = p.rowIdx[w];
-                constexpr int kVecPerRow = kNs / 4;
-#pragma unroll
-                for (int it = 0; it < kRowWindow * kVecPerRow / 128; ++it) {
-                    const int idx = it * 128 + et;
-                    const int r = idx / kVecPerRow, c4 = idx % kVecPerRow;
-                    const uint32_t row = row0 + r, feat = f0 + c4 * 4;
-                    if (row < p.rows && feat < p.n) {
-                        const float4 v = *reinterpret_cast<const float4 *>(staging + r * kNs + c4 * 4);
-                        if (p.c_is_half) {
-                            __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
-                            uint2 packed;
-                            packed.x = *reinterpret_cast<uint32_t *>(&lo);
-                            packed.y = *reinterpret_cast<uint32_t *>(&hi);
-                            *reinterpret_cast<uint2 *>(static_cast<__half *>(p.C) + (int64_t)row * p.ldc + feat) = packed;
-                        } else {
-                            *reinterpret_cast<float4 *>(static_cast<float *>(p.C) + (int64_t)row * p.ldc + feat) = v;
+                    // Rows of windows that hold no entries are absent from the format: clear the gap
+                    // that follows this window (and the one before the very first window).
+                    if (gap_hi > row0 + kRowWindow || (w == 0 && row0 > 0)) {
+                        const uint32_t slab_feats = min((uint32_t)kNs, p.n - f0);
+                        const uint32_t vec_per_row = slab_feats / 4;
+                        for (int pass = 0; pass < 2; ++pass) {
+                            const uint32_t lo = pass == 0 ? row0 + kRowWindow : 0u;
+                            const uint32_t hi = pass == 0 ? gap_hi : (w == 0 ? row0 : 0u);
+                            if (hi <= lo || lo >= p.rows) continue;
+                            const uint64_t total = (uint64_t)(hi - lo) * vec_per_row;
+                            for (uint64_t k = et; k < total; k += 128) {
+                                const uint32_t row = lo + (uint32_t)(k / vec_per_row), feat = f0 + (uint32_t)(k % vec_per_row) * 4;
+                                if (p.c_is_half)
+                                    *reinterpret_cast<uint2 *>(static_cast<__half *>(p.C) + (int64_t)row * p.ldc + feat) = make_uint2(0, 0);
+                                else
+                                    *reinterpret_cast<float4 *>(static_cast<float *>(p.C) + (int64_t)row * p.ldc + feat) = make_float4(0, 0, 0, 0);
+                            }
                         }
                     }
+                    // staging may be overwritten by the next window
+                    ptx::named_barrier_sync(kEpilogueBarrier, 128);
                 }
-                // Rows of windows that hold no entries are absent from the format: clear the gap
-                // that follows this window (and the one before the very first window).
-                {
-                    uint32_t gap_lo = row0 + kRowWindow;
-                    const uint32_t gap_hi = (w + 1 < p.eff_row_windows) ? p.rowIdx[w + 1] : p.rows;
-                    uint32_t lead_hi = 0;
-                    if (w == 0) lead_hi = row0;
-                    const uint32_t slab_feats = min((uint32_t)kNs, p.n - f0);
-                    const uint32_t vec_per_row = slab_feats / 4;
-                    for (int pass = 0; pass < 2; ++pass) {
-                        const uint32_t lo = pass == 0 ? gap_lo : 0u, hi = pass == 0 ? gap_hi : lead_hi;
-                        if (hi <= lo || lo >= p.rows) continue;
-                        const uint64_t total = (uint64_t)(hi - lo) * vec_per_row;
-                        for (uint64_t i = et; i < total; i += 128) {
-                            const uint32_t row = lo + (uint32_t)(i / vec_per_row), feat = f0 + (uint32_t)(i % vec_per_row) * 4;
-                            if (p.c_is_half)
-                                *reinterpret_cast<uint2 *>(static_cast<__half *>(p.C) + (int64_t)row * p.ldc + feat) = make_uint2(0, 0);
-                            else
-                                *reinterpret_cast<float4 *>(static_cast<float *>(p.C) + (int64_t)row * p.ldc + feat) = make_float4(0, 0, 0, 0);
-                        }
-                    }
-                }
-                // staging may be overwritten by the next window
-                ptx::named_barrier_sync(kEpilogueBarrier, 128);
             }
         }
     } else if (warp < 8) {
@@ -239,32 +265,57 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
             const uint32_t q = i * 32 + lane;
             const uint32_t k = q / Cfg::kChunksPerRow, piece = q % Cfg::kChunksPerRow;
             const uint32_t h = piece >> 3, cc = piece & 7u;  // 128-byte column block, piece inside it
-            uint32_t atom, kr;
-            if (kTf32) { atom = h; kr = k; } else { atom = h * 2 + (k >> 3); kr = k & 7u; }
-            dst_off[i] = atom * 1024u + kr * 128u + ((cc ^ kr) << 4);
+            if (kTf32) {
+                // 32-feature blocks of 4 k-rows x 128 B; 32-byte units are XORed with the row number
+                const uint32_t kr = k & 3u;
+                dst_off[i] = (h * 2 + (k >> 2)) * 512u + kr * 128u + ((((cc >> 1) ^ kr) << 5) | ((cc & 1u) << 4));
+            } else {
+                // 64-feature blocks of 8 k-rows x 128 B; 16-byte units are XORed with the row number
+                const uint32_t kr = k & 7u;
+                dst_off[i] = (h * 2 + (k >> 3)) * 1024u + kr * 128u + ((cc ^ kr) << 4);
+            }
             src_off[i] = piece * 16u;
             k_of[i] = k;
         }
+        // This warp's ring of column lists: slot (iteration % kIdxSlots) holds CW indices.
+        uint32_t *my_idx = idx_ring + pw * Cfg::kIdxSlots * Cfg::kCW;
+        const uint32_t my_idx_addr = idx_ring_addr + pw * Cfg::kIdxSlots * Cfg::kCW * 4;
+        constexpr int kIdxLanes = Cfg::kCW * 4 / 16;  // lanes that copy one column list (16 bytes each)
+
         bool failed = false;
         uint64_t it = 0;  // iterations this warp has issued
-        // Position of this warp's next tile in the CTA's stream: (slab, tile inside the slab pass),
-        // ring stage and how often that stage has been used.  The warp advances 4 tiles a time.
+        // Cursor of this warp's next tile in the CTA's stream - (slab, tile inside the slab pass) -
+        // and a second cursor kIdxAhead iterations further on for the column-list fetch.  Ring
+        // stage and how often that stage has been used.  The warp advances 4 tiles a time.
         uint32_t slab = 0, tpos = (uint32_t)pw, s = (uint32_t)pw, use = 0, s_arrive = (uint32_t)pw;
         auto normalise = [&](uint32_t &sl, uint32_t &tp) {
             while (tp >= n_tiles && sl < p.n_slabs) { tp -= n_tiles; ++sl; }
         };
         if (n_tiles == 0) slab = p.n_slabs; else normalise(slab, tpos);
-        uint32_t idx_next = 0;
-        if (slab < p.n_slabs) idx_next = p.tcA2B[(uint64_t)(tile_begin + tpos) * Cfg::kCW + (lane % Cfg::kCW)];
+        uint32_t slab_f = slab, tpos_f = tpos;  // fetch cursor
+        uint64_t it_f = 0;
+        auto fetch_list = [&]() {  // column list of the fetch cursor's tile -> its ring slot; then advance
+            if (slab_f < p.n_slabs) {
+                if (lane < kIdxLanes) {
+                    const uint32_t slot = (uint32_t)(it_f % Cfg::kIdxSlots);
+                    ptx::cp_async_16(my_idx_addr + slot * Cfg::kCW * 4 + lane * 16,
+                                     p.tcA2B + (uint64_t)(tile_begin + tpos_f) * Cfg::kCW + lane * 4, 16u);
+                }
+                tpos_f += kProducerWarps;
+                normalise(slab_f, tpos_f);
+            }
+            ++it_f;
+        };
+        for (int i = 0; i < Cfg::kIdxAhead; ++i) fetch_list();
+        ptx::cp_async_commit();
+        ptx::cp_async_wait_group<0>();
+        __syncwarp();
+
         const uint32_t n_bytes = p.n * Cfg::kEsz;
         while (slab < p.n_slabs) {
             const uint32_t tile = tile_begin + tpos;
             const uint32_t slab_byte0 = slab * kNs * Cfg::kEsz;
-            const uint32_t idx_cur = idx_next;
-            // column indices of this warp's next tile, fetched a whole iteration early
-            uint32_t slab_n = slab, tpos_n = tpos + kProducerWarps;
-            normalise(slab_n, tpos_n);
-            if (slab_n < p.n_slabs) idx_next = p.tcA2B[(uint64_t)(tile_begin + tpos_n) * Cfg::kCW + (lane % Cfg::kCW)];
+            const uint32_t *list = my_idx + (uint32_t)(it % Cfg::kIdxSlots) * Cfg::kCW;
 
             bool ok = ptx::mbar_wait(empty_bar(s), (use & 1u) ^ 1u, abort_flag, limit);
             if (__any_sync(0xffffffffu, !ok)) { failed = true; break; }
@@ -273,14 +324,16 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
                 ptx::tma_load_2d(atile_addr + s * kATileBytes, &tmap_a, 0, (int32_t)(tile * kRowWindow), full_bar(s));
             }
             const uint32_t stage_addr = gather_addr + s * Cfg::kGatherBytes;
+            if (!(p.debug & 1u))
 #pragma unroll
             for (int i = 0; i < Cfg::kCopiesPerLane; ++i) {
-                const uint32_t col = __shfl_sync(0xffffffffu, idx_cur, k_of[i]);
+                const uint32_t col = list[k_of[i]];
                 const uint32_t in_row = slab_byte0 + src_off[i];
                 const bool live = col < p.cols && in_row < n_bytes;  // padded slots hold 0xFFFFFFFF
                 const uint8_t *src = live ? Bbytes + (uint64_t)col * row_pitch + in_row : Bbytes;
                 ptx::cp_async_16(stage_addr + dst_off[i], src, live ? 16u : 0u);
             }
+            fetch_list();  // rides in the same group as this tile's rows
             ptx::cp_async_commit();
             if (it >= (uint64_t)Cfg::kLag) {  // the copies issued kLag iterations ago have landed
                 ptx::cp_async_wait_group<Cfg::kLag>();
@@ -291,8 +344,8 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
                 if (s_arrive >= (uint32_t)kStages) s_arrive -= kStages;
             }
             ++it;
-            slab = slab_n;
-            tpos = tpos_n;
+            tpos += kProducerWarps;
+            normalise(slab, tpos);
             s += kProducerWarps;
             if (s >= (uint32_t)kStages) { s -= kStages; ++use; }
         }
@@ -309,52 +362,66 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
             }
         }
     } else {
-        // =========================================================== MMA issuer (warp 8, lane 0)
-        if (lane == 0) {
-            constexpr uint32_t fmt = kTf32 ? ptx::kFmtTF32 : ptx::kFmtF16;
-            constexpr uint32_t idesc_full = ptx::make_instr_desc(fmt, 128, kRowWindow, true, false);
-            constexpr uint32_t idesc_half = ptx::make_instr_desc(fmt, 64, kRowWindow, true, false);
-            // gathered-B operand: MN-major, 128-byte swizzle.  fp16: 64-feature blocks 2 KiB apart,
-            // 8-row groups 1 KiB apart.  tf32: 32-feature blocks 1 KiB apart, one 8-row group.
-            constexpr uint32_t a_lbo = kTf32 ? 1024u : 2048u, a_sbo = 1024u;
-            const uint64_t a_hi = ptx::make_smem_desc(0, a_lbo, a_sbo, ptx::kSwizzle128B) & ~0x3FFFull;
-            // A-tile operand: K-major, 32-byte swizzle, 8-row groups 256 bytes apart.
-            const uint64_t b_hi = ptx::make_smem_desc(0, 16, 256, ptx::kSwizzle32B) & ~0x3FFFull;
-            uint32_t s = 0, phase = 0;  // ring stage and the parity of its current use
-            uint32_t acc_it = 0;
-            bool ok = true;
-            for (uint32_t slab = 0; slab < p.n_slabs && ok; ++slab) {
-                uint32_t off_lo = p.rowOffset[w_begin];
-                for (uint32_t w = w_begin; w < w_end && ok; ++w, ++acc_it) {
-                    const uint32_t off_hi = p.rowOffset[w + 1];
+        // =========================================================== MMA issuer (warp 8)
+        // Lane 0 issues every MMA.  The whole warp fetches the tile counts of 32 windows at a time
+        // (one per lane, the next block in flight while this one is worked on) and hands them to
+        // lane 0 by shuffle, so the issuing lane never waits on a global load.
+        constexpr uint32_t fmt = kTf32 ? ptx::kFmtTF32 : ptx::kFmtF16;
+        constexpr uint32_t idesc_full = ptx::make_instr_desc(fmt, 128, kRowWindow, true, false);
+        constexpr uint32_t idesc_half = ptx::make_instr_desc(fmt, 64, kRowWindow, true, false);
+        // gathered-B operand: MN-major, 128-byte swizzle.  fp16: 64-feature blocks 2 KiB apart,
+        // 8-row groups 1 KiB apart, 16-byte swizzle units.  tf32: the only MN-major layout for
+        // 32-bit operands swizzles 32-byte units over groups of 4 rows: 32-feature blocks
+        // 1 KiB apart, 4-row groups 512 B apart.
+        constexpr uint32_t a_lbo = kTf32 ? 1024u : 2048u, a_sbo = kTf32 ? 512u : 1024u;
+        const uint64_t a_hi =
+            ptx::make_smem_desc(0, a_lbo, a_sbo, kTf32 ? ptx::kSwizzle128BBase32B : ptx::kSwizzle128B) & ~0x3FFFull;
+        // A-tile operand: K-major, 32-byte swizzle, 8-row groups 256 bytes apart.
+        const uint64_t b_hi = ptx::make_smem_desc(0, 16, 256, ptx::kSwizzle32B) & ~0x3FFFull;
+        uint32_t s = 0, phase = 0;  // ring stage and the parity of its current use
+        uint32_t acc_it = 0;
+        uint32_t ok = 1;
+        for (uint32_t slab = 0; slab < p.n_slabs && ok; ++slab) {
+            auto load_ends = [&](uint32_t wb) { return wb + lane < w_end ? p.rowOffset[wb + lane + 1] : 0u; };
+            uint32_t ends_n = load_ends(w_begin);
+            uint32_t off_lo = tile_begin;
+            for (uint32_t wb = w_begin; wb < w_end && ok; wb += 32) {
+                const uint32_t ends_c = ends_n;
+                if (wb + 32 < w_end) ends_n = load_ends(wb + 32);
+                const uint32_t in_block = min(32u, w_end - wb);
+                for (uint32_t i = 0; i < in_block && ok; ++i, ++acc_it) {
+                    const uint32_t off_hi = __shfl_sync(0xffffffffu, ends_c, i);
                     const uint32_t nt = off_hi - off_lo;
                     off_lo = off_hi;
-                    const uint32_t a = acc_it & 1u;
-                    ok = ptx::mbar_wait(acc_empty_bar(a), ((acc_it >> 1) & 1u) ^ 1u, abort_flag, limit);
-                    if (!ok) break;
-                    ptx::tcgen05_fence_after_sync();
-                    for (uint32_t t = 0; t < nt; ++t) {
-                        ok = ptx::mbar_wait(full_bar(s), phase, abort_flag, limit);
-                        if (!ok) break;
+                    if (lane == 0) {
+                        const uint32_t a = acc_it & 1u;
+                        bool good = ptx::mbar_wait(acc_empty_bar(a), ((acc_it >> 1) & 1u) ^ 1u, abort_flag, limit);
                         ptx::tcgen05_fence_after_sync();
-                        const uint64_t bd = b_hi | (uint64_t)(((atile_addr + s * kATileBytes) >> 4) & 0x3FFFu);
-                        const uint32_t g = gather_addr + s * Cfg::kGatherBytes;
+                        for (uint32_t t = 0; t < nt && good; ++t) {
+                            good = ptx::mbar_wait(full_bar(s), phase, abort_flag, limit);
+                            if (!good) break;
+                            ptx::tcgen05_fence_after_sync();
+                            const uint64_t bd = b_hi | (uint64_t)(((atile_addr + s * kATileBytes) >> 4) & 0x3FFFu);
+                            const uint32_t g = gather_addr + s * Cfg::kGatherBytes;
+                            if (!(p.debug & 2u))
 #pragma unroll
-                        for (int c = 0; c < Cfg::kChunks; ++c) {
-                            const uint64_t ad = a_hi | (uint64_t)(((g + c * 4096u) >> 4) & 0x3FFFu);
-                            const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
-                            const uint32_t d = tmem_base + a * kAccCols + c * 16;
-                            if (kTf32) ptx::umma_tf32_ss(d, ad, bd, half_chunk ? idesc_half : idesc_full, t != 0);
-                            else ptx::umma_f16_ss(d, ad, bd, half_chunk ? idesc_half : idesc_full, t != 0);
+                            for (int c = 0; c < Cfg::kChunks; ++c) {
+                                const uint64_t ad = a_hi | (uint64_t)(((g + c * 4096u) >> 4) & 0x3FFFu);
+                                const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
+                                const uint32_t d = tmem_base + a * kAccCols + c * 16;
+                                if (kTf32) ptx::umma_tf32_ss(d, ad, bd, half_chunk ? idesc_half : idesc_full, t != 0);
+                                else ptx::umma_f16_ss(d, ad, bd, half_chunk ? idesc_half : idesc_full, t != 0);
+                            }
+                            ptx::umma_commit(empty_bar(s));
+                            if (++s == (uint32_t)kStages) { s = 0; phase ^= 1u; }
                         }
-                        ptx::umma_commit(empty_bar(s));
-                        if (++s == (uint32_t)kStages) { s = 0; phase ^= 1u; }
+                        if (good) ptx::umma_commit(acc_full_bar(a));
+                        ok = good ? 1u : 0u;
                     }
-                    if (ok) ptx::umma_commit(acc_full_bar(a));
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
                 }
             }
         }
-        __syncwarp();
     }
 
     // ---- teardown: every role ends up here, on success and on timeout alike

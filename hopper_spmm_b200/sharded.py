@@ -1,0 +1,48 @@
+"""Row-window sharding over the ranks of a torch.distributed job (one process per GPU).
+
+The matrix shards naturally: every 16-row window writes its own rows of C, so rank p converts
+and multiplies the contiguous, nnz-balanced row range [cuts[p], cuts[p+1]) with B replicated
+and never exchanges data while computing.  The only collective is the optional all-gather of
+the row-sharded C.  (The reference is single-GPU; its row windows over CTAs,
+src/fp16.cu:86,138, are the decomposition this extends to GPUs.)
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import spmm as _spmm
+
+
+def my_rows(rows: int, row_ptr, world: int, rank: int):
+    """(cuts, r0, r1): the nnz-balanced cuts for `world` ranks and this rank's row range."""
+    cuts = _spmm.shard_rows(rows, row_ptr, world).astype(np.int64)
+    return cuts, int(cuts[rank]), int(cuts[rank + 1])
+
+
+def slice_csr(row_ptr, col_idx, values, r0: int, r1: int):
+    """CSR arrays of rows [r0, r1) with row_ptr rebased to zero."""
+    lo, hi = int(row_ptr[r0]), int(row_ptr[r1])
+    rp = (np.asarray(row_ptr[r0:r1 + 1], dtype=np.int64) - lo).astype(np.uint32)
+    return rp, col_idx[lo:hi], values[lo:hi]
+
+
+def allgather_rows(C_local, cuts, group=None):
+    """All-gather of a row-sharded C: rank p holds rows [cuts[p], cuts[p+1]).  Works on CUDA
+    tensors (NCCL) and CPU tensors (gloo).  Ranges differ in length, so every rank broadcasts
+    its own slice into the full-size result in place; there is no staging copy."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    total = int(cuts[-1])
+    full = torch.empty((total, C_local.shape[1]), dtype=C_local.dtype, device=C_local.device)
+    full[int(cuts[rank]):int(cuts[rank + 1])].copy_(C_local)
+    work = []
+    for p in range(world):
+        part = full[int(cuts[p]):int(cuts[p + 1])]
+        if part.numel():
+            src = dist.get_global_rank(group, p) if group is not None else p
+            work.append(dist.broadcast(part, src=src, group=group, async_op=True))
+    for w in work:
+        w.wait()
+    return full

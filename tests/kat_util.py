@@ -3,7 +3,9 @@
 The packers put a logical matrix into the byte layout the SpMM kernel uses:
   * gathered rows of B (UMMA "A" operand, M = features): MN-major, 128-byte swizzle.
     fp16: 64-feature blocks of 8 k-rows x 128 B (1 KiB), block (h, g) at (2h + g) KiB where g is
-    the group of 8 k-rows; tf32: 32-feature blocks, block h at h KiB, one group of 8 k-rows.
+    the group of 8 k-rows, 16-byte units XORed with the row number; tf32: 32-feature blocks of
+    4 k-rows x 128 B (512 B), block (h, g) at (2h + g) * 512 B, 32-byte units XORed with the row
+    number (the only MN-major layout tcgen05 takes for 32-bit operands).
   * 16 x CW tile of the sparse matrix (UMMA "B" operand, N = 16 window rows): K-major rows of
     32 bytes with the 32-byte swizzle, i.e. the 16-byte half of a row is flipped on rows 4-7
     and 12-15.
@@ -22,14 +24,20 @@ def pack_gathered(mat: np.ndarray) -> bytes:
     per16 = 16 // esz                      # elements per 16-byte piece
     per_block = 128 // esz                 # features per 128-byte block row
     n_blocks = (m_dim + per_block - 1) // per_block
-    groups = (k_dim + 7) // 8
-    img = np.zeros(n_blocks * groups * 1024, np.uint8)
+    group_rows = 8 if esz == 2 else 4      # k-rows per swizzle group
+    groups = (k_dim + group_rows - 1) // group_rows
+    group_bytes = group_rows * 128
+    img = np.zeros(n_blocks * groups * group_bytes, np.uint8)
     raw = mat.view(np.uint8).reshape(m_dim, k_dim, esz)
     for m in range(m_dim):
         h, cc, e = m // per_block, (m % per_block) // per16, m % per16
         for k in range(k_dim):
-            g, kr = k // 8, k % 8
-            off = (h * groups + g) * 1024 + kr * 128 + ((cc ^ kr) << 4) + e * esz
+            g, kr = k // group_rows, k % group_rows
+            if esz == 2:    # 16-byte units XORed with the row number
+                unit = (cc ^ kr) << 4
+            else:           # 32-byte units XORed with the row number
+                unit = (((cc >> 1) ^ kr) << 5) | ((cc & 1) << 4)
+            off = (h * groups + g) * group_bytes + kr * 128 + unit + e * esz
             img[off:off + esz] = raw[m, k]
     return img.tobytes()
 
@@ -60,7 +68,8 @@ def run_umma(image: bytes, mmas, n_cols=16, device=0):
 def spmm_tile_mma(tf32: bool, m: int, a_off: int, b_off: int, d_col=0, accumulate=0):
     """The MMA the SpMM kernel issues for one tile and one feature chunk."""
     idesc = capi.lib().b200spmm_kat_instr_desc(2 if tf32 else 0, m, 16, 1, 0)
-    return capi.KatMma(a_off=a_off, a_lbo=1024 if tf32 else 2048, a_sbo=1024, a_swizzle=2, b_off=b_off, b_lbo=16,
+    return capi.KatMma(a_off=a_off, a_lbo=1024 if tf32 else 2048, a_sbo=512 if tf32 else 1024,
+                       a_swizzle=1 if tf32 else 2, b_off=b_off, b_lbo=16,
                        b_sbo=256, b_swizzle=6, idesc=idesc, d_col=d_col, accumulate=accumulate, kind=1 if tf32 else 0)
 
 

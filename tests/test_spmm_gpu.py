@@ -42,8 +42,11 @@ def test_single_entry_and_single_tile(dt):
     ci, v = np.array([3], np.uint32), np.array([2.0], dt)
     B = dense_b(9, 128, 0, dt)
     C_out, _ = run_host(16, 9, rp, ci, v, B)
+    b_seen = B[3].astype(np.float32)
+    if dt == np.float32:  # the tensor core reads fp32 operands as tf32: low 13 mantissa bits dropped
+        b_seen = (b_seen.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
     expect = np.zeros((16, 128), np.float32)
-    expect[5] = 2.0 * B[3].astype(np.float32)
+    expect[5] = 2.0 * b_seen
     assert np.array_equal(C_out, expect)
 
 
