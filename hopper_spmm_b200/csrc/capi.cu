@@ -103,10 +103,11 @@ int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, int n_ctas) {
     B200_CUDA_TRY(cudaMalloc(&p->d_status, sizeof(uint32_t)));
     B200_CUDA_TRY(cudaMemset(p->d_status, 0, sizeof(uint32_t)));
     if (info.total_tiles) {
-        // `data` seen as rows of 32 bytes: one tile is 16 consecutive rows.
+        // `data` seen as rows of 32 bytes: one tile is 16 consecutive rows, one box is the four
+        // consecutive tiles of a ring stage.
         const bool f16 = info.dtype == B200SPMM_F16;
         if (!encode_2d(&p->tmap_a, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p->d_data,
-                       f16 ? 16 : 8, info.total_tiles * kRowWindow, 32, f16 ? 16 : 8, kRowWindow,
+                       f16 ? 16 : 8, info.total_tiles * kRowWindow, 32, f16 ? 16 : 8, kRowWindow * kProducerWarps,
                        CU_TENSOR_MAP_SWIZZLE_32B)) {
             g_last_cuda_error = "cuTensorMapEncodeTiled failed for the tile array";
             return B200SPMM_ERR_CUDA;
@@ -116,6 +117,13 @@ int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, int n_ctas) {
 }
 
 }  // namespace
+
+#ifdef B200SPMM_PROFILE
+static unsigned long long *g_prof = nullptr;
+extern "C" int b200spmm_debug_read_profile(unsigned long long *out, int n_ctas) {
+    return cudaMemcpy(out, g_prof, (size_t)n_ctas * 16 * 8, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -5;
+}
+#endif
 
 extern "C" {
 
@@ -317,6 +325,11 @@ int b200spmm_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, v
     prm.c_is_half = c_dtype == B200SPMM_C_F16;
     prm.status = p->d_status;
     prm.wait_limit_ns = kDeviceWaitLimitNs;
+#ifdef B200SPMM_PROFILE
+    if (!g_prof) cudaMalloc(&g_prof, 1024 * 16 * 8);
+    cudaMemsetAsync(g_prof, 0, 1024 * 16 * 8, stream);
+    prm.prof = g_prof;
+#endif
     if (const char *dbg = std::getenv("B200SPMM_DEBUG")) prm.debug = (uint32_t)std::atoi(dbg);  // measurement aid, results invalid
     return p->info.dtype == B200SPMM_F16 ? launch_dtype<false>(p, prm, stream) : launch_dtype<true>(p, prm, stream);
 }

@@ -137,6 +137,11 @@ B200_DEVICE void cp_async_16(uint32_t dst, const void *src, uint32_t src_bytes) 
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 B200_DEVICE void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Makes `bar` receive one arrival (counted among the expected ones) once every cp.async this
+// thread has issued so far has completed.
+B200_DEVICE void cp_async_mbar_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 template <int N>
 B200_DEVICE void cp_async_wait_group() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");

@@ -17,11 +17,11 @@
 // Roles in a CTA of 288 threads:
 //   warps 0-3  epilogue: tcgen05.ld -> shared staging -> 16-byte coalesced row-major C stores,
 //              plus zero-fill of rows that belong to windows without entries
-//   warps 4-7  producers: warp p owns every 4th tile of the CTA's tile stream; lane 0 issues the
-//              TMA load of the 512-byte A tile, all lanes gather the tile's CW rows of B with
-//              16-byte cp.async copies straight into the swizzled operand layout.  The column
-//              lists themselves are fetched 24 tiles ahead into a per-warp ring, so no role ever
-//              waits on a dependent global load inside its per-tile loop
+//   warps 4-7  producers: a ring stage holds four consecutive tiles, one per producer warp.  One
+//              TMA load brings the stage's four 512-byte A tiles; every warp gathers the CW rows
+//              of B its tile selects with 16-byte cp.async copies straight into the swizzled
+//              operand layout.  The column lists themselves are fetched 24 stages ahead into a
+//              per-warp ring, so no role waits on a dependent global load in its loop
 //   warp  8    lane 0 issues tcgen05.mma / tcgen05.commit; the warp owns the TMEM allocation
 //
 // Every wait is bounded; on a timeout the roles drain and the kernel raises a status bit.
@@ -34,6 +34,19 @@
 
 #include "common.hpp"
 #include "ptx_sm100.cuh"
+
+// Optional cycle accounting of the roles' waits, compiled in only with -DB200SPMM_PROFILE.
+#ifdef B200SPMM_PROFILE
+#define B200_PROF_DECL(name) long long name = 0
+#define B200_PROF_T0() const long long prof_t0__ = clock64()
+#define B200_PROF_ADD(name) name += clock64() - prof_t0__
+#define B200_PROF_STORE(slot, value) p.prof[(size_t)blockIdx.x * 16 + (slot)] = (unsigned long long)(value)
+#else
+#define B200_PROF_DECL(name)
+#define B200_PROF_T0()
+#define B200_PROF_ADD(name)
+#define B200_PROF_STORE(slot, value)
+#endif
 
 namespace b200spmm {
 
@@ -60,6 +73,9 @@ struct SpmmParams {
     uint32_t *status;            // device status word
     uint32_t debug;              // measurement aid: bit 0 skips the B gathers, bit 1 skips the MMAs
     unsigned long long wait_limit_ns;
+#ifdef B200SPMM_PROFILE
+    unsigned long long *prof;    // [gridDim.x][16] cycle counters
+#endif
 };
 
 template <bool kTf32, int kNs>
@@ -67,20 +83,24 @@ struct SpmmCfg {
     static_assert(kNs == 64 || kNs == 128 || kNs == 192 || kNs == 256, "feature slab");
     static constexpr int kCW = kTf32 ? 8 : 16;           // condensed columns per tile
     static constexpr int kEsz = kTf32 ? 4 : 2;           // bytes per element of A and B
-    static constexpr int kGatherBytes = 32 * kNs;        // CW rows x kNs features
-    static constexpr int kStageBytes = kGatherBytes + kATileBytes;
+    static constexpr int kGatherBytes = 32 * kNs;        // CW rows x kNs features, one tile
+    static constexpr int kTilesPerStage = kProducerWarps;
+    static constexpr int kStageBytes = kTilesPerStage * (kGatherBytes + kATileBytes);
     static constexpr int kFullChunks = kNs / 128;        // M = 128 MMAs per tile
     static constexpr bool kHalfChunk = (kNs % 128) != 0; // plus one M = 64 MMA
     static constexpr int kChunks = kFullChunks + (kHalfChunk ? 1 : 0);
-    // cp.async groups each producer warp keeps in flight, and ring depth (multiple of 4).
-    static constexpr int kLag = kNs == 64 ? 11 : kNs == 128 ? 7 : kNs == 192 ? 5 : 3;
-    static constexpr int kStages = kNs == 64 ? 64 : kNs == 128 ? 40 : kNs == 192 ? 28 : 20;
-    static_assert(kStages % kProducerWarps == 0 && kStages / kProducerWarps > kLag, "ring too shallow");
+    // Ring depth, and how many stages' cp.async groups a producer warp keeps in flight before it
+    // reports the oldest as landed: 4 * (kLag + 1) tiles are in flight per SM (90-100 KB); the
+    // rest of the ring absorbs the round trip through the MMA issuer.  One barrier pair serves
+    // four tiles, which keeps the per-tile cost of waits, fences and commits low.
+    static constexpr int kStages = kNs == 64 ? 16 : kNs == 128 ? 10 : kNs == 192 ? 7 : 5;
+    static constexpr int kLag = kNs == 64 ? 8 : kNs == 128 ? 4 : kNs == 192 ? 3 : 2;
+    static_assert(kStages > kLag + 1, "ring too shallow");
     static constexpr int kChunksPerRow = kNs * kEsz / 16;           // 16-byte pieces per gathered row
     static constexpr int kCopiesPerLane = kCW * kChunksPerRow / 32;  // == kNs / 16
     static constexpr int kStagingBytes = kRowWindow * kNs * 4;
     // Each producer warp keeps the column lists of its next kIdxAhead tiles in a private ring of
-    // kIdxSlots entries, fetched with the same cp.async groups as the rows they will select.
+    // kIdxSlots entries, fetched in the same cp.async groups as the rows of the current tile.
     static constexpr int kIdxSlots = 32;
     static constexpr int kIdxAhead = 24;
     static_assert(kIdxAhead > kLag && kIdxAhead < kIdxSlots, "column lists must land before they are needed");
@@ -95,40 +115,43 @@ __global__ void __launch_bounds__(kThreads, 1)
 spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p) {
     using Cfg = SpmmCfg<kTf32, kNs>;
     constexpr int kStages = Cfg::kStages;
+    constexpr int kTps = Cfg::kTilesPerStage;
     extern __shared__ uint8_t smem_raw[];
 
     // ---- shared memory carve-up (1024-byte aligned: swizzle patterns follow address bits)
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
     uint8_t *base = smem_raw + pad;
-    const uint32_t gather_addr = raw_addr + pad;                               // kStages x kGatherBytes
-    const uint32_t atile_addr = gather_addr + kStages * Cfg::kGatherBytes;      // kStages x 512
+    const uint32_t gather_addr = raw_addr + pad;                                    // kStages x 4 x kGatherBytes
+    const uint32_t atile_addr = gather_addr + kStages * kTps * Cfg::kGatherBytes;    // kStages x 4 x 512
     float *staging = reinterpret_cast<float *>(base + kStages * Cfg::kStageBytes);
     uint32_t *idx_ring = reinterpret_cast<uint32_t *>(base + kStages * Cfg::kStageBytes + Cfg::kStagingBytes);
-    const uint32_t idx_ring_addr = atile_addr + kStages * kATileBytes + Cfg::kStagingBytes;
+    const uint32_t idx_ring_addr = atile_addr + kStages * kTps * kATileBytes + Cfg::kStagingBytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(base + kStages * Cfg::kStageBytes + Cfg::kStagingBytes + Cfg::kIdxBytes);
     const uint32_t bars_addr = idx_ring_addr + Cfg::kIdxBytes;
-    auto full_bar = [&](int s) { return bars_addr + 8u * (uint32_t)s; };
-    auto empty_bar = [&](int s) { return bars_addr + 8u * (uint32_t)(kStages + s); };
-    auto acc_full_bar = [&](int a) { return bars_addr + 8u * (uint32_t)(2 * kStages + a); };
-    auto acc_empty_bar = [&](int a) { return bars_addr + 8u * (uint32_t)(2 * kStages + 2 + a); };
+    auto full_bar = [&](uint32_t s) { return bars_addr + 8u * s; };
+    auto empty_bar = [&](uint32_t s) { return bars_addr + 8u * ((uint32_t)kStages + s); };
+    auto acc_full_bar = [&](uint32_t a) { return bars_addr + 8u * (uint32_t)(2 * kStages + a); };
+    auto acc_empty_bar = [&](uint32_t a) { return bars_addr + 8u * (uint32_t)(2 * kStages + 2 + a); };
     volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(bars + 2 * kStages + 4);
     uint32_t *tmem_slot = const_cast<uint32_t *>(abort_flag) + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint64_t limit = p.wait_limit_ns;
 
-    // ---- this CTA's share of the schedule
+    // ---- this CTA's share of the schedule.  Its tiles are streamed once per feature slab; a
+    // pass is cut into stages of four consecutive tiles (the last stage of a pass may be short).
     const uint32_t w_begin = p.cta_window[blockIdx.x], w_end = p.cta_window[blockIdx.x + 1];
     const uint32_t tile_begin = p.rowOffset[w_begin], tile_end = p.rowOffset[w_end];
     const uint32_t n_tiles = tile_end - tile_begin;
+    const uint32_t stages_per_pass = (n_tiles + kTps - 1) / kTps;
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            ptx::mbar_init(full_bar(s), 1);
-            ptx::mbar_init(empty_bar(s), 1);
+        for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {
+            ptx::mbar_init(full_bar(s), kProducerWarps);  // lane 0 of each producer warp (+ the A tiles' bytes)
+            ptx::mbar_init(empty_bar(s), 1);              // tcgen05.commit of the MMA issuer
         }
-        for (int a = 0; a < 2; ++a) {
+        for (uint32_t a = 0; a < 2; ++a) {
             ptx::mbar_init(acc_full_bar(a), 1);
             ptx::mbar_init(acc_empty_bar(a), 4);
         }
@@ -150,10 +173,14 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
         const int et = tid;  // 0..127
         uint32_t acc_it = 0;
         bool failed = false;
+        B200_PROF_DECL(prof_wait_accfull);
+#ifdef B200SPMM_PROFILE
+        const long long prof_start = clock64();
+#endif
         for (uint32_t slab = 0; slab < p.n_slabs && !failed; ++slab) {
             const uint32_t f0 = slab * kNs;  // first feature of the slab
             // First rows of 32 windows at a time, one per lane, the next block fetched while this one
-            // is worked on: row_here = first row of window wb + lane, row_after = first row of the
+            // is worked on: `here` = first row of window wb + lane, `after` = first row of the
             // window that follows it (or the row count).
             auto load_rows = [&](uint32_t wb, uint32_t &here, uint32_t &after) {
                 const uint32_t w = wb + lane;
@@ -171,7 +198,14 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
                     const uint32_t row0 = __shfl_sync(0xffffffffu, here_c, i);
                     const uint32_t gap_hi = __shfl_sync(0xffffffffu, after_c, i);
                     const uint32_t a = acc_it & 1u;
-                    bool ok = ptx::mbar_wait(acc_full_bar(a), (acc_it >> 1) & 1u, abort_flag, limit);
+                    // one lane polls; every mbarrier operation costs a shared-memory slot per thread
+                    uint32_t ok = 1;
+                    if (lane == 0) {
+                        B200_PROF_T0();
+                        ok = ptx::mbar_wait(acc_full_bar(a), (acc_it >> 1) & 1u, abort_flag, limit) ? 1u : 0u;
+                        B200_PROF_ADD(prof_wait_accfull);
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
                     ptx::tcgen05_fence_after_sync();
                     if (ok) {
 #pragma unroll
@@ -251,13 +285,20 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
                 }
             }
         }
+#ifdef B200SPMM_PROFILE
+        if (tid == 0) {
+            B200_PROF_STORE(8, clock64() - prof_start);
+            B200_PROF_STORE(9, prof_wait_accfull);
+            B200_PROF_STORE(10, acc_it);
+        }
+#endif
     } else if (warp < 8) {
         // =========================================================== producer warps
-        const int pw = warp - 4;
+        const uint32_t pw = (uint32_t)(warp - 4);  // this warp fills tile slot pw of every stage
         const uint8_t *Bbytes = static_cast<const uint8_t *>(p.B);
         const uint64_t row_pitch = (uint64_t)p.ldb * Cfg::kEsz;
         // Per-lane constants of the gather: copy i moves 16-byte piece (i*32 + lane) of the tile.
-        uint32_t dst_off[Cfg::kCopiesPerLane];   // byte offset inside the stage, swizzled
+        uint32_t dst_off[Cfg::kCopiesPerLane];   // byte offset inside the tile's operand area, swizzled
         uint32_t src_off[Cfg::kCopiesPerLane];   // byte offset inside the slab's part of a B row
         uint32_t k_of[Cfg::kCopiesPerLane];      // which of the tile's CW rows
 #pragma unroll
@@ -283,26 +324,29 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
         constexpr int kIdxLanes = Cfg::kCW * 4 / 16;  // lanes that copy one column list (16 bytes each)
 
         bool failed = false;
-        uint64_t it = 0;  // iterations this warp has issued
-        // Cursor of this warp's next tile in the CTA's stream - (slab, tile inside the slab pass) -
-        // and a second cursor kIdxAhead iterations further on for the column-list fetch.  Ring
-        // stage and how often that stage has been used.  The warp advances 4 tiles a time.
-        uint32_t slab = 0, tpos = (uint32_t)pw, s = (uint32_t)pw, use = 0, s_arrive = (uint32_t)pw;
-        auto normalise = [&](uint32_t &sl, uint32_t &tp) {
-            while (tp >= n_tiles && sl < p.n_slabs) { tp -= n_tiles; ++sl; }
-        };
-        if (n_tiles == 0) slab = p.n_slabs; else normalise(slab, tpos);
-        uint32_t slab_f = slab, tpos_f = tpos;  // fetch cursor
-        uint64_t it_f = 0;
+        B200_PROF_DECL(prof_wait_empty);
+        B200_PROF_DECL(prof_wait_group);
+        B200_PROF_DECL(prof_issue);
+        B200_PROF_DECL(prof_arrive);
+#ifdef B200SPMM_PROFILE
+        const long long prof_start = clock64();
+#endif
+        // Stage cursor of the main loop - (slab, stage inside the pass) - plus ring slot and use
+        // count, and a second cursor kIdxAhead stages further on for the column-list fetch.
+        const uint32_t total_stages_lo = stages_per_pass;  // per pass
+        uint32_t slab = 0, sp = 0, s = 0, use = 0, s_arrive = 0;
+        uint32_t slab_f = 0, sp_f = 0;
+        uint32_t it = 0, it_f = 0;  // iterations issued / fetched (only their low bits are used)
+        if (total_stages_lo == 0) { slab = p.n_slabs; slab_f = p.n_slabs; }
         auto fetch_list = [&]() {  // column list of the fetch cursor's tile -> its ring slot; then advance
             if (slab_f < p.n_slabs) {
-                if (lane < kIdxLanes) {
-                    const uint32_t slot = (uint32_t)(it_f % Cfg::kIdxSlots);
+                const uint32_t tpos = sp_f * kTps + pw;
+                if (lane < kIdxLanes && tpos < n_tiles) {
+                    const uint32_t slot = it_f % Cfg::kIdxSlots;
                     ptx::cp_async_16(my_idx_addr + slot * Cfg::kCW * 4 + lane * 16,
-                                     p.tcA2B + (uint64_t)(tile_begin + tpos_f) * Cfg::kCW + lane * 4, 16u);
+                                     p.tcA2B + (uint64_t)(tile_begin + tpos) * Cfg::kCW + lane * 4, 16u);
                 }
-                tpos_f += kProducerWarps;
-                normalise(slab_f, tpos_f);
+                if (++sp_f == total_stages_lo) { sp_f = 0; ++slab_f; }
             }
             ++it_f;
         };
@@ -312,60 +356,90 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
         __syncwarp();
 
         const uint32_t n_bytes = p.n * Cfg::kEsz;
+        uint32_t issued = 0;  // stages whose copies were issued and not yet reported
         while (slab < p.n_slabs) {
-            const uint32_t tile = tile_begin + tpos;
+            const uint32_t tpos = sp * kTps + pw;
+            const bool have_tile = tpos < n_tiles;  // the last stage of a pass may be short
             const uint32_t slab_byte0 = slab * kNs * Cfg::kEsz;
-            const uint32_t *list = my_idx + (uint32_t)(it % Cfg::kIdxSlots) * Cfg::kCW;
+            const uint32_t *list = my_idx + (it % Cfg::kIdxSlots) * Cfg::kCW;
 
-            bool ok = ptx::mbar_wait(empty_bar(s), (use & 1u) ^ 1u, abort_flag, limit);
-            if (__any_sync(0xffffffffu, !ok)) { failed = true; break; }
+            uint32_t ok = 1;
             if (lane == 0) {
-                ptx::mbar_expect_tx(full_bar(s), kATileBytes);
-                ptx::tma_load_2d(atile_addr + s * kATileBytes, &tmap_a, 0, (int32_t)(tile * kRowWindow), full_bar(s));
+                {
+                    B200_PROF_T0();
+                    ok = ptx::mbar_wait(empty_bar(s), (use & 1u) ^ 1u, abort_flag, limit) ? 1u : 0u;
+                    B200_PROF_ADD(prof_wait_empty);
+                }
+                if (ok && pw == 0 && !(p.debug & 4u)) {  // the stage's four A tiles: 64 rows of 32 bytes
+                    ptx::mbar_expect_tx(full_bar(s), kTps * kATileBytes);
+                    ptx::tma_load_2d(atile_addr + s * kTps * kATileBytes, &tmap_a, 0,
+                                     (int32_t)((tile_begin + sp * kTps) * kRowWindow), full_bar(s));
+                }
             }
-            const uint32_t stage_addr = gather_addr + s * Cfg::kGatherBytes;
-            if (!(p.debug & 1u))
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) { failed = true; break; }
+            {
+                B200_PROF_T0();
+                const uint32_t tile_area = gather_addr + (s * kTps + pw) * Cfg::kGatherBytes;
+                if (have_tile && !(p.debug & 1u)) {
 #pragma unroll
-            for (int i = 0; i < Cfg::kCopiesPerLane; ++i) {
-                const uint32_t col = list[k_of[i]];
-                const uint32_t in_row = slab_byte0 + src_off[i];
-                const bool live = col < p.cols && in_row < n_bytes;  // padded slots hold 0xFFFFFFFF
-                const uint8_t *src = live ? Bbytes + (uint64_t)col * row_pitch + in_row : Bbytes;
-                ptx::cp_async_16(stage_addr + dst_off[i], src, live ? 16u : 0u);
+                    for (int i = 0; i < Cfg::kCopiesPerLane; ++i) {
+                        const uint32_t col = list[k_of[i]];
+                        const uint32_t in_row = slab_byte0 + src_off[i];
+                        const bool live = col < p.cols && in_row < n_bytes;  // padded slots hold 0xFFFFFFFF
+                        const uint8_t *src = live ? Bbytes + (uint64_t)col * row_pitch + in_row : Bbytes;
+                        ptx::cp_async_16(tile_area + dst_off[i], src, live ? 16u : 0u);
+                    }
+                }
+                fetch_list();  // rides in the same group as this tile's rows
+                ptx::cp_async_commit();
+                B200_PROF_ADD(prof_issue);
             }
-            fetch_list();  // rides in the same group as this tile's rows
-            ptx::cp_async_commit();
-            if (it >= (uint64_t)Cfg::kLag) {  // the copies issued kLag iterations ago have landed
-                ptx::cp_async_wait_group<Cfg::kLag>();
+            ++issued;
+            if (issued > (uint32_t)Cfg::kLag) {  // the copies issued kLag stages ago have landed
+                {
+                    B200_PROF_T0();
+                    ptx::cp_async_wait_group<Cfg::kLag>();
+                    B200_PROF_ADD(prof_wait_group);
+                }
+                B200_PROF_T0();
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(full_bar(s_arrive));
-                s_arrive += kProducerWarps;
-                if (s_arrive >= (uint32_t)kStages) s_arrive -= kStages;
+                if (++s_arrive == (uint32_t)kStages) s_arrive = 0;
+                --issued;
+                B200_PROF_ADD(prof_arrive);
             }
             ++it;
-            tpos += kProducerWarps;
-            normalise(slab, tpos);
-            s += kProducerWarps;
-            if (s >= (uint32_t)kStages) { s -= kStages; ++use; }
+            if (++sp == total_stages_lo) { sp = 0; ++slab; }
+            if (++s == (uint32_t)kStages) { s = 0; ++use; }
         }
+#ifdef B200SPMM_PROFILE
+        if (lane == 0 && pw == 1) {
+            B200_PROF_STORE(0, clock64() - prof_start);
+            B200_PROF_STORE(1, prof_wait_empty);
+            B200_PROF_STORE(2, prof_wait_group);
+            B200_PROF_STORE(3, it);
+            B200_PROF_STORE(11, prof_issue);
+            B200_PROF_STORE(12, prof_arrive);
+        }
+#endif
         // drain: everything this warp issued has to land before the CTA may exit
         ptx::cp_async_wait_group<0>();
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (!failed && lane == 0) {
-            const uint64_t pending = it < (uint64_t)Cfg::kLag ? it : (uint64_t)Cfg::kLag;
-            for (uint64_t i = 0; i < pending; ++i) {
+            for (; issued > 0; --issued) {
                 ptx::mbar_arrive(full_bar(s_arrive));
-                s_arrive += kProducerWarps;
-                if (s_arrive >= (uint32_t)kStages) s_arrive -= kStages;
+                if (++s_arrive == (uint32_t)kStages) s_arrive = 0;
             }
         }
     } else {
         // =========================================================== MMA issuer (warp 8)
-        // Lane 0 issues every MMA.  The whole warp fetches the tile counts of 32 windows at a time
-        // (one per lane, the next block in flight while this one is worked on) and hands them to
-        // lane 0 by shuffle, so the issuing lane never waits on a global load.
+        // Lane 0 issues every MMA, wait and commit; the other lanes follow the same control flow
+        // (which depends only on tile counts) so the warp can fetch the tile counts of 32 windows at
+        // a time - one per lane, the next block in flight while this one is worked on - and hand
+        // them round by shuffle.  Lane 0 thus never waits on a global load.
         constexpr uint32_t fmt = kTf32 ? ptx::kFmtTF32 : ptx::kFmtF16;
         constexpr uint32_t idesc_full = ptx::make_instr_desc(fmt, 128, kRowWindow, true, false);
         constexpr uint32_t idesc_half = ptx::make_instr_desc(fmt, 64, kRowWindow, true, false);
@@ -378,32 +452,58 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
             ptx::make_smem_desc(0, a_lbo, a_sbo, kTf32 ? ptx::kSwizzle128BBase32B : ptx::kSwizzle128B) & ~0x3FFFull;
         // A-tile operand: K-major, 32-byte swizzle, 8-row groups 256 bytes apart.
         const uint64_t b_hi = ptx::make_smem_desc(0, 16, 256, ptx::kSwizzle32B) & ~0x3FFFull;
-        uint32_t s = 0, phase = 0;  // ring stage and the parity of its current use
+        uint32_t s = 0, phase = 0;   // ring stage in use and the parity of its current use
+        uint32_t slot = kTps;        // next tile slot inside the stage; kTps = no stage held
         uint32_t acc_it = 0;
-        uint32_t ok = 1;
-        for (uint32_t slab = 0; slab < p.n_slabs && ok; ++slab) {
+        bool alive = true;           // lane 0 only: false after a wait gave up; the rest is skipped
+        B200_PROF_DECL(prof_wait_full);
+        B200_PROF_DECL(prof_wait_acc);
+        B200_PROF_DECL(prof_mma);
+        B200_PROF_DECL(prof_commit);
+#ifdef B200SPMM_PROFILE
+        long long prof_tiles = 0;
+        const long long prof_start = clock64();
+#endif
+        auto release_stage = [&]() {  // lane 0: the stage's operands are free once its MMAs are done
+            B200_PROF_T0();
+            ptx::umma_commit(empty_bar(s));
+            if (++s == (uint32_t)kStages) { s = 0; phase ^= 1u; }
+            B200_PROF_ADD(prof_commit);
+        };
+        for (uint32_t slab = 0; slab < p.n_slabs; ++slab) {
             auto load_ends = [&](uint32_t wb) { return wb + lane < w_end ? p.rowOffset[wb + lane + 1] : 0u; };
             uint32_t ends_n = load_ends(w_begin);
             uint32_t off_lo = tile_begin;
-            for (uint32_t wb = w_begin; wb < w_end && ok; wb += 32) {
+            for (uint32_t wb = w_begin; wb < w_end; wb += 32) {
                 const uint32_t ends_c = ends_n;
                 if (wb + 32 < w_end) ends_n = load_ends(wb + 32);
                 const uint32_t in_block = min(32u, w_end - wb);
-                for (uint32_t i = 0; i < in_block && ok; ++i, ++acc_it) {
+                for (uint32_t i = 0; i < in_block; ++i, ++acc_it) {
                     const uint32_t off_hi = __shfl_sync(0xffffffffu, ends_c, i);
                     const uint32_t nt = off_hi - off_lo;
                     off_lo = off_hi;
-                    if (lane == 0) {
-                        const uint32_t a = acc_it & 1u;
-                        bool good = ptx::mbar_wait(acc_empty_bar(a), ((acc_it >> 1) & 1u) ^ 1u, abort_flag, limit);
+                    const uint32_t a = acc_it & 1u;
+                    if (lane == 0 && alive) {
+                        B200_PROF_T0();
+                        alive = ptx::mbar_wait(acc_empty_bar(a), ((acc_it >> 1) & 1u) ^ 1u, abort_flag, limit);
                         ptx::tcgen05_fence_after_sync();
-                        for (uint32_t t = 0; t < nt && good; ++t) {
-                            good = ptx::mbar_wait(full_bar(s), phase, abort_flag, limit);
-                            if (!good) break;
-                            ptx::tcgen05_fence_after_sync();
-                            const uint64_t bd = b_hi | (uint64_t)(((atile_addr + s * kATileBytes) >> 4) & 0x3FFFu);
-                            const uint32_t g = gather_addr + s * Cfg::kGatherBytes;
-                            if (!(p.debug & 2u))
+                        B200_PROF_ADD(prof_wait_acc);
+                    }
+                    for (uint32_t t = 0; t < nt; ++t) {
+                        if (slot == (uint32_t)kTps) {  // take the next stage of the ring
+                            slot = 0;
+                            if (lane == 0 && alive) {
+                                B200_PROF_T0();
+                                alive = ptx::mbar_wait(full_bar(s), phase, abort_flag, limit);
+                                ptx::tcgen05_fence_after_sync();
+                                B200_PROF_ADD(prof_wait_full);
+                            }
+                        }
+                        if (lane == 0 && alive && !(p.debug & 2u)) {
+                            B200_PROF_T0();
+                            const uint32_t ts = s * kTps + slot;
+                            const uint64_t bd = b_hi | (uint64_t)(((atile_addr + ts * kATileBytes) >> 4) & 0x3FFFu);
+                            const uint32_t g = gather_addr + ts * Cfg::kGatherBytes;
 #pragma unroll
                             for (int c = 0; c < Cfg::kChunks; ++c) {
                                 const uint64_t ad = a_hi | (uint64_t)(((g + c * 4096u) >> 4) & 0x3FFFu);
@@ -412,16 +512,33 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
                                 if (kTf32) ptx::umma_tf32_ss(d, ad, bd, half_chunk ? idesc_half : idesc_full, t != 0);
                                 else ptx::umma_f16_ss(d, ad, bd, half_chunk ? idesc_half : idesc_full, t != 0);
                             }
-                            ptx::umma_commit(empty_bar(s));
-                            if (++s == (uint32_t)kStages) { s = 0; phase ^= 1u; }
+                            B200_PROF_ADD(prof_mma);
+#ifdef B200SPMM_PROFILE
+                            ++prof_tiles;
+#endif
                         }
-                        if (good) ptx::umma_commit(acc_full_bar(a));
-                        ok = good ? 1u : 0u;
+                        if (++slot == (uint32_t)kTps && lane == 0 && alive) release_stage();
                     }
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (lane == 0 && alive) ptx::umma_commit(acc_full_bar(a));
                 }
             }
+            // a pass ends on a stage boundary: give back a partly used last stage
+            if (slot != (uint32_t)kTps) {
+                slot = kTps;
+                if (lane == 0 && alive) release_stage();
+            }
         }
+#ifdef B200SPMM_PROFILE
+        if (lane == 0) {
+            B200_PROF_STORE(4, clock64() - prof_start);
+            B200_PROF_STORE(5, prof_wait_full);
+            B200_PROF_STORE(6, prof_wait_acc);
+            B200_PROF_STORE(7, prof_tiles);
+            B200_PROF_STORE(13, prof_mma);
+            B200_PROF_STORE(14, prof_commit);
+        }
+#endif
+        __syncwarp();
     }
 
     // ---- teardown: every role ends up here, on success and on timeout alike
