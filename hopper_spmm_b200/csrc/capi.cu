@@ -51,16 +51,16 @@ struct b200spmm_plan {
 
 namespace {
 
-template <bool kTf32, int kNs>
-int launch_one(b200spmm_plan *p, const SpmmParams &prm, cudaStream_t stream) {
-    using Cfg = SpmmCfg<kTf32, kNs>;
-    auto kernel = spmm_sm100_kernel<kTf32, kNs>;
+template <bool kTf32, int kNs, bool kTma>
+int launch_one(b200spmm_plan *p, const SpmmParams &prm, const CUtensorMap &tmap_b, cudaStream_t stream) {
+    using Cfg = SpmmCfg<kTf32, kNs, kTma>;
+    auto kernel = spmm_sm100_kernel<kTf32, kNs, kTma>;
     static thread_local int configured_device = -1;
     if (configured_device != p->device) {
         B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes));
         configured_device = p->device;
     }
-    kernel<<<p->n_ctas, kThreads, Cfg::kSmemBytes, stream>>>(p->tmap_a, prm);
+    kernel<<<p->n_ctas, kThreads, Cfg::kSmemBytes, stream>>>(p->tmap_a, tmap_b, prm);
     B200_CUDA_TRY(cudaGetLastError());
     p->last.n_ctas = p->n_ctas;
     p->last.threads = kThreads;
@@ -69,20 +69,42 @@ int launch_one(b200spmm_plan *p, const SpmmParams &prm, cudaStream_t stream) {
     p->last.n_slabs = (int)prm.n_slabs;
     p->last.smem_bytes = (int64_t)Cfg::kSmemBytes;
     p->last.kernel_launches = 1;
+    p->last.tma_gather = kTma ? 1 : 0;
     return B200SPMM_OK;
 }
 
-template <bool kTf32>
-int launch_dtype(b200spmm_plan *p, SpmmParams &prm, cudaStream_t stream) {
+template <bool kTf32, bool kTma>
+int launch_slab(b200spmm_plan *p, SpmmParams &prm, const CUtensorMap &tmap_b, cudaStream_t stream) {
     const uint32_t n64 = (prm.n + 63u) / 64u * 64u;
     const uint32_t ns = std::min(256u, n64);
     prm.n_slabs = (prm.n + ns - 1) / ns;
     switch (ns) {
-        case 64: return launch_one<kTf32, 64>(p, prm, stream);
-        case 128: return launch_one<kTf32, 128>(p, prm, stream);
-        case 192: return launch_one<kTf32, 192>(p, prm, stream);
-        default: return launch_one<kTf32, 256>(p, prm, stream);
+        case 64: return launch_one<kTf32, 64, kTma>(p, prm, tmap_b, stream);
+        case 128: return launch_one<kTf32, 128, kTma>(p, prm, tmap_b, stream);
+        case 192: return launch_one<kTf32, 192, kTma>(p, prm, tmap_b, stream);
+        default: return launch_one<kTf32, 256, kTma>(p, prm, tmap_b, stream);
     }
+}
+
+// How the rows of B are gathered: TMA tile::gather4 unless the caller asks for the cp.async
+// path (B200SPMM_GATHER=cpasync) or B is narrower than one 128-byte TMA box.
+template <bool kTf32>
+int launch_dtype(b200spmm_plan *p, SpmmParams &prm, cudaStream_t stream) {
+    constexpr uint32_t esz = kTf32 ? 4 : 2, box = 128 / esz;
+    const char *mode = std::getenv("B200SPMM_GATHER");
+    const bool want_cpasync = mode && std::strcmp(mode, "cpasync") == 0;
+    CUtensorMap tmap_b{};
+    if (want_cpasync || prm.n < box) return launch_slab<kTf32, false>(p, prm, tmap_b, stream);
+    // B seen as [cols][n] with its real row pitch; a box is 128 bytes of one row.  Rows or
+    // features past the end read as zeros.
+    if (!encode_2d(&tmap_b, kTf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, prm.B, prm.n,
+                   prm.cols, (uint64_t)prm.ldb * esz, box, 1,
+                   kTf32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) {
+        g_last_cuda_error = "cuTensorMapEncodeTiled failed for B";
+        return B200SPMM_ERR_CUDA;
+    }
+    return launch_slab<kTf32, true>(p, prm, tmap_b, stream);
 }
 
 int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, int n_ctas) {
@@ -299,7 +321,7 @@ int b200spmm_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, v
     if (!p || !d_B || !d_C || n <= 0 || ldb < n || ldc < n) return B200SPMM_ERR_INVALID_ARG;
     if (c_dtype != B200SPMM_C_F32 && c_dtype != B200SPMM_C_F16) return B200SPMM_ERR_INVALID_ARG;
     const int esz = p->info.elt_size, csz = c_dtype == B200SPMM_C_F32 ? 4 : 2;
-    if (n % 8 || n > 0x7FFFFFFF) return B200SPMM_ERR_UNSUPPORTED;
+    if (n % 8 || n > 0x7FFFFFFF || p->info.cols > 0x7FFFFFFFull) return B200SPMM_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(d_B) & 15u) || (reinterpret_cast<uintptr_t>(d_C) & 15u)) return B200SPMM_ERR_UNSUPPORTED;
     if ((ldb * esz) % 16 || (ldc * csz) % 16) return B200SPMM_ERR_UNSUPPORTED;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);

@@ -180,7 +180,7 @@ extern "C" int b200spmm_kat_tma(const void *tensor, uint64_t inner_elems, uint64
                                 int n_loads, uint32_t expect_bytes, void *dump, uint32_t dump_bytes, int device) {
     if (!tensor || !loads || !dump || n_loads < 1 || dump_bytes % 4 || dump_bytes > 96u * 1024u) return B200SPMM_ERR_INVALID_ARG;
     if (elt_size != 1 && elt_size != 2 && elt_size != 4) return B200SPMM_ERR_INVALID_ARG;
-    if (pitch_bytes % 16 || swizzle < 0 || swizzle > 3) return B200SPMM_ERR_INVALID_ARG;
+    if (pitch_bytes % 16 || swizzle < 0 || swizzle > 4) return B200SPMM_ERR_INVALID_ARG;
     for (int i = 0; i < n_loads; ++i) {
         const int32_t *l = loads + i * 7;
         if ((l[0] != 0 && l[0] != 1) || l[1] < 0 || (l[1] % 128) || ((int64_t)l[2] * elt_size) % 16) return B200SPMM_ERR_INVALID_ARG;
@@ -200,7 +200,8 @@ extern "C" int b200spmm_kat_tma(const void *tensor, uint64_t inner_elems, uint64
     const CUtensorMapDataType type = elt_size == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                    : elt_size == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
     const CUtensorMapSwizzle sw = swizzle == 0 ? CU_TENSOR_MAP_SWIZZLE_NONE : swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_32B
-                                : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+                                : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                : swizzle == 3 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
     if (!encode_2d(&map, type, d_t.p, inner_elems, rows, pitch_bytes, box_inner, box_rows, sw)) return B200SPMM_ERR_CUDA;
     const size_t smem = (size_t)dump_bytes + 1024;
     B200_CUDA_TRY(cudaFuncSetAttribute(kat_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -14,15 +14,20 @@
 // tcgen05.mma per tile and 128-feature chunk.  The accumulator lives in TMEM (16 columns per
 // chunk), double-buffered so a window's epilogue overlaps the next window's MMAs.
 //
-// Roles in a CTA of 288 threads:
+// A single GPU thread retires roughly one dependent instruction every ten cycles, so the kernel
+// is organised around instruction counts on each role's critical path, not only around bytes.
+//
+// Roles in a CTA of 544 threads:
 //   warps 0-3  epilogue: tcgen05.ld -> shared staging -> 16-byte coalesced row-major C stores,
 //              plus zero-fill of rows that belong to windows without entries
-//   warps 4-7  producers: a ring stage holds four consecutive tiles, one per producer warp.  One
-//              TMA load brings the stage's four 512-byte A tiles; every warp gathers the CW rows
-//              of B its tile selects with 16-byte cp.async copies straight into the swizzled
-//              operand layout.  The column lists themselves are fetched 24 stages ahead into a
-//              per-warp ring, so no role waits on a dependent global load in its loop
-//   warp  8    lane 0 issues tcgen05.mma / tcgen05.commit; the warp owns the TMEM allocation
+//   warp  4    lane 0 issues tcgen05.mma / tcgen05.commit; the warp owns the TMEM allocation
+//   warps 5-16 producers, three groups of four warps.  A ring stage holds four consecutive tiles;
+//              group g fills stages g, g+3, g+6, ... - one tile per warp.  The first warp of the
+//              group brings the stage's four 512-byte A tiles with one TMA load; every warp
+//              fetches the CW rows of B its tile selects with TMA tile::gather4 (four rows per
+//              instruction, one instruction per lane, landing in the swizzled operand layout;
+//              a cp.async variant exists for comparison and for very narrow B).  Column lists
+//              are fetched 12 iterations ahead into a per-warp ring.
 //
 // Every wait is bounded; on a timeout the roles drain and the kernel raises a status bit.
 #pragma once
@@ -51,8 +56,11 @@
 namespace b200spmm {
 
 constexpr int kRowWindow = 16;       // rows per window the kernels consume
-constexpr int kThreads = 288;        // 9 warps
-constexpr int kProducerWarps = 4;
+constexpr int kProducerWarps = 4;    // warps per producer group = tiles per ring stage
+constexpr int kProducerGroups = 3;
+constexpr int kMmaWarp = 4;
+constexpr int kFirstProducerWarp = 5;
+constexpr int kThreads = 32 * (kFirstProducerWarp + kProducerWarps * kProducerGroups);  // 544
 constexpr int kATileBytes = 512;     // 16 rows x 32 bytes
 constexpr uint32_t kAccCols = 32;    // TMEM columns per accumulator buffer (2 chunks x 16)
 constexpr uint32_t kTmemCols = 64;   // two accumulator buffers
@@ -71,14 +79,17 @@ struct SpmmParams {
     uint32_t n_slabs;            // ceil(n / kNs)
     uint32_t c_is_half;          // 0: fp32 C, 1: fp16 C
     uint32_t *status;            // device status word
-    uint32_t debug;              // measurement aid: bit 0 skips the B gathers, bit 1 skips the MMAs
+    uint32_t debug;              // measurement aid: bit 0 skips the B gathers, bit 1 the MMAs, bit 2 the A tiles
     unsigned long long wait_limit_ns;
 #ifdef B200SPMM_PROFILE
     unsigned long long *prof;    // [gridDim.x][16] cycle counters
 #endif
 };
 
-template <bool kTf32, int kNs>
+// kTma selects how the rows of B reach shared memory: true = TMA tile::gather4 (four rows per
+// instruction, issued by a few lanes, completion counted in bytes on the stage's mbarrier);
+// false = 16-byte cp.async copies by all lanes of the producer warps.
+template <bool kTf32, int kNs, bool kTma = true>
 struct SpmmCfg {
     static_assert(kNs == 64 || kNs == 128 || kNs == 192 || kNs == 256, "feature slab");
     static constexpr int kCW = kTf32 ? 8 : 16;           // condensed columns per tile
@@ -94,26 +105,36 @@ struct SpmmCfg {
     // rest of the ring absorbs the round trip through the MMA issuer.  One barrier pair serves
     // four tiles, which keeps the per-tile cost of waits, fences and commits low.
     static constexpr int kStages = kNs == 64 ? 16 : kNs == 128 ? 10 : kNs == 192 ? 7 : 5;
-    static constexpr int kLag = kNs == 64 ? 8 : kNs == 128 ? 4 : kNs == 192 ? 3 : 2;
-    static_assert(kStages > kLag + 1, "ring too shallow");
+    // cp.async variant only: groups a warp keeps in flight before it reports the oldest as landed
+    static constexpr int kLag = kStages / kProducerGroups >= 3 ? kStages / kProducerGroups - 2 : 0;
+    static_assert(kStages > kProducerGroups * (kLag + 1), "ring too shallow");
     static constexpr int kChunksPerRow = kNs * kEsz / 16;           // 16-byte pieces per gathered row
     static constexpr int kCopiesPerLane = kCW * kChunksPerRow / 32;  // == kNs / 16
+    // TMA gather: a box is 128 bytes of a row (64 fp16 / 32 tf32 features); one instruction moves
+    // that box for four of the tile's rows.
+    static constexpr int kBoxFeatures = 128 / kEsz;
+    static constexpr int kRowQuads = kCW / 4;
+    static constexpr int kGatherOps = kRowQuads * (kNs / kBoxFeatures);  // per tile, at most 16
+    static constexpr int kWinAhead = 16;   // windows whose tile counts the MMA issuer prefetches
+    static constexpr int kWinSlots = 64;
     static constexpr int kStagingBytes = kRowWindow * kNs * 4;
     // Each producer warp keeps the column lists of its next kIdxAhead tiles in a private ring of
     // kIdxSlots entries, fetched in the same cp.async groups as the rows of the current tile.
-    static constexpr int kIdxSlots = 32;
-    static constexpr int kIdxAhead = 24;
+    static constexpr int kIdxSlots = 16;
+    static constexpr int kIdxAhead = 12;
     static_assert(kIdxAhead > kLag && kIdxAhead < kIdxSlots, "column lists must land before they are needed");
-    static constexpr int kIdxBytes = kProducerWarps * kIdxSlots * kCW * 4;
+    static constexpr int kIdxBytes = kProducerWarps * kProducerGroups * kIdxSlots * kCW * 4;
     static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
+    static constexpr int kWinBytes = kWinSlots * 4;
     static constexpr size_t kSmemBytes =
-        1024 + (size_t)kStages * kStageBytes + kStagingBytes + kIdxBytes + kBarrierBytes;
+        1024 + (size_t)kStages * kStageBytes + kStagingBytes + kIdxBytes + kBarrierBytes + kWinBytes;
 };
 
-template <bool kTf32, int kNs>
+template <bool kTf32, int kNs, bool kTma>
 __global__ void __launch_bounds__(kThreads, 1)
-spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p) {
-    using Cfg = SpmmCfg<kTf32, kNs>;
+spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const SpmmParams p) {
+    using Cfg = SpmmCfg<kTf32, kNs, kTma>;
     constexpr int kStages = Cfg::kStages;
     constexpr int kTps = Cfg::kTilesPerStage;
     extern __shared__ uint8_t smem_raw[];
@@ -135,6 +156,9 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
     auto acc_empty_bar = [&](uint32_t a) { return bars_addr + 8u * (uint32_t)(2 * kStages + 2 + a); };
     volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(bars + 2 * kStages + 4);
     uint32_t *tmem_slot = const_cast<uint32_t *>(abort_flag) + 1;
+    volatile uint32_t *mma_done = abort_flag + 2;
+    volatile uint32_t *win_ends = reinterpret_cast<volatile uint32_t *>(bars + 2 * kStages + 4 + 2);
+    const uint32_t win_ends_addr = bars_addr + 8u * (uint32_t)(2 * kStages + 4 + 2);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint64_t limit = p.wait_limit_ns;
@@ -156,10 +180,12 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
             ptx::mbar_init(acc_empty_bar(a), 4);
         }
         *abort_flag = 0;
+        *mma_done = 0;
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tmap_a);
+        if (kTma) ptx::prefetch_tensormap(&tmap_b);
     }
-    if (warp == 8) {
+    if (warp == kMmaWarp) {
         ptx::tmem_alloc(ptx::smem_u32(tmem_slot), kTmemCols);
         ptx::tmem_relinquish_alloc_permit();
     }
@@ -292,36 +318,53 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
             B200_PROF_STORE(10, acc_it);
         }
 #endif
-    } else if (warp < 8) {
+    } else if (warp >= kFirstProducerWarp) {
         // =========================================================== producer warps
-        const uint32_t pw = (uint32_t)(warp - 4);  // this warp fills tile slot pw of every stage
+        const uint32_t pid = (uint32_t)(warp - kFirstProducerWarp);
+        const uint32_t grp = pid / kProducerWarps;  // fills stages grp, grp + 3, grp + 6, ...
+        const uint32_t pw = pid % kProducerWarps;   // with tile slot pw of each of them
+        // This warp's ring of column lists: slot (iteration % kIdxSlots) holds CW indices.
+        uint32_t *my_idx = idx_ring + pid * Cfg::kIdxSlots * Cfg::kCW;
+        const uint32_t my_idx_addr = idx_ring_addr + pid * Cfg::kIdxSlots * Cfg::kCW * 4;
+        constexpr int kIdxLanes = Cfg::kCW * 4 / 16;  // lanes that copy one column list (16 bytes each)
+
+        // ---- per-lane constants of the gather
+        // TMA: lane o issues gather instruction o of the tile: row quad g = o % kRowQuads of
+        // 128-byte column block h = o / kRowQuads.
+        uint32_t op_dst = 0, op_x = 0, op_quad = 0;
+        if (kTma) {
+            const uint32_t g = (uint32_t)lane % Cfg::kRowQuads, h = (uint32_t)lane / Cfg::kRowQuads;
+            op_quad = g;
+            op_x = h * Cfg::kBoxFeatures;
+            // fp16: block (h, rows 8j..8j+7) is 1 KiB, a quad is half of it; tf32: block (h, quad) is 512 B
+            op_dst = kTf32 ? (h * 2 + g) * 512u : (h * 2 + (g >> 1)) * 1024u + (g & 1u) * 512u;
+        }
+        // cp.async: copy i of a lane moves 16-byte piece (i*32 + lane) of the tile.
         const uint8_t *Bbytes = static_cast<const uint8_t *>(p.B);
         const uint64_t row_pitch = (uint64_t)p.ldb * Cfg::kEsz;
-        // Per-lane constants of the gather: copy i moves 16-byte piece (i*32 + lane) of the tile.
-        uint32_t dst_off[Cfg::kCopiesPerLane];   // byte offset inside the tile's operand area, swizzled
-        uint32_t src_off[Cfg::kCopiesPerLane];   // byte offset inside the slab's part of a B row
-        uint32_t k_of[Cfg::kCopiesPerLane];      // which of the tile's CW rows
+        constexpr int kCopies = kTma ? 1 : Cfg::kCopiesPerLane;
+        uint32_t dst_off[kCopies];   // byte offset inside the tile's operand area, swizzled
+        uint32_t src_off[kCopies];   // byte offset inside the slab's part of a B row
+        uint32_t k_of[kCopies];      // which of the tile's CW rows
+        if (!kTma) {
 #pragma unroll
-        for (int i = 0; i < Cfg::kCopiesPerLane; ++i) {
-            const uint32_t q = i * 32 + lane;
-            const uint32_t k = q / Cfg::kChunksPerRow, piece = q % Cfg::kChunksPerRow;
-            const uint32_t h = piece >> 3, cc = piece & 7u;  // 128-byte column block, piece inside it
-            if (kTf32) {
-                // 32-feature blocks of 4 k-rows x 128 B; 32-byte units are XORed with the row number
-                const uint32_t kr = k & 3u;
-                dst_off[i] = (h * 2 + (k >> 2)) * 512u + kr * 128u + ((((cc >> 1) ^ kr) << 5) | ((cc & 1u) << 4));
-            } else {
-                // 64-feature blocks of 8 k-rows x 128 B; 16-byte units are XORed with the row number
-                const uint32_t kr = k & 7u;
-                dst_off[i] = (h * 2 + (k >> 3)) * 1024u + kr * 128u + ((cc ^ kr) << 4);
+            for (int i = 0; i < kCopies; ++i) {
+                const uint32_t q = i * 32 + lane;
+                const uint32_t k = q / Cfg::kChunksPerRow, piece = q % Cfg::kChunksPerRow;
+                const uint32_t h = piece >> 3, cc = piece & 7u;  // 128-byte column block, piece inside it
+                if (kTf32) {
+                    // 32-feature blocks of 4 k-rows x 128 B; 32-byte units are XORed with the row number
+                    const uint32_t kr = k & 3u;
+                    dst_off[i] = (h * 2 + (k >> 2)) * 512u + kr * 128u + ((((cc >> 1) ^ kr) << 5) | ((cc & 1u) << 4));
+                } else {
+                    // 64-feature blocks of 8 k-rows x 128 B; 16-byte units are XORed with the row number
+                    const uint32_t kr = k & 7u;
+                    dst_off[i] = (h * 2 + (k >> 3)) * 1024u + kr * 128u + ((cc ^ kr) << 4);
+                }
+                src_off[i] = piece * 16u;
+                k_of[i] = k;
             }
-            src_off[i] = piece * 16u;
-            k_of[i] = k;
         }
-        // This warp's ring of column lists: slot (iteration % kIdxSlots) holds CW indices.
-        uint32_t *my_idx = idx_ring + pw * Cfg::kIdxSlots * Cfg::kCW;
-        const uint32_t my_idx_addr = idx_ring_addr + pw * Cfg::kIdxSlots * Cfg::kCW * 4;
-        constexpr int kIdxLanes = Cfg::kCW * 4 / 16;  // lanes that copy one column list (16 bytes each)
 
         bool failed = false;
         B200_PROF_DECL(prof_wait_empty);
@@ -333,11 +376,13 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
 #endif
         // Stage cursor of the main loop - (slab, stage inside the pass) - plus ring slot and use
         // count, and a second cursor kIdxAhead stages further on for the column-list fetch.
-        const uint32_t total_stages_lo = stages_per_pass;  // per pass
-        uint32_t slab = 0, sp = 0, s = 0, use = 0, s_arrive = 0;
-        uint32_t slab_f = 0, sp_f = 0;
+        uint32_t slab = 0, sp = grp, s = grp, use = 0, s_arrive = grp;
         uint32_t it = 0, it_f = 0;  // iterations issued / fetched (only their low bits are used)
-        if (total_stages_lo == 0) { slab = p.n_slabs; slab_f = p.n_slabs; }
+        auto normalise = [&](uint32_t &sl, uint32_t &st) {  // stage cursor past the end of a pass
+            while (st >= stages_per_pass && sl < p.n_slabs) { st -= stages_per_pass; ++sl; }
+        };
+        if (stages_per_pass == 0) slab = p.n_slabs; else normalise(slab, sp);
+        uint32_t slab_f = slab, sp_f = sp;
         auto fetch_list = [&]() {  // column list of the fetch cursor's tile -> its ring slot; then advance
             if (slab_f < p.n_slabs) {
                 const uint32_t tpos = sp_f * kTps + pw;
@@ -346,7 +391,8 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
                     ptx::cp_async_16(my_idx_addr + slot * Cfg::kCW * 4 + lane * 16,
                                      p.tcA2B + (uint64_t)(tile_begin + tpos) * Cfg::kCW + lane * 4, 16u);
                 }
-                if (++sp_f == total_stages_lo) { sp_f = 0; ++slab_f; }
+                sp_f += kProducerGroups;
+                normalise(slab_f, sp_f);
             }
             ++it_f;
         };
@@ -356,13 +402,15 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
         __syncwarp();
 
         const uint32_t n_bytes = p.n * Cfg::kEsz;
-        uint32_t issued = 0;  // stages whose copies were issued and not yet reported
+        uint32_t issued = 0;  // cp.async path: stages whose copies were issued and not yet reported
         while (slab < p.n_slabs) {
             const uint32_t tpos = sp * kTps + pw;
-            const bool have_tile = tpos < n_tiles;  // the last stage of a pass may be short
-            const uint32_t slab_byte0 = slab * kNs * Cfg::kEsz;
+            const bool have_tile = tpos < n_tiles && !(p.debug & 1u);  // the last stage of a pass may be short
             const uint32_t *list = my_idx + (it % Cfg::kIdxSlots) * Cfg::kCW;
+            const uint32_t tile_area = gather_addr + (s * kTps + pw) * Cfg::kGatherBytes;
 
+            // One lane polls (every mbarrier operation costs a shared-memory pipeline slot per
+            // thread); the shuffle hands the verdict to the warp and lines the lanes up again.
             uint32_t ok = 1;
             if (lane == 0) {
                 {
@@ -370,52 +418,81 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
                     ok = ptx::mbar_wait(empty_bar(s), (use & 1u) ^ 1u, abort_flag, limit) ? 1u : 0u;
                     B200_PROF_ADD(prof_wait_empty);
                 }
-                if (ok && pw == 0 && !(p.debug & 4u)) {  // the stage's four A tiles: 64 rows of 32 bytes
-                    ptx::mbar_expect_tx(full_bar(s), kTps * kATileBytes);
-                    ptx::tma_load_2d(atile_addr + s * kTps * kATileBytes, &tmap_a, 0,
-                                     (int32_t)((tile_begin + sp * kTps) * kRowWindow), full_bar(s));
+                if (ok) {
+                    const bool a_tiles = pw == 0 && !(p.debug & 4u);
+                    if (kTma) {
+                        // this warp's arrival, announcing the bytes its TMA loads will deliver
+                        const uint32_t bytes = (have_tile ? Cfg::kGatherBytes : 0u) + (a_tiles ? kTps * kATileBytes : 0u);
+                        ptx::mbar_arrive_expect_tx(full_bar(s), bytes);
+                    } else if (a_tiles) {
+                        ptx::mbar_expect_tx(full_bar(s), kTps * kATileBytes);
+                    }
+                    if (a_tiles)  // the stage's four A tiles: 64 rows of 32 bytes
+                        ptx::tma_load_2d(atile_addr + s * kTps * kATileBytes, &tmap_a, 0,
+                                         (int32_t)((tile_begin + sp * kTps) * kRowWindow), full_bar(s));
                 }
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) { failed = true; break; }
-            {
+            if (kTma) {
                 B200_PROF_T0();
-                const uint32_t tile_area = gather_addr + (s * kTps + pw) * Cfg::kGatherBytes;
-                if (have_tile && !(p.debug & 1u)) {
-#pragma unroll
-                    for (int i = 0; i < Cfg::kCopiesPerLane; ++i) {
-                        const uint32_t col = list[k_of[i]];
-                        const uint32_t in_row = slab_byte0 + src_off[i];
-                        const bool live = col < p.cols && in_row < n_bytes;  // padded slots hold 0xFFFFFFFF
-                        const uint8_t *src = live ? Bbytes + (uint64_t)col * row_pitch + in_row : Bbytes;
-                        ptx::cp_async_16(tile_area + dst_off[i], src, live ? 16u : 0u);
-                    }
+                if (have_tile && lane < Cfg::kGatherOps) {
+                    const uint4 rows4 = *reinterpret_cast<const uint4 *>(list + op_quad * 4);
+                    // padded slots hold 0xFFFFFFFF: clamp to the first row past the end, which reads zeros
+                    ptx::tma_gather4_2d(tile_area + op_dst, &tmap_b, (int32_t)(slab * kNs + op_x),
+                                        (int32_t)min(rows4.x, p.cols), (int32_t)min(rows4.y, p.cols),
+                                        (int32_t)min(rows4.z, p.cols), (int32_t)min(rows4.w, p.cols), full_bar(s));
                 }
-                fetch_list();  // rides in the same group as this tile's rows
+                fetch_list();
                 ptx::cp_async_commit();
+                // The list needed next iteration was fetched kIdxAhead groups ago: this only blocks
+                // when that many groups are still pending, and makes the guarantee explicit.
+                ptx::cp_async_wait_group<Cfg::kIdxAhead - 1>();
+                __syncwarp();
                 B200_PROF_ADD(prof_issue);
-            }
-            ++issued;
-            if (issued > (uint32_t)Cfg::kLag) {  // the copies issued kLag stages ago have landed
+            } else {
                 {
                     B200_PROF_T0();
-                    ptx::cp_async_wait_group<Cfg::kLag>();
-                    B200_PROF_ADD(prof_wait_group);
+                    const uint32_t slab_byte0 = slab * kNs * Cfg::kEsz;
+                    if (have_tile) {
+#pragma unroll
+                        for (int i = 0; i < kCopies; ++i) {
+                            const uint32_t col = list[k_of[i]];
+                            const uint32_t in_row = slab_byte0 + src_off[i];
+                            const bool live = col < p.cols && in_row < n_bytes;  // padded slots hold 0xFFFFFFFF
+                            const uint8_t *src = live ? Bbytes + (uint64_t)col * row_pitch + in_row : Bbytes;
+                            ptx::cp_async_16(tile_area + dst_off[i], src, live ? 16u : 0u);
+                        }
+                    }
+                    fetch_list();  // rides in the same group as this tile's rows
+                    ptx::cp_async_commit();
+                    B200_PROF_ADD(prof_issue);
                 }
-                B200_PROF_T0();
-                ptx::fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(full_bar(s_arrive));
-                if (++s_arrive == (uint32_t)kStages) s_arrive = 0;
-                --issued;
-                B200_PROF_ADD(prof_arrive);
+                ++issued;
+                if (issued > (uint32_t)Cfg::kLag) {  // the copies issued kLag stages ago have landed
+                    {
+                        B200_PROF_T0();
+                        ptx::cp_async_wait_group<Cfg::kLag>();
+                        B200_PROF_ADD(prof_wait_group);
+                    }
+                    B200_PROF_T0();
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(full_bar(s_arrive));
+                    s_arrive += kProducerGroups;
+                    if (s_arrive >= (uint32_t)kStages) s_arrive -= kStages;
+                    --issued;
+                    B200_PROF_ADD(prof_arrive);
+                }
             }
             ++it;
-            if (++sp == total_stages_lo) { sp = 0; ++slab; }
-            if (++s == (uint32_t)kStages) { s = 0; ++use; }
+            sp += kProducerGroups;
+            normalise(slab, sp);
+            s += kProducerGroups;
+            if (s >= (uint32_t)kStages) { s -= kStages; ++use; }
         }
 #ifdef B200SPMM_PROFILE
-        if (lane == 0 && pw == 1) {
+        if (lane == 0 && pid == 1) {
             B200_PROF_STORE(0, clock64() - prof_start);
             B200_PROF_STORE(1, prof_wait_empty);
             B200_PROF_STORE(2, prof_wait_group);
@@ -426,20 +503,25 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
 #endif
         // drain: everything this warp issued has to land before the CTA may exit
         ptx::cp_async_wait_group<0>();
-        ptx::fence_proxy_async_smem();
         __syncwarp();
-        if (!failed && lane == 0) {
-            for (; issued > 0; --issued) {
-                ptx::mbar_arrive(full_bar(s_arrive));
-                if (++s_arrive == (uint32_t)kStages) s_arrive = 0;
+        if (!kTma) {
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (!failed && lane == 0) {
+                for (; issued > 0; --issued) {
+                    ptx::mbar_arrive(full_bar(s_arrive));
+                    s_arrive += kProducerGroups;
+                    if (s_arrive >= (uint32_t)kStages) s_arrive -= kStages;
+                }
             }
         }
-    } else {
-        // =========================================================== MMA issuer (warp 8)
-        // Lane 0 issues every MMA, wait and commit; the other lanes follow the same control flow
-        // (which depends only on tile counts) so the warp can fetch the tile counts of 32 windows at
-        // a time - one per lane, the next block in flight while this one is worked on - and hand
-        // them round by shuffle.  Lane 0 thus never waits on a global load.
+        (void)failed; (void)n_bytes; (void)Bbytes; (void)row_pitch; (void)op_dst; (void)op_x; (void)op_quad; (void)s_arrive;
+    } else if (warp == kMmaWarp && lane == 0) {
+        // =========================================================== MMA issuer (warp 4, lane 0)
+        // A single thread: every instruction it executes per tile is on the critical path, so the
+        // loop is kept to a wait per four tiles, one or two MMAs per tile and a commit per four
+        // tiles.  The tile counts of the next kWinAhead windows are prefetched into shared memory
+        // with 4-byte cp.async copies, one group per window.
         constexpr uint32_t fmt = kTf32 ? ptx::kFmtTF32 : ptx::kFmtF16;
         constexpr uint32_t idesc_full = ptx::make_instr_desc(fmt, 128, kRowWindow, true, false);
         constexpr uint32_t idesc_half = ptx::make_instr_desc(fmt, 64, kRowWindow, true, false);
@@ -448,14 +530,21 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
         // 32-bit operands swizzles 32-byte units over groups of 4 rows: 32-feature blocks
         // 1 KiB apart, 4-row groups 512 B apart.
         constexpr uint32_t a_lbo = kTf32 ? 1024u : 2048u, a_sbo = kTf32 ? 512u : 1024u;
-        const uint64_t a_hi =
-            ptx::make_smem_desc(0, a_lbo, a_sbo, kTf32 ? ptx::kSwizzle128BBase32B : ptx::kSwizzle128B) & ~0x3FFFull;
+        // Descriptors are handled as 32-bit halves: the high word is constant, the low word is
+        // (leading byte offset << 16) | (address >> 4), so moving to another tile is one add.
+        const uint64_t a_desc0 =
+            ptx::make_smem_desc(gather_addr, a_lbo, a_sbo, kTf32 ? ptx::kSwizzle128BBase32B : ptx::kSwizzle128B);
         // A-tile operand: K-major, 32-byte swizzle, 8-row groups 256 bytes apart.
-        const uint64_t b_hi = ptx::make_smem_desc(0, 16, 256, ptx::kSwizzle32B) & ~0x3FFFull;
+        const uint64_t b_desc0 = ptx::make_smem_desc(atile_addr, 16, 256, ptx::kSwizzle32B);
+        const uint32_t a_hi = (uint32_t)(a_desc0 >> 32), b_hi = (uint32_t)(b_desc0 >> 32);
+        const uint32_t a_lo0 = (uint32_t)a_desc0, b_lo0 = (uint32_t)b_desc0;  // stage 0, tile slot 0
+        constexpr uint32_t kATile16 = kATileBytes >> 4, kGather16 = Cfg::kGatherBytes >> 4;
         uint32_t s = 0, phase = 0;   // ring stage in use and the parity of its current use
-        uint32_t slot = kTps;        // next tile slot inside the stage; kTps = no stage held
+        uint32_t slot = 0;           // next tile slot inside the stage; 0 = the stage still has to be awaited
+        uint32_t ad_lo = a_lo0, bd_lo = b_lo0;  // low descriptor words of tile (s, slot)
         uint32_t acc_it = 0;
-        bool alive = true;           // lane 0 only: false after a wait gave up; the rest is skipped
+        bool alive = true;
+        const bool do_mma = !(p.debug & 2u);
         B200_PROF_DECL(prof_wait_full);
         B200_PROF_DECL(prof_wait_acc);
         B200_PROF_DECL(prof_mma);
@@ -464,87 +553,144 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const SpmmParams p
         long long prof_tiles = 0;
         const long long prof_start = clock64();
 #endif
-        auto release_stage = [&]() {  // lane 0: the stage's operands are free once its MMAs are done
+        auto release_stage = [&]() {  // the stage's operands are free once the MMAs issued so far are done
             B200_PROF_T0();
             ptx::umma_commit(empty_bar(s));
-            if (++s == (uint32_t)kStages) { s = 0; phase ^= 1u; }
+            slot = 0;
+            if (++s == (uint32_t)kStages) {
+                s = 0;
+                phase ^= 1u;
+                ad_lo = a_lo0;
+                bd_lo = b_lo0;
+            }
             B200_PROF_ADD(prof_commit);
         };
-        for (uint32_t slab = 0; slab < p.n_slabs; ++slab) {
-            auto load_ends = [&](uint32_t wb) { return wb + lane < w_end ? p.rowOffset[wb + lane + 1] : 0u; };
-            uint32_t ends_n = load_ends(w_begin);
+        auto issue = [&](uint32_t d, uint32_t alo, uint32_t blo, uint32_t idesc, uint32_t acc) {
+            if (kTf32) ptx::umma_tf32_ss_lohi(d, alo, a_hi, blo, b_hi, idesc, acc);
+            else ptx::umma_f16_ss_lohi(d, alo, a_hi, blo, b_hi, idesc, acc);
+        };
+        const uint32_t n_win = w_end - w_begin;
+        for (uint32_t slab = 0; slab < p.n_slabs && alive; ++slab) {
+            // window i's last tile + 1 goes to slot i % kWinSlots, one cp.async group per window
+            for (uint32_t i = 0; i < (uint32_t)Cfg::kWinAhead; ++i) {
+                if (i < n_win) ptx::cp_async_4(win_ends_addr + (i % Cfg::kWinSlots) * 4, p.rowOffset + w_begin + i + 1);
+                ptx::cp_async_commit();
+            }
             uint32_t off_lo = tile_begin;
-            for (uint32_t wb = w_begin; wb < w_end; wb += 32) {
-                const uint32_t ends_c = ends_n;
-                if (wb + 32 < w_end) ends_n = load_ends(wb + 32);
-                const uint32_t in_block = min(32u, w_end - wb);
-                for (uint32_t i = 0; i < in_block; ++i, ++acc_it) {
-                    const uint32_t off_hi = __shfl_sync(0xffffffffu, ends_c, i);
-                    const uint32_t nt = off_hi - off_lo;
-                    off_lo = off_hi;
-                    const uint32_t a = acc_it & 1u;
-                    if (lane == 0 && alive) {
+            for (uint32_t i = 0; i < n_win && alive; ++i, ++acc_it) {
+                const uint32_t ahead = i + Cfg::kWinAhead;
+                if (ahead < n_win) ptx::cp_async_4(win_ends_addr + (ahead % Cfg::kWinSlots) * 4, p.rowOffset + w_begin + ahead + 1);
+                ptx::cp_async_commit();
+                ptx::cp_async_wait_group<Cfg::kWinAhead>();  // window i's group has landed
+                const uint32_t off_hi = win_ends[i % Cfg::kWinSlots];
+                uint32_t nt = off_hi - off_lo;
+                off_lo = off_hi;
+                const uint32_t a = acc_it & 1u;
+                {
+                    B200_PROF_T0();
+                    alive = ptx::mbar_wait(acc_empty_bar(a), ((acc_it >> 1) & 1u) ^ 1u, abort_flag, limit);
+                    ptx::tcgen05_fence_after_sync();
+                    B200_PROF_ADD(prof_wait_acc);
+                }
+                const uint32_t d = tmem_base + a * kAccCols;
+                uint32_t accumulate = 0;
+                // A segment is the run of tiles that share a ring stage and a window: at most four.
+                // Branches are what a lone thread can least afford, so a segment is straight-line
+                // code: unconditional for a whole stage inside one window, predicated otherwise.
+                while (nt != 0 && alive) {
+                    if (slot == 0) {  // first tile of a stage: its operands must have landed
                         B200_PROF_T0();
-                        alive = ptx::mbar_wait(acc_empty_bar(a), ((acc_it >> 1) & 1u) ^ 1u, abort_flag, limit);
+                        alive = ptx::mbar_wait(full_bar(s), phase, abort_flag, limit);
                         ptx::tcgen05_fence_after_sync();
-                        B200_PROF_ADD(prof_wait_acc);
+                        B200_PROF_ADD(prof_wait_full);
+                        if (!alive) break;
                     }
-                    for (uint32_t t = 0; t < nt; ++t) {
-                        if (slot == (uint32_t)kTps) {  // take the next stage of the ring
-                            slot = 0;
-                            if (lane == 0 && alive) {
-                                B200_PROF_T0();
-                                alive = ptx::mbar_wait(full_bar(s), phase, abort_flag, limit);
-                                ptx::tcgen05_fence_after_sync();
-                                B200_PROF_ADD(prof_wait_full);
-                            }
-                        }
-                        if (lane == 0 && alive && !(p.debug & 2u)) {
+                    if (slot == 0 && nt >= (uint32_t)kTps) {
+                        if (do_mma) {
                             B200_PROF_T0();
-                            const uint32_t ts = s * kTps + slot;
-                            const uint64_t bd = b_hi | (uint64_t)(((atile_addr + ts * kATileBytes) >> 4) & 0x3FFFu);
-                            const uint32_t g = gather_addr + ts * Cfg::kGatherBytes;
 #pragma unroll
-                            for (int c = 0; c < Cfg::kChunks; ++c) {
-                                const uint64_t ad = a_hi | (uint64_t)(((g + c * 4096u) >> 4) & 0x3FFFu);
-                                const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
-                                const uint32_t d = tmem_base + a * kAccCols + c * 16;
-                                if (kTf32) ptx::umma_tf32_ss(d, ad, bd, half_chunk ? idesc_half : idesc_full, t != 0);
-                                else ptx::umma_f16_ss(d, ad, bd, half_chunk ? idesc_half : idesc_full, t != 0);
+                            for (int q = 0; q < kTps; ++q) {
+#pragma unroll
+                                for (int c = 0; c < Cfg::kChunks; ++c) {
+                                    const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
+                                    issue(d + c * 16, ad_lo + q * kGather16 + c * 256u, bd_lo + q * kATile16,
+                                          half_chunk ? idesc_half : idesc_full, q == 0 ? accumulate : 1u);
+                                }
                             }
                             B200_PROF_ADD(prof_mma);
-#ifdef B200SPMM_PROFILE
-                            ++prof_tiles;
-#endif
                         }
-                        if (++slot == (uint32_t)kTps && lane == 0 && alive) release_stage();
+#ifdef B200SPMM_PROFILE
+                        prof_tiles += kTps;
+#endif
+                        accumulate = 1;
+                        nt -= kTps;
+                        ad_lo += kTps * kGather16;
+                        bd_lo += kTps * kATile16;
+                        release_stage();
+                        continue;
                     }
-                    if (lane == 0 && alive) ptx::umma_commit(acc_full_bar(a));
+                    const uint32_t k = min(nt, (uint32_t)kTps - slot);
+                    {
+                        B200_PROF_T0();
+#pragma unroll
+                        for (int q = 0; q < kTps; ++q) {
+                            const uint32_t on = (do_mma && (uint32_t)q < k) ? 1u : 0u;
+#pragma unroll
+                            for (int c = 0; c < Cfg::kChunks; ++c) {
+                                const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
+                                const uint32_t idesc = half_chunk ? idesc_half : idesc_full;
+                                const uint32_t acc = q == 0 ? accumulate : 1u;
+                                const uint32_t alo = ad_lo + q * kGather16 + c * 256u, blo = bd_lo + q * kATile16;
+                                if (kTf32) ptx::umma_tf32_ss_lohi_if(on, d + c * 16, alo, a_hi, blo, b_hi, idesc, acc);
+                                else ptx::umma_f16_ss_lohi_if(on, d + c * 16, alo, a_hi, blo, b_hi, idesc, acc);
+                            }
+                        }
+                        B200_PROF_ADD(prof_mma);
+                    }
+#ifdef B200SPMM_PROFILE
+                    prof_tiles += k;
+#endif
+                    accumulate = 1;
+                    nt -= k;
+                    slot += k;
+                    ad_lo += k * kGather16;
+                    bd_lo += k * kATile16;
+                    if (slot == (uint32_t)kTps) release_stage();
                 }
+                if (alive) ptx::umma_commit(acc_full_bar(a));
             }
             // a pass ends on a stage boundary: give back a partly used last stage
-            if (slot != (uint32_t)kTps) {
-                slot = kTps;
-                if (lane == 0 && alive) release_stage();
+            if (slot != 0 && alive) {
+                ad_lo += ((uint32_t)kTps - slot) * kGather16;
+                bd_lo += ((uint32_t)kTps - slot) * kATile16;
+                release_stage();
             }
         }
+        ptx::cp_async_wait_group<0>();
 #ifdef B200SPMM_PROFILE
-        if (lane == 0) {
-            B200_PROF_STORE(4, clock64() - prof_start);
-            B200_PROF_STORE(5, prof_wait_full);
-            B200_PROF_STORE(6, prof_wait_acc);
-            B200_PROF_STORE(7, prof_tiles);
-            B200_PROF_STORE(13, prof_mma);
-            B200_PROF_STORE(14, prof_commit);
-        }
+        B200_PROF_STORE(4, clock64() - prof_start);
+        B200_PROF_STORE(5, prof_wait_full);
+        B200_PROF_STORE(6, prof_wait_acc);
+        B200_PROF_STORE(7, prof_tiles);
+        B200_PROF_STORE(13, prof_mma);
+        B200_PROF_STORE(14, prof_commit);
 #endif
-        __syncwarp();
     }
 
+    // The idle lanes of the MMA warp sleep until lane 0 is done instead of waiting at the CTA
+    // barrier below while their warp-mate is still issuing.
+    if (warp == kMmaWarp) {
+        if (lane == 0) {
+            *mma_done = 1;
+        } else {
+            while (*mma_done == 0) __nanosleep(2000);
+        }
+        __syncwarp();
+    }
     // ---- teardown: every role ends up here, on success and on timeout alike
     ptx::tcgen05_fence_before_sync();
     __syncthreads();
-    if (warp == 8) {
+    if (warp == kMmaWarp) {
         ptx::tcgen05_fence_after_sync();
         ptx::tmem_dealloc(tmem_base, kTmemCols);
     }

@@ -179,6 +179,7 @@ typedef struct {
     int32_t n_slabs;
     int64_t smem_bytes;
     int64_t kernel_launches; /* launches issued by that call */
+    int32_t tma_gather;      /* 1: rows of B fetched by TMA tile::gather4, 0: by cp.async copies */
 } b200spmm_launch_info_t;
 int b200spmm_plan_launch_info(const b200spmm_plan_t *p, b200spmm_launch_info_t *info);
 

@@ -42,7 +42,7 @@ uint32_t b200spmm_kat_instr_desc(int fmt, int m, int n, int a_mn_major, int b_mn
 
 /*
  * Uploads a 2-D row-major tensor (rows x inner_elems, pitch_bytes between rows), encodes a tiled
- * tensor map over it (box_inner x box_rows elements, swizzle 0 none / 1 32B / 2 64B / 3 128B),
+ * tensor map over it (box_inner x box_rows elements, swizzle 0 none / 1 32B / 2 64B / 3 128B / 4 128B over 32-byte units),
  * issues `n_loads` TMA loads and dumps dump_bytes of shared memory (from its 1024-byte-aligned
  * start) to `dump`.  loads[i] = {mode, smem_off, x, y0, y1, y2, y3}: mode 0 is a tiled load of the
  * box at (x, y0); mode 1 is a four-row gather (tile::gather4) of rows y0..y3 starting at column x.

@@ -96,3 +96,27 @@ def test_tma_tile_load_past_the_end_reads_zero():
     tile = np.zeros((16, 16), np.uint16)
     tile[:8] = data[24:32]
     assert dump.tobytes() == ku.pack_tile(tile.view(np.float16))
+
+
+@pytest.mark.parametrize("dt", [np.float16, np.float32])
+def test_tma_gather4_lands_in_operand_layout(dt):
+    # 16 (fp16) / 8 (tf32) rows of B picked by index, 128 features: what one producer warp issues per tile
+    cw = 16 if dt == np.float16 else 8
+    box = 128 // np.dtype(dt).itemsize
+    K, N = 96, 128
+    B = (np.arange(K * N) % 2039).astype(np.float32).astype(dt).reshape(K, N)
+    rows = [5, 95, 3, 40, 41, 0, 63, 9, 77, 1, 2, 96, 50, 96, 96, 96][:cw]  # 96 = first row past the end
+    loads = []
+    for h in range(N // box):
+        for g in range(cw // 4):
+            dst = ((h * 2 + g) * 512) if dt == np.float32 else ((h * 2 + g // 2) * 1024 + (g % 2) * 512)
+            loads.append([1, dst, h * box] + rows[4 * g:4 * g + 4])
+    total = cw * N * np.dtype(dt).itemsize
+    as_bits = B.view(np.uint16 if dt == np.float16 else np.uint32)
+    st, dump = ku.run_tma(as_bits, box, 1, 3 if dt == np.float16 else 4, loads, total, total)
+    assert st == 0
+    gathered = np.zeros((cw, N), dt)
+    for k, r in enumerate(rows):
+        if r < K:
+            gathered[k] = B[r]
+    assert dump.tobytes() == ku.pack_gathered(np.ascontiguousarray(gathered.T))
