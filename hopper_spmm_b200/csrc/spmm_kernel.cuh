@@ -17,11 +17,14 @@
 // A single GPU thread retires roughly one dependent instruction every ten cycles, so the kernel
 // is organised around instruction counts on each role's critical path, not only around bytes.
 //
-// Roles in a CTA of 544 threads:
-//   warps 0-3  epilogue: tcgen05.ld -> shared staging -> 16-byte coalesced row-major C stores,
-//              plus zero-fill of rows that belong to windows without entries
-//   warp  4    lane 0 issues tcgen05.mma / tcgen05.commit; the warp owns the TMEM allocation
-//   warps 5-16 producers, three groups of four warps.  A ring stage holds four consecutive tiles;
+// Roles in a CTA of 672 threads:
+//   warps 0-7  epilogue, two sets of four warps; set e drains accumulator buffer e, i.e. every
+//              other window.  Warp q of a set owns TMEM lanes 32q..32q+31 (32 features):
+//              tcgen05.ld -> a private 16 x 32 staging block in shared memory -> 16-byte
+//              row-major C stores (eight lanes cover 128 contiguous bytes of a row); no barrier
+//              between warps.  Also zero-fills rows that belong to windows without entries
+//   warp  8    lane 0 issues tcgen05.mma / tcgen05.commit; the warp owns the TMEM allocation
+//   warps 9-20 producers, three groups of four warps.  A ring stage holds four consecutive tiles;
 //              group g fills stages g, g+3, g+6, ... - one tile per warp.  The first warp of the
 //              group brings the stage's four 512-byte A tiles with one TMA load; every warp
 //              fetches the CW rows of B its tile selects with TMA tile::gather4 (four rows per
@@ -58,13 +61,13 @@ namespace b200spmm {
 constexpr int kRowWindow = 16;       // rows per window the kernels consume
 constexpr int kProducerWarps = 4;    // warps per producer group = tiles per ring stage
 constexpr int kProducerGroups = 3;
-constexpr int kMmaWarp = 4;
-constexpr int kFirstProducerWarp = 5;
-constexpr int kThreads = 32 * (kFirstProducerWarp + kProducerWarps * kProducerGroups);  // 544
+constexpr int kEpilogueWarps = 8;    // two sets of four: set e drains accumulator buffer e
+constexpr int kMmaWarp = 8;
+constexpr int kFirstProducerWarp = 9;
+constexpr int kThreads = 32 * (kFirstProducerWarp + kProducerWarps * kProducerGroups);  // 672
 constexpr int kATileBytes = 512;     // 16 rows x 32 bytes
 constexpr uint32_t kAccCols = 32;    // TMEM columns per accumulator buffer (2 chunks x 16)
 constexpr uint32_t kTmemCols = 64;   // two accumulator buffers
-constexpr uint32_t kEpilogueBarrier = 1;  // named barrier id of the four epilogue warps
 
 struct SpmmParams {
     const uint32_t *rowOffset;   // [eff+1] tiles
@@ -117,7 +120,7 @@ struct SpmmCfg {
     static constexpr int kGatherOps = kRowQuads * (kNs / kBoxFeatures);  // per tile, at most 16
     static constexpr int kWinAhead = 16;   // windows whose tile counts the MMA issuer prefetches
     static constexpr int kWinSlots = 64;
-    static constexpr int kStagingBytes = kRowWindow * kNs * 4;
+    static constexpr int kStagingBytes = kEpilogueWarps * kRowWindow * 32 * 4;  // 16 x 32 floats per warp
     // Each producer warp keeps the column lists of its next kIdxAhead tiles in a private ring of
     // kIdxSlots entries, fetched in the same cp.async groups as the rows of the current tile.
     static constexpr int kIdxSlots = 16;
@@ -194,128 +197,119 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     ptx::tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp < 4) {
+    if (warp < kEpilogueWarps) {
         // =========================================================== epilogue warps
-        const int et = tid;  // 0..127
-        uint32_t acc_it = 0;
-        bool failed = false;
+        const uint32_t e = (uint32_t)warp >> 2;  // accumulator buffer this set drains
+        const uint32_t q = (uint32_t)warp & 3u;  // TMEM lane quarter = which 32 features of a 128-chunk
+        float *stg = staging + warp * (kRowWindow * 32);
+        const uint32_t n_win = w_end - w_begin;
+        const uint32_t total = p.n_slabs * n_win;  // accumulators this CTA produces, in order
         B200_PROF_DECL(prof_wait_accfull);
 #ifdef B200SPMM_PROFILE
         const long long prof_start = clock64();
+        uint32_t prof_windows = 0;
 #endif
-        for (uint32_t slab = 0; slab < p.n_slabs && !failed; ++slab) {
+        // First row of a window and of the window after it (or the row count), fetched two of
+        // this set's windows ahead so the loads are never waited for.
+        auto meta = [&](uint32_t it, uint32_t &row0, uint32_t &after) {
+            if (it < total) {
+                const uint32_t w = w_begin + it % n_win;
+                row0 = p.rowIdx[w];
+                after = w + 1 < p.eff_row_windows ? p.rowIdx[w + 1] : p.rows;
+            }
+        };
+        uint32_t row0_a = 0, after_a = 0, row0_b = 0, after_b = 0;
+        meta(e, row0_a, after_a);
+        meta(e + 2, row0_b, after_b);
+        uint32_t slab = 0, i = e;  // position of accumulator `it`: window i of slab `slab`
+        while (n_win != 0 && i >= n_win) { i -= n_win; ++slab; }
+        for (uint32_t it = e; it < total; it += 2) {
+            const uint32_t row0 = row0_a, gap_hi = after_a;
+            row0_a = row0_b;
+            after_a = after_b;
+            meta(it + 4, row0_b, after_b);
             const uint32_t f0 = slab * kNs;  // first feature of the slab
-            // First rows of 32 windows at a time, one per lane, the next block fetched while this one
-            // is worked on: `here` = first row of window wb + lane, `after` = first row of the
-            // window that follows it (or the row count).
-            auto load_rows = [&](uint32_t wb, uint32_t &here, uint32_t &after) {
-                const uint32_t w = wb + lane;
-                here = w < w_end ? p.rowIdx[w] : 0u;
-                after = (w < w_end && w + 1 < p.eff_row_windows) ? p.rowIdx[w + 1] : p.rows;
-            };
-            uint32_t here_n = 0, after_n = 0;
-            load_rows(w_begin, here_n, after_n);
-            for (uint32_t wb = w_begin; wb < w_end && !failed; wb += 32) {
-                const uint32_t here_c = here_n, after_c = after_n;
-                if (wb + 32 < w_end) load_rows(wb + 32, here_n, after_n);
-                const uint32_t in_block = min(32u, w_end - wb);
-                for (uint32_t i = 0; i < in_block; ++i, ++acc_it) {
-                    const uint32_t w = wb + i;
-                    const uint32_t row0 = __shfl_sync(0xffffffffu, here_c, i);
-                    const uint32_t gap_hi = __shfl_sync(0xffffffffu, after_c, i);
-                    const uint32_t a = acc_it & 1u;
-                    // one lane polls; every mbarrier operation costs a shared-memory slot per thread
-                    uint32_t ok = 1;
-                    if (lane == 0) {
-                        B200_PROF_T0();
-                        ok = ptx::mbar_wait(acc_full_bar(a), (acc_it >> 1) & 1u, abort_flag, limit) ? 1u : 0u;
-                        B200_PROF_ADD(prof_wait_accfull);
-                    }
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
-                    ptx::tcgen05_fence_after_sync();
-                    if (ok) {
+            uint32_t ok = 1;
+            if (lane == 0) {  // one lane polls; every mbarrier operation costs a shared-memory slot per thread
+                B200_PROF_T0();
+                ok = ptx::mbar_wait(acc_full_bar(e), (it >> 1) & 1u, abort_flag, limit) ? 1u : 0u;
+                B200_PROF_ADD(prof_wait_accfull);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            ptx::tcgen05_fence_after_sync();
+            uint32_t r[Cfg::kChunks][16];
 #pragma unroll
-                        for (int c = 0; c < Cfg::kChunks; ++c) {
-                            uint32_t r[16];
-                            ptx::tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(warp * 32) << 16) + a * kAccCols + c * 16, r);
-                            ptx::tmem_ld_wait();
-                            const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
-                            // M = 128: lane l of warp q holds feature 32q + l.  M = 64: lanes 0-15 of
-                            // warp q hold features 16q + l.
-                            const int f = half_chunk ? c * 128 + warp * 16 + lane : c * 128 + warp * 32 + lane;
-                            if (!half_chunk || lane < 16) {
+            for (int c = 0; c < Cfg::kChunks; ++c)
+                ptx::tmem_ld_32x32b_x16(tmem_base + ((q * 32u) << 16) + e * kAccCols + c * 16, r[c]);
+            ptx::tmem_ld_wait();
+            ptx::tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(acc_empty_bar(e));  // the buffer may be overwritten from here on
 #pragma unroll
-                                for (int j = 0; j < 16; ++j) staging[j * kNs + f] = __uint_as_float(r[j]);
-                            }
-                        }
-                        ptx::tcgen05_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(acc_empty_bar(a));
-                    }
-                    // staging complete for all four warps (also agrees on failure)
-                    uint32_t any_fail;
-                    asm volatile(
-                        "{\n"
-                        ".reg .pred q, r;\n"
-                        "setp.ne.u32 q, %1, 0;\n"
-                        "barrier.cta.red.or.pred r, %2, %3, q;\n"
-                        "selp.u32 %0, 1, 0, r;\n"
-                        "}\n"
-                        : "=r"(any_fail)
-                        : "r"((uint32_t)(ok ? 0 : 1)), "r"(kEpilogueBarrier), "r"(128u)
-                        : "memory");
-                    if (any_fail) {
-                        failed = true;
-                        break;
-                    }
-                    constexpr int kVecPerRow = kNs / 4;
+            for (int c = 0; c < Cfg::kChunks; ++c) {
+                const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
+                // M = 128: lane l of quarter q holds feature 32q + l.  M = 64: lanes 0-15 hold 16q + l.
+                const int width = half_chunk ? 16 : 32;  // features this warp owns in the chunk
+                if (!half_chunk || lane < 16) {
 #pragma unroll
-                    for (int it = 0; it < kRowWindow * kVecPerRow / 128; ++it) {
-                        const int idx = it * 128 + et;
-                        const int r = idx / kVecPerRow, c4 = idx % kVecPerRow;
-                        const uint32_t row = row0 + r, feat = f0 + c4 * 4;
-                        if (row < p.rows && feat < p.n) {
-                            const float4 v = *reinterpret_cast<const float4 *>(staging + r * kNs + c4 * 4);
-                            if (p.c_is_half) {
-                                __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
-                                uint2 packed;
-                                packed.x = *reinterpret_cast<uint32_t *>(&lo);
-                                packed.y = *reinterpret_cast<uint32_t *>(&hi);
-                                *reinterpret_cast<uint2 *>(static_cast<__half *>(p.C) + (int64_t)row * p.ldc + feat) = packed;
-                            } else {
-                                *reinterpret_cast<float4 *>(static_cast<float *>(p.C) + (int64_t)row * p.ldc + feat) = v;
-                            }
+                    for (int j = 0; j < 16; ++j) stg[j * width + lane] = __uint_as_float(r[c][j]);
+                }
+                __syncwarp();
+                const int vec_per_row = width / 4;
+                const uint32_t feat0 = f0 + c * 128 + q * width;
+#pragma unroll
+                for (int t = 0; t < kRowWindow * width / 4 / 32; ++t) {
+                    const int idx = t * 32 + lane;
+                    const int rr = idx / vec_per_row, c4 = idx % vec_per_row;
+                    const uint32_t row = row0 + rr, feat = feat0 + c4 * 4;
+                    if (row < p.rows && feat < p.n) {
+                        const float4 v = *reinterpret_cast<const float4 *>(stg + rr * width + c4 * 4);
+                        if (p.c_is_half) {
+                            __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+                            uint2 packed;
+                            packed.x = *reinterpret_cast<uint32_t *>(&lo);
+                            packed.y = *reinterpret_cast<uint32_t *>(&hi);
+                            *reinterpret_cast<uint2 *>(static_cast<__half *>(p.C) + (int64_t)row * p.ldc + feat) = packed;
+                        } else {
+                            *reinterpret_cast<float4 *>(static_cast<float *>(p.C) + (int64_t)row * p.ldc + feat) = v;
                         }
                     }
-                    // Rows of windows that hold no entries are absent from the format: clear the gap
-                    // that follows this window (and the one before the very first window).
-                    if (gap_hi > row0 + kRowWindow || (w == 0 && row0 > 0)) {
-                        const uint32_t slab_feats = min((uint32_t)kNs, p.n - f0);
-                        const uint32_t vec_per_row = slab_feats / 4;
-                        for (int pass = 0; pass < 2; ++pass) {
-                            const uint32_t lo = pass == 0 ? row0 + kRowWindow : 0u;
-                            const uint32_t hi = pass == 0 ? gap_hi : (w == 0 ? row0 : 0u);
-                            if (hi <= lo || lo >= p.rows) continue;
-                            const uint64_t total = (uint64_t)(hi - lo) * vec_per_row;
-                            for (uint64_t k = et; k < total; k += 128) {
-                                const uint32_t row = lo + (uint32_t)(k / vec_per_row), feat = f0 + (uint32_t)(k % vec_per_row) * 4;
-                                if (p.c_is_half)
-                                    *reinterpret_cast<uint2 *>(static_cast<__half *>(p.C) + (int64_t)row * p.ldc + feat) = make_uint2(0, 0);
-                                else
-                                    *reinterpret_cast<float4 *>(static_cast<float *>(p.C) + (int64_t)row * p.ldc + feat) = make_float4(0, 0, 0, 0);
-                            }
+                }
+                __syncwarp();
+            }
+            // Rows of windows that hold no entries are absent from the format: clear the gap that
+            // follows this window (and the one before the very first window).  Warp q of the set
+            // takes every fourth row.
+            const bool lead = (w_begin + i == 0) && row0 > 0;
+            if (gap_hi > row0 + kRowWindow || lead) {
+                const uint32_t slab_feats = min((uint32_t)kNs, p.n - f0);
+                const uint32_t vec_per_row = slab_feats / 4;
+                for (int pass = 0; pass < 2; ++pass) {
+                    const uint32_t lo = pass == 0 ? row0 + kRowWindow : 0u;
+                    const uint32_t hi = pass == 0 ? min(gap_hi, p.rows) : (lead ? row0 : 0u);
+                    for (uint32_t row = lo + q; row < hi; row += 4) {
+                        for (uint32_t v4 = lane; v4 < vec_per_row; v4 += 32) {
+                            const uint32_t feat = f0 + v4 * 4;
+                            if (p.c_is_half)
+                                *reinterpret_cast<uint2 *>(static_cast<__half *>(p.C) + (int64_t)row * p.ldc + feat) = make_uint2(0, 0);
+                            else
+                                *reinterpret_cast<float4 *>(static_cast<float *>(p.C) + (int64_t)row * p.ldc + feat) = make_float4(0, 0, 0, 0);
                         }
                     }
-                    // staging may be overwritten by the next window
-                    ptx::named_barrier_sync(kEpilogueBarrier, 128);
                 }
             }
+            i += 2;
+            while (i >= n_win) { i -= n_win; ++slab; }
+#ifdef B200SPMM_PROFILE
+            ++prof_windows;
+#endif
         }
 #ifdef B200SPMM_PROFILE
         if (tid == 0) {
             B200_PROF_STORE(8, clock64() - prof_start);
             B200_PROF_STORE(9, prof_wait_accfull);
-            B200_PROF_STORE(10, acc_it);
+            B200_PROF_STORE(10, prof_windows);
         }
 #endif
     } else if (warp >= kFirstProducerWarp) {

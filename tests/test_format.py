@@ -136,5 +136,6 @@ def test_schedule_covers_every_window_once_and_balances_tiles():
         assert st == capi.OK
         assert cuts[0] == 0 and cuts[-1] == eff and np.all(np.diff(cuts.astype(np.int64)) >= 0)
         if eff >= n_ctas * 4:
-            load = np.diff(row_offset[cuts].astype(np.int64)) + np.diff(cuts.astype(np.int64))
-            assert load.max() <= (row_offset[-1] + eff) / n_ctas + tiles.max() + 1
+            charge = 12  # tile-equivalents per window in the schedule's cost model
+            load = np.diff(row_offset[cuts].astype(np.int64)) + charge * np.diff(cuts.astype(np.int64))
+            assert load.max() <= (row_offset[-1] + charge * eff) / n_ctas + tiles.max() + charge
