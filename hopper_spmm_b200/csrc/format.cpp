@@ -184,11 +184,7 @@ int shard_rows(uint64_t rows, const uint32_t *row_ptr, int row_window, int parts
 void build_cta_schedule(const uint32_t *rowOffset, uint64_t eff, int n_ctas, std::vector<uint32_t> *cta_window) {
     cta_window->assign((size_t)n_ctas + 1, (uint32_t)eff);
     (*cta_window)[0] = 0;
-    // Cost of windows [0, w): their tiles plus a fixed charge per window.  Starting and draining an
-    // accumulator costs the MMA issuer and the epilogue warps about as much time as a dozen tiles,
-    // so matrices with many short windows (the tail of a power-law graph) are split by time, not
-    // by tile count alone.
-    constexpr uint64_t kWindowCharge = 12;
+    // Cost of windows [0, w): their tiles plus a fixed charge per window.
     auto cost = [&](uint64_t w) { return (uint64_t)rowOffset[w] + kWindowCharge * w; };
     const uint64_t total = eff ? cost(eff) : 0;
     uint64_t w = 0;

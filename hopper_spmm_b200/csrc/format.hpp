@@ -10,6 +10,12 @@ namespace b200spmm {
 
 constexpr uint32_t kIdxMax = 0xFFFFFFFFu;  // IDX_MAX, src/common.h:47
 
+// Schedule cost model.  Starting and draining an accumulator costs the MMA issuer and the epilogue
+// warps about as much time as a dozen tiles, so a window is charged its tiles plus this constant;
+// matrices with many short windows (the tail of a power-law graph) are then split by time, not by
+// tile count alone.
+constexpr uint64_t kWindowCharge = 12;
+
 struct Btcf {
     uint64_t rows = 0, cols = 0, nnzs = 0;
     uint64_t total_row_windows = 0, eff_row_windows = 0, total_tiles = 0;
