@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <string>
 #include <vector>
@@ -107,6 +108,21 @@ int launch_dtype(b200spmm_plan *p, SpmmParams &prm, cudaStream_t stream) {
     return launch_slab<kTf32, true>(p, prm, tmap_b, stream);
 }
 
+// Tensor map over `data` seen as rows of 32 bytes: one tile is 16 consecutive rows, one box is
+// the four consecutive tiles of a ring stage.
+int encode_tile_map(b200spmm_plan *p) {
+    const auto &info = p->info;
+    if (!info.total_tiles) return B200SPMM_OK;
+    const bool f16 = info.dtype == B200SPMM_F16;
+    if (!encode_2d(&p->tmap_a, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p->d_data,
+                   f16 ? 16 : 8, info.total_tiles * kRowWindow, 32, f16 ? 16 : 8, kRowWindow * kProducerWarps,
+                   CU_TENSOR_MAP_SWIZZLE_32B)) {
+        g_last_cuda_error = "cuTensorMapEncodeTiled failed for the tile array";
+        return B200SPMM_ERR_CUDA;
+    }
+    return B200SPMM_OK;
+}
+
 int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, int n_ctas) {
     const auto &info = p->info;
     if (info.row_window != kRowWindow) return B200SPMM_ERR_UNSUPPORTED;
@@ -124,21 +140,66 @@ int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, int n_ctas) {
     B200_CUDA_TRY(cudaMemcpy(p->d_cta_window, cta_window.data(), cta_window.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
     B200_CUDA_TRY(cudaMalloc(&p->d_status, sizeof(uint32_t)));
     B200_CUDA_TRY(cudaMemset(p->d_status, 0, sizeof(uint32_t)));
-    if (info.total_tiles) {
-        // `data` seen as rows of 32 bytes: one tile is 16 consecutive rows, one box is the four
-        // consecutive tiles of a ring stage.
-        const bool f16 = info.dtype == B200SPMM_F16;
-        if (!encode_2d(&p->tmap_a, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p->d_data,
-                       f16 ? 16 : 8, info.total_tiles * kRowWindow, 32, f16 ? 16 : 8, kRowWindow * kProducerWarps,
-                       CU_TENSOR_MAP_SWIZZLE_32B)) {
-            g_last_cuda_error = "cuTensorMapEncodeTiled failed for the tile array";
-            return B200SPMM_ERR_CUDA;
-        }
+    {
+        int st = encode_tile_map(p);
+        if (st != B200SPMM_OK) return st;
     }
     return B200SPMM_OK;
 }
 
 }  // namespace
+
+// ------------------------------------------------------------------ allocation-free launch path
+namespace noalloc {
+//
+// Working memory of b200spmm_spmm_noalloc: the schedule table (cuts of the row windows over the
+// CTAs) and the kernel status word.  It is part of the library image, so every GPU that loads the
+// library holds these 8 KiB until the process exits and no call ever has to allocate them.
+constexpr int kNoAllocMaxCtas = 1024;
+constexpr int kNoAllocStatusWord = kNoAllocMaxCtas + 1;  // index of the status word behind the cuts
+static __device__ __align__(256) uint32_t g_noalloc_scratch[2048];
+
+// Cuts of the effective row windows over n_ctas CTAs by the same cost model as the host
+// scheduler; thread c finds cut c.  Also clears the status word.
+__global__ void noalloc_schedule_kernel(const uint32_t *__restrict__ rowOffset, uint32_t eff, int n_ctas,
+                                        uint32_t *__restrict__ scratch) {
+    if (threadIdx.x == 0) scratch[kNoAllocStatusWord] = 0;
+    auto cost = [&](uint64_t w) { return (uint64_t)rowOffset[w] + kWindowCharge * w; };
+    const uint64_t total = eff ? cost(eff) : 0;
+    for (int c = (int)threadIdx.x; c <= n_ctas; c += (int)blockDim.x) {
+        uint64_t lo = 0, hi = eff;
+        if (c == n_ctas) {
+            lo = eff;
+        } else if (c > 0) {
+            const uint64_t target = total * (uint64_t)c / (uint64_t)n_ctas;
+            while (lo < hi) {
+                const uint64_t mid = (lo + hi) / 2;
+                if (cost(mid) < target) lo = mid + 1; else hi = mid;
+            }
+        }
+        scratch[c] = (uint32_t)lo;
+    }
+}
+
+// Device address of g_noalloc_scratch on `device`, looked up on first use.  The name of a
+// __device__ array is only a host-side handle; kernels must be given this address.
+int noalloc_scratch_address(int device, uint32_t **out) {
+    constexpr int kMaxDevices = 64;
+    static uint32_t *cache[kMaxDevices] = {};
+    static std::mutex lock;
+    if (device < 0 || device >= kMaxDevices) return B200SPMM_ERR_INVALID_ARG;
+    std::lock_guard<std::mutex> guard(lock);
+    if (!cache[device]) {
+        void *ptr = nullptr;
+        B200_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));  // `device` is current (set by the caller)
+        cache[device] = static_cast<uint32_t *>(ptr);
+    }
+    *out = cache[device];
+    return B200SPMM_OK;
+}
+
+}  // namespace noalloc
+using namespace noalloc;
 
 #ifdef B200SPMM_PROFILE
 static unsigned long long *g_prof = nullptr;
@@ -434,6 +495,76 @@ int b200spmm_bench(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, 
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
     return st;
+}
+
+int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_rowOffset, const uint32_t *d_tcA2B,
+                          const void *d_data, const uint32_t *d_rowIdx, const void *d_B, int64_t ldb, int64_t n,
+                          void *d_C, int64_t ldc, int c_dtype, int device, int n_ctas, void *stream_v) {
+    if (!info || !d_rowOffset || !d_B || !d_C || n <= 0 || ldb < n || ldc < n) return B200SPMM_ERR_INVALID_ARG;
+    if (info->total_tiles && (!d_tcA2B || !d_data || !d_rowIdx)) return B200SPMM_ERR_INVALID_ARG;
+    if (c_dtype != B200SPMM_C_F32 && c_dtype != B200SPMM_C_F16) return B200SPMM_ERR_INVALID_ARG;
+    if (info->dtype != B200SPMM_F16 && info->dtype != B200SPMM_TF32) return B200SPMM_ERR_INVALID_ARG;
+    if (info->row_window != kRowWindow || info->col_window != (info->dtype == B200SPMM_F16 ? 16 : 8))
+        return B200SPMM_ERR_UNSUPPORTED;
+    if (n_ctas > kNoAllocMaxCtas) {
+        g_last_cuda_error = "b200spmm_spmm_noalloc: n_ctas exceeds the 1024 CTAs the built-in schedule table holds";
+        return B200SPMM_ERR_UNSUPPORTED;
+    }
+    if (info->total_tiles * (uint64_t)kRowWindow >= 0x7FFFFFFFull || info->cols > 0x7FFFFFFFull || n > 0x7FFFFFFF || n % 8)
+        return B200SPMM_ERR_UNSUPPORTED;
+    const int esz = info->dtype == B200SPMM_F16 ? 2 : 4, csz = c_dtype == B200SPMM_C_F32 ? 4 : 2;
+    if ((reinterpret_cast<uintptr_t>(d_B) & 15u) || (reinterpret_cast<uintptr_t>(d_C) & 15u) ||
+        (reinterpret_cast<uintptr_t>(d_data) & 15u) || (reinterpret_cast<uintptr_t>(d_tcA2B) & 15u) ||
+        (ldb * esz) % 16 || (ldc * csz) % 16)
+        return B200SPMM_ERR_UNSUPPORTED;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    B200_CUDA_TRY(cudaSetDevice(device));
+    if (n_ctas <= 0) {
+        B200_CUDA_TRY(cudaDeviceGetAttribute(&n_ctas, cudaDevAttrMultiProcessorCount, device));
+        if (n_ctas > kNoAllocMaxCtas) n_ctas = kNoAllocMaxCtas;
+    }
+    if (info->eff_row_windows == 0) {  // nothing stored: C is all zeros
+        B200_CUDA_TRY(cudaMemset2DAsync(d_C, (size_t)ldc * csz, 0, (size_t)n * csz, info->rows, stream));
+        return B200SPMM_OK;
+    }
+    uint32_t *scratch = nullptr;
+    int st = noalloc_scratch_address(device, &scratch);
+    if (st != B200SPMM_OK) return st;
+
+    b200spmm_plan tmp;  // lives on the stack; owns nothing
+    tmp.info = *info;
+    tmp.device = device;
+    tmp.n_ctas = n_ctas;
+    tmp.d_rowOffset = const_cast<uint32_t *>(d_rowOffset);
+    tmp.d_tcA2B = const_cast<uint32_t *>(d_tcA2B);
+    tmp.d_rowIdx = const_cast<uint32_t *>(d_rowIdx);
+    tmp.d_data = const_cast<void *>(d_data);
+    st = encode_tile_map(&tmp);
+    if (st != B200SPMM_OK) return st;
+
+    // The table and the status word keep the previous call's contents: both are rewritten here,
+    // on the same stream, before the SpMM kernel reads them.
+    noalloc_schedule_kernel<<<1, 256, 0, stream>>>(
+        d_rowOffset, (uint32_t)info->eff_row_windows, n_ctas, scratch);
+    B200_CUDA_TRY(cudaGetLastError());
+
+    SpmmParams prm{};
+    prm.rowOffset = d_rowOffset;
+    prm.tcA2B = d_tcA2B;
+    prm.rowIdx = d_rowIdx;
+    prm.cta_window = scratch;
+    prm.B = d_B;
+    prm.C = d_C;
+    prm.ldb = ldb;
+    prm.ldc = ldc;
+    prm.rows = (uint32_t)info->rows;
+    prm.cols = (uint32_t)info->cols;
+    prm.n = (uint32_t)n;
+    prm.eff_row_windows = (uint32_t)info->eff_row_windows;
+    prm.c_is_half = c_dtype == B200SPMM_C_F16;
+    prm.status = scratch + kNoAllocStatusWord;
+    prm.wait_limit_ns = kDeviceWaitLimitNs;
+    return info->dtype == B200SPMM_F16 ? launch_dtype<false>(&tmp, prm, stream) : launch_dtype<true>(&tmp, prm, stream);
 }
 
 }  // extern "C"

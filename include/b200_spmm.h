@@ -172,6 +172,40 @@ int b200spmm_spmm_host(b200spmm_plan_t *p, const void *h_B, int64_t n, void *h_C
 int b200spmm_bench(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, void *d_C, int64_t ldc,
                    int c_dtype, int warmup, int runs, void *stream, float *total_ms);
 
+/*
+ * Allocation-free SpMM.  No counterpart in the reference, whose operator allocates and frees
+ * all device memory on every call (src/fp16.cu:236-279).
+ *
+ * For callers that must not, or cannot, allocate device memory at the moment they need the
+ * product: a serving loop that has handed every free byte of HBM to its own pool allocator, a
+ * host thread inside a latency budget where cudaMalloc's implicit device synchronisation is not
+ * acceptable, or a component that is simply not allowed to grow the process's footprint after
+ * start-up.  b200spmm_plan_create allocates (the device copy of the matrix, the schedule table,
+ * a status word); this entry point allocates nothing, on the host heap or on the device, and
+ * calls no allocating library routine.  The caller passes the converted matrix as four arrays
+ * that already live on `device` (for example carved out of its own pool), B and C.
+ *
+ * The kernel still needs working memory: the schedule table (one cut per CTA) and its status
+ * word.  Both live in an 8 KiB array that is part of the library image on every GPU that loads
+ * the library.  Consequences:
+ *   - n_ctas may be at most 1024 (0 = one CTA per SM); more is refused with
+ *     B200SPMM_ERR_UNSUPPORTED and a message in b200spmm_last_cuda_error().
+ *   - The first call on a device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and keeps it; make that first call
+ *     outside any stream capture.
+ *   - Every call rewrites the table and clears the status word on `stream` before the SpMM
+ *     kernel reads them, so nothing is carried over from the previous call - but all calls on
+ *     a device share the one array: two calls whose kernels can overlap on the GPU (different
+ *     streams, no dependency) race on it.  Serialise them.
+ *   - The device-side timeout flag is not read back by this call; results after a suspected
+ *     hang should be checked by the caller.
+ * Same requirements on shapes and alignment as b200spmm_spmm; d_tcA2B and d_data 16-byte aligned.
+ * Asynchronous on `stream`.
+ */
+int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_rowOffset, const uint32_t *d_tcA2B,
+                          const void *d_data, const uint32_t *d_rowIdx, const void *d_B, int64_t ldb, int64_t n,
+                          void *d_C, int64_t ldc, int c_dtype, int device, int n_ctas, void *stream);
+
 /* Per-launch facts of the most recent b200spmm_spmm on this plan. */
 typedef struct {
     int32_t n_ctas, threads, stages;
