@@ -163,7 +163,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     dtype_name, n_feat, desc = synth.CONFIGS[args.workload]
     config = {"workload": args.workload, "description": desc, "scale_down": args.scale_down, "features": n_feat,
-              "row_window": 16, "c_dtype": "f32", "parallelism": f"row-window shards x{world}, B replicated",
+              "row_window": 16, "c_dtype": "f32", "parallelism": f"row-window shards x{world} (balanced on nnz + 12 per row), B replicated",
               "l2": "operands larger than L2 (no flush needed)"}
 
     if args.impl == "reference":
@@ -202,8 +202,8 @@ def main():
     torch.cuda.synchronize()
     log(f"rank {rank}: generated {csr.rows}x{csr.cols}, nnz={csr.nnz} in {time.perf_counter() - t0:.1f}s")
     rp_full = csr.row_ptr.cpu().numpy().astype(np.uint32)
-    cuts = hs.shard_rows(csr.rows, rp_full, world).astype(np.int64)
-    r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
+    from hopper_spmm_b200 import sharded
+    cuts, r0, r1 = sharded.my_rows(csr.rows, rp_full, world, rank)
     part = csr.row_slice(r0, r1)
     rp, ci, v = part.numpy()
     total_nnz = csr.nnz
@@ -221,19 +221,20 @@ def main():
     del btcf
     C_dev = torch.empty((rows_local, n_feat), dtype=torch.float32, device=dev)
 
-    # ---- device-resident timing
+    # ---- device-resident timing (clocks are sampled from the warm-up to the end of the run)
+    clocks = ClockSampler(local_rank)
+    clocks.__enter__()
     for _ in range(args.warmup):
         plan.spmm(B, C_dev, sync=False)
     plan.sync()
     barrier()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    with ClockSampler(local_rank) as clocks:
-        ev[0].record()
-        for i in range(args.steps):
-            plan.spmm(B, C_dev, sync=False)
-            ev[i + 1].record()
-        plan.sync()
-        barrier()
+    ev[0].record()
+    for i in range(args.steps):
+        plan.spmm(B, C_dev, sync=False)
+        ev[i + 1].record()
+    plan.sync()
+    barrier()
     step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
     total_ms = ev[0].elapsed_time(ev[-1])
     info = plan.launch_info()
@@ -285,6 +286,7 @@ def main():
                 "traffic": traffic, "peak_source": f"of {peak_kind}", "kernel": "spmm_sm100_kernel",
                 "kernel_ms": kernel_ms, "algorithmic_bytes": alg}
 
+    clocks.__exit__(None, None, None)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu, _ = time_cpu_oracle(rp, ci, v, B.cpu().numpy(), 2, 1, budget_s=15.0)

@@ -267,7 +267,12 @@ const uint32_t *b200spmm_btcf_rowIdx(const b200spmm_btcf_t *h) { return h ? h->f
 void b200spmm_btcf_destroy(b200spmm_btcf_t *h) { delete h; }
 
 int b200spmm_shard_rows(uint64_t rows, const uint32_t *row_ptr, int row_window, int parts, uint64_t *row_begin) {
-    return shard_rows(rows, row_ptr, row_window, parts, row_begin);
+    return shard_rows(rows, row_ptr, row_window, parts, 0, row_begin);
+}
+
+int b200spmm_shard_rows_weighted(uint64_t rows, const uint32_t *row_ptr, int row_window, int parts,
+                                 uint64_t row_charge, uint64_t *row_begin) {
+    return shard_rows(rows, row_ptr, row_window, parts, row_charge, row_begin);
 }
 
 int b200spmm_build_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_ctas, uint32_t *cta_window) {

@@ -159,20 +159,23 @@ int convert_csr_to_btcf(uint64_t rows, uint64_t cols, uint64_t nnz, const uint32
     return B200SPMM_OK;
 }
 
-int shard_rows(uint64_t rows, const uint32_t *row_ptr, int row_window, int parts, uint64_t *row_begin) {
+int shard_rows(uint64_t rows, const uint32_t *row_ptr, int row_window, int parts, uint64_t row_charge,
+               uint64_t *row_begin) {
     if (!row_ptr || !row_begin || parts < 1 || row_window < 1) return B200SPMM_ERR_INVALID_ARG;
     const uint64_t RW = (uint64_t)row_window;
     const uint64_t n_windows = (rows + RW - 1) / RW;
-    const uint64_t nnz = row_ptr[rows];
+    // cost of rows [0, r): their entries plus a fixed charge per row (0 = balance on nnz alone)
+    auto cost = [&](uint64_t r) { return (uint64_t)row_ptr[r] + row_charge * r; };
+    const uint64_t total = cost(rows);
     row_begin[0] = 0;
     uint64_t w = 0;
     for (int p = 1; p < parts; ++p) {
-        // first window whose starting nnz offset reaches p/parts of the total
-        const uint64_t target = (nnz * (uint64_t)p + parts - 1) / parts;
+        // first window whose starting cost reaches p/parts of the total
+        const uint64_t target = (total * (uint64_t)p + parts - 1) / parts;
         uint64_t lo = w, hi = n_windows;
         while (lo < hi) {
             uint64_t mid = (lo + hi) / 2;
-            if (row_ptr[std::min(rows, mid * RW)] < target) lo = mid + 1; else hi = mid;
+            if (cost(std::min(rows, mid * RW)) < target) lo = mid + 1; else hi = mid;
         }
         w = lo;
         row_begin[p] = std::min(rows, w * RW);

@@ -35,7 +35,8 @@ int convert_csr_to_btcf(uint64_t rows, uint64_t cols, uint64_t nnz, const uint32
                         const uint32_t *col_idx, const void *values, int dtype, int row_window, int col_window,
                         int n_threads, Btcf *out);
 
-int shard_rows(uint64_t rows, const uint32_t *row_ptr, int row_window, int parts, uint64_t *row_begin);
+int shard_rows(uint64_t rows, const uint32_t *row_ptr, int row_window, int parts, uint64_t row_charge,
+               uint64_t *row_begin);
 
 // Persistent schedule: CTA c owns effective windows [cta_window[c], cta_window[c+1]); the cuts
 // follow the running tile count so every CTA streams about total_tiles / n_ctas tiles.

@@ -489,7 +489,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (lane == 0 && pid == 1) {
             B200_PROF_STORE(0, clock64() - prof_start);
             B200_PROF_STORE(1, prof_wait_empty);
-            B200_PROF_STORE(2, prof_wait_group);
+
             B200_PROF_STORE(3, it);
             B200_PROF_STORE(11, prof_issue);
             B200_PROF_STORE(12, prof_arrive);
@@ -543,6 +543,8 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         B200_PROF_DECL(prof_wait_acc);
         B200_PROF_DECL(prof_mma);
         B200_PROF_DECL(prof_commit);
+        B200_PROF_DECL(prof_head);
+        B200_PROF_DECL(prof_tail);
 #ifdef B200SPMM_PROFILE
         long long prof_tiles = 0;
         const long long prof_start = clock64();
@@ -572,11 +574,18 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
             uint32_t off_lo = tile_begin;
             for (uint32_t i = 0; i < n_win && alive; ++i, ++acc_it) {
+#ifdef B200SPMM_PROFILE
+                const long long prof_h0 = clock64();
+#endif
                 const uint32_t ahead = i + Cfg::kWinAhead;
                 if (ahead < n_win) ptx::cp_async_4(win_ends_addr + (ahead % Cfg::kWinSlots) * 4, p.rowOffset + w_begin + ahead + 1);
                 ptx::cp_async_commit();
                 ptx::cp_async_wait_group<Cfg::kWinAhead>();  // window i's group has landed
                 const uint32_t off_hi = win_ends[i % Cfg::kWinSlots];
+#ifdef B200SPMM_PROFILE
+                prof_head += clock64() - prof_h0;
+                prof_tiles += off_hi - off_lo;
+#endif
                 uint32_t nt = off_hi - off_lo;
                 off_lo = off_hi;
                 const uint32_t a = acc_it & 1u;
@@ -589,19 +598,48 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 const uint32_t d = tmem_base + a * kAccCols;
                 uint32_t accumulate = 0;
                 // A segment is the run of tiles that share a ring stage and a window: at most four.
-                // Branches are what a lone thread can least afford, so a segment is straight-line
-                // code: unconditional for a whole stage inside one window, predicated otherwise.
-                while (nt != 0 && alive) {
-                    if (slot == 0) {  // first tile of a stage: its operands must have landed
-                        B200_PROF_T0();
-                        alive = ptx::mbar_wait(full_bar(s), phase, abort_flag, limit);
-                        ptx::tcgen05_fence_after_sync();
-                        B200_PROF_ADD(prof_wait_full);
-                        if (!alive) break;
+                // Branches are what a lone thread can least afford, so the window is walked as
+                //   head - the rest of a stage the previous window left partly used (predicated MMAs),
+                //   body - whole stages: wait, four MMAs, commit; ring bookkeeping by selects,
+                //   tail - the first tiles of a stage the next window will finish (predicated MMAs).
+                auto partial = [&](uint32_t k) {  // k tiles starting at (s, slot), 0 < k < 4 or closing a stage
+                    B200_PROF_T0();
+#pragma unroll
+                    for (int q = 0; q < kTps; ++q) {
+                        const uint32_t on = (do_mma && (uint32_t)q < k) ? 1u : 0u;
+#pragma unroll
+                        for (int c = 0; c < Cfg::kChunks; ++c) {
+                            const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
+                            const uint32_t idesc = half_chunk ? idesc_half : idesc_full;
+                            const uint32_t acc = q == 0 ? accumulate : 1u;
+                            const uint32_t alo = ad_lo + q * kGather16 + c * 256u, blo = bd_lo + q * kATile16;
+                            if (kTf32) ptx::umma_tf32_ss_lohi_if(on, d + c * 16, alo, a_hi, blo, b_hi, idesc, acc);
+                            else ptx::umma_f16_ss_lohi_if(on, d + c * 16, alo, a_hi, blo, b_hi, idesc, acc);
+                        }
                     }
-                    if (slot == 0 && nt >= (uint32_t)kTps) {
+                    accumulate = 1;
+                    nt -= k;
+                    slot += k;
+                    ad_lo += k * kGather16;
+                    bd_lo += k * kATile16;
+                    B200_PROF_ADD(prof_mma);
+                };
+                auto await_stage = [&]() {  // the operands of stage s must have landed
+                    B200_PROF_T0();
+                    alive = ptx::mbar_wait(full_bar(s), phase, abort_flag, limit);
+                    ptx::tcgen05_fence_after_sync();
+                    B200_PROF_ADD(prof_wait_full);
+                };
+                if (slot != 0 && alive) {  // head
+                    partial(min(nt, (uint32_t)kTps - slot));
+                    if (slot == (uint32_t)kTps) release_stage();
+                }
+                while (nt >= (uint32_t)kTps && alive) {  // body: slot == 0 here
+                    await_stage();
+                    if (!alive) break;
+                    {
+                        B200_PROF_T0();
                         if (do_mma) {
-                            B200_PROF_T0();
 #pragma unroll
                             for (int q = 0; q < kTps; ++q) {
 #pragma unroll
@@ -611,47 +649,31 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                                           half_chunk ? idesc_half : idesc_full, q == 0 ? accumulate : 1u);
                                 }
                             }
-                            B200_PROF_ADD(prof_mma);
-                        }
-#ifdef B200SPMM_PROFILE
-                        prof_tiles += kTps;
-#endif
-                        accumulate = 1;
-                        nt -= kTps;
-                        ad_lo += kTps * kGather16;
-                        bd_lo += kTps * kATile16;
-                        release_stage();
-                        continue;
-                    }
-                    const uint32_t k = min(nt, (uint32_t)kTps - slot);
-                    {
-                        B200_PROF_T0();
-#pragma unroll
-                        for (int q = 0; q < kTps; ++q) {
-                            const uint32_t on = (do_mma && (uint32_t)q < k) ? 1u : 0u;
-#pragma unroll
-                            for (int c = 0; c < Cfg::kChunks; ++c) {
-                                const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
-                                const uint32_t idesc = half_chunk ? idesc_half : idesc_full;
-                                const uint32_t acc = q == 0 ? accumulate : 1u;
-                                const uint32_t alo = ad_lo + q * kGather16 + c * 256u, blo = bd_lo + q * kATile16;
-                                if (kTf32) ptx::umma_tf32_ss_lohi_if(on, d + c * 16, alo, a_hi, blo, b_hi, idesc, acc);
-                                else ptx::umma_f16_ss_lohi_if(on, d + c * 16, alo, a_hi, blo, b_hi, idesc, acc);
-                            }
                         }
                         B200_PROF_ADD(prof_mma);
                     }
-#ifdef B200SPMM_PROFILE
-                    prof_tiles += k;
-#endif
                     accumulate = 1;
-                    nt -= k;
-                    slot += k;
-                    ad_lo += k * kGather16;
-                    bd_lo += k * kATile16;
-                    if (slot == (uint32_t)kTps) release_stage();
+                    nt -= kTps;
+                    {
+                        B200_PROF_T0();
+                        ptx::umma_commit(empty_bar(s));
+                        const bool wrap = s + 1 == (uint32_t)kStages;  // selects, no branch
+                        s = wrap ? 0u : s + 1;
+                        phase ^= wrap ? 1u : 0u;
+                        ad_lo = wrap ? a_lo0 : ad_lo + kTps * kGather16;
+                        bd_lo = wrap ? b_lo0 : bd_lo + kTps * kATile16;
+                        B200_PROF_ADD(prof_commit);
+                    }
                 }
-                if (alive) ptx::umma_commit(acc_full_bar(a));
+                if (nt != 0 && alive) {  // tail: slot == 0, 0 < nt < 4
+                    await_stage();
+                    if (alive) partial(nt);
+                }
+                {
+                    B200_PROF_T0();
+                    if (alive) ptx::umma_commit(acc_full_bar(a));
+                    B200_PROF_ADD(prof_tail);
+                }
             }
             // a pass ends on a stage boundary: give back a partly used last stage
             if (slot != 0 && alive) {
@@ -668,6 +690,8 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         B200_PROF_STORE(7, prof_tiles);
         B200_PROF_STORE(13, prof_mma);
         B200_PROF_STORE(14, prof_commit);
+        B200_PROF_STORE(15, prof_head);
+        B200_PROF_STORE(2, prof_tail);
 #endif
     }
 

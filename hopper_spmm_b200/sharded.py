@@ -13,9 +13,13 @@ import numpy as np
 from . import spmm as _spmm
 
 
-def my_rows(rows: int, row_ptr, world: int, rank: int):
-    """(cuts, r0, r1): the nnz-balanced cuts for `world` ranks and this rank's row range."""
-    cuts = _spmm.shard_rows(rows, row_ptr, world).astype(np.int64)
+ROW_CHARGE = 12  # entries a row is charged on top of its own when the ranks' shares are cut
+
+
+def my_rows(rows: int, row_ptr, world: int, rank: int, row_charge: int = ROW_CHARGE):
+    """(cuts, r0, r1): the cuts for `world` ranks, balanced on nnz + row_charge per row, and this
+    rank's row range."""
+    cuts = _spmm.shard_rows(rows, row_ptr, world, row_charge=row_charge).astype(np.int64)
     return cuts, int(cuts[rank]), int(cuts[rank + 1])
 
 

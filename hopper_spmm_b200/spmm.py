@@ -126,12 +126,13 @@ def CSR2BTCFNOBITMAP(csr: CSR_MTX, btcf: BTCF_MTX_NO_BITMAP | None = None, row_w
     return btcf
 
 
-def shard_rows(rows: int, row_ptr, parts: int, row_window: int = ROW_WINDOW) -> np.ndarray:
-    """nnz-balanced row cuts on window boundaries: part p owns rows [cuts[p], cuts[p+1])."""
+def shard_rows(rows: int, row_ptr, parts: int, row_window: int = ROW_WINDOW, row_charge: int = 0) -> np.ndarray:
+    """Row cuts on window boundaries balanced on nnz + row_charge * rows: part p owns rows
+    [cuts[p], cuts[p+1]).  row_charge 0 is plain nnz balance."""
     row_ptr = np.ascontiguousarray(row_ptr, dtype=np.uint32)
     cuts = np.zeros(parts + 1, np.uint64)
-    capi.check(capi.lib().b200spmm_shard_rows(rows, row_ptr.ctypes.data, row_window, parts, cuts.ctypes.data),
-               "b200spmm_shard_rows")
+    capi.check(capi.lib().b200spmm_shard_rows_weighted(rows, row_ptr.ctypes.data, row_window, parts, row_charge,
+                                                       cuts.ctypes.data), "b200spmm_shard_rows_weighted")
     return cuts
 
 
