@@ -4,8 +4,8 @@ The computing code is CUDA/C++ in ``csrc/`` behind the C ABI of ``include/b200_s
 ``spmm`` mirrors the reference's host interface over it, ``synth`` makes the seeded synthetic
 benchmark inputs.
 """
-from .spmm import (BTCF_MTX_NO_BITMAP, CSR2BTCFNOBITMAP, CSR_MTX, DENSE_MTX, IDX_MAX, PERF_RESULT, ROW_WINDOW, RUNS,
+from .spmm import (BTCF_MTX_NO_BITMAP, CSR2BTCFNOBITMAP, CSR_MTX, DENSE_MTX, DeviceBtcf, IDX_MAX, PERF_RESULT, ROW_WINDOW, RUNS,
                    WARMUP_RUNS, SpmmPlan, fp16_spmm, shard_rows, tf32_spmm)
 
-__all__ = ["BTCF_MTX_NO_BITMAP", "CSR2BTCFNOBITMAP", "CSR_MTX", "DENSE_MTX", "IDX_MAX", "PERF_RESULT", "ROW_WINDOW",
+__all__ = ["BTCF_MTX_NO_BITMAP", "CSR2BTCFNOBITMAP", "CSR_MTX", "DENSE_MTX", "DeviceBtcf", "IDX_MAX", "PERF_RESULT", "ROW_WINDOW",
            "RUNS", "WARMUP_RUNS", "SpmmPlan", "fp16_spmm", "shard_rows", "tf32_spmm"]

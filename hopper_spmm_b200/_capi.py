@@ -44,6 +44,15 @@ SIGNATURES = {
     "b200spmm_btcf_data": (vp, [vp]),
     "b200spmm_btcf_rowIdx": (vp, [vp]),
     "b200spmm_btcf_destroy": (None, [vp]),
+    "b200spmm_csr2btcf_nobitmap_device": (C.c_int, [u64, u64, u64, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp,
+                                                    C.POINTER(vp)]),
+    "b200spmm_dbtcf_info": (C.c_int, [vp, C.POINTER(BtcfInfo)]),
+    "b200spmm_dbtcf_rowOffset": (vp, [vp]),
+    "b200spmm_dbtcf_tcA2B": (vp, [vp]),
+    "b200spmm_dbtcf_data": (vp, [vp]),
+    "b200spmm_dbtcf_rowIdx": (vp, [vp]),
+    "b200spmm_dbtcf_copy_to_host": (C.c_int, [vp, vp, vp, vp, vp]),
+    "b200spmm_dbtcf_destroy": (None, [vp]),
     "b200spmm_shard_rows": (C.c_int, [u64, vp, C.c_int, C.c_int, vp]),
     "b200spmm_shard_rows_weighted": (C.c_int, [u64, vp, C.c_int, C.c_int, u64, vp]),
     "b200spmm_build_schedule": (C.c_int, [vp, u64, C.c_int, vp]),

@@ -126,6 +126,61 @@ def CSR2BTCFNOBITMAP(csr: CSR_MTX, btcf: BTCF_MTX_NO_BITMAP | None = None, row_w
     return btcf
 
 
+class DeviceBtcf:
+    """BTCF_MTX_NO_BITMAP (src/utils/class.h:74-85) resident on the GPU, made by the device-side
+    converter from CSR tensors that already live there."""
+
+    def __init__(self, rows, cols, row_ptr, col_idx, values, row_window: int = ROW_WINDOW, col_window: int = 0,
+                 device: int = 0):
+        """row_ptr / col_idx: CUDA int32 tensors (bit patterns of uint32), values: CUDA float16 or
+        float32; columns ascending and distinct inside every row."""
+        import torch
+        if not (row_ptr.is_cuda and col_idx.is_cuda and values.is_cuda):
+            raise ValueError("DeviceBtcf takes CUDA tensors")
+        if row_ptr.dtype != torch.int32 or col_idx.dtype != torch.int32 or values.dtype not in (torch.float16, torch.float32):
+            raise TypeError("row_ptr/col_idx must be int32, values float16 or float32")
+        lib = capi.lib()
+        self._h = C.c_void_p()
+        dtype = capi.F16 if values.dtype == torch.float16 else capi.TF32
+        s = torch.cuda.current_stream(values.device).cuda_stream
+        st = lib.b200spmm_csr2btcf_nobitmap_device(rows, cols, col_idx.numel(), row_ptr.data_ptr(), col_idx.data_ptr(),
+                                                   values.data_ptr(), dtype, row_window, col_window, device, s,
+                                                   C.byref(self._h))
+        capi.check(st, "b200spmm_csr2btcf_nobitmap_device")
+        self.info = capi.BtcfInfo()
+        capi.check(lib.b200spmm_dbtcf_info(self._h, C.byref(self.info)), "b200spmm_dbtcf_info")
+        self.device = device
+        self.dtype = np.float16 if dtype == capi.F16 else np.float32
+        for k in ("rows", "cols", "nnzs", "total_row_windows", "eff_row_windows", "total_tiles", "row_window",
+                  "col_window"):
+            setattr(self, k, getattr(self.info, k))
+        self.ptr = {k: getattr(lib, f"b200spmm_dbtcf_{k}")(self._h) for k in ("rowOffset", "tcA2B", "data", "rowIdx")}
+
+    def to_host(self):
+        """The four arrays copied to numpy (for comparison with the host converter)."""
+        cw, rw = self.col_window, self.row_window
+        out = {"rowOffset": np.zeros(self.eff_row_windows + 1, np.uint32),
+               "tcA2B": np.zeros(self.total_tiles * cw, np.uint32),
+               "data": np.zeros(self.total_tiles * rw * cw, self.dtype),
+               "rowIdx": np.zeros(self.eff_row_windows, np.uint32)}
+        capi.check(capi.lib().b200spmm_dbtcf_copy_to_host(self._h, *(out[k].ctypes.data if out[k].size else
+                                                                     np.zeros(1, np.uint32).ctypes.data
+                                                                     for k in ("rowOffset", "tcA2B", "data", "rowIdx"))),
+                   "b200spmm_dbtcf_copy_to_host")
+        return out
+
+    def close(self):
+        if getattr(self, "_h", None):
+            capi.lib().b200spmm_dbtcf_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def shard_rows(rows: int, row_ptr, parts: int, row_window: int = ROW_WINDOW, row_charge: int = 0) -> np.ndarray:
     """Row cuts on window boundaries balanced on nnz + row_charge * rows: part p owns rows
     [cuts[p], cuts[p+1]).  row_charge 0 is plain nnz balance."""
@@ -145,7 +200,12 @@ class SpmmPlan:
         lib = capi.lib()
         self._p = C.c_void_p()
         self._keep = device_arrays  # borrowed device tensors must outlive the plan
-        if device_arrays is not None:
+        if isinstance(btcf, DeviceBtcf):
+            self._keep = btcf  # the plan borrows the arrays
+            st = lib.b200spmm_plan_create_device(C.byref(btcf.info), btcf.ptr["rowOffset"], btcf.ptr["tcA2B"],
+                                                 btcf.ptr["data"], btcf.ptr["rowIdx"], device, n_ctas, C.byref(self._p))
+            capi.check(st, "b200spmm_plan_create_device")
+        elif device_arrays is not None:
             info, d_rowOffset, d_tcA2B, d_data, d_rowIdx = device_arrays
             st = lib.b200spmm_plan_create_device(C.byref(info), d_rowOffset.data_ptr(), d_tcA2B.data_ptr(),
                                                  d_data.data_ptr(), d_rowIdx.data_ptr(), device, n_ctas,

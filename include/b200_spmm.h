@@ -89,6 +89,27 @@ const uint32_t *b200spmm_btcf_rowIdx(const b200spmm_btcf_t *f);    /* [eff_row_w
 /* The reference's structs are freed by going out of scope (std::vector members). */
 void b200spmm_btcf_destroy(b200spmm_btcf_t *f);
 
+/*
+ * The same conversion on the GPU, for CSR arrays that already live on `device`; output arrays
+ * stay on the device (hand them to b200spmm_plan_create_device).  Bit-identical to
+ * b200spmm_csr2btcf_nobitmap - and so to src/utils/convert.h:146-225 - for rows whose columns are
+ * ascending and distinct, which is what the reference's loader produces (src/utils/load.h:137-145);
+ * anything else is refused with B200SPMM_ERR_BAD_CSR.  Synchronous with respect to `stream`.
+ */
+typedef struct b200spmm_dbtcf b200spmm_dbtcf_t;
+int b200spmm_csr2btcf_nobitmap_device(uint64_t rows, uint64_t cols, uint64_t nnz, const uint32_t *d_row_ptr,
+                                      const uint32_t *d_col_idx, const void *d_values, int dtype, int row_window,
+                                      int col_window, int device, void *stream, b200spmm_dbtcf_t **out);
+int b200spmm_dbtcf_info(const b200spmm_dbtcf_t *f, b200spmm_btcf_info_t *info);
+const uint32_t *b200spmm_dbtcf_rowOffset(const b200spmm_dbtcf_t *f); /* device pointers, valid until destroy */
+const uint32_t *b200spmm_dbtcf_tcA2B(const b200spmm_dbtcf_t *f);
+const void *b200spmm_dbtcf_data(const b200spmm_dbtcf_t *f);
+const uint32_t *b200spmm_dbtcf_rowIdx(const b200spmm_dbtcf_t *f);
+/* Copies the four arrays into host buffers sized from b200spmm_dbtcf_info. */
+int b200spmm_dbtcf_copy_to_host(const b200spmm_dbtcf_t *f, uint32_t *rowOffset, uint32_t *tcA2B, void *data,
+                                uint32_t *rowIdx);
+void b200spmm_dbtcf_destroy(b200spmm_dbtcf_t *f);
+
 /* ------------------------------------------------------------------ row-window sharding */
 
 /*
