@@ -41,7 +41,13 @@ struct b200spmm_plan {
     bool owns_format = false;
     uint32_t *d_rowOffset = nullptr, *d_tcA2B = nullptr, *d_rowIdx = nullptr;
     void *d_data = nullptr;
-    uint32_t *d_cta_window = nullptr;
+    // schedule: tile cuts, first / last window per CTA; split windows and their partial-result slots
+    uint32_t *d_cta_tile = nullptr, *d_cta_wfirst = nullptr, *d_cta_wlast = nullptr;
+    SplitWindow *d_splits = nullptr;
+    uint32_t *d_piece_slots = nullptr;
+    uint32_t n_splits = 0;
+    float *d_partial = nullptr;  // [2 * n_ctas][16][n] fp32, grown to the widest n seen
+    size_t partial_floats = 0;
     uint32_t *d_status = nullptr;
     CUtensorMap tmap_a{};
     // buffers of the host-pointer entry point, grown on demand
@@ -134,10 +140,23 @@ int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, int n_ctas) {
     if (prop.major != 10) return B200SPMM_ERR_NO_DEVICE;
     if (n_ctas <= 0) n_ctas = prop.multiProcessorCount;
     p->n_ctas = n_ctas;
-    std::vector<uint32_t> cta_window;
-    build_cta_schedule(h_rowOffset, info.eff_row_windows, n_ctas, &cta_window);
-    B200_CUDA_TRY(cudaMalloc(&p->d_cta_window, cta_window.size() * sizeof(uint32_t)));
-    B200_CUDA_TRY(cudaMemcpy(p->d_cta_window, cta_window.data(), cta_window.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
+    TileSchedule sc;
+    build_tile_schedule(h_rowOffset, info.eff_row_windows, n_ctas, /*allow_split=*/true, &sc);
+    auto upload = [](auto **dst, const auto &v) -> int {
+        using T = typename std::remove_reference<decltype(v)>::type::value_type;
+        B200_CUDA_TRY(cudaMalloc(dst, std::max<size_t>(v.size() * sizeof(T), 16)));
+        if (!v.empty()) B200_CUDA_TRY(cudaMemcpy(*dst, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice));
+        return B200SPMM_OK;
+    };
+    std::vector<SplitWindow> splits;
+    for (const auto &sp : sc.splits) splits.push_back(SplitWindow{sp.window, sp.piece_begin, sp.piece_end});
+    int st_up = upload(&p->d_cta_tile, sc.tile);
+    if (st_up == B200SPMM_OK) st_up = upload(&p->d_cta_wfirst, sc.wfirst);
+    if (st_up == B200SPMM_OK) st_up = upload(&p->d_cta_wlast, sc.wlast);
+    if (st_up == B200SPMM_OK) st_up = upload(&p->d_splits, splits);
+    if (st_up == B200SPMM_OK) st_up = upload(&p->d_piece_slots, sc.piece_slots);
+    if (st_up != B200SPMM_OK) return st_up;
+    p->n_splits = (uint32_t)splits.size();
     B200_CUDA_TRY(cudaMalloc(&p->d_status, sizeof(uint32_t)));
     B200_CUDA_TRY(cudaMemset(p->d_status, 0, sizeof(uint32_t)));
     {
@@ -152,17 +171,22 @@ int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, int n_ctas) {
 // ------------------------------------------------------------------ allocation-free launch path
 namespace noalloc {
 //
-// Working memory of b200spmm_spmm_noalloc: the schedule table (cuts of the row windows over the
-// CTAs) and the kernel status word.  It is part of the library image, so every GPU that loads the
-// library holds these 8 KiB until the process exits and no call ever has to allocate them.
+// Working memory of b200spmm_spmm_noalloc: the schedule tables (tile cuts, first and last window
+// per CTA) and the kernel status word.  It is part of the library image, so every GPU that loads
+// the library holds these 16 KiB until the process exits and no call ever has to allocate them.
 constexpr int kNoAllocMaxCtas = 1024;
-constexpr int kNoAllocStatusWord = kNoAllocMaxCtas + 1;  // index of the status word behind the cuts
-static __device__ __align__(256) uint32_t g_noalloc_scratch[2048];
+constexpr int kNoAllocTile = 0;                                  // [kNoAllocMaxCtas + 1]
+constexpr int kNoAllocWfirst = kNoAllocTile + kNoAllocMaxCtas + 1;  // [kNoAllocMaxCtas]
+constexpr int kNoAllocWlast = kNoAllocWfirst + kNoAllocMaxCtas;     // [kNoAllocMaxCtas]
+constexpr int kNoAllocStatusWord = kNoAllocWlast + kNoAllocMaxCtas;
+static __device__ __align__(256) uint32_t g_noalloc_scratch[4096];
 
 // Cuts of the effective row windows over n_ctas CTAs by the same cost model as the host
-// scheduler; thread c finds cut c.  Also clears the status word.
+// scheduler, always on window boundaries (no window is shared between CTAs, so no partial-result
+// slots are needed).  One block; also clears the status word.
 __global__ void noalloc_schedule_kernel(const uint32_t *__restrict__ rowOffset, uint32_t eff, int n_ctas,
                                         uint32_t *__restrict__ scratch) {
+    __shared__ uint32_t cut[kNoAllocMaxCtas + 1];
     if (threadIdx.x == 0) scratch[kNoAllocStatusWord] = 0;
     auto cost = [&](uint64_t w) { return (uint64_t)rowOffset[w] + kWindowCharge * w; };
     const uint64_t total = eff ? cost(eff) : 0;
@@ -177,7 +201,13 @@ __global__ void noalloc_schedule_kernel(const uint32_t *__restrict__ rowOffset, 
                 if (cost(mid) < target) lo = mid + 1; else hi = mid;
             }
         }
-        scratch[c] = (uint32_t)lo;
+        cut[c] = (uint32_t)lo;
+        scratch[kNoAllocTile + c] = rowOffset[lo];
+    }
+    __syncthreads();
+    for (int c = (int)threadIdx.x; c < n_ctas; c += (int)blockDim.x) {
+        scratch[kNoAllocWfirst + c] = cut[c];
+        scratch[kNoAllocWlast + c] = cut[c + 1] > cut[c] ? cut[c + 1] - 1 : cut[c];
     }
 }
 
@@ -283,6 +313,20 @@ int b200spmm_build_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows,
     return B200SPMM_OK;
 }
 
+int b200spmm_build_tile_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_ctas, uint32_t *cta_tile,
+                                 uint32_t *cta_wfirst, uint32_t *cta_wlast, uint32_t *slot_window) {
+    if (!rowOffset || !cta_tile || !cta_wfirst || !cta_wlast || !slot_window || n_ctas < 1) return B200SPMM_ERR_INVALID_ARG;
+    TileSchedule sc;
+    build_tile_schedule(rowOffset, eff_row_windows, n_ctas, /*allow_split=*/true, &sc);
+    std::memcpy(cta_tile, sc.tile.data(), sc.tile.size() * sizeof(uint32_t));
+    std::memcpy(cta_wfirst, sc.wfirst.data(), sc.wfirst.size() * sizeof(uint32_t));
+    std::memcpy(cta_wlast, sc.wlast.data(), sc.wlast.size() * sizeof(uint32_t));
+    for (int s = 0; s < 2 * n_ctas; ++s) slot_window[s] = 0xFFFFFFFFu;
+    for (const auto &sp : sc.splits)
+        for (uint32_t k = sp.piece_begin; k < sp.piece_end; ++k) slot_window[sc.piece_slots[k]] = sp.window;
+    return B200SPMM_OK;
+}
+
 void b200spmm_plan_destroy(b200spmm_plan_t *p) {
     if (!p) return;
     cudaSetDevice(p->device);
@@ -292,7 +336,12 @@ void b200spmm_plan_destroy(b200spmm_plan_t *p) {
         cudaFree(p->d_rowIdx);
         cudaFree(p->d_data);
     }
-    cudaFree(p->d_cta_window);
+    cudaFree(p->d_cta_tile);
+    cudaFree(p->d_cta_wfirst);
+    cudaFree(p->d_cta_wlast);
+    cudaFree(p->d_splits);
+    cudaFree(p->d_piece_slots);
+    cudaFree(p->d_partial);
     cudaFree(p->d_status);
     cudaFree(p->d_B);
     cudaFree(p->d_C);
@@ -401,7 +450,20 @@ int b200spmm_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, v
     prm.rowOffset = p->d_rowOffset;
     prm.tcA2B = p->d_tcA2B;
     prm.rowIdx = p->d_rowIdx;
-    prm.cta_window = p->d_cta_window;
+    prm.cta_tile = p->d_cta_tile;
+    prm.cta_wfirst = p->d_cta_wfirst;
+    prm.cta_wlast = p->d_cta_wlast;
+    if (p->n_splits) {  // slots for the pieces of windows that span CTAs
+        const size_t need = (size_t)2 * p->n_ctas * kRowWindow * (size_t)n;
+        if (need > p->partial_floats) {
+            cudaFree(p->d_partial);
+            p->d_partial = nullptr;
+            p->partial_floats = 0;
+            B200_CUDA_TRY(cudaMalloc(&p->d_partial, need * sizeof(float)));
+            p->partial_floats = need;
+        }
+    }
+    prm.partial = p->d_partial;
     prm.B = d_B;
     prm.C = d_C;
     prm.ldb = ldb;
@@ -419,7 +481,14 @@ int b200spmm_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, v
     prm.prof = g_prof;
 #endif
     if (const char *dbg = std::getenv("B200SPMM_DEBUG")) prm.debug = (uint32_t)std::atoi(dbg);  // measurement aid, results invalid
-    return p->info.dtype == B200SPMM_F16 ? launch_dtype<false>(p, prm, stream) : launch_dtype<true>(p, prm, stream);
+    int st = p->info.dtype == B200SPMM_F16 ? launch_dtype<false>(p, prm, stream) : launch_dtype<true>(p, prm, stream);
+    if (st != B200SPMM_OK || !p->n_splits) return st;
+    // windows shared out over several CTAs: sum their pieces
+    spmm_fixup_kernel<<<p->n_splits, 256, 0, stream>>>(p->d_splits, p->d_piece_slots, p->d_partial, p->d_rowIdx, d_C, ldc,
+                                                       prm.rows, prm.n, prm.c_is_half);
+    B200_CUDA_TRY(cudaGetLastError());
+    p->last.kernel_launches = 2;
+    return B200SPMM_OK;
 }
 
 int b200spmm_fp16_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, void *d_C, int64_t ldc, int c_dtype,
@@ -557,7 +626,10 @@ int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_ro
     prm.rowOffset = d_rowOffset;
     prm.tcA2B = d_tcA2B;
     prm.rowIdx = d_rowIdx;
-    prm.cta_window = scratch;
+    prm.cta_tile = scratch + kNoAllocTile;
+    prm.cta_wfirst = scratch + kNoAllocWfirst;
+    prm.cta_wlast = scratch + kNoAllocWlast;
+    prm.partial = nullptr;  // cuts lie on window boundaries: no shared windows
     prm.B = d_B;
     prm.C = d_C;
     prm.ldb = ldb;

@@ -204,4 +204,69 @@ void build_cta_schedule(const uint32_t *rowOffset, uint64_t eff, int n_ctas, std
     (*cta_window)[n_ctas] = (uint32_t)eff;
 }
 
+void build_tile_schedule(const uint32_t *rowOffset, uint64_t eff, int n_ctas, bool allow_split, TileSchedule *out) {
+    TileSchedule &sc = *out;
+    const uint64_t tiles = eff ? rowOffset[eff] : 0;
+    sc.tile.assign((size_t)n_ctas + 1, (uint32_t)tiles);
+    sc.wfirst.assign((size_t)n_ctas, 0);
+    sc.wlast.assign((size_t)n_ctas, 0);
+    sc.splits.clear();
+    sc.piece_slots.clear();
+    sc.tile[0] = 0;
+    if (!eff) return;
+    auto cost_start = [&](uint64_t w) { return (uint64_t)rowOffset[w] + kWindowCharge * w; };  // cost before window w
+    const uint64_t total = cost_start(eff);
+    const uint64_t tol = std::max<uint64_t>(32, tiles / (uint64_t)n_ctas / 16);
+    uint64_t prev = 0;
+    for (int c = 1; c < n_ctas; ++c) {
+        const uint64_t target = total * (uint64_t)c / (uint64_t)n_ctas;
+        // last window whose starting cost does not exceed the target
+        uint64_t lo = 0, hi = eff;
+        while (hi - lo > 1) {
+            const uint64_t mid = (lo + hi) / 2;
+            if (cost_start(mid) <= target) lo = mid; else hi = mid;
+        }
+        const uint64_t w = lo, w_tiles = (uint64_t)rowOffset[w + 1] - rowOffset[w];
+        uint64_t inside = target - cost_start(w);
+        inside = inside > kWindowCharge ? inside - kWindowCharge : 0;  // the window's fixed charge comes first
+        inside = std::min(inside, w_tiles);
+        if (!allow_split) inside = inside * 2 < w_tiles ? 0 : w_tiles;  // nearest window boundary
+        else if (inside <= tol) inside = 0;
+        else if (w_tiles - inside <= tol) inside = w_tiles;
+        uint64_t cut = (uint64_t)rowOffset[w] + inside;
+        cut = std::max(cut, prev);
+        sc.tile[c] = (uint32_t)cut;
+        prev = cut;
+    }
+    auto window_of_tile = [&](uint64_t t) {  // window holding tile t < tiles
+        return (uint32_t)(std::upper_bound(rowOffset, rowOffset + eff + 1, (uint32_t)t) - rowOffset - 1);
+    };
+    for (int c = 0; c < n_ctas; ++c) {
+        if (sc.tile[c + 1] > sc.tile[c]) {
+            sc.wfirst[c] = window_of_tile(sc.tile[c]);
+            sc.wlast[c] = window_of_tile(sc.tile[c + 1] - 1);
+        } else {
+            sc.wfirst[c] = sc.wlast[c] = c ? sc.wlast[c - 1] : 0;
+        }
+    }
+    // split windows: a CTA whose last window is cut at its end opens one; following CTAs that begin
+    // inside the same window add their head piece
+    for (int c = 0; c < n_ctas; ++c) {
+        if (sc.tile[c + 1] == sc.tile[c]) continue;
+        const uint32_t w = sc.wlast[c];
+        if (rowOffset[w + 1] <= sc.tile[c + 1]) continue;          // window ends inside this CTA
+        if (rowOffset[w] < sc.tile[c]) continue;                     // not the first piece: it began in an earlier CTA
+        TileSchedule::Split sp{w, (uint32_t)sc.piece_slots.size(), 0};
+        sc.piece_slots.push_back(2u * (uint32_t)c + 1u);
+        for (int d = c + 1; d < n_ctas; ++d) {
+            if (sc.tile[d + 1] == sc.tile[d]) continue;
+            if (sc.wfirst[d] != w || rowOffset[w] >= sc.tile[d]) break;
+            sc.piece_slots.push_back(2u * (uint32_t)d);
+            if (rowOffset[w + 1] <= sc.tile[d + 1]) break;          // the window's last piece
+        }
+        sp.piece_end = (uint32_t)sc.piece_slots.size();
+        sc.splits.push_back(sp);
+    }
+}
+
 }  // namespace b200spmm

@@ -73,7 +73,10 @@ struct SpmmParams {
     const uint32_t *rowOffset;   // [eff+1] tiles
     const uint32_t *tcA2B;       // [tiles*CW]
     const uint32_t *rowIdx;      // [eff]
-    const uint32_t *cta_window;  // [gridDim.x+1] schedule: windows owned by each CTA
+    const uint32_t *cta_tile;    // [gridDim.x+1] schedule: CTA c streams tiles [cta_tile[c], cta_tile[c+1])
+    const uint32_t *cta_wfirst;  // [gridDim.x] window holding the CTA's first tile
+    const uint32_t *cta_wlast;   // [gridDim.x] window holding the CTA's last tile
+    float *partial;              // [2*gridDim.x][16][n] fp32 slots for windows cut at a CTA boundary (may be null)
     const void *B;               // [cols, n] row-major
     void *C;                     // [rows, n] row-major
     int64_t ldb, ldc;            // elements
@@ -168,10 +171,16 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
     // ---- this CTA's share of the schedule.  Its tiles are streamed once per feature slab; a
     // pass is cut into stages of four consecutive tiles (the last stage of a pass may be short).
-    const uint32_t w_begin = p.cta_window[blockIdx.x], w_end = p.cta_window[blockIdx.x + 1];
-    const uint32_t tile_begin = p.rowOffset[w_begin], tile_end = p.rowOffset[w_end];
+    // The schedule may cut inside a window: then this CTA computes a piece of it, which goes to a
+    // partial-result slot instead of C (slot 2c when the CTA starts inside its first window, slot
+    // 2c+1 when its last window continues in the next CTA) and is summed by spmm_fixup_kernel.
+    const uint32_t tile_begin = p.cta_tile[blockIdx.x], tile_end = p.cta_tile[blockIdx.x + 1];
     const uint32_t n_tiles = tile_end - tile_begin;
     const uint32_t stages_per_pass = (n_tiles + kTps - 1) / kTps;
+    const uint32_t w_begin = p.cta_wfirst[blockIdx.x];
+    const uint32_t w_end = n_tiles ? p.cta_wlast[blockIdx.x] + 1 : w_begin;
+    const bool head_cut = n_tiles && p.rowOffset[w_begin] < tile_begin;
+    const bool tail_cut = n_tiles && p.rowOffset[w_end] > tile_end;
 
     if (tid == 0) {
         for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {
@@ -229,6 +238,10 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             after_a = after_b;
             meta(it + 4, row0_b, after_b);
             const uint32_t f0 = slab * kNs;  // first feature of the slab
+            // a piece of a window shared with a neighbouring CTA goes to a partial-result slot
+            const bool is_head_piece = i == 0 && head_cut, is_tail_piece = i + 1 == n_win && tail_cut;
+            const bool piece = is_head_piece || is_tail_piece;
+            float *slot_rows = p.partial + (size_t)(2 * blockIdx.x + (is_head_piece ? 0 : 1)) * kRowWindow * p.n;
             uint32_t ok = 1;
             if (lane == 0) {  // one lane polls; every mbarrier operation costs a shared-memory slot per thread
                 B200_PROF_T0();
@@ -263,7 +276,11 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     const int idx = t * 32 + lane;
                     const int rr = idx / vec_per_row, c4 = idx % vec_per_row;
                     const uint32_t row = row0 + rr, feat = feat0 + c4 * 4;
-                    if (row < p.rows && feat < p.n) {
+                    if (piece) {
+                        if (feat < p.n)
+                            *reinterpret_cast<float4 *>(slot_rows + (size_t)rr * p.n + feat) =
+                                *reinterpret_cast<const float4 *>(stg + rr * width + c4 * 4);
+                    } else if (row < p.rows && feat < p.n) {
                         const float4 v = *reinterpret_cast<const float4 *>(stg + rr * width + c4 * 4);
                         if (p.c_is_half) {
                             __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
@@ -281,13 +298,14 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             // Rows of windows that hold no entries are absent from the format: clear the gap that
             // follows this window (and the one before the very first window).  Warp q of the set
             // takes every fourth row.
-            const bool lead = (w_begin + i == 0) && row0 > 0;
-            if (gap_hi > row0 + kRowWindow || lead) {
+            // (the CTA that finishes a window clears the gap after it; the one that starts window 0 the lead)
+            const bool lead = (w_begin + i == 0) && row0 > 0 && !is_head_piece;
+            if ((gap_hi > row0 + kRowWindow && !is_tail_piece) || lead) {
                 const uint32_t slab_feats = min((uint32_t)kNs, p.n - f0);
                 const uint32_t vec_per_row = slab_feats / 4;
                 for (int pass = 0; pass < 2; ++pass) {
                     const uint32_t lo = pass == 0 ? row0 + kRowWindow : 0u;
-                    const uint32_t hi = pass == 0 ? min(gap_hi, p.rows) : (lead ? row0 : 0u);
+                    const uint32_t hi = pass == 0 ? (is_tail_piece ? 0u : min(gap_hi, p.rows)) : (lead ? row0 : 0u);
                     for (uint32_t row = lo + q; row < hi; row += 4) {
                         for (uint32_t v4 = lane; v4 < vec_per_row; v4 += 32) {
                             const uint32_t feat = f0 + v4 * 4;
@@ -581,7 +599,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 if (ahead < n_win) ptx::cp_async_4(win_ends_addr + (ahead % Cfg::kWinSlots) * 4, p.rowOffset + w_begin + ahead + 1);
                 ptx::cp_async_commit();
                 ptx::cp_async_wait_group<Cfg::kWinAhead>();  // window i's group has landed
-                const uint32_t off_hi = win_ends[i % Cfg::kWinSlots];
+                const uint32_t off_hi = min(win_ends[i % Cfg::kWinSlots], tile_end);  // the last window may be cut
 #ifdef B200SPMM_PROFILE
                 prof_head += clock64() - prof_h0;
                 prof_tiles += off_hi - off_lo;
@@ -713,6 +731,41 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         ptx::tmem_dealloc(tmem_base, kTmemCols);
     }
     if (tid == 0 && *abort_flag) atomicOr(p.status, kDevStatusTimeout);
+}
+
+// A window whose tiles were shared out over several CTAs: pieces piece_begin .. piece_end-1 of
+// piece_slots name the partial-result slots that hold its pieces, in tile order.
+struct SplitWindow {
+    uint32_t window, piece_begin, piece_end;
+};
+
+// Sums the pieces of every split window in a fixed order and writes the window's rows of C.
+// One CTA per split window; thread t handles four consecutive features of one row at a time.
+__global__ void __launch_bounds__(256)
+spmm_fixup_kernel(const SplitWindow *__restrict__ splits, const uint32_t *__restrict__ piece_slots,
+                  const float *__restrict__ partial, const uint32_t *__restrict__ rowIdx, void *__restrict__ C,
+                  int64_t ldc, uint32_t rows, uint32_t n, uint32_t c_is_half) {
+    const SplitWindow sp = splits[blockIdx.x];
+    const uint32_t row0 = rowIdx[sp.window];
+    const uint32_t vec_per_row = n / 4;
+    for (uint32_t idx = threadIdx.x; idx < kRowWindow * vec_per_row; idx += blockDim.x) {
+        const uint32_t r = idx / vec_per_row, c4 = idx % vec_per_row;
+        if (row0 + r >= rows) continue;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t k = sp.piece_begin; k < sp.piece_end; ++k) {
+            const float4 v = *reinterpret_cast<const float4 *>(partial + ((size_t)piece_slots[k] * kRowWindow + r) * n + c4 * 4);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        if (c_is_half) {
+            __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
+            uint2 packed;
+            packed.x = *reinterpret_cast<uint32_t *>(&lo);
+            packed.y = *reinterpret_cast<uint32_t *>(&hi);
+            *reinterpret_cast<uint2 *>(static_cast<__half *>(C) + (int64_t)(row0 + r) * ldc + c4 * 4) = packed;
+        } else {
+            *reinterpret_cast<float4 *>(static_cast<float *>(C) + (int64_t)(row0 + r) * ldc + c4 * 4) = acc;
+        }
+    }
 }
 
 }  // namespace b200spmm

@@ -136,6 +136,19 @@ int b200spmm_shard_rows_weighted(uint64_t rows, const uint32_t *row_ptr, int row
  * round-robin (src/fp16.cu:86,138) and its unused Scheduler singleton (src/scheduler.h:5-42).
  */
 int b200spmm_build_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_ctas, uint32_t *cta_window);
+/*
+ * The schedule the plan-based SpMM runs: cuts on TILES, so a window heavier than one CTA's share
+ * (a hub row window of a power-law graph) is shared out over several CTAs.  CTA c streams tiles
+ * [cta_tile[c], cta_tile[c+1]), which lie in windows cta_wfirst[c] .. cta_wlast[c].  A window cut
+ * at a CTA boundary is computed in pieces: each piece goes to an fp32 slot (slot 2c = the piece at
+ * the head of CTA c's range, 2c+1 = the piece at its tail) and a second small kernel sums a
+ * window's slots in tile order, so results do not depend on timing.  slot_window[2*n_ctas]
+ * receives, per slot, the window whose piece it holds, or 0xFFFFFFFF for an unused slot.  Cuts
+ * snap to a window boundary when one is near, so most windows stay whole.  No counterpart in the
+ * reference (one CTA per window, src/fp16.cu:86,138).
+ */
+int b200spmm_build_tile_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_ctas, uint32_t *cta_tile,
+                                 uint32_t *cta_wfirst, uint32_t *cta_wlast, uint32_t *slot_window);
 
 /* ------------------------------------------------------------------ device plan */
 
@@ -215,7 +228,7 @@ int b200spmm_bench(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, 
  * that already live on `device` (for example carved out of its own pool), B and C.
  *
  * The kernel still needs working memory: the schedule table (one cut per CTA) and its status
- * word.  Both live in an 8 KiB array that is part of the library image on every GPU that loads
+ * word.  Both live in a 16 KiB array that is part of the library image on every GPU that loads
  * the library.  Consequences:
  *   - n_ctas may be at most 1024 (0 = one CTA per SM); more is refused with
  *     B200SPMM_ERR_UNSUPPORTED and a message in b200spmm_last_cuda_error().

@@ -139,3 +139,44 @@ def test_schedule_covers_every_window_once_and_balances_tiles():
             charge = 12  # tile-equivalents per window in the schedule's cost model
             load = np.diff(row_offset[cuts].astype(np.int64)) + charge * np.diff(cuts.astype(np.int64))
             assert load.max() <= (row_offset[-1] + charge * eff) / n_ctas + tiles.max() + charge
+
+
+def test_tile_schedule_covers_every_tile_once_and_accounts_for_every_piece():
+    rng = np.random.default_rng(1)
+    for eff, n_ctas in ((0, 4), (1, 148), (3, 16), (50, 148), (5000, 148), (5000, 7), (40000, 148)):
+        tiles = rng.integers(1, 40, eff)
+        if eff > 10:
+            tiles[:3] = (30000, 2000, 700)  # hub windows, the first far heavier than one CTA's share
+        if eff == 1:
+            tiles[:] = 5000
+        row_offset = np.concatenate([[0], np.cumsum(tiles)]).astype(np.uint32)
+        total = int(row_offset[-1])
+        cta_tile = np.zeros(n_ctas + 1, np.uint32)
+        wfirst = np.zeros(n_ctas, np.uint32)
+        wlast = np.zeros(n_ctas, np.uint32)
+        slot_window = np.zeros(2 * n_ctas, np.uint32)
+        st = capi.lib().b200spmm_build_tile_schedule(row_offset.ctypes.data, eff, n_ctas, cta_tile.ctypes.data,
+                                                     wfirst.ctypes.data, wlast.ctypes.data, slot_window.ctypes.data)
+        assert st == capi.OK
+        t = cta_tile.astype(np.int64)
+        assert t[0] == 0 and t[-1] == total and np.all(np.diff(t) >= 0)
+        expect_slot = np.full(2 * n_ctas, 0xFFFFFFFF, np.uint32)
+        for c in range(n_ctas):
+            if t[c + 1] == t[c]:
+                continue
+            wf = int(np.searchsorted(row_offset, t[c], side="right")) - 1
+            wl = int(np.searchsorted(row_offset, t[c + 1] - 1, side="right")) - 1
+            assert (wfirst[c], wlast[c]) == (wf, wl)
+            head = row_offset[wf] < t[c]
+            tail = row_offset[wl + 1] > t[c + 1]
+            if head:
+                expect_slot[2 * c] = wf
+            if tail and not (head and wf == wl):  # a piece cut on both sides sits in the head slot
+                expect_slot[2 * c + 1] = wl
+        assert np.array_equal(slot_window, expect_slot)
+        if eff:
+            charge = 12
+            load = np.diff(t) + charge * (wlast.astype(np.int64) - wfirst + 1) * (np.diff(t) > 0)
+            share = (total + charge * eff) / n_ctas
+            slack = max(32, total // n_ctas // 16) + 3 * charge
+            assert load.max() <= share + slack, (eff, n_ctas, load.max(), share)

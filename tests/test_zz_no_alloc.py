@@ -6,7 +6,10 @@ rules out an allocating call.  b200spmm_spmm_noalloc serves them: it takes the c
 as arrays the caller already holds on the device and keeps its own working memory (schedule
 table, status word) in a fixed array inside the library.  Because that array is shared by all
 calls and keeps the last call's contents, the check is made on two calls in a row, on matrices
-of different size, each compared bit for bit with the plan-based entry point.
+of different size.  Each result must pass the parity rule of the other device tests, and equal
+the plan-based entry point bit for bit whenever that one computed every window in one piece (it
+may share a heavy window between CTAs, which changes the order of the fp32 additions; the
+allocation-free path never does, having no memory for the pieces).
 
 Collected last on purpose: a run that stops at the first failure has then seen every other test.
 """
@@ -16,6 +19,7 @@ import numpy as np
 import pytest
 
 import hopper_spmm_b200 as hs
+import parity
 from cases import dense_b, random_csr
 from hopper_spmm_b200 import _capi as capi
 
@@ -51,12 +55,17 @@ def test_two_calls_in_a_row_match_the_plan_based_entry_point(dt):
         dB = torch.from_numpy(dense_b(cols, n, 30 + k, dt)).cuda()
         plan = hs.SpmmPlan(btcf)
         want = plan.spmm(dB)
+        whole_windows = plan.launch_info().kernel_launches == 1
         plan.close()
         info, d_ro, d_a2b, d_data, d_ridx = _device_format(btcf, torch)
         for n_ctas in (0, 37):
             got = torch.full((rows, n), float("nan"), device="cuda")  # every row must be written
             _noalloc(info, d_ro, d_a2b, d_data, d_ridx, dB, got, n_ctas, torch)
-            assert torch.equal(got, want), f"case {k}, n_ctas {n_ctas}"
+            parity.check(got.cpu().numpy(), rows, rp, ci, v, dB.cpu().numpy())
+            if whole_windows:
+                assert torch.equal(got, want), f"case {k}, n_ctas {n_ctas}"
+            else:
+                assert torch.allclose(got, want, rtol=1e-4, atol=1e-4), f"case {k}, n_ctas {n_ctas}"
 
 
 def test_sizes_beyond_the_built_in_table_are_refused():
