@@ -37,16 +37,21 @@ struct b200spmm_btcf {
 struct b200spmm_plan {
     b200spmm_btcf_info_t info{};
     int device = 0;
-    int n_ctas = 0;
     bool owns_format = false;
     uint32_t *d_rowOffset = nullptr, *d_tcA2B = nullptr, *d_rowIdx = nullptr;
     void *d_data = nullptr;
-    // schedule: tile cuts, first / last window per CTA; split windows and their partial-result slots
-    uint32_t *d_cta_tile = nullptr, *d_cta_wfirst = nullptr, *d_cta_wlast = nullptr;
-    SplitWindow *d_splits = nullptr;
-    uint32_t *d_piece_slots = nullptr;
-    uint32_t n_splits = 0;
-    float *d_partial = nullptr;  // [2 * n_ctas][16][n] fp32, grown to the widest n seen
+    // A schedule: tile cuts, first / last window per CTA; split windows and their partial-result
+    // slots.  The plan keeps one for the kernels that run one CTA per SM (wide feature slabs) and
+    // one for those that run two, and the launch picks by the width of B.
+    struct Sched {
+        int n_ctas = 0;
+        uint32_t *d_cta_tile = nullptr, *d_cta_wfirst = nullptr, *d_cta_wlast = nullptr;
+        SplitWindow *d_splits = nullptr;
+        uint32_t *d_piece_slots = nullptr;
+        uint32_t n_splits = 0;
+    } sched[2];
+    const Sched *launch_sched = nullptr;  // the one the next launch uses
+    float *d_partial = nullptr;  // [2 * n_ctas][16][n] fp32, grown to the largest need seen
     size_t partial_floats = 0;
     uint32_t *d_status = nullptr;
     CUtensorMap tmap_a{};
@@ -66,11 +71,17 @@ int launch_one(b200spmm_plan *p, const SpmmParams &prm, const CUtensorMap &tmap_
     if (configured_device != p->device) {
         B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes));
         configured_device = p->device;
+        if (std::getenv("B200SPMM_VERBOSE")) {
+            int occ = 0;
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, Cfg::kThreads, Cfg::kSmemBytes);
+            std::fprintf(stderr, "[b200spmm] slab %d stages %d smem %zu: %d CTAs per SM\n", kNs, Cfg::kStages,
+                         (size_t)Cfg::kSmemBytes, occ);
+        }
     }
-    kernel<<<p->n_ctas, kThreads, Cfg::kSmemBytes, stream>>>(p->tmap_a, tmap_b, prm);
+    kernel<<<p->launch_sched->n_ctas, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p->tmap_a, tmap_b, prm);
     B200_CUDA_TRY(cudaGetLastError());
-    p->last.n_ctas = p->n_ctas;
-    p->last.threads = kThreads;
+    p->last.n_ctas = p->launch_sched->n_ctas;
+    p->last.threads = Cfg::kThreads;
     p->last.stages = Cfg::kStages;
     p->last.feature_slab = kNs;
     p->last.n_slabs = (int)prm.n_slabs;
@@ -80,10 +91,13 @@ int launch_one(b200spmm_plan *p, const SpmmParams &prm, const CUtensorMap &tmap_
     return B200SPMM_OK;
 }
 
+// Feature slab a launch uses for B of width n, and how many CTAs of that kernel share an SM.
+inline uint32_t slab_for(uint32_t n) { return std::min(256u, (n + 63u) / 64u * 64u); }
+inline int ctas_per_sm_for(uint32_t n) { return slab_for(n) <= 128 ? 2 : 1; }
+
 template <bool kTf32, bool kTma>
 int launch_slab(b200spmm_plan *p, SpmmParams &prm, const CUtensorMap &tmap_b, cudaStream_t stream) {
-    const uint32_t n64 = (prm.n + 63u) / 64u * 64u;
-    const uint32_t ns = std::min(256u, n64);
+    const uint32_t ns = slab_for(prm.n);
     prm.n_slabs = (prm.n + ns - 1) / ns;
     switch (ns) {
         case 64: return launch_one<kTf32, 64, kTma>(p, prm, tmap_b, stream);
@@ -138,25 +152,27 @@ int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, int n_ctas) {
     cudaDeviceProp prop;
     B200_CUDA_TRY(cudaGetDeviceProperties(&prop, p->device));
     if (prop.major != 10) return B200SPMM_ERR_NO_DEVICE;
-    if (n_ctas <= 0) n_ctas = prop.multiProcessorCount;
-    p->n_ctas = n_ctas;
-    TileSchedule sc;
-    build_tile_schedule(h_rowOffset, info.eff_row_windows, n_ctas, /*allow_split=*/true, &sc);
     auto upload = [](auto **dst, const auto &v) -> int {
         using T = typename std::remove_reference<decltype(v)>::type::value_type;
         B200_CUDA_TRY(cudaMalloc(dst, std::max<size_t>(v.size() * sizeof(T), 16)));
         if (!v.empty()) B200_CUDA_TRY(cudaMemcpy(*dst, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice));
         return B200SPMM_OK;
     };
-    std::vector<SplitWindow> splits;
-    for (const auto &sp : sc.splits) splits.push_back(SplitWindow{sp.window, sp.piece_begin, sp.piece_end});
-    int st_up = upload(&p->d_cta_tile, sc.tile);
-    if (st_up == B200SPMM_OK) st_up = upload(&p->d_cta_wfirst, sc.wfirst);
-    if (st_up == B200SPMM_OK) st_up = upload(&p->d_cta_wlast, sc.wlast);
-    if (st_up == B200SPMM_OK) st_up = upload(&p->d_splits, splits);
-    if (st_up == B200SPMM_OK) st_up = upload(&p->d_piece_slots, sc.piece_slots);
-    if (st_up != B200SPMM_OK) return st_up;
-    p->n_splits = (uint32_t)splits.size();
+    for (int k = 0; k < 2; ++k) {  // k + 1 resident CTAs per SM
+        b200spmm_plan::Sched &ps = p->sched[k];
+        ps.n_ctas = n_ctas > 0 ? n_ctas : prop.multiProcessorCount * (k + 1);
+        TileSchedule sc;
+        build_tile_schedule(h_rowOffset, info.eff_row_windows, ps.n_ctas, /*allow_split=*/true, &sc);
+        std::vector<SplitWindow> splits;
+        for (const auto &sp : sc.splits) splits.push_back(SplitWindow{sp.window, sp.piece_begin, sp.piece_end});
+        int st_up = upload(&ps.d_cta_tile, sc.tile);
+        if (st_up == B200SPMM_OK) st_up = upload(&ps.d_cta_wfirst, sc.wfirst);
+        if (st_up == B200SPMM_OK) st_up = upload(&ps.d_cta_wlast, sc.wlast);
+        if (st_up == B200SPMM_OK) st_up = upload(&ps.d_splits, splits);
+        if (st_up == B200SPMM_OK) st_up = upload(&ps.d_piece_slots, sc.piece_slots);
+        if (st_up != B200SPMM_OK) return st_up;
+        ps.n_splits = (uint32_t)splits.size();
+    }
     B200_CUDA_TRY(cudaMalloc(&p->d_status, sizeof(uint32_t)));
     B200_CUDA_TRY(cudaMemset(p->d_status, 0, sizeof(uint32_t)));
     {
@@ -336,11 +352,13 @@ void b200spmm_plan_destroy(b200spmm_plan_t *p) {
         cudaFree(p->d_rowIdx);
         cudaFree(p->d_data);
     }
-    cudaFree(p->d_cta_tile);
-    cudaFree(p->d_cta_wfirst);
-    cudaFree(p->d_cta_wlast);
-    cudaFree(p->d_splits);
-    cudaFree(p->d_piece_slots);
+    for (auto &ps : p->sched) {
+        cudaFree(ps.d_cta_tile);
+        cudaFree(ps.d_cta_wfirst);
+        cudaFree(ps.d_cta_wlast);
+        cudaFree(ps.d_splits);
+        cudaFree(ps.d_piece_slots);
+    }
     cudaFree(p->d_partial);
     cudaFree(p->d_status);
     cudaFree(p->d_B);
@@ -450,11 +468,13 @@ int b200spmm_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, v
     prm.rowOffset = p->d_rowOffset;
     prm.tcA2B = p->d_tcA2B;
     prm.rowIdx = p->d_rowIdx;
-    prm.cta_tile = p->d_cta_tile;
-    prm.cta_wfirst = p->d_cta_wfirst;
-    prm.cta_wlast = p->d_cta_wlast;
-    if (p->n_splits) {  // slots for the pieces of windows that span CTAs
-        const size_t need = (size_t)2 * p->n_ctas * kRowWindow * (size_t)n;
+    const b200spmm_plan::Sched &sc = p->sched[ctas_per_sm_for((uint32_t)n) - 1];
+    p->launch_sched = &sc;
+    prm.cta_tile = sc.d_cta_tile;
+    prm.cta_wfirst = sc.d_cta_wfirst;
+    prm.cta_wlast = sc.d_cta_wlast;
+    if (sc.n_splits) {  // slots for the pieces of windows that span CTAs
+        const size_t need = (size_t)2 * sc.n_ctas * kRowWindow * (size_t)n;
         if (need > p->partial_floats) {
             cudaFree(p->d_partial);
             p->d_partial = nullptr;
@@ -482,9 +502,9 @@ int b200spmm_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, v
 #endif
     if (const char *dbg = std::getenv("B200SPMM_DEBUG")) prm.debug = (uint32_t)std::atoi(dbg);  // measurement aid, results invalid
     int st = p->info.dtype == B200SPMM_F16 ? launch_dtype<false>(p, prm, stream) : launch_dtype<true>(p, prm, stream);
-    if (st != B200SPMM_OK || !p->n_splits) return st;
+    if (st != B200SPMM_OK || !sc.n_splits) return st;
     // windows shared out over several CTAs: sum their pieces
-    spmm_fixup_kernel<<<p->n_splits, 256, 0, stream>>>(p->d_splits, p->d_piece_slots, p->d_partial, p->d_rowIdx, d_C, ldc,
+    spmm_fixup_kernel<<<sc.n_splits, 256, 0, stream>>>(sc.d_splits, sc.d_piece_slots, p->d_partial, p->d_rowIdx, d_C, ldc,
                                                        prm.rows, prm.n, prm.c_is_half);
     B200_CUDA_TRY(cudaGetLastError());
     p->last.kernel_launches = 2;
@@ -595,6 +615,7 @@ int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_ro
     B200_CUDA_TRY(cudaSetDevice(device));
     if (n_ctas <= 0) {
         B200_CUDA_TRY(cudaDeviceGetAttribute(&n_ctas, cudaDevAttrMultiProcessorCount, device));
+        n_ctas *= ctas_per_sm_for((uint32_t)n);
         if (n_ctas > kNoAllocMaxCtas) n_ctas = kNoAllocMaxCtas;
     }
     if (info->eff_row_windows == 0) {  // nothing stored: C is all zeros
@@ -608,7 +629,8 @@ int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_ro
     b200spmm_plan tmp;  // lives on the stack; owns nothing
     tmp.info = *info;
     tmp.device = device;
-    tmp.n_ctas = n_ctas;
+    tmp.sched[0].n_ctas = n_ctas;  // the tables themselves are in the built-in array
+    tmp.launch_sched = &tmp.sched[0];
     tmp.d_rowOffset = const_cast<uint32_t *>(d_rowOffset);
     tmp.d_tcA2B = const_cast<uint32_t *>(d_tcA2B);
     tmp.d_rowIdx = const_cast<uint32_t *>(d_rowIdx);

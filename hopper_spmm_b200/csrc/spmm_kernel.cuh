@@ -60,11 +60,9 @@ namespace b200spmm {
 
 constexpr int kRowWindow = 16;       // rows per window the kernels consume
 constexpr int kProducerWarps = 4;    // warps per producer group = tiles per ring stage
-constexpr int kProducerGroups = 3;
 constexpr int kEpilogueWarps = 8;    // two sets of four: set e drains accumulator buffer e
 constexpr int kMmaWarp = 8;
 constexpr int kFirstProducerWarp = 9;
-constexpr int kThreads = 32 * (kFirstProducerWarp + kProducerWarps * kProducerGroups);  // 672
 constexpr int kATileBytes = 512;     // 16 rows x 32 bytes
 constexpr uint32_t kAccCols = 32;    // TMEM columns per accumulator buffer (2 chunks x 16)
 constexpr uint32_t kTmemCols = 64;   // two accumulator buffers
@@ -98,6 +96,12 @@ struct SpmmParams {
 template <bool kTf32, int kNs, bool kTma = true>
 struct SpmmCfg {
     static_assert(kNs == 64 || kNs == 128 || kNs == 192 || kNs == 256, "feature slab");
+    // One thread issues a CTA's MMAs, and with 16-row windows every MMA is small: the issuing
+    // thread, not the tensor core, sets the pace.  Up to 128 features a CTA is small enough for
+    // two to share an SM, which gives the SM two issuing threads and two rings to keep full.
+    static constexpr int kCtasPerSm = kNs <= 128 ? 2 : 1;
+    static constexpr int kProducerGroups = kCtasPerSm == 2 ? 2 : 3;
+    static constexpr int kThreads = 32 * (kFirstProducerWarp + kProducerWarps * kProducerGroups);  // 544 or 672
     static constexpr int kCW = kTf32 ? 8 : 16;           // condensed columns per tile
     static constexpr int kEsz = kTf32 ? 4 : 2;           // bytes per element of A and B
     static constexpr int kGatherBytes = 32 * kNs;        // CW rows x kNs features, one tile
@@ -110,7 +114,7 @@ struct SpmmCfg {
     // reports the oldest as landed: 4 * (kLag + 1) tiles are in flight per SM (90-100 KB); the
     // rest of the ring absorbs the round trip through the MMA issuer.  One barrier pair serves
     // four tiles, which keeps the per-tile cost of waits, fences and commits low.
-    static constexpr int kStages = kNs == 64 ? 16 : kNs == 128 ? 10 : kNs == 192 ? 7 : 5;
+    static constexpr int kStages = kNs == 64 ? 8 : kNs == 128 ? 5 : kNs == 192 ? 7 : 5;
     // cp.async variant only: groups a warp keeps in flight before it reports the oldest as landed
     static constexpr int kLag = kStages / kProducerGroups >= 3 ? kStages / kProducerGroups - 2 : 0;
     static_assert(kStages > kProducerGroups * (kLag + 1), "ring too shallow");
@@ -126,8 +130,8 @@ struct SpmmCfg {
     static constexpr int kStagingBytes = kEpilogueWarps * kRowWindow * 32 * 4;  // 16 x 32 floats per warp
     // Each producer warp keeps the column lists of its next kIdxAhead tiles in a private ring of
     // kIdxSlots entries, fetched in the same cp.async groups as the rows of the current tile.
-    static constexpr int kIdxSlots = 16;
-    static constexpr int kIdxAhead = 12;
+    static constexpr int kIdxSlots = kCtasPerSm == 2 ? 8 : 16;
+    static constexpr int kIdxAhead = kCtasPerSm == 2 ? 6 : 12;
     static_assert(kIdxAhead > kLag && kIdxAhead < kIdxSlots, "column lists must land before they are needed");
     static constexpr int kIdxBytes = kProducerWarps * kProducerGroups * kIdxSlots * kCW * 4;
     static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
@@ -137,12 +141,13 @@ struct SpmmCfg {
 };
 
 template <bool kTf32, int kNs, bool kTma>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((SpmmCfg<kTf32, kNs, kTma>::kThreads), (SpmmCfg<kTf32, kNs, kTma>::kCtasPerSm))
 spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const SpmmParams p) {
     using Cfg = SpmmCfg<kTf32, kNs, kTma>;
     constexpr int kStages = Cfg::kStages;
     constexpr int kTps = Cfg::kTilesPerStage;
+    constexpr int kProducerGroups = Cfg::kProducerGroups;
     extern __shared__ uint8_t smem_raw[];
 
     // ---- shared memory carve-up (1024-byte aligned: swizzle patterns follow address bits)
