@@ -40,18 +40,21 @@ struct b200spmm_plan {
     bool owns_format = false;
     uint32_t *d_rowOffset = nullptr, *d_tcA2B = nullptr, *d_rowIdx = nullptr;
     void *d_data = nullptr;
-    // A schedule: tile cuts, first / last window per CTA; split windows and their partial-result
-    // slots.  The plan keeps one for the kernels that run one CTA per SM (wide feature slabs) and
-    // one for those that run two, and the launch picks by the width of B.
+    // A schedule: the tile stream cut into chunks (tile cuts, first / last window and the
+    // partial-result slots of each chunk), which the CTAs take in turn - CTA b runs chunks b,
+    // b + n_ctas, ... - plus the split windows and their slots for the fix-up kernel.  The plan
+    // keeps one for the kernels that run one CTA per SM (wide feature slabs) and one for those
+    // that run two, and the launch picks by the width of B.
     struct Sched {
         int n_ctas = 0;
-        uint32_t *d_cta_tile = nullptr, *d_cta_wfirst = nullptr, *d_cta_wlast = nullptr;
+        uint32_t n_chunks = 0;
+        uint32_t *d_tile = nullptr, *d_wfirst = nullptr, *d_wlast = nullptr, *d_head_slot = nullptr, *d_tail_slot = nullptr;
         SplitWindow *d_splits = nullptr;
         uint32_t *d_piece_slots = nullptr;
-        uint32_t n_splits = 0;
+        uint32_t n_splits = 0, n_slots = 0;
     } sched[2];
     const Sched *launch_sched = nullptr;  // the one the next launch uses
-    float *d_partial = nullptr;  // [2 * n_ctas][16][n] fp32, grown to the largest need seen
+    float *d_partial = nullptr;  // [n_slots][16][n] fp32, grown to the largest need seen
     size_t partial_floats = 0;
     uint32_t *d_status = nullptr;
     CUtensorMap tmap_a{};
@@ -70,6 +73,8 @@ int launch_one(b200spmm_plan *p, const SpmmParams &prm, const CUtensorMap &tmap_
     static thread_local int configured_device = -1;
     if (configured_device != p->device) {
         B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes));
+        // all of the SM's shared-memory/L1 array as shared memory: two CTAs of the narrow slabs fit only then
+        B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         configured_device = p->device;
         if (std::getenv("B200SPMM_VERBOSE")) {
             int occ = 0;
@@ -92,6 +97,7 @@ int launch_one(b200spmm_plan *p, const SpmmParams &prm, const CUtensorMap &tmap_
 }
 
 // Feature slab a launch uses for B of width n, and how many CTAs of that kernel share an SM.
+constexpr uint64_t kMaxChunksPerCta = 16;
 inline uint32_t slab_for(uint32_t n) { return std::min(256u, (n + 63u) / 64u * 64u); }
 inline int ctas_per_sm_for(uint32_t n) { return slab_for(n) <= 128 ? 2 : 1; }
 
@@ -161,20 +167,30 @@ int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, int n_ctas) {
     for (int k = 0; k < 2; ++k) {  // k + 1 resident CTAs per SM
         b200spmm_plan::Sched &ps = p->sched[k];
         ps.n_ctas = n_ctas > 0 ? n_ctas : prop.multiProcessorCount * (k + 1);
+        // Several chunks per CTA, taken from all over the matrix, even out regions whose tiles
+        // cost more than the schedule's model says; a chunk stays long enough (512 tiles or
+        // more) for the hand-over at its start not to matter.
+        const uint64_t per_cta = info.total_tiles / (uint64_t)ps.n_ctas;
+        const int chunks_per_cta = (int)std::min<uint64_t>(kMaxChunksPerCta, std::max<uint64_t>(1, per_cta / 512));
+        ps.n_chunks = (uint32_t)(ps.n_ctas * chunks_per_cta);
         TileSchedule sc;
-        build_tile_schedule(h_rowOffset, info.eff_row_windows, ps.n_ctas, /*allow_split=*/true, &sc);
+        build_tile_schedule(h_rowOffset, info.eff_row_windows, (int)ps.n_chunks, /*allow_split=*/true, &sc);
         std::vector<SplitWindow> splits;
         for (const auto &sp : sc.splits) splits.push_back(SplitWindow{sp.window, sp.piece_begin, sp.piece_end});
-        int st_up = upload(&ps.d_cta_tile, sc.tile);
-        if (st_up == B200SPMM_OK) st_up = upload(&ps.d_cta_wfirst, sc.wfirst);
-        if (st_up == B200SPMM_OK) st_up = upload(&ps.d_cta_wlast, sc.wlast);
+        int st_up = upload(&ps.d_tile, sc.tile);
+        if (st_up == B200SPMM_OK) st_up = upload(&ps.d_wfirst, sc.wfirst);
+        if (st_up == B200SPMM_OK) st_up = upload(&ps.d_wlast, sc.wlast);
+        if (st_up == B200SPMM_OK) st_up = upload(&ps.d_head_slot, sc.head_slot);
+        if (st_up == B200SPMM_OK) st_up = upload(&ps.d_tail_slot, sc.tail_slot);
         if (st_up == B200SPMM_OK) st_up = upload(&ps.d_splits, splits);
         if (st_up == B200SPMM_OK) st_up = upload(&ps.d_piece_slots, sc.piece_slots);
         if (st_up != B200SPMM_OK) return st_up;
         ps.n_splits = (uint32_t)splits.size();
+        ps.n_slots = sc.n_slots;
     }
-    B200_CUDA_TRY(cudaMalloc(&p->d_status, sizeof(uint32_t)));
-    B200_CUDA_TRY(cudaMemset(p->d_status, 0, sizeof(uint32_t)));
+    // status word, then the two counters of the chunk hand-out (the kernel leaves them at zero)
+    B200_CUDA_TRY(cudaMalloc(&p->d_status, 4 * sizeof(uint32_t)));
+    B200_CUDA_TRY(cudaMemset(p->d_status, 0, 4 * sizeof(uint32_t)));
     {
         int st = encode_tile_map(p);
         if (st != B200SPMM_OK) return st;
@@ -250,7 +266,7 @@ using namespace noalloc;
 #ifdef B200SPMM_PROFILE
 static unsigned long long *g_prof = nullptr;
 extern "C" int b200spmm_debug_read_profile(unsigned long long *out, int n_ctas) {
-    return cudaMemcpy(out, g_prof, (size_t)n_ctas * 16 * 8, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -5;
+    return cudaMemcpy(out, g_prof, (size_t)n_ctas * 24 * 8, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -5;
 }
 #endif
 
@@ -337,9 +353,10 @@ int b200spmm_build_tile_schedule(const uint32_t *rowOffset, uint64_t eff_row_win
     std::memcpy(cta_tile, sc.tile.data(), sc.tile.size() * sizeof(uint32_t));
     std::memcpy(cta_wfirst, sc.wfirst.data(), sc.wfirst.size() * sizeof(uint32_t));
     std::memcpy(cta_wlast, sc.wlast.data(), sc.wlast.size() * sizeof(uint32_t));
-    for (int s = 0; s < 2 * n_ctas; ++s) slot_window[s] = 0xFFFFFFFFu;
-    for (const auto &sp : sc.splits)
-        for (uint32_t k = sp.piece_begin; k < sp.piece_end; ++k) slot_window[sc.piece_slots[k]] = sp.window;
+    for (int c = 0; c < n_ctas; ++c) {
+        slot_window[2 * c] = sc.head_slot[c] != kNoSlot ? sc.wfirst[c] : 0xFFFFFFFFu;
+        slot_window[2 * c + 1] = sc.tail_slot[c] != kNoSlot ? sc.wlast[c] : 0xFFFFFFFFu;
+    }
     return B200SPMM_OK;
 }
 
@@ -353,9 +370,11 @@ void b200spmm_plan_destroy(b200spmm_plan_t *p) {
         cudaFree(p->d_data);
     }
     for (auto &ps : p->sched) {
-        cudaFree(ps.d_cta_tile);
-        cudaFree(ps.d_cta_wfirst);
-        cudaFree(ps.d_cta_wlast);
+        cudaFree(ps.d_tile);
+        cudaFree(ps.d_wfirst);
+        cudaFree(ps.d_wlast);
+        cudaFree(ps.d_head_slot);
+        cudaFree(ps.d_tail_slot);
         cudaFree(ps.d_splits);
         cudaFree(ps.d_piece_slots);
     }
@@ -470,11 +489,15 @@ int b200spmm_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, v
     prm.rowIdx = p->d_rowIdx;
     const b200spmm_plan::Sched &sc = p->sched[ctas_per_sm_for((uint32_t)n) - 1];
     p->launch_sched = &sc;
-    prm.cta_tile = sc.d_cta_tile;
-    prm.cta_wfirst = sc.d_cta_wfirst;
-    prm.cta_wlast = sc.d_cta_wlast;
-    if (sc.n_splits) {  // slots for the pieces of windows that span CTAs
-        const size_t need = (size_t)2 * sc.n_ctas * kRowWindow * (size_t)n;
+    prm.chunk_tile = sc.d_tile;
+    prm.chunk_wfirst = sc.d_wfirst;
+    prm.chunk_wlast = sc.d_wlast;
+    prm.chunk_head_slot = sc.d_head_slot;
+    prm.chunk_tail_slot = sc.d_tail_slot;
+    prm.n_chunks = sc.n_chunks;
+    prm.sched_counter = sc.n_chunks > (uint32_t)sc.n_ctas ? p->d_status + 1 : nullptr;
+    if (sc.n_slots) {  // slots for the pieces of windows that span chunks
+        const size_t need = (size_t)sc.n_slots * kRowWindow * (size_t)n;
         if (need > p->partial_floats) {
             cudaFree(p->d_partial);
             p->d_partial = nullptr;
@@ -496,8 +519,8 @@ int b200spmm_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, v
     prm.status = p->d_status;
     prm.wait_limit_ns = kDeviceWaitLimitNs;
 #ifdef B200SPMM_PROFILE
-    if (!g_prof) cudaMalloc(&g_prof, 1024 * 16 * 8);
-    cudaMemsetAsync(g_prof, 0, 1024 * 16 * 8, stream);
+    if (!g_prof) cudaMalloc(&g_prof, 1024 * 24 * 8);
+    cudaMemsetAsync(g_prof, 0, 1024 * 24 * 8, stream);
     prm.prof = g_prof;
 #endif
     if (const char *dbg = std::getenv("B200SPMM_DEBUG")) prm.debug = (uint32_t)std::atoi(dbg);  // measurement aid, results invalid
@@ -532,7 +555,7 @@ int b200spmm_plan_sync(b200spmm_plan_t *p, void *stream_v) {
     uint32_t status = 0;
     B200_CUDA_TRY(cudaMemcpy(&status, p->d_status, sizeof(status), cudaMemcpyDeviceToHost));
     if (status) {
-        B200_CUDA_TRY(cudaMemset(p->d_status, 0, sizeof(status)));
+        B200_CUDA_TRY(cudaMemset(p->d_status, 0, 4 * sizeof(uint32_t)));  // status and the hand-out counters
         return B200SPMM_ERR_DEVICE_TIMEOUT;
     }
     return B200SPMM_OK;
@@ -648,10 +671,13 @@ int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_ro
     prm.rowOffset = d_rowOffset;
     prm.tcA2B = d_tcA2B;
     prm.rowIdx = d_rowIdx;
-    prm.cta_tile = scratch + kNoAllocTile;
-    prm.cta_wfirst = scratch + kNoAllocWfirst;
-    prm.cta_wlast = scratch + kNoAllocWlast;
-    prm.partial = nullptr;  // cuts lie on window boundaries: no shared windows
+    prm.chunk_tile = scratch + kNoAllocTile;  // one chunk per CTA
+    prm.chunk_wfirst = scratch + kNoAllocWfirst;
+    prm.chunk_wlast = scratch + kNoAllocWlast;
+    prm.chunk_head_slot = prm.chunk_tail_slot = nullptr;  // cuts lie on window boundaries: no shared windows
+    prm.n_chunks = (uint32_t)n_ctas;
+    prm.sched_counter = nullptr;
+    prm.partial = nullptr;
     prm.B = d_B;
     prm.C = d_C;
     prm.ldb = ldb;

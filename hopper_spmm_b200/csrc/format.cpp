@@ -212,6 +212,9 @@ void build_tile_schedule(const uint32_t *rowOffset, uint64_t eff, int n_ctas, bo
     sc.wlast.assign((size_t)n_ctas, 0);
     sc.splits.clear();
     sc.piece_slots.clear();
+    sc.head_slot.assign((size_t)n_ctas, kNoSlot);
+    sc.tail_slot.assign((size_t)n_ctas, kNoSlot);
+    sc.n_slots = 0;
     sc.tile[0] = 0;
     if (!eff) return;
     auto cost_start = [&](uint64_t w) { return (uint64_t)rowOffset[w] + kWindowCharge * w; };  // cost before window w
@@ -249,19 +252,21 @@ void build_tile_schedule(const uint32_t *rowOffset, uint64_t eff, int n_ctas, bo
             sc.wfirst[c] = sc.wlast[c] = c ? sc.wlast[c - 1] : 0;
         }
     }
-    // split windows: a CTA whose last window is cut at its end opens one; following CTAs that begin
-    // inside the same window add their head piece
+    // split windows: a chunk whose last window is cut at its end opens one; following chunks that
+    // begin inside the same window add their piece
     for (int c = 0; c < n_ctas; ++c) {
         if (sc.tile[c + 1] == sc.tile[c]) continue;
         const uint32_t w = sc.wlast[c];
-        if (rowOffset[w + 1] <= sc.tile[c + 1]) continue;          // window ends inside this CTA
-        if (rowOffset[w] < sc.tile[c]) continue;                     // not the first piece: it began in an earlier CTA
+        if (rowOffset[w + 1] <= sc.tile[c + 1]) continue;          // window ends inside this chunk
+        if (rowOffset[w] < sc.tile[c]) continue;                     // not the first piece: it began in an earlier chunk
         TileSchedule::Split sp{w, (uint32_t)sc.piece_slots.size(), 0};
-        sc.piece_slots.push_back(2u * (uint32_t)c + 1u);
+        sc.tail_slot[c] = sc.n_slots++;
+        sc.piece_slots.push_back(sc.tail_slot[c]);
         for (int d = c + 1; d < n_ctas; ++d) {
             if (sc.tile[d + 1] == sc.tile[d]) continue;
             if (sc.wfirst[d] != w || rowOffset[w] >= sc.tile[d]) break;
-            sc.piece_slots.push_back(2u * (uint32_t)d);
+            sc.head_slot[d] = sc.n_slots++;
+            sc.piece_slots.push_back(sc.head_slot[d]);
             if (rowOffset[w + 1] <= sc.tile[d + 1]) break;          // the window's last piece
         }
         sp.piece_end = (uint32_t)sc.piece_slots.size();

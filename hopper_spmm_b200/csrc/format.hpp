@@ -43,21 +43,25 @@ int shard_rows(uint64_t rows, const uint32_t *row_ptr, int row_window, int parts
 void build_cta_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_ctas,
                         std::vector<uint32_t> *cta_window);
 
-// Finer schedule: CTA c streams tiles [tile[c], tile[c+1]) of the whole tile array, cut wherever the
-// running cost (tiles + kWindowCharge per window) says, so a window heavier than a CTA's share is
-// spread over several CTAs.  wfirst / wlast are the windows holding the CTA's first and last
-// tile.  A window whose tiles end up in more than one CTA is a "split": its pieces are summed
-// afterwards from partial-result slots (slot 2c for a CTA's first window when it continues from
-// the previous CTA, slot 2c+1 for a window cut at the CTA's end).  Cuts closer than a small
-// tolerance to a window boundary snap to it.  With allow_split == false every cut is a window
-// boundary.
+// Tile-granular schedule: the tile stream is cut into `n_parts` chunks of about equal cost
+// (tiles + kWindowCharge per window); chunk c holds tiles [tile[c], tile[c+1]), which lie in
+// windows wfirst[c] .. wlast[c].  Cutting on tiles lets a window heavier than one chunk be shared
+// out.  A window whose tiles end up in more than one chunk is a "split": each chunk writes its
+// piece to a partial-result slot (head_slot[c] for the chunk's first window when it began in an
+// earlier chunk, tail_slot[c] for a window cut at the chunk's end, kNoSlot otherwise; a piece cut
+// on both sides uses the head slot) and the pieces are summed afterwards in tile order.  Cuts
+// closer than a small tolerance to a window boundary snap to it.  With allow_split == false every
+// cut is a window boundary.
+constexpr uint32_t kNoSlot = 0xFFFFFFFFu;
 struct TileSchedule {
-    std::vector<uint32_t> tile, wfirst, wlast;  // [n_ctas + 1], [n_ctas], [n_ctas]
+    std::vector<uint32_t> tile, wfirst, wlast;  // [n_parts + 1], [n_parts], [n_parts]
+    std::vector<uint32_t> head_slot, tail_slot;  // [n_parts]
+    uint32_t n_slots = 0;
     struct Split { uint32_t window, piece_begin, piece_end; };
     std::vector<Split> splits;
-    std::vector<uint32_t> piece_slots;  // partial-result slots of every split window, in CTA order
+    std::vector<uint32_t> piece_slots;  // slots of every split window's pieces, in tile order
 };
-void build_tile_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_ctas, bool allow_split,
+void build_tile_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_parts, bool allow_split,
                          TileSchedule *out);
 
 }  // namespace b200spmm

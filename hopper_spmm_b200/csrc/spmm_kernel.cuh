@@ -17,20 +17,24 @@
 // A single GPU thread retires roughly one dependent instruction every ten cycles, so the kernel
 // is organised around instruction counts on each role's critical path, not only around bytes.
 //
-// Roles in a CTA of 672 threads:
+// Roles in a CTA (544 threads for feature slabs up to 128, where two CTAs share an SM and give it
+// two MMA-issuing threads; 672 threads, one CTA per SM, for wider slabs):
 //   warps 0-7  epilogue, two sets of four warps; set e drains accumulator buffer e, i.e. every
-//              other window.  Warp q of a set owns TMEM lanes 32q..32q+31 (32 features):
-//              tcgen05.ld -> a private 16 x 32 staging block in shared memory -> 16-byte
-//              row-major C stores (eight lanes cover 128 contiguous bytes of a row); no barrier
+//              other window.  Warp q of a set owns TMEM lanes 32q..32q+31 (32 features): after
+//              tcgen05.ld lane l holds one feature of the 16 window rows and stores them straight
+//              to C, 32 lanes covering one 128-byte line of a row per instruction; no barrier
 //              between warps.  Also zero-fills rows that belong to windows without entries
 //   warp  8    lane 0 issues tcgen05.mma / tcgen05.commit; the warp owns the TMEM allocation
-//   warps 9-20 producers, three groups of four warps.  A ring stage holds four consecutive tiles;
-//              group g fills stages g, g+3, g+6, ... - one tile per warp.  The first warp of the
-//              group brings the stage's four 512-byte A tiles with one TMA load; every warp
+//   warps 9-   producers, two or three groups of four warps.  A ring stage holds four consecutive
+//              tiles; group g fills stages g, g+G, g+2G, ... - one tile per warp.  The first warp of
+//              the group brings the stage's four 512-byte A tiles with one TMA load; every warp
 //              fetches the CW rows of B its tile selects with TMA tile::gather4 (four rows per
 //              instruction, one instruction per lane, landing in the swizzled operand layout;
 //              a cp.async variant exists for comparison and for very narrow B).  Column lists
-//              are fetched 12 iterations ahead into a per-warp ring.
+//              are fetched several iterations ahead into a per-warp ring.
+//
+// The schedule cuts the tile stream, not the window list, so a window heavier than a CTA's share
+// is computed in pieces by several CTAs; pieces go to fp32 slots and spmm_fixup_kernel adds them.
 //
 // Every wait is bounded; on a timeout the roles drain and the kernel raises a status bit.
 #pragma once
@@ -41,6 +45,7 @@
 #include <cuda_runtime.h>
 
 #include "common.hpp"
+#include "format.hpp"
 #include "ptx_sm100.cuh"
 
 // Optional cycle accounting of the roles' waits, compiled in only with -DB200SPMM_PROFILE.
@@ -48,7 +53,7 @@
 #define B200_PROF_DECL(name) long long name = 0
 #define B200_PROF_T0() const long long prof_t0__ = clock64()
 #define B200_PROF_ADD(name) name += clock64() - prof_t0__
-#define B200_PROF_STORE(slot, value) p.prof[(size_t)blockIdx.x * 16 + (slot)] = (unsigned long long)(value)
+#define B200_PROF_STORE(slot, value) p.prof[(size_t)blockIdx.x * 24 + (slot)] = (unsigned long long)(value)
 #else
 #define B200_PROF_DECL(name)
 #define B200_PROF_T0()
@@ -71,10 +76,17 @@ struct SpmmParams {
     const uint32_t *rowOffset;   // [eff+1] tiles
     const uint32_t *tcA2B;       // [tiles*CW]
     const uint32_t *rowIdx;      // [eff]
-    const uint32_t *cta_tile;    // [gridDim.x+1] schedule: CTA c streams tiles [cta_tile[c], cta_tile[c+1])
-    const uint32_t *cta_wfirst;  // [gridDim.x] window holding the CTA's first tile
-    const uint32_t *cta_wlast;   // [gridDim.x] window holding the CTA's last tile
-    float *partial;              // [2*gridDim.x][16][n] fp32 slots for windows cut at a CTA boundary (may be null)
+    // schedule: chunk c holds tiles [chunk_tile[c], chunk_tile[c+1]); CTA b starts with chunk b and takes
+    // further chunks, from gridDim.x on, in the order in which the CTAs ask for them
+    const uint32_t *chunk_tile;       // [n_chunks+1]
+    const uint32_t *chunk_wfirst;     // [n_chunks] window holding the chunk's first tile
+    const uint32_t *chunk_wlast;      // [n_chunks] window holding the chunk's last tile
+    const uint32_t *chunk_head_slot;  // [n_chunks] slot for the piece at the chunk's head, or kNoSlot (null: no pieces)
+    const uint32_t *chunk_tail_slot;  // [n_chunks] slot for the piece at the chunk's tail, or kNoSlot
+    uint32_t n_chunks;
+    uint32_t *sched_counter;     // [2] chunks handed out beyond the first gridDim.x, CTAs finished; both zero
+                                 // at launch and again at exit (null: every CTA runs its first chunk only)
+    float *partial;              // [slots][16][n] fp32 pieces of windows cut at a chunk boundary (may be null)
     const void *B;               // [cols, n] row-major
     void *C;                     // [rows, n] row-major
     int64_t ldb, ldc;            // elements
@@ -114,7 +126,7 @@ struct SpmmCfg {
     // reports the oldest as landed: 4 * (kLag + 1) tiles are in flight per SM (90-100 KB); the
     // rest of the ring absorbs the round trip through the MMA issuer.  One barrier pair serves
     // four tiles, which keeps the per-tile cost of waits, fences and commits low.
-    static constexpr int kStages = kNs == 64 ? 8 : kNs == 128 ? 5 : kNs == 192 ? 7 : 5;
+    static constexpr int kStages = kNs == 64 ? 10 : kNs == 128 ? 6 : kNs == 192 ? 8 : 6;
     // cp.async variant only: groups a warp keeps in flight before it reports the oldest as landed
     static constexpr int kLag = kStages / kProducerGroups >= 3 ? kStages / kProducerGroups - 2 : 0;
     static_assert(kStages > kProducerGroups * (kLag + 1), "ring too shallow");
@@ -126,18 +138,19 @@ struct SpmmCfg {
     static constexpr int kRowQuads = kCW / 4;
     static constexpr int kGatherOps = kRowQuads * (kNs / kBoxFeatures);  // per tile, at most 16
     static constexpr int kWinAhead = 16;   // windows whose tile counts the MMA issuer prefetches
-    static constexpr int kWinSlots = 64;
-    static constexpr int kStagingBytes = kEpilogueWarps * kRowWindow * 32 * 4;  // 16 x 32 floats per warp
+    static constexpr int kWinSlots = 32;
     // Each producer warp keeps the column lists of its next kIdxAhead tiles in a private ring of
     // kIdxSlots entries, fetched in the same cp.async groups as the rows of the current tile.
-    static constexpr int kIdxSlots = kCtasPerSm == 2 ? 8 : 16;
-    static constexpr int kIdxAhead = kCtasPerSm == 2 ? 6 : 12;
+    static constexpr int kIdxSlots = kCtasPerSm == 2 ? 7 : 16;
+    static constexpr int kIdxAhead = kCtasPerSm == 2 ? 5 : 12;
     static_assert(kIdxAhead > kLag && kIdxAhead < kIdxSlots, "column lists must land before they are needed");
     static constexpr int kIdxBytes = kProducerWarps * kProducerGroups * kIdxSlots * kCW * 4;
     static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
     static constexpr int kWinBytes = kWinSlots * 4;
+    static constexpr int kChunkSlots = 32;  // chunks one CTA may take; the last entry always ends the list
+    static constexpr int kChunkBytes = kChunkSlots * 4 + 8;
     static constexpr size_t kSmemBytes =
-        1024 + (size_t)kStages * kStageBytes + kStagingBytes + kIdxBytes + kBarrierBytes + kWinBytes;
+        1024 + (size_t)kStages * kStageBytes + kIdxBytes + kBarrierBytes + kWinBytes + kChunkBytes;
 };
 
 template <bool kTf32, int kNs, bool kTma>
@@ -156,10 +169,9 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     uint8_t *base = smem_raw + pad;
     const uint32_t gather_addr = raw_addr + pad;                                    // kStages x 4 x kGatherBytes
     const uint32_t atile_addr = gather_addr + kStages * kTps * Cfg::kGatherBytes;    // kStages x 4 x 512
-    float *staging = reinterpret_cast<float *>(base + kStages * Cfg::kStageBytes);
-    uint32_t *idx_ring = reinterpret_cast<uint32_t *>(base + kStages * Cfg::kStageBytes + Cfg::kStagingBytes);
-    const uint32_t idx_ring_addr = atile_addr + kStages * kTps * kATileBytes + Cfg::kStagingBytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(base + kStages * Cfg::kStageBytes + Cfg::kStagingBytes + Cfg::kIdxBytes);
+    uint32_t *idx_ring = reinterpret_cast<uint32_t *>(base + kStages * Cfg::kStageBytes);
+    const uint32_t idx_ring_addr = atile_addr + kStages * kTps * kATileBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(base + kStages * Cfg::kStageBytes + Cfg::kIdxBytes);
     const uint32_t bars_addr = idx_ring_addr + Cfg::kIdxBytes;
     auto full_bar = [&](uint32_t s) { return bars_addr + 8u * s; };
     auto empty_bar = [&](uint32_t s) { return bars_addr + 8u * ((uint32_t)kStages + s); };
@@ -170,22 +182,57 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     volatile uint32_t *mma_done = abort_flag + 2;
     volatile uint32_t *win_ends = reinterpret_cast<volatile uint32_t *>(bars + 2 * kStages + 4 + 2);
     const uint32_t win_ends_addr = bars_addr + 8u * (uint32_t)(2 * kStages + 4 + 2);
+    volatile uint32_t *chunk_list = win_ends + Cfg::kWinSlots;          // chunks this CTA runs, in order
+    volatile uint32_t *chunk_avail = chunk_list + Cfg::kChunkSlots;     // entries of chunk_list written so far
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef B200SPMM_PROFILE
+    const unsigned long long prof_cta_t0 = ptx::global_timer_ns();
+#endif
     const uint64_t limit = p.wait_limit_ns;
 
-    // ---- this CTA's share of the schedule.  Its tiles are streamed once per feature slab; a
-    // pass is cut into stages of four consecutive tiles (the last stage of a pass may be short).
-    // The schedule may cut inside a window: then this CTA computes a piece of it, which goes to a
-    // partial-result slot instead of C (slot 2c when the CTA starts inside its first window, slot
-    // 2c+1 when its last window continues in the next CTA) and is summed by spmm_fixup_kernel.
-    const uint32_t tile_begin = p.cta_tile[blockIdx.x], tile_end = p.cta_tile[blockIdx.x + 1];
-    const uint32_t n_tiles = tile_end - tile_begin;
-    const uint32_t stages_per_pass = (n_tiles + kTps - 1) / kTps;
-    const uint32_t w_begin = p.cta_wfirst[blockIdx.x];
-    const uint32_t w_end = n_tiles ? p.cta_wlast[blockIdx.x] + 1 : w_begin;
-    const bool head_cut = n_tiles && p.rowOffset[w_begin] < tile_begin;
-    const bool tail_cut = n_tiles && p.rowOffset[w_end] > tile_end;
+    // ---- this CTA's share of the schedule.  The tile stream is cut into many more chunks than
+    // there are CTAs.  CTA b starts with chunk b; whenever its producers get near the end of a
+    // chunk, the first producer warp takes the next unclaimed one from a global counter and
+    // appends it to a list in shared memory, which all roles follow at their own pace.  So a CTA
+    // that gets through its tiles faster (warmer columns of B, or simply the better share of the
+    // SM it lives on) ends up with more chunks, and all CTAs finish together.  Which CTA ran a
+    // chunk has no influence on the result.
+    // A chunk's tiles are streamed once per feature slab; a pass is cut into stages of four
+    // consecutive tiles (the last stage of a pass may be short).  Ring stages, barrier phases and
+    // accumulator buffers simply carry on from one pass and chunk to the next.
+    // The schedule may cut inside a window: then the chunk computes a piece of it, which goes to
+    // a partial-result slot instead of C and is summed by spmm_fixup_kernel.
+    constexpr uint32_t kNoChunk = 0xFFFFFFFFu;
+    // k-th chunk of this CTA, or kNoChunk after the last (also when the wait for the entry gives up)
+    auto chunk_id = [&](uint32_t k) -> uint32_t {
+        if (*chunk_avail <= k) {
+            const uint64_t t0 = ptx::global_timer_ns();
+            while (*chunk_avail <= k) {
+                __nanosleep(100);
+                if (*abort_flag) return kNoChunk;
+                if (ptx::global_timer_ns() - t0 > limit) {
+                    *abort_flag = 1;
+                    return kNoChunk;
+                }
+            }
+        }
+        __threadfence_block();
+        return chunk_list[k];
+    };
+    struct Chunk {
+        uint32_t tile_begin, tile_end, w_begin, n_win, head_slot, tail_slot;
+    };
+    auto load_chunk = [&](uint32_t c) {
+        Chunk ch;
+        ch.tile_begin = p.chunk_tile[c];
+        ch.tile_end = p.chunk_tile[c + 1];
+        ch.w_begin = p.chunk_wfirst[c];
+        ch.n_win = ch.tile_end > ch.tile_begin ? p.chunk_wlast[c] + 1 - ch.w_begin : 0u;
+        ch.head_slot = p.chunk_head_slot ? p.chunk_head_slot[c] : kNoSlot;
+        ch.tail_slot = p.chunk_tail_slot ? p.chunk_tail_slot[c] : kNoSlot;
+        return ch;
+    };
 
     if (tid == 0) {
         for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {
@@ -198,6 +245,8 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
         *abort_flag = 0;
         *mma_done = 0;
+        chunk_list[0] = blockIdx.x < p.n_chunks ? blockIdx.x : kNoChunk;
+        *chunk_avail = 1;
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tmap_a);
         if (kTma) ptx::prefetch_tensormap(&tmap_b);
@@ -215,9 +264,8 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // =========================================================== epilogue warps
         const uint32_t e = (uint32_t)warp >> 2;  // accumulator buffer this set drains
         const uint32_t q = (uint32_t)warp & 3u;  // TMEM lane quarter = which 32 features of a 128-chunk
-        float *stg = staging + warp * (kRowWindow * 32);
-        const uint32_t n_win = w_end - w_begin;
-        const uint32_t total = p.n_slabs * n_win;  // accumulators this CTA produces, in order
+        uint32_t g0 = 0;  // accumulators this CTA has produced before the current chunk
+        bool epi_alive = true;
         B200_PROF_DECL(prof_wait_accfull);
 #ifdef B200SPMM_PROFILE
         const long long prof_start = clock64();
@@ -225,6 +273,14 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #endif
         // First row of a window and of the window after it (or the row count), fetched two of
         // this set's windows ahead so the loads are never waited for.
+        for (uint32_t round = 0; epi_alive; ++round) {
+        const uint32_t chunk = chunk_id(round);
+        if (chunk == kNoChunk) break;
+        const Chunk ch = load_chunk(chunk);
+        const uint32_t n_win = ch.n_win, w_begin = ch.w_begin;
+        if (n_win == 0) continue;
+        const uint32_t total = p.n_slabs * n_win;  // accumulators this chunk produces, in order
+        const uint32_t first = (e ^ g0) & 1u;      // this set drains the accumulators whose running number is e mod 2
         auto meta = [&](uint32_t it, uint32_t &row0, uint32_t &after) {
             if (it < total) {
                 const uint32_t w = w_begin + it % n_win;
@@ -233,28 +289,29 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
         };
         uint32_t row0_a = 0, after_a = 0, row0_b = 0, after_b = 0;
-        meta(e, row0_a, after_a);
-        meta(e + 2, row0_b, after_b);
-        uint32_t slab = 0, i = e;  // position of accumulator `it`: window i of slab `slab`
-        while (n_win != 0 && i >= n_win) { i -= n_win; ++slab; }
-        for (uint32_t it = e; it < total; it += 2) {
+        meta(first, row0_a, after_a);
+        meta(first + 2, row0_b, after_b);
+        uint32_t slab = 0, i = first;  // position of accumulator `it`: window i of slab `slab`
+        while (i >= n_win) { i -= n_win; ++slab; }
+        for (uint32_t it = first; it < total; it += 2) {
             const uint32_t row0 = row0_a, gap_hi = after_a;
             row0_a = row0_b;
             after_a = after_b;
             meta(it + 4, row0_b, after_b);
             const uint32_t f0 = slab * kNs;  // first feature of the slab
             // a piece of a window shared with a neighbouring CTA goes to a partial-result slot
-            const bool is_head_piece = i == 0 && head_cut, is_tail_piece = i + 1 == n_win && tail_cut;
+            const bool is_head_piece = i == 0 && ch.head_slot != kNoSlot;
+            const bool is_tail_piece = i + 1 == n_win && ch.tail_slot != kNoSlot;
             const bool piece = is_head_piece || is_tail_piece;
-            float *slot_rows = p.partial + (size_t)(2 * blockIdx.x + (is_head_piece ? 0 : 1)) * kRowWindow * p.n;
+            float *slot_rows = p.partial + (size_t)(is_head_piece ? ch.head_slot : ch.tail_slot) * kRowWindow * p.n;
             uint32_t ok = 1;
             if (lane == 0) {  // one lane polls; every mbarrier operation costs a shared-memory slot per thread
                 B200_PROF_T0();
-                ok = ptx::mbar_wait(acc_full_bar(e), (it >> 1) & 1u, abort_flag, limit) ? 1u : 0u;
+                ok = ptx::mbar_wait(acc_full_bar(e), ((g0 + it) >> 1) & 1u, abort_flag, limit) ? 1u : 0u;
                 B200_PROF_ADD(prof_wait_accfull);
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
+            if (!ok) { epi_alive = false; break; }
             ptx::tcgen05_fence_after_sync();
             uint32_t r[Cfg::kChunks][16];
 #pragma unroll
@@ -264,41 +321,30 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             ptx::tcgen05_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(acc_empty_bar(e));  // the buffer may be overwritten from here on
+            // Lane l of this warp holds one feature of the 16 window rows (M = 128: feature 32q + l
+            // of the chunk; M = 64: lanes 0-15 hold feature 16q + l), so a row of C receives 32
+            // consecutive values from the warp: one full 128-byte line per store instruction.
 #pragma unroll
             for (int c = 0; c < Cfg::kChunks; ++c) {
                 const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
-                // M = 128: lane l of quarter q holds feature 32q + l.  M = 64: lanes 0-15 hold 16q + l.
-                const int width = half_chunk ? 16 : 32;  // features this warp owns in the chunk
-                if (!half_chunk || lane < 16) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) stg[j * width + lane] = __uint_as_float(r[c][j]);
-                }
-                __syncwarp();
-                const int vec_per_row = width / 4;
-                const uint32_t feat0 = f0 + c * 128 + q * width;
-#pragma unroll
-                for (int t = 0; t < kRowWindow * width / 4 / 32; ++t) {
-                    const int idx = t * 32 + lane;
-                    const int rr = idx / vec_per_row, c4 = idx % vec_per_row;
-                    const uint32_t row = row0 + rr, feat = feat0 + c4 * 4;
+                const uint32_t width = half_chunk ? 16 : 32;  // features this warp owns in the chunk
+                const uint32_t feat = f0 + c * 128 + q * width + lane;
+                if (lane < width && feat < p.n) {
                     if (piece) {
-                        if (feat < p.n)
-                            *reinterpret_cast<float4 *>(slot_rows + (size_t)rr * p.n + feat) =
-                                *reinterpret_cast<const float4 *>(stg + rr * width + c4 * 4);
-                    } else if (row < p.rows && feat < p.n) {
-                        const float4 v = *reinterpret_cast<const float4 *>(stg + rr * width + c4 * 4);
-                        if (p.c_is_half) {
-                            __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
-                            uint2 packed;
-                            packed.x = *reinterpret_cast<uint32_t *>(&lo);
-                            packed.y = *reinterpret_cast<uint32_t *>(&hi);
-                            *reinterpret_cast<uint2 *>(static_cast<__half *>(p.C) + (int64_t)row * p.ldc + feat) = packed;
-                        } else {
-                            *reinterpret_cast<float4 *>(static_cast<float *>(p.C) + (int64_t)row * p.ldc + feat) = v;
-                        }
+#pragma unroll
+                        for (int j = 0; j < kRowWindow; ++j) slot_rows[(size_t)j * p.n + feat] = __uint_as_float(r[c][j]);
+                    } else if (p.c_is_half) {
+                        __half *dst = static_cast<__half *>(p.C) + (int64_t)row0 * p.ldc + feat;
+#pragma unroll
+                        for (int j = 0; j < kRowWindow; ++j)
+                            if (row0 + j < p.rows) dst[(int64_t)j * p.ldc] = __float2half_rn(__uint_as_float(r[c][j]));
+                    } else {
+                        float *dst = static_cast<float *>(p.C) + (int64_t)row0 * p.ldc + feat;
+#pragma unroll
+                        for (int j = 0; j < kRowWindow; ++j)
+                            if (row0 + j < p.rows) dst[(int64_t)j * p.ldc] = __uint_as_float(r[c][j]);
                     }
                 }
-                __syncwarp();
             }
             // Rows of windows that hold no entries are absent from the format: clear the gap that
             // follows this window (and the one before the very first window).  Warp q of the set
@@ -328,6 +374,8 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             ++prof_windows;
 #endif
         }
+        g0 += total;
+        }  // chunks
 #ifdef B200SPMM_PROFILE
         if (tid == 0) {
             B200_PROF_STORE(8, clock64() - prof_start);
@@ -391,25 +439,63 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #ifdef B200SPMM_PROFILE
         const long long prof_start = clock64();
 #endif
-        // Stage cursor of the main loop - (slab, stage inside the pass) - plus ring slot and use
-        // count, and a second cursor kIdxAhead stages further on for the column-list fetch.
-        uint32_t slab = 0, sp = grp, s = grp, use = 0, s_arrive = grp;
-        uint32_t it = 0, it_f = 0;  // iterations issued / fetched (only their low bits are used)
-        auto normalise = [&](uint32_t &sl, uint32_t &st) {  // stage cursor past the end of a pass
-            while (st >= stages_per_pass && sl < p.n_slabs) { st -= stages_per_pass; ++sl; }
+        // Stage cursor of the main loop - (chunk, slab, stage inside the pass) with the chunk's
+        // tile range - plus ring slot and use count, and a second cursor kIdxAhead iterations
+        // further on for the column-list fetch.
+        struct Cursor {
+            uint32_t round, slab, sp, tile_begin, n_tiles, stages, done;
         };
-        if (stages_per_pass == 0) slab = p.n_slabs; else normalise(slab, sp);
-        uint32_t slab_f = slab, sp_f = sp;
+        uint32_t grabbed = 1;  // first producer warp: entries of the CTA's chunk list written so far
+        auto open_chunk = [&](Cursor &c) {  // the cursor enters its c.round-th chunk
+            if (pid == 0 && c.round == grabbed) {  // nobody has asked for this one yet: claim the next chunk
+                if (lane == 0) {
+                    uint32_t next = kNoChunk;
+                    if (p.sched_counter && c.round + 1 < (uint32_t)Cfg::kChunkSlots) {
+                        next = gridDim.x + atomicAdd(p.sched_counter, 1u);
+                        if (next >= p.n_chunks) next = kNoChunk;
+                    }
+                    chunk_list[c.round] = next;
+                    __threadfence_block();
+                    *chunk_avail = c.round + 1;
+                }
+                ++grabbed;
+                __syncwarp();
+            }
+            const uint32_t chunk = chunk_id(c.round);
+            if (chunk == kNoChunk) {
+                c.done = 1;
+                return;
+            }
+            c.tile_begin = p.chunk_tile[chunk];
+            c.n_tiles = p.chunk_tile[chunk + 1] - c.tile_begin;
+            c.stages = (c.n_tiles + kTps - 1) / kTps;
+        };
+        auto normalise = [&](Cursor &c) {  // stage cursor past the end of a pass: next slab, then next chunk
+            while (!c.done && c.sp >= c.stages) {
+                c.sp -= c.stages;
+                if (++c.slab == p.n_slabs || c.stages == 0) {
+                    c.slab = 0;
+                    ++c.round;
+                    open_chunk(c);
+                }
+            }
+        };
+        Cursor cur{0, 0, grp, 0, 0, 0, 0};
+        open_chunk(cur);
+        normalise(cur);
+        Cursor fc = cur;
+        uint32_t s = grp, use = 0, s_arrive = grp;
+        uint32_t it = 0, it_f = 0;  // iterations issued / fetched (only their low bits are used)
         auto fetch_list = [&]() {  // column list of the fetch cursor's tile -> its ring slot; then advance
-            if (slab_f < p.n_slabs) {
-                const uint32_t tpos = sp_f * kTps + pw;
-                if (lane < kIdxLanes && tpos < n_tiles) {
+            if (!fc.done) {
+                const uint32_t tpos = fc.sp * kTps + pw;
+                if (lane < kIdxLanes && tpos < fc.n_tiles) {
                     const uint32_t slot = it_f % Cfg::kIdxSlots;
                     ptx::cp_async_16(my_idx_addr + slot * Cfg::kCW * 4 + lane * 16,
-                                     p.tcA2B + (uint64_t)(tile_begin + tpos) * Cfg::kCW + lane * 4, 16u);
+                                     p.tcA2B + (uint64_t)(fc.tile_begin + tpos) * Cfg::kCW + lane * 4, 16u);
                 }
-                sp_f += kProducerGroups;
-                normalise(slab_f, sp_f);
+                fc.sp += kProducerGroups;
+                normalise(fc);
             }
             ++it_f;
         };
@@ -420,9 +506,10 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
         const uint32_t n_bytes = p.n * Cfg::kEsz;
         uint32_t issued = 0;  // cp.async path: stages whose copies were issued and not yet reported
-        while (slab < p.n_slabs) {
+        while (!cur.done) {
+            const uint32_t slab = cur.slab, sp = cur.sp, tile_begin = cur.tile_begin;
             const uint32_t tpos = sp * kTps + pw;
-            const bool have_tile = tpos < n_tiles && !(p.debug & 1u);  // the last stage of a pass may be short
+            const bool have_tile = tpos < cur.n_tiles && !(p.debug & 1u);  // the last stage of a pass may be short
             const uint32_t *list = my_idx + (it % Cfg::kIdxSlots) * Cfg::kCW;
             const uint32_t tile_area = gather_addr + (s * kTps + pw) * Cfg::kGatherBytes;
 
@@ -503,8 +590,8 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 }
             }
             ++it;
-            sp += kProducerGroups;
-            normalise(slab, sp);
+            cur.sp += kProducerGroups;
+            normalise(cur);
             s += kProducerGroups;
             if (s >= (uint32_t)kStages) { s -= kStages; ++use; }
         }
@@ -588,7 +675,11 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             if (kTf32) ptx::umma_tf32_ss_lohi(d, alo, a_hi, blo, b_hi, idesc, acc);
             else ptx::umma_f16_ss_lohi(d, alo, a_hi, blo, b_hi, idesc, acc);
         };
-        const uint32_t n_win = w_end - w_begin;
+        for (uint32_t round = 0; alive; ++round) {
+        const uint32_t chunk = chunk_id(round);
+        if (chunk == kNoChunk) break;
+        const Chunk ch = load_chunk(chunk);
+        const uint32_t n_win = ch.n_win, w_begin = ch.w_begin, tile_begin = ch.tile_begin, tile_end = ch.tile_end;
         for (uint32_t slab = 0; slab < p.n_slabs && alive; ++slab) {
             // window i's last tile + 1 goes to slot i % kWinSlots, one cp.async group per window
             for (uint32_t i = 0; i < (uint32_t)Cfg::kWinAhead; ++i) {
@@ -705,6 +796,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 release_stage();
             }
         }
+        }  // chunks
         ptx::cp_async_wait_group<0>();
 #ifdef B200SPMM_PROFILE
         B200_PROF_STORE(4, clock64() - prof_start);
@@ -736,6 +828,22 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         ptx::tmem_dealloc(tmem_base, kTmemCols);
     }
     if (tid == 0 && *abort_flag) atomicOr(p.status, kDevStatusTimeout);
+    if (tid == 0 && p.sched_counter) {  // the last CTA to finish leaves both counters at zero for the next launch
+        __threadfence();
+        if (atomicAdd(p.sched_counter + 1, 1u) == gridDim.x - 1u) {
+            p.sched_counter[0] = 0;
+            p.sched_counter[1] = 0;
+        }
+    }
+#ifdef B200SPMM_PROFILE
+    if (tid == 0) {  // where and when this CTA ran
+        uint32_t smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        B200_PROF_STORE(16, smid);
+        B200_PROF_STORE(17, prof_cta_t0);
+        B200_PROF_STORE(18, ptx::global_timer_ns());
+    }
+#endif
 }
 
 // A window whose tiles were shared out over several CTAs: pieces piece_begin .. piece_end-1 of

@@ -137,17 +137,20 @@ int b200spmm_shard_rows_weighted(uint64_t rows, const uint32_t *row_ptr, int row
  */
 int b200spmm_build_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_ctas, uint32_t *cta_window);
 /*
- * The schedule the plan-based SpMM runs: cuts on TILES, so a window heavier than one CTA's share
- * (a hub row window of a power-law graph) is shared out over several CTAs.  CTA c streams tiles
- * [cta_tile[c], cta_tile[c+1]), which lie in windows cta_wfirst[c] .. cta_wlast[c].  A window cut
- * at a CTA boundary is computed in pieces: each piece goes to an fp32 slot (slot 2c = the piece at
- * the head of CTA c's range, 2c+1 = the piece at its tail) and a second small kernel sums a
- * window's slots in tile order, so results do not depend on timing.  slot_window[2*n_ctas]
- * receives, per slot, the window whose piece it holds, or 0xFFFFFFFF for an unused slot.  Cuts
+ * The schedule the plan-based SpMM runs: the tile stream cut into n_parts chunks of about equal
+ * cost.  Cutting on TILES lets a window heavier than one chunk (a hub row window of a power-law
+ * graph) be shared out.  Chunk c holds tiles [cta_tile[c], cta_tile[c+1]), which lie in windows
+ * cta_wfirst[c] .. cta_wlast[c]; the plan cuts several chunks per CTA and CTA b runs chunks b,
+ * b + n_ctas, ..., so every CTA works in all regions of the matrix.  A window cut at a chunk
+ * boundary is computed in pieces: each piece goes to an fp32 slot and a second small kernel sums
+ * a window's pieces in tile order, so results do not depend on timing.  slot_window[2*n_parts]
+ * receives, for chunk c, at [2c] the window whose piece sits at the head of the chunk (it began
+ * in an earlier chunk) and at [2c+1] the window cut at the chunk's end, or 0xFFFFFFFF where the
+ * chunk's first / last window is whole; a piece cut on both sides counts as a head piece.  Cuts
  * snap to a window boundary when one is near, so most windows stay whole.  No counterpart in the
  * reference (one CTA per window, src/fp16.cu:86,138).
  */
-int b200spmm_build_tile_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_ctas, uint32_t *cta_tile,
+int b200spmm_build_tile_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_parts, uint32_t *cta_tile,
                                  uint32_t *cta_wfirst, uint32_t *cta_wlast, uint32_t *slot_window);
 
 /* ------------------------------------------------------------------ device plan */
