@@ -23,7 +23,7 @@ class BtcfInfo(C.Structure):
 
 class LaunchInfo(C.Structure):
     _fields_ = [("n_ctas", i32), ("threads", i32), ("stages", i32), ("feature_slab", i32), ("n_slabs", i32),
-                ("smem_bytes", i64), ("kernel_launches", i64), ("tma_gather", i32)]
+                ("smem_bytes", i64), ("kernel_launches", i64), ("tma_gather", i32), ("bitmap_tiles", i32)]
 
 
 class KatMma(C.Structure):

@@ -7,7 +7,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200spmm.so")
-SOURCES = ["capi.cu", "kat.cu", "convert_gpu.cu", "format.cpp"]
+SOURCES = ["capi.cu", "kat.cu", "convert_gpu.cu", "compress_gpu.cu", "format.cpp"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",  # -arch=sm_100a would add a generic PTX pass that rejects tcgen05
     "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared",

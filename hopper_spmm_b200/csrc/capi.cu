@@ -11,6 +11,7 @@
 
 #include "../../include/b200_spmm.h"
 #include "common.hpp"
+#include "compress_gpu.hpp"
 #include "format.hpp"
 #include "spmm_kernel.cuh"
 #include "tensormap.hpp"
@@ -54,6 +55,7 @@ struct b200spmm_plan {
         uint32_t n_splits = 0, n_slots = 0;
     } sched[2];
     const Sched *launch_sched = nullptr;  // the one the next launch uses
+    CompressedTiles comp;                 // the tiles as bitmap + stored values (empty: dense tiles only)
     float *d_partial = nullptr;  // [n_slots][16][n] fp32, grown to the largest need seen
     size_t partial_floats = 0;
     uint32_t *d_status = nullptr;
@@ -66,10 +68,10 @@ struct b200spmm_plan {
 
 namespace {
 
-template <bool kTf32, int kNs, bool kTma>
+template <bool kTf32, int kNs, bool kTma, bool kBitmap>
 int launch_one(b200spmm_plan *p, const SpmmParams &prm, const CUtensorMap &tmap_b, cudaStream_t stream) {
-    using Cfg = SpmmCfg<kTf32, kNs, kTma>;
-    auto kernel = spmm_sm100_kernel<kTf32, kNs, kTma>;
+    using Cfg = SpmmCfg<kTf32, kNs, kTma, kBitmap>;
+    auto kernel = spmm_sm100_kernel<kTf32, kNs, kTma, kBitmap>;
     static thread_local int configured_device = -1;
     if (configured_device != p->device) {
         B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes));
@@ -93,6 +95,7 @@ int launch_one(b200spmm_plan *p, const SpmmParams &prm, const CUtensorMap &tmap_
     p->last.smem_bytes = (int64_t)Cfg::kSmemBytes;
     p->last.kernel_launches = 1;
     p->last.tma_gather = kTma ? 1 : 0;
+    p->last.bitmap_tiles = kBitmap ? 1 : 0;
     return B200SPMM_OK;
 }
 
@@ -101,15 +104,15 @@ constexpr uint64_t kMaxChunksPerCta = 16;
 inline uint32_t slab_for(uint32_t n) { return std::min(256u, (n + 63u) / 64u * 64u); }
 inline int ctas_per_sm_for(uint32_t n) { return slab_for(n) <= 128 ? 2 : 1; }
 
-template <bool kTf32, bool kTma>
+template <bool kTf32, bool kTma, bool kBitmap>
 int launch_slab(b200spmm_plan *p, SpmmParams &prm, const CUtensorMap &tmap_b, cudaStream_t stream) {
     const uint32_t ns = slab_for(prm.n);
     prm.n_slabs = (prm.n + ns - 1) / ns;
     switch (ns) {
-        case 64: return launch_one<kTf32, 64, kTma>(p, prm, tmap_b, stream);
-        case 128: return launch_one<kTf32, 128, kTma>(p, prm, tmap_b, stream);
-        case 192: return launch_one<kTf32, 192, kTma>(p, prm, tmap_b, stream);
-        default: return launch_one<kTf32, 256, kTma>(p, prm, tmap_b, stream);
+        case 64: return launch_one<kTf32, 64, kTma, kBitmap>(p, prm, tmap_b, stream);
+        case 128: return launch_one<kTf32, 128, kTma, kBitmap>(p, prm, tmap_b, stream);
+        case 192: return launch_one<kTf32, 192, kTma, kBitmap>(p, prm, tmap_b, stream);
+        default: return launch_one<kTf32, 256, kTma, kBitmap>(p, prm, tmap_b, stream);
     }
 }
 
@@ -121,7 +124,7 @@ int launch_dtype(b200spmm_plan *p, SpmmParams &prm, cudaStream_t stream) {
     const char *mode = std::getenv("B200SPMM_GATHER");
     const bool want_cpasync = mode && std::strcmp(mode, "cpasync") == 0;
     CUtensorMap tmap_b{};
-    if (want_cpasync || prm.n < box) return launch_slab<kTf32, false>(p, prm, tmap_b, stream);
+    if (want_cpasync || prm.n < box) return launch_slab<kTf32, false, false>(p, prm, tmap_b, stream);
     // B seen as [cols][n] with its real row pitch; a box is 128 bytes of one row.  Rows or
     // features past the end read as zeros.
     if (!encode_2d(&tmap_b, kTf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, prm.B, prm.n,
@@ -131,7 +134,13 @@ int launch_dtype(b200spmm_plan *p, SpmmParams &prm, cudaStream_t stream) {
         g_last_cuda_error = "cuTensorMapEncodeTiled failed for B";
         return B200SPMM_ERR_CUDA;
     }
-    return launch_slab<kTf32, true>(p, prm, tmap_b, stream);
+    if (p->comp.tcBit) {  // stream the compressed tiles
+        prm.tcBit = p->comp.tcBit;
+        prm.nnzOffset = p->comp.nnzOffset;
+        prm.values = p->comp.values;
+        return launch_slab<kTf32, true, true>(p, prm, tmap_b, stream);
+    }
+    return launch_slab<kTf32, true, false>(p, prm, tmap_b, stream);
 }
 
 // Tensor map over `data` seen as rows of 32 bytes: one tile is 16 consecutive rows, one box is
@@ -193,6 +202,16 @@ int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, int n_ctas) {
     B200_CUDA_TRY(cudaMemset(p->d_status, 0, 4 * sizeof(uint32_t)));
     {
         int st = encode_tile_map(p);
+        if (st != B200SPMM_OK) return st;
+    }
+    // On request (B200SPMM_TILES=bitmap) the kernels stream the tiles in compressed form - bitmap +
+    // stored values, expanded by the producer warps - instead of the dense 512-byte tiles; both
+    // give the same C bit for bit.  The compressed form moves an eighth of the tile bytes at a
+    // few per cent fill but costs the producer warps more instructions per tile than they can
+    // spare today, so dense tiles are the default.
+    const char *tiles_mode = std::getenv("B200SPMM_TILES");
+    if (info.total_tiles && tiles_mode && std::strcmp(tiles_mode, "bitmap") == 0) {
+        int st = compress_tiles_device(p->d_data, info.total_tiles, info.dtype, &p->comp);
         if (st != B200SPMM_OK) return st;
     }
     return B200SPMM_OK;
@@ -378,6 +397,7 @@ void b200spmm_plan_destroy(b200spmm_plan_t *p) {
         cudaFree(ps.d_splits);
         cudaFree(ps.d_piece_slots);
     }
+    free_compressed_tiles(&p->comp);
     cudaFree(p->d_partial);
     cudaFree(p->d_status);
     cudaFree(p->d_B);

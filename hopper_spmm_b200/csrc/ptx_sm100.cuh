@@ -129,6 +129,10 @@ B200_DEVICE void tma_gather4_2d(uint32_t dst, const void *tmap, int32_t x, int32
         : "memory");
 }
 
+B200_DEVICE void st_shared_v4(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 // ------------------------------------------------------------------ cp.async (16-byte gathers)
 
 // Copies 16 bytes global -> shared, bypassing L1; src_bytes < 16 zero-fills the rest

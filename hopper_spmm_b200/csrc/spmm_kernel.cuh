@@ -87,6 +87,10 @@ struct SpmmParams {
     uint32_t *sched_counter;     // [2] chunks handed out beyond the first gridDim.x, CTAs finished; both zero
                                  // at launch and again at exit (null: every CTA runs its first chunk only)
     float *partial;              // [slots][16][n] fp32 pieces of windows cut at a chunk boundary (may be null)
+    // bitmap kernels only: the tiles in compressed form instead of the dense `data` behind the tile tensor map
+    const uint64_t *tcBit;       // [tiles * 16*CW/64] one bit per tile slot, row-major, low bit first
+    const uint32_t *nnzOffset;   // [tiles+1] first stored value of each tile
+    const void *values;          // stored values, tile after tile, row-major inside a tile
     const void *B;               // [cols, n] row-major
     void *C;                     // [rows, n] row-major
     int64_t ldb, ldc;            // elements
@@ -95,7 +99,8 @@ struct SpmmParams {
     uint32_t n_slabs;            // ceil(n / kNs)
     uint32_t c_is_half;          // 0: fp32 C, 1: fp16 C
     uint32_t *status;            // device status word
-    uint32_t debug;              // measurement aid: bit 0 skips the B gathers, bit 1 the MMAs, bit 2 the A tiles
+    uint32_t debug;              // measurement aid: bit 0 skips the B gathers, bit 1 the MMAs, bit 2 the A tiles,
+                                 // bit 3 the loads of a compressed tile's stored values
     unsigned long long wait_limit_ns;
 #ifdef B200SPMM_PROFILE
     unsigned long long *prof;    // [gridDim.x][16] cycle counters
@@ -105,8 +110,11 @@ struct SpmmParams {
 // kTma selects how the rows of B reach shared memory: true = TMA tile::gather4 (four rows per
 // instruction, issued by a few lanes, completion counted in bytes on the stage's mbarrier);
 // false = 16-byte cp.async copies by all lanes of the producer warps.
-template <bool kTf32, int kNs, bool kTma = true>
+// kBitmap: the sparse tiles come compressed (bitmap + stored values) and the producer warps expand
+// them into the ring, instead of TMA copying 512 dense bytes per tile.
+template <bool kTf32, int kNs, bool kTma = true, bool kBitmap = false>
 struct SpmmCfg {
+    static_assert(kTma || !kBitmap, "compressed tiles go with the TMA gather");
     static_assert(kNs == 64 || kNs == 128 || kNs == 192 || kNs == 256, "feature slab");
     // One thread issues a CTA's MMAs, and with 16-row windows every MMA is small: the issuing
     // thread, not the tensor core, sets the pace.  Up to 128 features a CTA is small enough for
@@ -126,7 +134,7 @@ struct SpmmCfg {
     // reports the oldest as landed: 4 * (kLag + 1) tiles are in flight per SM (90-100 KB); the
     // rest of the ring absorbs the round trip through the MMA issuer.  One barrier pair serves
     // four tiles, which keeps the per-tile cost of waits, fences and commits low.
-    static constexpr int kStages = kNs == 64 ? 10 : kNs == 128 ? 6 : kNs == 192 ? 8 : 6;
+    static constexpr int kStages = kNs == 64 ? 10 : kNs == 128 ? (kBitmap ? 5 : 6) : kNs == 192 ? 8 : 6;
     // cp.async variant only: groups a warp keeps in flight before it reports the oldest as landed
     static constexpr int kLag = kStages / kProducerGroups >= 3 ? kStages / kProducerGroups - 2 : 0;
     static_assert(kStages > kProducerGroups * (kLag + 1), "ring too shallow");
@@ -141,10 +149,16 @@ struct SpmmCfg {
     static constexpr int kWinSlots = 32;
     // Each producer warp keeps the column lists of its next kIdxAhead tiles in a private ring of
     // kIdxSlots entries, fetched in the same cp.async groups as the rows of the current tile.
-    static constexpr int kIdxSlots = kCtasPerSm == 2 ? 7 : 16;
-    static constexpr int kIdxAhead = kCtasPerSm == 2 ? 5 : 12;
-    static_assert(kIdxAhead > kLag && kIdxAhead < kIdxSlots, "column lists must land before they are needed");
-    static constexpr int kIdxBytes = kProducerWarps * kProducerGroups * kIdxSlots * kCW * 4;
+    // With compressed tiles a slot also holds the tile's bitmap and its two value offsets.
+    static constexpr int kIdxSlots = kBitmap ? 8 : (kCtasPerSm == 2 ? 7 : 16);
+    static constexpr int kIdxAhead = kBitmap ? 7 : (kCtasPerSm == 2 ? 5 : 12);
+    // Compressed tiles: the slot of the tile after the current one has to be in shared memory
+    // when the current one is expanded, because the loads of its stored values start right then.
+    static constexpr int kSlotLead = kBitmap ? 2 : 1;
+    static_assert((kTma || kIdxAhead > kLag) && kIdxAhead < kIdxSlots, "column lists must land before they are needed");
+    static constexpr int kBitWords = kRowWindow * kCW / 64;  // 64-bit bitmap words per tile
+    static constexpr int kSlotBytes = kBitmap ? (kCW * 4 + kBitWords * 8 + 8 + 15) / 16 * 16 : kCW * 4;
+    static constexpr int kIdxBytes = kProducerWarps * kProducerGroups * kIdxSlots * kSlotBytes;
     static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
     static constexpr int kWinBytes = kWinSlots * 4;
     static constexpr int kChunkSlots = 32;  // chunks one CTA may take; the last entry always ends the list
@@ -153,11 +167,11 @@ struct SpmmCfg {
         1024 + (size_t)kStages * kStageBytes + kIdxBytes + kBarrierBytes + kWinBytes + kChunkBytes;
 };
 
-template <bool kTf32, int kNs, bool kTma>
-__global__ void __launch_bounds__((SpmmCfg<kTf32, kNs, kTma>::kThreads), (SpmmCfg<kTf32, kNs, kTma>::kCtasPerSm))
+template <bool kTf32, int kNs, bool kTma, bool kBitmap>
+__global__ void __launch_bounds__((SpmmCfg<kTf32, kNs, kTma, kBitmap>::kThreads), (SpmmCfg<kTf32, kNs, kTma, kBitmap>::kCtasPerSm))
 spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const SpmmParams p) {
-    using Cfg = SpmmCfg<kTf32, kNs, kTma>;
+    using Cfg = SpmmCfg<kTf32, kNs, kTma, kBitmap>;
     constexpr int kStages = Cfg::kStages;
     constexpr int kTps = Cfg::kTilesPerStage;
     constexpr int kProducerGroups = Cfg::kProducerGroups;
@@ -248,7 +262,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         chunk_list[0] = blockIdx.x < p.n_chunks ? blockIdx.x : kNoChunk;
         *chunk_avail = 1;
         ptx::fence_mbar_init();
-        ptx::prefetch_tensormap(&tmap_a);
+        if (!kBitmap) ptx::prefetch_tensormap(&tmap_a);
         if (kTma) ptx::prefetch_tensormap(&tmap_b);
     }
     if (warp == kMmaWarp) {
@@ -274,107 +288,107 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // First row of a window and of the window after it (or the row count), fetched two of
         // this set's windows ahead so the loads are never waited for.
         for (uint32_t round = 0; epi_alive; ++round) {
-        const uint32_t chunk = chunk_id(round);
-        if (chunk == kNoChunk) break;
-        const Chunk ch = load_chunk(chunk);
-        const uint32_t n_win = ch.n_win, w_begin = ch.w_begin;
-        if (n_win == 0) continue;
-        const uint32_t total = p.n_slabs * n_win;  // accumulators this chunk produces, in order
-        const uint32_t first = (e ^ g0) & 1u;      // this set drains the accumulators whose running number is e mod 2
-        auto meta = [&](uint32_t it, uint32_t &row0, uint32_t &after) {
-            if (it < total) {
-                const uint32_t w = w_begin + it % n_win;
-                row0 = p.rowIdx[w];
-                after = w + 1 < p.eff_row_windows ? p.rowIdx[w + 1] : p.rows;
-            }
-        };
-        uint32_t row0_a = 0, after_a = 0, row0_b = 0, after_b = 0;
-        meta(first, row0_a, after_a);
-        meta(first + 2, row0_b, after_b);
-        uint32_t slab = 0, i = first;  // position of accumulator `it`: window i of slab `slab`
-        while (i >= n_win) { i -= n_win; ++slab; }
-        for (uint32_t it = first; it < total; it += 2) {
-            const uint32_t row0 = row0_a, gap_hi = after_a;
-            row0_a = row0_b;
-            after_a = after_b;
-            meta(it + 4, row0_b, after_b);
-            const uint32_t f0 = slab * kNs;  // first feature of the slab
-            // a piece of a window shared with a neighbouring CTA goes to a partial-result slot
-            const bool is_head_piece = i == 0 && ch.head_slot != kNoSlot;
-            const bool is_tail_piece = i + 1 == n_win && ch.tail_slot != kNoSlot;
-            const bool piece = is_head_piece || is_tail_piece;
-            float *slot_rows = p.partial + (size_t)(is_head_piece ? ch.head_slot : ch.tail_slot) * kRowWindow * p.n;
-            uint32_t ok = 1;
-            if (lane == 0) {  // one lane polls; every mbarrier operation costs a shared-memory slot per thread
-                B200_PROF_T0();
-                ok = ptx::mbar_wait(acc_full_bar(e), ((g0 + it) >> 1) & 1u, abort_flag, limit) ? 1u : 0u;
-                B200_PROF_ADD(prof_wait_accfull);
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) { epi_alive = false; break; }
-            ptx::tcgen05_fence_after_sync();
-            uint32_t r[Cfg::kChunks][16];
-#pragma unroll
-            for (int c = 0; c < Cfg::kChunks; ++c)
-                ptx::tmem_ld_32x32b_x16(tmem_base + ((q * 32u) << 16) + e * kAccCols + c * 16, r[c]);
-            ptx::tmem_ld_wait();
-            ptx::tcgen05_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(acc_empty_bar(e));  // the buffer may be overwritten from here on
-            // Lane l of this warp holds one feature of the 16 window rows (M = 128: feature 32q + l
-            // of the chunk; M = 64: lanes 0-15 hold feature 16q + l), so a row of C receives 32
-            // consecutive values from the warp: one full 128-byte line per store instruction.
-#pragma unroll
-            for (int c = 0; c < Cfg::kChunks; ++c) {
-                const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
-                const uint32_t width = half_chunk ? 16 : 32;  // features this warp owns in the chunk
-                const uint32_t feat = f0 + c * 128 + q * width + lane;
-                if (lane < width && feat < p.n) {
-                    if (piece) {
-#pragma unroll
-                        for (int j = 0; j < kRowWindow; ++j) slot_rows[(size_t)j * p.n + feat] = __uint_as_float(r[c][j]);
-                    } else if (p.c_is_half) {
-                        __half *dst = static_cast<__half *>(p.C) + (int64_t)row0 * p.ldc + feat;
-#pragma unroll
-                        for (int j = 0; j < kRowWindow; ++j)
-                            if (row0 + j < p.rows) dst[(int64_t)j * p.ldc] = __float2half_rn(__uint_as_float(r[c][j]));
-                    } else {
-                        float *dst = static_cast<float *>(p.C) + (int64_t)row0 * p.ldc + feat;
-#pragma unroll
-                        for (int j = 0; j < kRowWindow; ++j)
-                            if (row0 + j < p.rows) dst[(int64_t)j * p.ldc] = __uint_as_float(r[c][j]);
-                    }
+            const uint32_t chunk = chunk_id(round);
+            if (chunk == kNoChunk) break;
+            const Chunk ch = load_chunk(chunk);
+            const uint32_t n_win = ch.n_win, w_begin = ch.w_begin;
+            if (n_win == 0) continue;
+            const uint32_t total = p.n_slabs * n_win;  // accumulators this chunk produces, in order
+            const uint32_t first = (e ^ g0) & 1u;      // this set drains the accumulators whose running number is e mod 2
+            auto meta = [&](uint32_t it, uint32_t &row0, uint32_t &after) {
+                if (it < total) {
+                    const uint32_t w = w_begin + it % n_win;
+                    row0 = p.rowIdx[w];
+                    after = w + 1 < p.eff_row_windows ? p.rowIdx[w + 1] : p.rows;
                 }
-            }
-            // Rows of windows that hold no entries are absent from the format: clear the gap that
-            // follows this window (and the one before the very first window).  Warp q of the set
-            // takes every fourth row.
-            // (the CTA that finishes a window clears the gap after it; the one that starts window 0 the lead)
-            const bool lead = (w_begin + i == 0) && row0 > 0 && !is_head_piece;
-            if ((gap_hi > row0 + kRowWindow && !is_tail_piece) || lead) {
-                const uint32_t slab_feats = min((uint32_t)kNs, p.n - f0);
-                const uint32_t vec_per_row = slab_feats / 4;
-                for (int pass = 0; pass < 2; ++pass) {
-                    const uint32_t lo = pass == 0 ? row0 + kRowWindow : 0u;
-                    const uint32_t hi = pass == 0 ? (is_tail_piece ? 0u : min(gap_hi, p.rows)) : (lead ? row0 : 0u);
-                    for (uint32_t row = lo + q; row < hi; row += 4) {
-                        for (uint32_t v4 = lane; v4 < vec_per_row; v4 += 32) {
-                            const uint32_t feat = f0 + v4 * 4;
-                            if (p.c_is_half)
-                                *reinterpret_cast<uint2 *>(static_cast<__half *>(p.C) + (int64_t)row * p.ldc + feat) = make_uint2(0, 0);
-                            else
-                                *reinterpret_cast<float4 *>(static_cast<float *>(p.C) + (int64_t)row * p.ldc + feat) = make_float4(0, 0, 0, 0);
+            };
+            uint32_t row0_a = 0, after_a = 0, row0_b = 0, after_b = 0;
+            meta(first, row0_a, after_a);
+            meta(first + 2, row0_b, after_b);
+            uint32_t slab = 0, i = first;  // position of accumulator `it`: window i of slab `slab`
+            while (i >= n_win) { i -= n_win; ++slab; }
+            for (uint32_t it = first; it < total; it += 2) {
+                const uint32_t row0 = row0_a, gap_hi = after_a;
+                row0_a = row0_b;
+                after_a = after_b;
+                meta(it + 4, row0_b, after_b);
+                const uint32_t f0 = slab * kNs;  // first feature of the slab
+                // a piece of a window shared with a neighbouring CTA goes to a partial-result slot
+                const bool is_head_piece = i == 0 && ch.head_slot != kNoSlot;
+                const bool is_tail_piece = i + 1 == n_win && ch.tail_slot != kNoSlot;
+                const bool piece = is_head_piece || is_tail_piece;
+                float *slot_rows = p.partial + (size_t)(is_head_piece ? ch.head_slot : ch.tail_slot) * kRowWindow * p.n;
+                uint32_t ok = 1;
+                if (lane == 0) {  // one lane polls; every mbarrier operation costs a shared-memory slot per thread
+                    B200_PROF_T0();
+                    ok = ptx::mbar_wait(acc_full_bar(e), ((g0 + it) >> 1) & 1u, abort_flag, limit) ? 1u : 0u;
+                    B200_PROF_ADD(prof_wait_accfull);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) { epi_alive = false; break; }
+                ptx::tcgen05_fence_after_sync();
+                uint32_t r[Cfg::kChunks][16];
+#pragma unroll
+                for (int c = 0; c < Cfg::kChunks; ++c)
+                    ptx::tmem_ld_32x32b_x16(tmem_base + ((q * 32u) << 16) + e * kAccCols + c * 16, r[c]);
+                ptx::tmem_ld_wait();
+                ptx::tcgen05_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(acc_empty_bar(e));  // the buffer may be overwritten from here on
+                // Lane l of this warp holds one feature of the 16 window rows (M = 128: feature 32q + l
+                // of the chunk; M = 64: lanes 0-15 hold feature 16q + l), so a row of C receives 32
+                // consecutive values from the warp: one full 128-byte line per store instruction.
+#pragma unroll
+                for (int c = 0; c < Cfg::kChunks; ++c) {
+                    const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
+                    const uint32_t width = half_chunk ? 16 : 32;  // features this warp owns in the chunk
+                    const uint32_t feat = f0 + c * 128 + q * width + lane;
+                    if (lane < width && feat < p.n) {
+                        if (piece) {
+#pragma unroll
+                            for (int j = 0; j < kRowWindow; ++j) slot_rows[(size_t)j * p.n + feat] = __uint_as_float(r[c][j]);
+                        } else if (p.c_is_half) {
+                            __half *dst = static_cast<__half *>(p.C) + (int64_t)row0 * p.ldc + feat;
+#pragma unroll
+                            for (int j = 0; j < kRowWindow; ++j)
+                                if (row0 + j < p.rows) dst[(int64_t)j * p.ldc] = __float2half_rn(__uint_as_float(r[c][j]));
+                        } else {
+                            float *dst = static_cast<float *>(p.C) + (int64_t)row0 * p.ldc + feat;
+#pragma unroll
+                            for (int j = 0; j < kRowWindow; ++j)
+                                if (row0 + j < p.rows) dst[(int64_t)j * p.ldc] = __uint_as_float(r[c][j]);
                         }
                     }
                 }
-            }
-            i += 2;
-            while (i >= n_win) { i -= n_win; ++slab; }
+                // Rows of windows that hold no entries are absent from the format: clear the gap that
+                // follows this window (and the one before the very first window).  Warp q of the set
+                // takes every fourth row.
+                // (the CTA that finishes a window clears the gap after it; the one that starts window 0 the lead)
+                const bool lead = (w_begin + i == 0) && row0 > 0 && !is_head_piece;
+                if ((gap_hi > row0 + kRowWindow && !is_tail_piece) || lead) {
+                    const uint32_t slab_feats = min((uint32_t)kNs, p.n - f0);
+                    const uint32_t vec_per_row = slab_feats / 4;
+                    for (int pass = 0; pass < 2; ++pass) {
+                        const uint32_t lo = pass == 0 ? row0 + kRowWindow : 0u;
+                        const uint32_t hi = pass == 0 ? (is_tail_piece ? 0u : min(gap_hi, p.rows)) : (lead ? row0 : 0u);
+                        for (uint32_t row = lo + q; row < hi; row += 4) {
+                            for (uint32_t v4 = lane; v4 < vec_per_row; v4 += 32) {
+                                const uint32_t feat = f0 + v4 * 4;
+                                if (p.c_is_half)
+                                    *reinterpret_cast<uint2 *>(static_cast<__half *>(p.C) + (int64_t)row * p.ldc + feat) = make_uint2(0, 0);
+                                else
+                                    *reinterpret_cast<float4 *>(static_cast<float *>(p.C) + (int64_t)row * p.ldc + feat) = make_float4(0, 0, 0, 0);
+                            }
+                        }
+                    }
+                }
+                i += 2;
+                while (i >= n_win) { i -= n_win; ++slab; }
 #ifdef B200SPMM_PROFILE
-            ++prof_windows;
+                ++prof_windows;
 #endif
-        }
-        g0 += total;
+            }
+            g0 += total;
         }  // chunks
 #ifdef B200SPMM_PROFILE
         if (tid == 0) {
@@ -389,9 +403,12 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const uint32_t grp = pid / kProducerWarps;  // fills stages grp, grp + 3, grp + 6, ...
         const uint32_t pw = pid % kProducerWarps;   // with tile slot pw of each of them
         // This warp's ring of column lists: slot (iteration % kIdxSlots) holds CW indices.
-        uint32_t *my_idx = idx_ring + pid * Cfg::kIdxSlots * Cfg::kCW;
-        const uint32_t my_idx_addr = idx_ring_addr + pid * Cfg::kIdxSlots * Cfg::kCW * 4;
+        // With compressed tiles the slot continues with the tile's bitmap and its two value offsets.
+        constexpr uint32_t kSlotWords = Cfg::kSlotBytes / 4, kBitOff = Cfg::kCW * 4, kNnzOff = kBitOff + Cfg::kBitWords * 8;
+        uint32_t *my_idx = idx_ring + pid * Cfg::kIdxSlots * kSlotWords;
+        const uint32_t my_idx_addr = idx_ring_addr + pid * Cfg::kIdxSlots * Cfg::kSlotBytes;
         constexpr int kIdxLanes = Cfg::kCW * 4 / 16;  // lanes that copy one column list (16 bytes each)
+        constexpr int kBitLanes = Cfg::kBitWords / 2;  // lanes that copy one bitmap
 
         // ---- per-lane constants of the gather
         // TMA: lane o issues gather instruction o of the tile: row quad g = o % kRowQuads of
@@ -489,10 +506,18 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         auto fetch_list = [&]() {  // column list of the fetch cursor's tile -> its ring slot; then advance
             if (!fc.done) {
                 const uint32_t tpos = fc.sp * kTps + pw;
-                if (lane < kIdxLanes && tpos < fc.n_tiles) {
-                    const uint32_t slot = it_f % Cfg::kIdxSlots;
-                    ptx::cp_async_16(my_idx_addr + slot * Cfg::kCW * 4 + lane * 16,
-                                     p.tcA2B + (uint64_t)(fc.tile_begin + tpos) * Cfg::kCW + lane * 4, 16u);
+                if (tpos < fc.n_tiles) {
+                    const uint32_t slot_addr = my_idx_addr + (it_f % Cfg::kIdxSlots) * Cfg::kSlotBytes;
+                    const uint64_t t = fc.tile_begin + tpos;
+                    if (lane < kIdxLanes) {
+                        ptx::cp_async_16(slot_addr + lane * 16, p.tcA2B + t * Cfg::kCW + lane * 4, 16u);
+                    } else if (kBitmap && lane < kIdxLanes + kBitLanes) {
+                        const uint32_t j = lane - kIdxLanes;
+                        ptx::cp_async_16(slot_addr + kBitOff + j * 16, p.tcBit + t * Cfg::kBitWords + j * 2, 16u);
+                    } else if (kBitmap && lane < kIdxLanes + kBitLanes + 2) {
+                        const uint32_t j = lane - kIdxLanes - kBitLanes;
+                        ptx::cp_async_4(slot_addr + kNnzOff + j * 4, p.nnzOffset + t + j);
+                    }
                 }
                 fc.sp += kProducerGroups;
                 normalise(fc);
@@ -504,13 +529,59 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         ptx::cp_async_wait_group<0>();
         __syncwarp();
 
+        // Compressed tiles.  Lane l owns the 16-byte piece of the tile that holds row l/2, columns
+        // (l%2) * CW/2 ... of it: kPer slots, whose bits are consecutive in the bitmap.  The stored
+        // values of a tile follow the bit order, so the lane's first value sits at the tile's
+        // offset plus the number of bits set before its own.  The loads of the NEXT tile's values
+        // are issued right after the current tile has been expanded and fenced - a proxy fence
+        // waits for the thread's loads in flight, so none may be pending when it executes - and
+        // have one whole iteration to land.
+        constexpr int kPer = Cfg::kCW / 2;
+        uint32_t my_vals[kPer] = {};  // stored values (fp16 in the low half), zero where the bit is clear
+        Cursor vc = cur;              // the tile whose values are loaded next
+        uint32_t it_v = 0;
+        auto prefetch_values = [&]() {  // loads the value cursor's tile into my_vals, then advances the cursor
+            if (!kBitmap) return;
+            const uint32_t *slot_words = my_idx + (it_v % Cfg::kIdxSlots) * kSlotWords;
+            const bool tile_here = !vc.done && vc.sp * kTps + pw < vc.n_tiles && !(p.debug & 8u);
+#pragma unroll
+            for (int b = 0; b < kPer; ++b) my_vals[b] = 0;
+            if (tile_here) {
+                const uint64_t *bits = reinterpret_cast<const uint64_t *>(slot_words + kBitOff / 4);
+                const uint32_t first_bit = (uint32_t)lane * kPer, w = first_bit >> 6, sh = first_bit & 63u;
+                uint32_t before = 0;
+#pragma unroll
+                for (int j = 0; j < Cfg::kBitWords; ++j) before += (uint32_t)j < w ? (uint32_t)__popcll(bits[j]) : 0u;
+                const uint64_t word = bits[w];
+                before += (uint32_t)__popcll(word & ((1ull << sh) - 1ull));
+                const uint32_t mine = (uint32_t)(word >> sh) & ((1u << kPer) - 1u);
+                uint32_t idx = slot_words[kNnzOff / 4] + before;
+#pragma unroll
+                for (int b = 0; b < kPer; ++b) {
+                    if (mine & (1u << b)) {
+                        if (kTf32) my_vals[b] = __ldg(static_cast<const uint32_t *>(p.values) + idx);
+                        else my_vals[b] = __ldg(static_cast<const uint16_t *>(p.values) + idx);
+                        ++idx;
+                    }
+                }
+            }
+            if (!vc.done) {
+                vc.sp += kProducerGroups;
+                normalise(vc);
+            }
+            ++it_v;
+        };
+        // where the lane's piece goes: K-major rows of 32 bytes, 16-byte halves swapped in rows 4-7 and 12-15
+        const uint32_t piece_off = ((uint32_t)lane >> 1) * 32u + ((((uint32_t)lane & 1u) ^ (((uint32_t)lane >> 3) & 1u)) << 4);
+        prefetch_values();
+
         const uint32_t n_bytes = p.n * Cfg::kEsz;
         uint32_t issued = 0;  // cp.async path: stages whose copies were issued and not yet reported
         while (!cur.done) {
             const uint32_t slab = cur.slab, sp = cur.sp, tile_begin = cur.tile_begin;
             const uint32_t tpos = sp * kTps + pw;
             const bool have_tile = tpos < cur.n_tiles && !(p.debug & 1u);  // the last stage of a pass may be short
-            const uint32_t *list = my_idx + (it % Cfg::kIdxSlots) * Cfg::kCW;
+            const uint32_t *list = my_idx + (it % Cfg::kIdxSlots) * kSlotWords;
             const uint32_t tile_area = gather_addr + (s * kTps + pw) * Cfg::kGatherBytes;
 
             // One lane polls (every mbarrier operation costs a shared-memory pipeline slot per
@@ -522,7 +593,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     ok = ptx::mbar_wait(empty_bar(s), (use & 1u) ^ 1u, abort_flag, limit) ? 1u : 0u;
                     B200_PROF_ADD(prof_wait_empty);
                 }
-                if (ok) {
+                if (ok && !kBitmap) {
                     const bool a_tiles = pw == 0 && !(p.debug & 4u);
                     if (kTma) {
                         // this warp's arrival, announcing the bytes its TMA loads will deliver
@@ -538,6 +609,23 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) { failed = true; break; }
+            if (kBitmap) {
+                // expand this warp's tile into its 512 bytes of the stage, then announce the gather's bytes
+                if (tpos < cur.n_tiles && !(p.debug & 4u)) {
+                    uint4 piece;
+                    const uint32_t *v = my_vals;
+                    if constexpr (kTf32) {
+                        piece = make_uint4(v[0], v[1], v[2], v[3]);
+                    } else {
+                        piece = make_uint4(v[0] | (v[1] << 16), v[2] | (v[3] << 16), v[4] | (v[5] << 16), v[6] | (v[7] << 16));
+                    }
+                    ptx::st_shared_v4(atile_addr + (s * kTps + pw) * kATileBytes + piece_off, piece);
+                    ptx::fence_proxy_async_smem();
+                }
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive_expect_tx(full_bar(s), have_tile ? Cfg::kGatherBytes : 0u);
+                prefetch_values();  // the next tile's, whose slot landed an iteration ago (see the wait below)
+            }
             if (kTma) {
                 B200_PROF_T0();
                 if (have_tile && lane < Cfg::kGatherOps) {
@@ -551,7 +639,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 ptx::cp_async_commit();
                 // The list needed next iteration was fetched kIdxAhead groups ago: this only blocks
                 // when that many groups are still pending, and makes the guarantee explicit.
-                ptx::cp_async_wait_group<Cfg::kIdxAhead - 1>();
+                ptx::cp_async_wait_group<Cfg::kIdxAhead - Cfg::kSlotLead>();
                 __syncwarp();
                 B200_PROF_ADD(prof_issue);
             } else {
@@ -676,126 +764,126 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             else ptx::umma_f16_ss_lohi(d, alo, a_hi, blo, b_hi, idesc, acc);
         };
         for (uint32_t round = 0; alive; ++round) {
-        const uint32_t chunk = chunk_id(round);
-        if (chunk == kNoChunk) break;
-        const Chunk ch = load_chunk(chunk);
-        const uint32_t n_win = ch.n_win, w_begin = ch.w_begin, tile_begin = ch.tile_begin, tile_end = ch.tile_end;
-        for (uint32_t slab = 0; slab < p.n_slabs && alive; ++slab) {
-            // window i's last tile + 1 goes to slot i % kWinSlots, one cp.async group per window
-            for (uint32_t i = 0; i < (uint32_t)Cfg::kWinAhead; ++i) {
-                if (i < n_win) ptx::cp_async_4(win_ends_addr + (i % Cfg::kWinSlots) * 4, p.rowOffset + w_begin + i + 1);
-                ptx::cp_async_commit();
-            }
-            uint32_t off_lo = tile_begin;
-            for (uint32_t i = 0; i < n_win && alive; ++i, ++acc_it) {
-#ifdef B200SPMM_PROFILE
-                const long long prof_h0 = clock64();
-#endif
-                const uint32_t ahead = i + Cfg::kWinAhead;
-                if (ahead < n_win) ptx::cp_async_4(win_ends_addr + (ahead % Cfg::kWinSlots) * 4, p.rowOffset + w_begin + ahead + 1);
-                ptx::cp_async_commit();
-                ptx::cp_async_wait_group<Cfg::kWinAhead>();  // window i's group has landed
-                const uint32_t off_hi = min(win_ends[i % Cfg::kWinSlots], tile_end);  // the last window may be cut
-#ifdef B200SPMM_PROFILE
-                prof_head += clock64() - prof_h0;
-                prof_tiles += off_hi - off_lo;
-#endif
-                uint32_t nt = off_hi - off_lo;
-                off_lo = off_hi;
-                const uint32_t a = acc_it & 1u;
-                {
-                    B200_PROF_T0();
-                    alive = ptx::mbar_wait(acc_empty_bar(a), ((acc_it >> 1) & 1u) ^ 1u, abort_flag, limit);
-                    ptx::tcgen05_fence_after_sync();
-                    B200_PROF_ADD(prof_wait_acc);
+            const uint32_t chunk = chunk_id(round);
+            if (chunk == kNoChunk) break;
+            const Chunk ch = load_chunk(chunk);
+            const uint32_t n_win = ch.n_win, w_begin = ch.w_begin, tile_begin = ch.tile_begin, tile_end = ch.tile_end;
+            for (uint32_t slab = 0; slab < p.n_slabs && alive; ++slab) {
+                // window i's last tile + 1 goes to slot i % kWinSlots, one cp.async group per window
+                for (uint32_t i = 0; i < (uint32_t)Cfg::kWinAhead; ++i) {
+                    if (i < n_win) ptx::cp_async_4(win_ends_addr + (i % Cfg::kWinSlots) * 4, p.rowOffset + w_begin + i + 1);
+                    ptx::cp_async_commit();
                 }
-                const uint32_t d = tmem_base + a * kAccCols;
-                uint32_t accumulate = 0;
-                // A segment is the run of tiles that share a ring stage and a window: at most four.
-                // Branches are what a lone thread can least afford, so the window is walked as
-                //   head - the rest of a stage the previous window left partly used (predicated MMAs),
-                //   body - whole stages: wait, four MMAs, commit; ring bookkeeping by selects,
-                //   tail - the first tiles of a stage the next window will finish (predicated MMAs).
-                auto partial = [&](uint32_t k) {  // k tiles starting at (s, slot), 0 < k < 4 or closing a stage
-                    B200_PROF_T0();
-#pragma unroll
-                    for (int q = 0; q < kTps; ++q) {
-                        const uint32_t on = (do_mma && (uint32_t)q < k) ? 1u : 0u;
-#pragma unroll
-                        for (int c = 0; c < Cfg::kChunks; ++c) {
-                            const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
-                            const uint32_t idesc = half_chunk ? idesc_half : idesc_full;
-                            const uint32_t acc = q == 0 ? accumulate : 1u;
-                            const uint32_t alo = ad_lo + q * kGather16 + c * 256u, blo = bd_lo + q * kATile16;
-                            if (kTf32) ptx::umma_tf32_ss_lohi_if(on, d + c * 16, alo, a_hi, blo, b_hi, idesc, acc);
-                            else ptx::umma_f16_ss_lohi_if(on, d + c * 16, alo, a_hi, blo, b_hi, idesc, acc);
-                        }
-                    }
-                    accumulate = 1;
-                    nt -= k;
-                    slot += k;
-                    ad_lo += k * kGather16;
-                    bd_lo += k * kATile16;
-                    B200_PROF_ADD(prof_mma);
-                };
-                auto await_stage = [&]() {  // the operands of stage s must have landed
-                    B200_PROF_T0();
-                    alive = ptx::mbar_wait(full_bar(s), phase, abort_flag, limit);
-                    ptx::tcgen05_fence_after_sync();
-                    B200_PROF_ADD(prof_wait_full);
-                };
-                if (slot != 0 && alive) {  // head
-                    partial(min(nt, (uint32_t)kTps - slot));
-                    if (slot == (uint32_t)kTps) release_stage();
-                }
-                while (nt >= (uint32_t)kTps && alive) {  // body: slot == 0 here
-                    await_stage();
-                    if (!alive) break;
+                uint32_t off_lo = tile_begin;
+                for (uint32_t i = 0; i < n_win && alive; ++i, ++acc_it) {
+#ifdef B200SPMM_PROFILE
+                    const long long prof_h0 = clock64();
+#endif
+                    const uint32_t ahead = i + Cfg::kWinAhead;
+                    if (ahead < n_win) ptx::cp_async_4(win_ends_addr + (ahead % Cfg::kWinSlots) * 4, p.rowOffset + w_begin + ahead + 1);
+                    ptx::cp_async_commit();
+                    ptx::cp_async_wait_group<Cfg::kWinAhead>();  // window i's group has landed
+                    const uint32_t off_hi = min(win_ends[i % Cfg::kWinSlots], tile_end);  // the last window may be cut
+#ifdef B200SPMM_PROFILE
+                    prof_head += clock64() - prof_h0;
+                    prof_tiles += off_hi - off_lo;
+#endif
+                    uint32_t nt = off_hi - off_lo;
+                    off_lo = off_hi;
+                    const uint32_t a = acc_it & 1u;
                     {
                         B200_PROF_T0();
-                        if (do_mma) {
+                        alive = ptx::mbar_wait(acc_empty_bar(a), ((acc_it >> 1) & 1u) ^ 1u, abort_flag, limit);
+                        ptx::tcgen05_fence_after_sync();
+                        B200_PROF_ADD(prof_wait_acc);
+                    }
+                    const uint32_t d = tmem_base + a * kAccCols;
+                    uint32_t accumulate = 0;
+                    // A segment is the run of tiles that share a ring stage and a window: at most four.
+                    // Branches are what a lone thread can least afford, so the window is walked as
+                    //   head - the rest of a stage the previous window left partly used (predicated MMAs),
+                    //   body - whole stages: wait, four MMAs, commit; ring bookkeeping by selects,
+                    //   tail - the first tiles of a stage the next window will finish (predicated MMAs).
+                    auto partial = [&](uint32_t k) {  // k tiles starting at (s, slot), 0 < k < 4 or closing a stage
+                        B200_PROF_T0();
 #pragma unroll
-                            for (int q = 0; q < kTps; ++q) {
+                        for (int q = 0; q < kTps; ++q) {
+                            const uint32_t on = (do_mma && (uint32_t)q < k) ? 1u : 0u;
 #pragma unroll
-                                for (int c = 0; c < Cfg::kChunks; ++c) {
-                                    const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
-                                    issue(d + c * 16, ad_lo + q * kGather16 + c * 256u, bd_lo + q * kATile16,
-                                          half_chunk ? idesc_half : idesc_full, q == 0 ? accumulate : 1u);
-                                }
+                            for (int c = 0; c < Cfg::kChunks; ++c) {
+                                const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
+                                const uint32_t idesc = half_chunk ? idesc_half : idesc_full;
+                                const uint32_t acc = q == 0 ? accumulate : 1u;
+                                const uint32_t alo = ad_lo + q * kGather16 + c * 256u, blo = bd_lo + q * kATile16;
+                                if (kTf32) ptx::umma_tf32_ss_lohi_if(on, d + c * 16, alo, a_hi, blo, b_hi, idesc, acc);
+                                else ptx::umma_f16_ss_lohi_if(on, d + c * 16, alo, a_hi, blo, b_hi, idesc, acc);
                             }
                         }
+                        accumulate = 1;
+                        nt -= k;
+                        slot += k;
+                        ad_lo += k * kGather16;
+                        bd_lo += k * kATile16;
                         B200_PROF_ADD(prof_mma);
+                    };
+                    auto await_stage = [&]() {  // the operands of stage s must have landed
+                        B200_PROF_T0();
+                        alive = ptx::mbar_wait(full_bar(s), phase, abort_flag, limit);
+                        ptx::tcgen05_fence_after_sync();
+                        B200_PROF_ADD(prof_wait_full);
+                    };
+                    if (slot != 0 && alive) {  // head
+                        partial(min(nt, (uint32_t)kTps - slot));
+                        if (slot == (uint32_t)kTps) release_stage();
                     }
-                    accumulate = 1;
-                    nt -= kTps;
+                    while (nt >= (uint32_t)kTps && alive) {  // body: slot == 0 here
+                        await_stage();
+                        if (!alive) break;
+                        {
+                            B200_PROF_T0();
+                            if (do_mma) {
+#pragma unroll
+                                for (int q = 0; q < kTps; ++q) {
+#pragma unroll
+                                    for (int c = 0; c < Cfg::kChunks; ++c) {
+                                        const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
+                                        issue(d + c * 16, ad_lo + q * kGather16 + c * 256u, bd_lo + q * kATile16,
+                                              half_chunk ? idesc_half : idesc_full, q == 0 ? accumulate : 1u);
+                                    }
+                                }
+                            }
+                            B200_PROF_ADD(prof_mma);
+                        }
+                        accumulate = 1;
+                        nt -= kTps;
+                        {
+                            B200_PROF_T0();
+                            ptx::umma_commit(empty_bar(s));
+                            const bool wrap = s + 1 == (uint32_t)kStages;  // selects, no branch
+                            s = wrap ? 0u : s + 1;
+                            phase ^= wrap ? 1u : 0u;
+                            ad_lo = wrap ? a_lo0 : ad_lo + kTps * kGather16;
+                            bd_lo = wrap ? b_lo0 : bd_lo + kTps * kATile16;
+                            B200_PROF_ADD(prof_commit);
+                        }
+                    }
+                    if (nt != 0 && alive) {  // tail: slot == 0, 0 < nt < 4
+                        await_stage();
+                        if (alive) partial(nt);
+                    }
                     {
                         B200_PROF_T0();
-                        ptx::umma_commit(empty_bar(s));
-                        const bool wrap = s + 1 == (uint32_t)kStages;  // selects, no branch
-                        s = wrap ? 0u : s + 1;
-                        phase ^= wrap ? 1u : 0u;
-                        ad_lo = wrap ? a_lo0 : ad_lo + kTps * kGather16;
-                        bd_lo = wrap ? b_lo0 : bd_lo + kTps * kATile16;
-                        B200_PROF_ADD(prof_commit);
+                        if (alive) ptx::umma_commit(acc_full_bar(a));
+                        B200_PROF_ADD(prof_tail);
                     }
                 }
-                if (nt != 0 && alive) {  // tail: slot == 0, 0 < nt < 4
-                    await_stage();
-                    if (alive) partial(nt);
-                }
-                {
-                    B200_PROF_T0();
-                    if (alive) ptx::umma_commit(acc_full_bar(a));
-                    B200_PROF_ADD(prof_tail);
+                // a pass ends on a stage boundary: give back a partly used last stage
+                if (slot != 0 && alive) {
+                    ad_lo += ((uint32_t)kTps - slot) * kGather16;
+                    bd_lo += ((uint32_t)kTps - slot) * kATile16;
+                    release_stage();
                 }
             }
-            // a pass ends on a stage boundary: give back a partly used last stage
-            if (slot != 0 && alive) {
-                ad_lo += ((uint32_t)kTps - slot) * kGather16;
-                bd_lo += ((uint32_t)kTps - slot) * kATile16;
-                release_stage();
-            }
-        }
         }  // chunks
         ptx::cp_async_wait_group<0>();
 #ifdef B200SPMM_PROFILE

@@ -260,6 +260,7 @@ typedef struct {
     int64_t smem_bytes;
     int64_t kernel_launches; /* launches issued by that call */
     int32_t tma_gather;      /* 1: rows of B fetched by TMA tile::gather4, 0: by cp.async copies */
+    int32_t bitmap_tiles;    /* 1: tiles streamed as bitmap + stored values and expanded in the kernel, 0: dense tiles */
 } b200spmm_launch_info_t;
 int b200spmm_plan_launch_info(const b200spmm_plan_t *p, b200spmm_launch_info_t *info);
 

@@ -100,6 +100,25 @@ def test_more_ctas_than_windows_and_one_cta():
         assert info.n_ctas == n_ctas
 
 
+@pytest.mark.parametrize("dt", [np.float16, np.float32])
+@pytest.mark.parametrize("n", [64, 128, 320])
+def test_compressed_tiles_give_the_same_bits_as_dense_tiles(dt, n, monkeypatch):
+    # bitmap + stored values expanded by the producer warps (the shape of the reference's BTCF_MTX,
+    # src/utils/class.h:55-67) against the dense 512-byte tiles; explicit zeros, -0.0, a full tile
+    rows, cols, rp, ci, v = random_csr(331, 4000, 0.01, 33, dt, empty_rows=[(32, 80)], dense_rows=[5, 300])
+    v = v.copy()
+    v[::7] = 0
+    v[3::11] = -0.0
+    B = dense_b(cols, n, 6, dt)
+    monkeypatch.setenv("B200SPMM_TILES", "dense")
+    dense, info_d = run_host(rows, cols, rp, ci, v, B)
+    monkeypatch.setenv("B200SPMM_TILES", "bitmap")
+    packed, info_b = run_host(rows, cols, rp, ci, v, B)
+    assert info_d.bitmap_tiles == 0 and info_b.bitmap_tiles == 1
+    assert np.array_equal(dense.view(np.uint32), packed.view(np.uint32))
+    parity.check(packed, rows, rp, ci, v, B)
+
+
 def test_fp16_output():
     rows, cols, rp, ci, v = random_csr(130, 200, 0.1, 9)
     B = dense_b(cols, 128, 5)
