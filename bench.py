@@ -143,6 +143,9 @@ def time_cpu_oracle(rp, ci, v, B_host, steps, warmup, budget_s=12.0):
                       f"{t * 1e3:.1f} ms each"}, t
 
 
+from hopper_spmm_b200.sharded import ROW_CHARGE as sharded_charge
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -163,7 +166,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     dtype_name, n_feat, desc = synth.CONFIGS[args.workload]
     config = {"workload": args.workload, "description": desc, "scale_down": args.scale_down, "features": n_feat,
-              "row_window": 16, "c_dtype": "f32", "parallelism": f"row-window shards x{world} (balanced on nnz + 12 per row), B replicated",
+              "row_window": 16, "c_dtype": "f32", "parallelism": f"row-window shards x{world} (balanced on nnz + {sharded_charge} per row), B replicated",
               "l2": "operands larger than L2 (no flush needed)"}
 
     if args.impl == "reference":
@@ -246,6 +249,11 @@ def main():
     if world > 1:
         dist.all_reduce(t_all, op=dist.ReduceOp.MAX)
     ms_per_step = float(t_all.item()) / args.steps
+    rank_ms = [total_ms / args.steps]  # every rank's own time: shows how well the row cuts balance the GPUs
+    if world > 1:
+        gathered = [torch.zeros(1, dtype=torch.float64, device=dev) for _ in range(world)]
+        dist.all_gather(gathered, torch.tensor([total_ms / args.steps], dtype=torch.float64, device=dev))
+        rank_ms = [float(g.item()) for g in gathered]
     flops = 2.0 * total_nnz * n_feat
     value = flops / (ms_per_step * 1e-3) / 1e9
 
@@ -298,7 +306,7 @@ def main():
     if rank == 0:
         config.update(rows=int(cuts[-1]), cols=int(B.shape[0]), nnz=int(total_nnz), tiles_rank0=int(tiles_local),
                       fill_rank0=fill, n_ctas=info.n_ctas, feature_slab=info.feature_slab, stages=info.stages,
-                      convert_s_rank0=t_conv)
+                      convert_s_rank0=t_conv, rank_ms=[round(x, 4) for x in rank_ms])
         line = {"metric": "SpMM effective GFLOP/s (2*nnz*N)", "value": value, "unit": "GFLOP/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f16" if dtype_name == "f16" else "tf32",

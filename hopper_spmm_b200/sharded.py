@@ -13,7 +13,7 @@ import numpy as np
 from . import spmm as _spmm
 
 
-ROW_CHARGE = 12  # entries a row is charged on top of its own when the ranks' shares are cut
+ROW_CHARGE = 6  # entries a row is charged on top of its own when the ranks' shares are cut
 
 
 def my_rows(rows: int, row_ptr, world: int, rank: int, row_charge: int = ROW_CHARGE):

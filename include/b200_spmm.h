@@ -122,7 +122,7 @@ int b200spmm_shard_rows(uint64_t rows, const uint32_t *row_ptr, int row_window, 
 /*
  * Same cuts on the cost  nnz + row_charge * rows.  Every row costs a GPU time whatever it holds
  * (its share of a window's accumulator hand-over and of C's bytes), so on power-law matrices a
- * charge of about 12 entries per row evens out the ranks' times where pure nnz balance leaves the
+ * charge of about 6 entries per row evens out the ranks' times where pure nnz balance leaves the
  * rank with the long sparse tail slower.  row_charge = 0 is b200spmm_shard_rows.
  */
 int b200spmm_shard_rows_weighted(uint64_t rows, const uint32_t *row_ptr, int row_window, int parts,
