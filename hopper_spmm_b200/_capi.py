@@ -53,6 +53,29 @@ SIGNATURES = {
     "b200spmm_dbtcf_rowIdx": (vp, [vp]),
     "b200spmm_dbtcf_copy_to_host": (C.c_int, [vp, vp, vp, vp, vp]),
     "b200spmm_dbtcf_destroy": (None, [vp]),
+    "b200spmm_csr2btcf": (C.c_int, [u64, u64, u64, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(vp)]),
+    "b200spmm_btcfb_info": (C.c_int, [vp, C.POINTER(BtcfInfo), C.POINTER(C.c_int)]),
+    "b200spmm_btcfb_rowOffset": (vp, [vp]),
+    "b200spmm_btcfb_nnzOffset": (vp, [vp]),
+    "b200spmm_btcfb_tcA2B": (vp, [vp]),
+    "b200spmm_btcfb_tcBit": (vp, [vp]),
+    "b200spmm_btcfb_data": (vp, [vp]),
+    "b200spmm_btcfb_rowIdx": (vp, [vp]),
+    "b200spmm_btcfb_destroy": (None, [vp]),
+    "b200spmm_btcfb_expand": (C.c_int, [vp, C.POINTER(vp)]),
+    "b200spmm_btcf2gbtcf": (C.c_int, [vp, vp, u64, C.POINTER(vp)]),
+    "b200spmm_gbtcf_info": (C.c_int, [vp, C.POINTER(u64), C.POINTER(u32)]),
+    "b200spmm_gbtcf_groupOffset": (vp, [vp]),
+    "b200spmm_gbtcf_rowIdx": (vp, [vp]),
+    "b200spmm_gbtcf_atomic": (vp, [vp]),
+    "b200spmm_gbtcf_destroy": (None, [vp]),
+    "b200spmm_gbtcf_validate": (C.c_int, [vp, vp, u64, vp, vp, vp, u64, C.POINTER(u64)]),
+    "b200spmm_load_matrix": (C.c_int, [C.c_char_p, C.c_int, C.POINTER(vp)]),
+    "b200spmm_csr_info": (C.c_int, [vp, C.POINTER(u64), C.POINTER(u64), C.POINTER(u64), C.POINTER(u64)]),
+    "b200spmm_csr_row_ptr": (vp, [vp]),
+    "b200spmm_csr_col_idx": (vp, [vp]),
+    "b200spmm_csr_values": (vp, [vp]),
+    "b200spmm_csr_destroy": (None, [vp]),
     "b200spmm_shard_rows": (C.c_int, [u64, vp, C.c_int, C.c_int, vp]),
     "b200spmm_shard_rows_weighted": (C.c_int, [u64, vp, C.c_int, C.c_int, u64, vp]),
     "b200spmm_build_schedule": (C.c_int, [vp, u64, C.c_int, vp]),

@@ -7,7 +7,8 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200spmm.so")
-SOURCES = ["capi.cu", "kat.cu", "convert_gpu.cu", "compress_gpu.cu", "format.cpp"]
+CLI = os.path.join(HERE, "spmm_test")  # spmm_test <matrix.mtx> <feature_dim> [fp16|tf32]
+SOURCES = ["capi.cu", "kat.cu", "convert_gpu.cu", "compress_gpu.cu", "formats_ext.cu", "capi_formats.cpp", "format.cpp"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",  # -arch=sm_100a would add a generic PTX pass that rejects tcgen05
     "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared",
@@ -29,6 +30,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return LIB
     cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + SOURCES
     subprocess.run(cmd, cwd=CSRC, check=True)
+    # the command-line run of the reference's main, linked against the library next to it
+    cli = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17", "-o", CLI, "spmm_test.cu",
+           "-L" + HERE, "-lb200spmm", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+    subprocess.run(cli, cwd=CSRC, check=True)
     return LIB
 
 

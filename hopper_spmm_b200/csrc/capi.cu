@@ -13,6 +13,7 @@
 #include "common.hpp"
 #include "compress_gpu.hpp"
 #include "format.hpp"
+#include "handles.hpp"
 #include "spmm_kernel.cuh"
 #include "tensormap.hpp"
 
@@ -31,9 +32,6 @@ void record_cuda_error(cudaError_t e, const char *what) {
 
 using namespace b200spmm;
 
-struct b200spmm_btcf {
-    Btcf f;
-};
 
 struct b200spmm_plan {
     b200spmm_btcf_info_t info{};

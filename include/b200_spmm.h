@@ -153,6 +153,78 @@ int b200spmm_build_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows,
 int b200spmm_build_tile_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_parts, uint32_t *cta_tile,
                                  uint32_t *cta_wfirst, uint32_t *cta_wlast, uint32_t *slot_window);
 
+/* ------------------------------------------------------------------ the reference's other formats */
+
+/*
+ * Bitmap-compressed condensed format: BTCF_MTX (src/utils/class.h:55-67) built by CSR2BTCF
+ * (src/utils/convert.h:22-139).  Windows, column lists and tile order are those of the
+ * uncompressed format; a tile keeps one bit per slot (bit lr*col_window + lc, row-major) in
+ * row_window*col_window/64 consecutive 64-bit words, its stored values in bit order, and
+ * nnzOffset[tiles+1] gives the first stored value of each tile.  The reference's fp16 build
+ * indexes the second bitmap word of a tile by tile number (convert.h:98-100), so its words
+ * overlap; here word j of tile t is tcBit[t*words + j].  With 8-row windows every other array
+ * equals the reference's bit for bit, and tcBit too in the tf32 build.  Rows must hold strictly
+ * ascending columns (B200SPMM_ERR_BAD_CSR otherwise).  col_window 0 selects 16 (fp16) / 8 (tf32).
+ */
+typedef struct b200spmm_btcfb b200spmm_btcfb_t;
+int b200spmm_csr2btcf(uint64_t rows, uint64_t cols, uint64_t nnz, const uint32_t *row_ptr, const uint32_t *col_idx,
+                      const void *values, int dtype, int row_window, int col_window, int n_threads,
+                      b200spmm_btcfb_t **out);
+int b200spmm_btcfb_info(const b200spmm_btcfb_t *f, b200spmm_btcf_info_t *info, int *bitmap_words);
+const uint32_t *b200spmm_btcfb_rowOffset(const b200spmm_btcfb_t *f); /* [eff+1] */
+const uint32_t *b200spmm_btcfb_nnzOffset(const b200spmm_btcfb_t *f); /* [tiles+1] */
+const uint32_t *b200spmm_btcfb_tcA2B(const b200spmm_btcfb_t *f);     /* [tiles*col_window] */
+const uint64_t *b200spmm_btcfb_tcBit(const b200spmm_btcfb_t *f);     /* [tiles*bitmap_words] */
+const void *b200spmm_btcfb_data(const b200spmm_btcfb_t *f);          /* [nnz] stored values */
+const uint32_t *b200spmm_btcfb_rowIdx(const b200spmm_btcfb_t *f);    /* [eff] */
+void b200spmm_btcfb_destroy(b200spmm_btcfb_t *f);
+/* The same matrix in the uncompressed format (dense tiles), e.g. to build an SpMM plan from it. */
+int b200spmm_btcfb_expand(const b200spmm_btcfb_t *f, b200spmm_btcf_t **out);
+
+/*
+ * Group-split work list: GBTCF_MTX (src/utils/class.h:93-108) built by BTCF2GBTCF
+ * (src/utils/convert.h:232-276).  The group length is max(floor(mean tiles per window), 32); a
+ * window of T tiles becomes ceil(T/length) groups of ceil(T/groups) tiles; groupOffset[groups+1]
+ * holds each group's first tile, rowIdx[groups] the first row of its window, atomic[groups] is 1
+ * for the groups of a window that has several (their results must be added).  The tile arrays
+ * (nnzOffset, tcA2B, tcBit, data) are those of the format the offsets came from, unchanged.
+ */
+typedef struct b200spmm_gbtcf b200spmm_gbtcf_t;
+int b200spmm_btcf2gbtcf(const uint32_t *rowOffset, const uint32_t *rowIdx, uint64_t eff_row_windows, b200spmm_gbtcf_t **out);
+int b200spmm_gbtcf_info(const b200spmm_gbtcf_t *g, uint64_t *total_groups, uint32_t *group_len);
+const uint32_t *b200spmm_gbtcf_groupOffset(const b200spmm_gbtcf_t *g);
+const uint32_t *b200spmm_gbtcf_rowIdx(const b200spmm_gbtcf_t *g);
+const uint8_t *b200spmm_gbtcf_atomic(const b200spmm_gbtcf_t *g);
+void b200spmm_gbtcf_destroy(b200spmm_gbtcf_t *g);
+/*
+ * Checks a group list against the windows it was cut from: groups tile every window in order,
+ * carry its first row, none is empty, and atomic marks exactly the windows with several groups.
+ * Stands in for validateBTCF2GBTCFConversion (src/utils/convert.h:283-402), which assumes a group
+ * length of 4 and reads past empty windows.  first_bad_group receives 0, or the 1-based number of
+ * the first offending group; the return value is B200SPMM_ERR_BAD_CSR in that case.
+ */
+int b200spmm_gbtcf_validate(const uint32_t *rowOffset, const uint32_t *rowIdx, uint64_t eff_row_windows,
+                            const uint32_t *groupOffset, const uint32_t *group_rowIdx, const uint8_t *atomic,
+                            uint64_t total_groups, uint64_t *first_bad_group);
+
+/*
+ * MatrixMarket coordinate text -> CSR: load_matrix (src/utils/load.h:152-322).  Leading '%' lines
+ * are skipped, the size line is "rows cols entries", every later line that reads as
+ * "row col value" (1-based) is an entry and other lines are ignored, reading stops after the
+ * promised number of entries and a short file simply has fewer.  The banner is not interpreted
+ * (no mirroring of symmetric files; pattern files give no entries).  Entries are ordered by
+ * (row, column), repeated pairs in file order.  Values are rounded to fp16 (round to nearest
+ * even, load.h:225) or kept as fp32.  Indices outside the matrix give B200SPMM_ERR_BAD_CSR, a
+ * file that cannot be opened B200SPMM_ERR_INVALID_ARG.
+ */
+typedef struct b200spmm_csr b200spmm_csr_t;
+int b200spmm_load_matrix(const char *path, int dtype, b200spmm_csr_t **out);
+int b200spmm_csr_info(const b200spmm_csr_t *m, uint64_t *rows, uint64_t *cols, uint64_t *nnz, uint64_t *declared_nnz);
+const uint32_t *b200spmm_csr_row_ptr(const b200spmm_csr_t *m);
+const uint32_t *b200spmm_csr_col_idx(const b200spmm_csr_t *m);
+const void *b200spmm_csr_values(const b200spmm_csr_t *m);
+void b200spmm_csr_destroy(b200spmm_csr_t *m); /* free_csr_matrix, src/utils/load.h:338 */
+
 /* ------------------------------------------------------------------ device plan */
 
 /* Device-resident format + persistent schedule. Replaces the cudaMalloc/cudaMemcpy block and

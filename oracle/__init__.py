@@ -209,3 +209,128 @@ def ref_convert(flavour: str, rows, cols, row_ptr, col_idx, values) -> Btcf:
     out = Btcf(rows, cols, len(col_idx), rw, cw, rowOffset, tcA2B, data, rowIdx)
     assert out.total_tiles == tiles
     return out
+
+
+# ------------------------------------------------------------------ bitmap and group formats
+
+
+class BtcfBitmap:
+    """Field set of the reference's BTCF_MTX (src/utils/class.h:55-67)."""
+
+    def __init__(self, row_window, col_window, rowOffset, nnzOffset, tcA2B, tcBit, data, rowIdx):
+        self.row_window, self.col_window = int(row_window), int(col_window)
+        self.rowOffset, self.nnzOffset, self.tcA2B, self.tcBit = rowOffset, nnzOffset, tcA2B, tcBit
+        self.data, self.rowIdx = data, rowIdx
+        self.eff_row_windows = len(rowIdx)
+        self.total_tiles = int(rowOffset[-1]) if len(rowOffset) else 0
+
+
+def csr2btcf_bitmap(rows, row_ptr, col_idx, values, row_window, col_window, legacy_word_index=False) -> BtcfBitmap:
+    """Restated CSR2BTCF (convert.h:22-139); legacy_word_index repeats the reference's fp16 bitmap
+    word addressing (convert.h:98-102) for the comparison with the reference itself."""
+    row_ptr, col_idx = _c(row_ptr, np.uint32), _c(col_idx, np.uint32)
+    values = np.ascontiguousarray(values)
+    eff, tiles = _i64(), _i64()
+    assert lib().oracle_btcf_count(rows, _ptr(row_ptr), _ptr(col_idx), row_window, col_window, C.byref(eff),
+                                   C.byref(tiles)) == 0
+    eff, tiles, words = eff.value, tiles.value, row_window * col_window // 64
+    rowOffset, nnzOffset = np.zeros(eff + 1, np.uint32), np.zeros(tiles + 1, np.uint32)
+    tcA2B, tcBit = np.zeros(tiles * col_window, np.uint32), np.zeros(tiles * words, np.uint64)
+    data, rowIdx = np.zeros(len(col_idx), values.dtype), np.zeros(eff, np.uint32)
+    fn = lib().oracle_csr2btcf_bitmap
+    fn.argtypes = [C.c_int64, _p, _p, _p, C.c_int, C.c_int, C.c_int, C.c_int, _p, _p, _p, _p, _p, _p]
+    assert fn(rows, _ptr(row_ptr), _ptr(col_idx), _ptr(values), values.dtype.itemsize, row_window, col_window,
+              int(bool(legacy_word_index)), _ptr(rowOffset), _ptr(nnzOffset), _ptr(tcA2B), _ptr(tcBit), _ptr(data),
+              _ptr(rowIdx)) == 0
+    return BtcfBitmap(row_window, col_window, rowOffset, nnzOffset, tcA2B, tcBit, data, rowIdx)
+
+
+def btcf2gbtcf(rowOffset, rowIdx):
+    """Restated BTCF2GBTCF (convert.h:232-276): (groupOffset, rowIdx, atomic, group_len)."""
+    rowOffset, rowIdx = _c(rowOffset, np.uint32), _c(rowIdx, np.uint32)
+    fn = lib().oracle_btcf2gbtcf
+    fn.argtypes = [_p, _p, C.c_int64, _p, _p, _p, C.POINTER(C.c_int64), C.POINTER(C.c_uint32)]
+    groups, length = C.c_int64(), C.c_uint32()
+    assert fn(_ptr(rowOffset), _ptr(rowIdx), len(rowIdx), None, None, None, C.byref(groups), C.byref(length)) == 0
+    go, gr, at = np.zeros(groups.value + 1, np.uint32), np.zeros(groups.value, np.uint32), np.zeros(groups.value, np.uint8)
+    assert fn(_ptr(rowOffset), _ptr(rowIdx), len(rowIdx), _ptr(go), _ptr(gr), _ptr(at), C.byref(groups),
+              C.byref(length)) == 0
+    return go, gr, at, int(length.value)
+
+
+_MTX_ENTRY = None
+
+
+def load_matrix_text(text: str, dtype=np.float16):
+    """Restated load_matrix (load.h:152-322) over the file's text: (rows, cols, row_ptr, col_idx,
+    values).  Pure Python, for small files."""
+    import re
+    global _MTX_ENTRY
+    if _MTX_ENTRY is None:
+        num = r"[+-]?(?:\d+\.?\d*(?:[eE][+-]?\d+)?|\.\d+(?:[eE][+-]?\d+)?|inf(?:inity)?|nan)"
+        _MTX_ENTRY = re.compile(r"^\s*\+?(\d+)\s+\+?(\d+)\s+(" + num + ")", re.IGNORECASE)
+    lines = text.split("\n")
+    k = 0
+    while k < len(lines) and lines[k].startswith("%"):  # load.h:189-193
+        k += 1
+    rows, cols, declared = (int(x) for x in lines[k].split()[:3])  # load.h:196
+    entries = []
+    for line in lines[k + 1:]:
+        if len(entries) >= declared:  # load.h:214
+            break
+        m = _MTX_ENTRY.match(line)
+        if m:  # other lines are ignored (load.h:218)
+            entries.append((int(m.group(1)) - 1, int(m.group(2)) - 1, float(m.group(3))))
+    order = sorted(range(len(entries)), key=lambda i: (entries[i][0], entries[i][1]))  # load.h:256
+    row_ptr = np.zeros(rows + 1, np.uint32)
+    for r, _, _ in entries:
+        row_ptr[r + 1] += 1
+    row_ptr = np.cumsum(row_ptr, dtype=np.uint64).astype(np.uint32)
+    col_idx = np.array([entries[i][1] for i in order], np.uint32)
+    values = np.array([entries[i][2] for i in order], np.float32).astype(dtype)  # fp16: round to nearest even (load.h:225)
+    return rows, cols, row_ptr, col_idx, values
+
+
+def _ref_lib(flavour: str):
+    return C.CDLL(os.path.join(_HERE, "_ref", f"libref_{flavour}.so"))
+
+
+def ref_convert_bitmap(flavour: str, rows, cols, row_ptr, col_idx, values):
+    """The reference's own CSR2BTCF followed by its BTCF2GBTCF: (BtcfBitmap, (groupOffset, rowIdx, atomic))."""
+    r = _ref_lib(flavour)
+    r.ref_convert_bitmap.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, _p, _p, _p, _p]
+    r.ref_fetch_bitmap.argtypes = [_p] * 6
+    r.ref_group.argtypes = [_p]
+    r.ref_fetch_groups.argtypes = [_p] * 3
+    row_ptr, col_idx = _c(row_ptr, np.uint32), _c(col_idx, np.uint32)
+    dt = np.float16 if flavour == "fp16" else np.float32
+    values = _c(values, dt)
+    assert r.ref_map_word_size() == 8
+    sizes = np.zeros(5, np.uint64)
+    r.ref_convert_bitmap(rows, cols, len(col_idx), _ptr(row_ptr), _ptr(col_idx), _ptr(values), _ptr(sizes))
+    eff, n_off, n_a2b, n_bit, n_data = (int(x) for x in sizes)
+    rowOffset, nnzOffset = np.zeros(eff + 1, np.uint32), np.zeros(n_off, np.uint32)
+    tcA2B, tcBit = np.zeros(n_a2b, np.uint32), np.zeros(n_bit, np.uint64)
+    data, rowIdx = np.zeros(n_data, dt), np.zeros(eff, np.uint32)
+    assert r.ref_fetch_bitmap(_ptr(rowOffset), _ptr(nnzOffset), _ptr(tcA2B), _ptr(tcBit), _ptr(data), _ptr(rowIdx)) == 0
+    groups = np.zeros(1, np.uint64)
+    assert r.ref_group(_ptr(groups)) == 0
+    g = int(groups[0])
+    go, gr, at = np.zeros(g + 1, np.uint32), np.zeros(g, np.uint32), np.zeros(g, np.uint8)
+    assert r.ref_fetch_groups(_ptr(go), _ptr(gr), _ptr(at)) == 0
+    return (BtcfBitmap(r.ref_row_window(), r.ref_col_window(), rowOffset, nnzOffset, tcA2B, tcBit, data, rowIdx),
+            (go, gr, at))
+
+
+def ref_load_matrix(flavour: str, path: str):
+    """The reference's own load_matrix: (rows, cols, row_ptr, col_idx, values)."""
+    r = _ref_lib(flavour)
+    r.ref_load.argtypes = [C.c_char_p, _p]
+    r.ref_fetch_loaded.argtypes = [_p] * 3
+    dims = np.zeros(3, np.uint32)
+    assert r.ref_load(path.encode(), _ptr(dims)) == 0
+    rows, cols, nnz = (int(x) for x in dims)
+    dt = np.float16 if flavour == "fp16" else np.float32
+    row_ptr, col_idx, values = np.zeros(rows + 1, np.uint32), np.zeros(nnz, np.uint32), np.zeros(nnz, dt)
+    assert r.ref_fetch_loaded(_ptr(row_ptr), _ptr(col_idx), _ptr(values)) == 0
+    return rows, cols, row_ptr, col_idx, values

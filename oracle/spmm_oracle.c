@@ -222,6 +222,126 @@ int oracle_csr2btcf_nobitmap(int64_t rows, const uint32_t *row_ptr, const uint32
     return 0;
 }
 
+/*
+ * Bitmap-compressed format, restating CSR2BTCF (convert.h:22-139).  Caller-allocated arrays sized
+ * from oracle_btcf_count: rowOffset[eff+1], nnzOffset[tiles+1], tcA2B[tiles*CW],
+ * tcBit[tiles*words] with words = RW*CW/64, data[nnz*elt_size bytes], rowIdx[eff].
+ * Per entry: nnzOffset[tile]++ (made a running sum with a leading zero at the end, :136-137),
+ * bit (r % RW)*CW + (slot % CW) of the tile set (:88-96), value appended to the tile's list in
+ * CSR order (:115), lists concatenated tile after tile (:127-130).
+ * legacy_word_index != 0 repeats the reference's fp16 indexing, which addresses the bitmap word of
+ * bit b of tile t as tcBit[t + b/64] (:98-102) although it reserves two words per tile (:62-66):
+ * that is what the reference binary produces, kept here only to pin this restatement against it.
+ * Otherwise word j of tile t is tcBit[t*words + j].
+ */
+int oracle_csr2btcf_bitmap(int64_t rows, const uint32_t *row_ptr, const uint32_t *col_idx, const void *values,
+                           int elt_size, int row_window, int col_window, int legacy_word_index,
+                           uint32_t *rowOffset, uint32_t *nnzOffset, uint32_t *tcA2B, uint64_t *tcBit,
+                           void *data, uint32_t *rowIdx) {
+    const int words = row_window * col_window / 64;
+    int64_t eff = 0, tiles = 0, cap = 0, total_tiles = 0, placed = 0;
+    uint32_t *uniq = NULL;
+    int64_t *cursor = NULL, cursor_cap = 0;
+    /* total tiles first: nnzOffset and tcBit are cleared up front like the reference's resize(…, 0) */
+    {
+        int64_t e = 0;
+        if (oracle_btcf_count(rows, row_ptr, col_idx, row_window, col_window, &e, &total_tiles)) return -1;
+    }
+    memset(nnzOffset, 0, (size_t)(total_tiles + 1) * sizeof(uint32_t));
+    memset(tcBit, 0, (size_t)(total_tiles * words) * sizeof(uint64_t));
+    rowOffset[0] = 0;
+    for (int64_t first = 0; first < rows; first += row_window) {
+        int64_t last = first + row_window < rows ? first + row_window : rows;
+        int64_t lo = row_ptr[first], hi = row_ptr[last];
+        if (hi == lo) continue;
+        if (hi - lo > cap) {
+            cap = (hi - lo) * 2;
+            free(uniq);
+            uniq = (uint32_t *)malloc((size_t)cap * sizeof(uint32_t));
+            if (!uniq) return -1;
+        }
+        int64_t u = window_unique_cols(col_idx, lo, hi, uniq);
+        int64_t wtiles = (u + col_window - 1) / col_window;
+        uint32_t *list = tcA2B + tiles * col_window;
+        memcpy(list, uniq, (size_t)u * sizeof(uint32_t));
+        for (int64_t i = u; i < wtiles * col_window; ++i) list[i] = ORACLE_IDX_MAX;
+        rowOffset[eff + 1] = (uint32_t)(tiles + wtiles);
+        rowIdx[eff] = (uint32_t)first;
+        if (wtiles > cursor_cap) {
+            cursor_cap = wtiles * 2;
+            free(cursor);
+            cursor = (int64_t *)malloc((size_t)cursor_cap * sizeof(int64_t));
+            if (!cursor) return -1;
+        }
+        /* count per tile (kept in nnzOffset[tile+1] until the final running sum), set bits */
+        for (int64_t r = first; r < last; ++r) {
+            for (int64_t p = row_ptr[r]; p < row_ptr[r + 1]; ++p) {
+                uint32_t key = col_idx[p];
+                const uint32_t *hit = (const uint32_t *)bsearch(&key, uniq, (size_t)u, sizeof(uint32_t), cmp_u32);
+                int64_t slot = hit - uniq, t = tiles + slot / col_window;
+                int64_t bit = (r % row_window) * col_window + slot % col_window;
+                nnzOffset[t + 1]++;
+                if (legacy_word_index) {
+                    if (t + bit / 64 < total_tiles * words) tcBit[t + bit / 64] |= 1ull << (bit % 64);
+                } else {
+                    tcBit[t * words + bit / 64] |= 1ull << (bit % 64);
+                }
+            }
+        }
+        /* values: tile after tile, inside a tile in CSR order */
+        int64_t run = placed;
+        for (int64_t t = 0; t < wtiles; ++t) {
+            cursor[t] = run;
+            run += nnzOffset[tiles + t + 1];
+        }
+        for (int64_t r = first; r < last; ++r) {
+            for (int64_t p = row_ptr[r]; p < row_ptr[r + 1]; ++p) {
+                uint32_t key = col_idx[p];
+                const uint32_t *hit = (const uint32_t *)bsearch(&key, uniq, (size_t)u, sizeof(uint32_t), cmp_u32);
+                int64_t t = (hit - uniq) / col_window;
+                memcpy((char *)data + cursor[t]++ * elt_size, (const char *)values + p * elt_size, (size_t)elt_size);
+            }
+        }
+        placed = run;
+        tiles += wtiles;
+        ++eff;
+    }
+    for (int64_t t = 0; t < total_tiles; ++t) nnzOffset[t + 1] += nnzOffset[t];
+    free(uniq);
+    free(cursor);
+    return 0;
+}
+
+/*
+ * Group split, restating BTCF2GBTCF (convert.h:232-276).  With groupOffset == NULL only counts
+ * (total_groups, group_len).  group_len = max((uint32)mean tiles per window, 32) (:244-245); a
+ * window of T tiles gets ceil(T/len) groups starting at rowOffset + ceil(T/groups)*j (:250-253),
+ * each carrying the window's first row and atomic = (groups != 1) (:255-259); one closing offset
+ * (:262).
+ */
+int oracle_btcf2gbtcf(const uint32_t *rowOffset, const uint32_t *rowIdx, int64_t eff, uint32_t *groupOffset,
+                      uint32_t *group_rowIdx, uint8_t *atomic, int64_t *total_groups, uint32_t *group_len) {
+    double sum = 0.0;
+    for (int64_t i = 0; i < eff; ++i) sum += (double)(rowOffset[i + 1] - rowOffset[i]);
+    uint32_t len = eff ? (uint32_t)(sum / (double)eff) : 0;
+    if (len < 32) len = 32;
+    int64_t g = 0;
+    for (int64_t i = 0; i < eff; ++i) {
+        uint32_t T = rowOffset[i + 1] - rowOffset[i];
+        uint32_t n = (T + len - 1) / len;
+        for (uint32_t j = 0; j < n; ++j, ++g) {
+            if (!groupOffset) continue;
+            groupOffset[g] = rowOffset[i] + (T + n - 1) / n * j;
+            group_rowIdx[g] = rowIdx[i];
+            atomic[g] = n == 1 ? 0 : 1;
+        }
+    }
+    if (groupOffset) groupOffset[g] = eff ? rowOffset[eff] : 0;
+    *total_groups = g;
+    *group_len = len;
+    return 0;
+}
+
 /* ---------------------------------------------------------------- SpMM, CSR form (O1) */
 
 /* C[r,:] = sum_p A[p] * B[col[p],:], fp16 inputs widened to fp32, fp32 accumulate, CSR order. */

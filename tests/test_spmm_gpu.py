@@ -192,3 +192,33 @@ def test_rmat_rows_sum_to_one_at_scale():
     err = (Cd - want).abs().max().item()
     assert err < 2e-3, err  # 1/deg is rounded to fp16: relative 2^-11 per term
     plan.close()
+
+
+def test_bitmap_format_feeds_the_spmm_after_expansion():
+    # CSR2BTCF at the kernels' 16-row windows -> dense tiles -> plan -> product
+    rows, cols, rp, ci, v = random_csr(300, 900, 0.02, 41, empty_rows=[(16, 48)], dense_rows=[100])
+    B = dense_b(cols, 128, 7)
+    f = hs.CSR2BTCF(hs.CSR_MTX(rows, cols, rp, ci, v), row_window=16)
+    plan = hs.SpmmPlan(f.expand())
+    try:
+        parity.check(plan.spmm_host(B), rows, rp, ci, v, B)
+    finally:
+        plan.close()
+
+
+@pytest.mark.parametrize("kind", ["fp16", "tf32"])
+def test_command_line_run_on_a_matrix_market_file(kind, tmp_path):
+    # spmm_test <file> <N>: the reference's main (src/fp16.cu:283-319) with a result check added
+    import os
+    import subprocess
+    rows, cols, rp, ci, v = random_csr(500, 400, 0.03, 42, np.float32)
+    path = tmp_path / "m.mtx"
+    with open(path, "w") as fh:
+        fh.write("%%MatrixMarket matrix coordinate real general\n%d %d %d\n" % (rows, cols, len(ci)))
+        for r in range(rows):
+            for p in range(rp[r], rp[r + 1]):
+                fh.write("%d %d %.6f\n" % (r + 1, ci[p] + 1, v[p]))
+    exe = os.path.join(os.path.dirname(hs.__file__), "spmm_test")
+    out = subprocess.run([exe, str(path), "64", kind], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert "nonzeros: %d" % len(ci) in out.stdout and "SPMM mean time" in out.stdout and "(ok," in out.stdout
