@@ -262,15 +262,18 @@ def main():
     if not args.no_e2e:
         hB = torch.empty(B.shape, dtype=B.dtype, pin_memory=True)
         hB.copy_(B)
-        hC = torch.empty(C_dev.shape, dtype=C_dev.dtype, pin_memory=True)
+        # the reference's operator keeps C in the matrix's element type (DENSE_MTX.values is MAT_VAL_TYPE,
+        # src/utils/class.h:44-48: fp16 in the fp16 build): the host-buffer call is made the same way
+        c_half = dtype_name == "f16"
+        hC = torch.empty(C_dev.shape, dtype=torch.float16 if c_half else torch.float32, pin_memory=True)
         torch.cuda.synchronize()
         hBn, hCn = hB.numpy(), hC.numpy()
-        plan.spmm_host(hBn, hCn)  # warm-up: allocates the plan's device buffers
+        plan.spmm_host(hBn, hCn, c_half=c_half)  # warm-up: allocates the plan's device buffers
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.steps):
-            plan.spmm_host(hBn, hCn)
+            plan.spmm_host(hBn, hCn, c_half=c_half)
         e1.record()
         barrier()
         t_e = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
@@ -279,7 +282,8 @@ def main():
         e_ms = float(t_e.item()) / args.steps
         e2e = {"value": flops / (e_ms * 1e-3) / 1e9, "unit": "GFLOP/s", "ms_per_step": e_ms,
                "h2d_bytes_per_step": int(hB.numel() * hB.element_size()),
-               "d2h_bytes_per_step": int(hC.numel() * hC.element_size())}
+               "d2h_bytes_per_step": int(hC.numel() * hC.element_size()),
+               "c_dtype": "f16" if c_half else "f32", "call": "b200spmm_spmm_host (fp16_spmm / tf32_spmm with host B and C)"}
         assert bool(torch.isfinite(hC[:: max(1, hC.shape[0] // 4096)]).all())
 
     # ---- roofline of the SpMM kernel on this rank's launch

@@ -148,7 +148,7 @@ int encode_tile_map(b200spmm_plan *p) {
     if (!info.total_tiles) return B200SPMM_OK;
     const bool f16 = info.dtype == B200SPMM_F16;
     if (!encode_2d(&p->tmap_a, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p->d_data,
-                   f16 ? 16 : 8, info.total_tiles * kRowWindow, 32, f16 ? 16 : 8, kRowWindow * kProducerWarps,
+                   f16 ? 16 : 8, info.total_tiles * kRowWindow, 32, f16 ? 16 : 8, kRowWindow * kTilesPerStage,
                    CU_TENSOR_MAP_SWIZZLE_32B)) {
         g_last_cuda_error = "cuTensorMapEncodeTiled failed for the tile array";
         return B200SPMM_ERR_CUDA;

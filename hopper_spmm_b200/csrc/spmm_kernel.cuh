@@ -64,7 +64,9 @@
 namespace b200spmm {
 
 constexpr int kRowWindow = 16;       // rows per window the kernels consume
-constexpr int kProducerWarps = 4;    // warps per producer group = tiles per ring stage
+constexpr int kProducerWarps = 4;    // warps per producer group
+constexpr int kTilesPerWarp = 2;     // tiles a producer warp brings per iteration (16 lanes each)
+constexpr int kTilesPerStage = kProducerWarps * kTilesPerWarp;  // a ring stage: eight consecutive tiles
 constexpr int kEpilogueWarps = 8;    // two sets of four: set e drains accumulator buffer e
 constexpr int kMmaWarp = 8;
 constexpr int kFirstProducerWarp = 9;
@@ -120,12 +122,12 @@ struct SpmmCfg {
     // thread, not the tensor core, sets the pace.  Up to 128 features a CTA is small enough for
     // two to share an SM, which gives the SM two issuing threads and two rings to keep full.
     static constexpr int kCtasPerSm = kNs <= 128 ? 2 : 1;
-    static constexpr int kProducerGroups = kCtasPerSm == 2 ? 2 : 3;
-    static constexpr int kThreads = 32 * (kFirstProducerWarp + kProducerWarps * kProducerGroups);  // 544 or 672
+    static constexpr int kProducerGroups = 2;
+    static constexpr int kThreads = 32 * (kFirstProducerWarp + kProducerWarps * kProducerGroups);  // 544
     static constexpr int kCW = kTf32 ? 8 : 16;           // condensed columns per tile
     static constexpr int kEsz = kTf32 ? 4 : 2;           // bytes per element of A and B
     static constexpr int kGatherBytes = 32 * kNs;        // CW rows x kNs features, one tile
-    static constexpr int kTilesPerStage = kProducerWarps;
+    static constexpr int kTilesPerStage = b200spmm::kTilesPerStage;
     static constexpr int kStageBytes = kTilesPerStage * (kGatherBytes + kATileBytes);
     static constexpr int kFullChunks = kNs / 128;        // M = 128 MMAs per tile
     static constexpr bool kHalfChunk = (kNs % 128) != 0; // plus one M = 64 MMA
@@ -134,10 +136,10 @@ struct SpmmCfg {
     // reports the oldest as landed: 4 * (kLag + 1) tiles are in flight per SM (90-100 KB); the
     // rest of the ring absorbs the round trip through the MMA issuer.  One barrier pair serves
     // four tiles, which keeps the per-tile cost of waits, fences and commits low.
-    static constexpr int kStages = kNs == 64 ? 10 : kNs == 128 ? (kBitmap ? 5 : 6) : kNs == 192 ? 8 : 6;
+    static constexpr int kStages = kNs == 64 ? 5 : kNs == 128 ? (kBitmap ? 2 : 3) : kNs == 192 ? 4 : 3;
     // cp.async variant only: groups a warp keeps in flight before it reports the oldest as landed
     static constexpr int kLag = kStages / kProducerGroups >= 3 ? kStages / kProducerGroups - 2 : 0;
-    static_assert(kStages > kProducerGroups * (kLag + 1), "ring too shallow");
+    static_assert(kTma ? kStages >= kProducerGroups : kStages > kProducerGroups * (kLag + 1), "ring too shallow");
     static constexpr int kChunksPerRow = kNs * kEsz / 16;           // 16-byte pieces per gathered row
     static constexpr int kCopiesPerLane = kCW * kChunksPerRow / 32;  // == kNs / 16
     // TMA gather: a box is 128 bytes of a row (64 fp16 / 32 tf32 features); one instruction moves
@@ -150,14 +152,16 @@ struct SpmmCfg {
     // Each producer warp keeps the column lists of its next kIdxAhead tiles in a private ring of
     // kIdxSlots entries, fetched in the same cp.async groups as the rows of the current tile.
     // With compressed tiles a slot also holds the tile's bitmap and its two value offsets.
-    static constexpr int kIdxSlots = kBitmap ? 8 : (kCtasPerSm == 2 ? 7 : 16);
-    static constexpr int kIdxAhead = kBitmap ? 7 : (kCtasPerSm == 2 ? 5 : 12);
+    static constexpr int kIdxSlots = kBitmap ? 4 : (kCtasPerSm == 2 ? 3 : 8);
+    static constexpr int kIdxAhead = kIdxSlots - 1;
     // Compressed tiles: the slot of the tile after the current one has to be in shared memory
     // when the current one is expanded, because the loads of its stored values start right then.
     static constexpr int kSlotLead = kBitmap ? 2 : 1;
     static_assert((kTma || kIdxAhead > kLag) && kIdxAhead < kIdxSlots, "column lists must land before they are needed");
     static constexpr int kBitWords = kRowWindow * kCW / 64;  // 64-bit bitmap words per tile
-    static constexpr int kSlotBytes = kBitmap ? (kCW * 4 + kBitWords * 8 + 8 + 15) / 16 * 16 : kCW * 4;
+    static constexpr int kSlotBytes =
+        kBitmap ? (kTilesPerWarp * (kCW * 4 + kBitWords * 8) + (kTilesPerWarp + 1) * 4 + 15) / 16 * 16 : kTilesPerWarp * kCW * 4;
+    static_assert(kTilesPerWarp == 2 && kGatherOps <= 16, "a producer warp splits into two halves of 16 lanes, one per tile");
     static constexpr int kIdxBytes = kProducerWarps * kProducerGroups * kIdxSlots * kSlotBytes;
     static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
     static constexpr int kWinBytes = kWinSlots * 4;
@@ -401,10 +405,12 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // =========================================================== producer warps
         const uint32_t pid = (uint32_t)(warp - kFirstProducerWarp);
         const uint32_t grp = pid / kProducerWarps;  // fills stages grp, grp + 3, grp + 6, ...
-        const uint32_t pw = pid % kProducerWarps;   // with tile slot pw of each of them
-        // This warp's ring of column lists: slot (iteration % kIdxSlots) holds CW indices.
-        // With compressed tiles the slot continues with the tile's bitmap and its two value offsets.
-        constexpr uint32_t kSlotWords = Cfg::kSlotBytes / 4, kBitOff = Cfg::kCW * 4, kNnzOff = kBitOff + Cfg::kBitWords * 8;
+        const uint32_t pw = pid % kProducerWarps;   // with tile slots 2*pw and 2*pw + 1 of each of them
+        constexpr uint32_t kTpw = kTilesPerWarp;
+        const uint32_t half = (uint32_t)lane >> 4, hl = (uint32_t)lane & 15u;  // TMA gathers: lanes 16*j.. serve tile j of the warp
+        // This warp's ring of column lists: slot (iteration % kIdxSlots) holds the CW indices of its
+        // two tiles.  With compressed tiles the slot continues with the two bitmaps and three value offsets.
+        constexpr uint32_t kSlotWords = Cfg::kSlotBytes / 4, kBitOff = kTpw * Cfg::kCW * 4, kNnzOff = kBitOff + kTpw * Cfg::kBitWords * 8;
         uint32_t *my_idx = idx_ring + pid * Cfg::kIdxSlots * kSlotWords;
         const uint32_t my_idx_addr = idx_ring_addr + pid * Cfg::kIdxSlots * Cfg::kSlotBytes;
         constexpr int kIdxLanes = Cfg::kCW * 4 / 16;  // lanes that copy one column list (16 bytes each)
@@ -415,7 +421,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // 128-byte column block h = o / kRowQuads.
         uint32_t op_dst = 0, op_x = 0, op_quad = 0;
         if (kTma) {
-            const uint32_t g = (uint32_t)lane % Cfg::kRowQuads, h = (uint32_t)lane / Cfg::kRowQuads;
+            const uint32_t g = hl % Cfg::kRowQuads, h = hl / Cfg::kRowQuads;
             op_quad = g;
             op_x = h * Cfg::kBoxFeatures;
             // fp16: block (h, rows 8j..8j+7) is 1 KiB, a quad is half of it; tf32: block (h, quad) is 512 B
@@ -505,17 +511,21 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         uint32_t it = 0, it_f = 0;  // iterations issued / fetched (only their low bits are used)
         auto fetch_list = [&]() {  // column list of the fetch cursor's tile -> its ring slot; then advance
             if (!fc.done) {
-                const uint32_t tpos = fc.sp * kTps + pw;
-                if (tpos < fc.n_tiles) {
+                const uint32_t tpos0 = fc.sp * kTps + pw * kTpw;
+                if (tpos0 < fc.n_tiles) {
+                    const uint32_t here = min(kTpw, fc.n_tiles - tpos0);  // the warp's tiles in this stage
                     const uint32_t slot_addr = my_idx_addr + (it_f % Cfg::kIdxSlots) * Cfg::kSlotBytes;
-                    const uint64_t t = fc.tile_begin + tpos;
-                    if (lane < kIdxLanes) {
-                        ptx::cp_async_16(slot_addr + lane * 16, p.tcA2B + t * Cfg::kCW + lane * 4, 16u);
-                    } else if (kBitmap && lane < kIdxLanes + kBitLanes) {
-                        const uint32_t j = lane - kIdxLanes;
-                        ptx::cp_async_16(slot_addr + kBitOff + j * 16, p.tcBit + t * Cfg::kBitWords + j * 2, 16u);
-                    } else if (kBitmap && lane < kIdxLanes + kBitLanes + 2) {
-                        const uint32_t j = lane - kIdxLanes - kBitLanes;
+                    const uint64_t t = fc.tile_begin + tpos0;
+                    constexpr uint32_t kL0 = kIdxLanes * kTpw, kL1 = kL0 + kBitLanes * kTpw;
+                    if ((uint32_t)lane < kL0) {  // the tiles are neighbours: so are their lists, bitmaps and offsets
+                        if ((uint32_t)lane / kIdxLanes < here)
+                            ptx::cp_async_16(slot_addr + lane * 16, p.tcA2B + t * Cfg::kCW + lane * 4, 16u);
+                    } else if (kBitmap && (uint32_t)lane < kL1) {
+                        const uint32_t j = (uint32_t)lane - kL0;
+                        if (j / kBitLanes < here)
+                            ptx::cp_async_16(slot_addr + kBitOff + j * 16, p.tcBit + t * Cfg::kBitWords + j * 2, 16u);
+                    } else if (kBitmap && (uint32_t)lane <= kL1 + here) {
+                        const uint32_t j = (uint32_t)lane - kL1;
                         ptx::cp_async_4(slot_addr + kNnzOff + j * 4, p.nnzOffset + t + j);
                     }
                 }
@@ -537,31 +547,35 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // waits for the thread's loads in flight, so none may be pending when it executes - and
         // have one whole iteration to land.
         constexpr int kPer = Cfg::kCW / 2;
-        uint32_t my_vals[kPer] = {};  // stored values (fp16 in the low half), zero where the bit is clear
-        Cursor vc = cur;              // the tile whose values are loaded next
+        uint32_t my_vals[kTpw][kPer] = {};  // stored values (fp16 in the low half), zero where the bit is clear
+        Cursor vc = cur;                    // the stage whose values are loaded next
         uint32_t it_v = 0;
-        auto prefetch_values = [&]() {  // loads the value cursor's tile into my_vals, then advances the cursor
+        auto prefetch_values = [&]() {  // loads the value cursor's two tiles into my_vals, then advances the cursor
             if (!kBitmap) return;
             const uint32_t *slot_words = my_idx + (it_v % Cfg::kIdxSlots) * kSlotWords;
-            const bool tile_here = !vc.done && vc.sp * kTps + pw < vc.n_tiles && !(p.debug & 8u);
+            const uint32_t tpos0 = vc.sp * kTps + pw * kTpw;
+            const uint32_t here = (!vc.done && tpos0 < vc.n_tiles && !(p.debug & 8u)) ? min(kTpw, vc.n_tiles - tpos0) : 0u;
 #pragma unroll
-            for (int b = 0; b < kPer; ++b) my_vals[b] = 0;
-            if (tile_here) {
-                const uint64_t *bits = reinterpret_cast<const uint64_t *>(slot_words + kBitOff / 4);
-                const uint32_t first_bit = (uint32_t)lane * kPer, w = first_bit >> 6, sh = first_bit & 63u;
-                uint32_t before = 0;
+            for (uint32_t j = 0; j < kTpw; ++j) {
 #pragma unroll
-                for (int j = 0; j < Cfg::kBitWords; ++j) before += (uint32_t)j < w ? (uint32_t)__popcll(bits[j]) : 0u;
-                const uint64_t word = bits[w];
-                before += (uint32_t)__popcll(word & ((1ull << sh) - 1ull));
-                const uint32_t mine = (uint32_t)(word >> sh) & ((1u << kPer) - 1u);
-                uint32_t idx = slot_words[kNnzOff / 4] + before;
+                for (int b = 0; b < kPer; ++b) my_vals[j][b] = 0;
+                if (j < here) {
+                    const uint64_t *bits = reinterpret_cast<const uint64_t *>(slot_words + kBitOff / 4) + j * Cfg::kBitWords;
+                    const uint32_t first_bit = (uint32_t)lane * kPer, w = first_bit >> 6, sh = first_bit & 63u;
+                    uint32_t before = 0;
 #pragma unroll
-                for (int b = 0; b < kPer; ++b) {
-                    if (mine & (1u << b)) {
-                        if (kTf32) my_vals[b] = __ldg(static_cast<const uint32_t *>(p.values) + idx);
-                        else my_vals[b] = __ldg(static_cast<const uint16_t *>(p.values) + idx);
-                        ++idx;
+                    for (int k = 0; k < Cfg::kBitWords; ++k) before += (uint32_t)k < w ? (uint32_t)__popcll(bits[k]) : 0u;
+                    const uint64_t word = bits[w];
+                    before += (uint32_t)__popcll(word & ((1ull << sh) - 1ull));
+                    const uint32_t mine = (uint32_t)(word >> sh) & ((1u << kPer) - 1u);
+                    uint32_t idx = slot_words[kNnzOff / 4 + j] + before;
+#pragma unroll
+                    for (int b = 0; b < kPer; ++b) {
+                        if (mine & (1u << b)) {
+                            if (kTf32) my_vals[j][b] = __ldg(static_cast<const uint32_t *>(p.values) + idx);
+                            else my_vals[j][b] = __ldg(static_cast<const uint16_t *>(p.values) + idx);
+                            ++idx;
+                        }
                     }
                 }
             }
@@ -579,10 +593,12 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         uint32_t issued = 0;  // cp.async path: stages whose copies were issued and not yet reported
         while (!cur.done) {
             const uint32_t slab = cur.slab, sp = cur.sp, tile_begin = cur.tile_begin;
-            const uint32_t tpos = sp * kTps + pw;
-            const bool have_tile = tpos < cur.n_tiles && !(p.debug & 1u);  // the last stage of a pass may be short
-            const uint32_t *list = my_idx + (it % Cfg::kIdxSlots) * kSlotWords;
-            const uint32_t tile_area = gather_addr + (s * kTps + pw) * Cfg::kGatherBytes;
+            const uint32_t tpos0 = sp * kTps + pw * kTpw;
+            // the warp's tiles in this stage (the last stage of a pass may be short), and those it gathers rows for
+            const uint32_t here = tpos0 < cur.n_tiles ? min(kTpw, cur.n_tiles - tpos0) : 0u;
+            const uint32_t gather_here = (p.debug & 1u) ? 0u : here;
+            const uint32_t *slot_words = my_idx + (it % Cfg::kIdxSlots) * kSlotWords;
+            const uint32_t first_slot = s * kTps + pw * kTpw;  // the warp's first tile slot of the ring
 
             // One lane polls (every mbarrier operation costs a shared-memory pipeline slot per
             // thread); the shuffle hands the verdict to the warp and lines the lanes up again.
@@ -597,12 +613,12 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     const bool a_tiles = pw == 0 && !(p.debug & 4u);
                     if (kTma) {
                         // this warp's arrival, announcing the bytes its TMA loads will deliver
-                        const uint32_t bytes = (have_tile ? Cfg::kGatherBytes : 0u) + (a_tiles ? kTps * kATileBytes : 0u);
+                        const uint32_t bytes = gather_here * Cfg::kGatherBytes + (a_tiles ? kTps * kATileBytes : 0u);
                         ptx::mbar_arrive_expect_tx(full_bar(s), bytes);
                     } else if (a_tiles) {
                         ptx::mbar_expect_tx(full_bar(s), kTps * kATileBytes);
                     }
-                    if (a_tiles)  // the stage's four A tiles: 64 rows of 32 bytes
+                    if (a_tiles)  // the stage's eight A tiles: 128 rows of 32 bytes
                         ptx::tma_load_2d(atile_addr + s * kTps * kATileBytes, &tmap_a, 0,
                                          (int32_t)((tile_begin + sp * kTps) * kRowWindow), full_bar(s));
                 }
@@ -610,28 +626,34 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) { failed = true; break; }
             if (kBitmap) {
-                // expand this warp's tile into its 512 bytes of the stage, then announce the gather's bytes
-                if (tpos < cur.n_tiles && !(p.debug & 4u)) {
-                    uint4 piece;
-                    const uint32_t *v = my_vals;
-                    if constexpr (kTf32) {
-                        piece = make_uint4(v[0], v[1], v[2], v[3]);
-                    } else {
-                        piece = make_uint4(v[0] | (v[1] << 16), v[2] | (v[3] << 16), v[4] | (v[5] << 16), v[6] | (v[7] << 16));
+                // expand this warp's tiles into their 512 bytes of the stage, then announce the gathers' bytes
+                if (here && !(p.debug & 4u)) {
+#pragma unroll
+                    for (uint32_t j = 0; j < kTpw; ++j) {
+                        if (j < here) {
+                            uint4 piece;
+                            const uint32_t *v = my_vals[j];
+                            if constexpr (kTf32) {
+                                piece = make_uint4(v[0], v[1], v[2], v[3]);
+                            } else {
+                                piece = make_uint4(v[0] | (v[1] << 16), v[2] | (v[3] << 16), v[4] | (v[5] << 16), v[6] | (v[7] << 16));
+                            }
+                            ptx::st_shared_v4(atile_addr + (first_slot + j) * kATileBytes + piece_off, piece);
+                        }
                     }
-                    ptx::st_shared_v4(atile_addr + (s * kTps + pw) * kATileBytes + piece_off, piece);
                     ptx::fence_proxy_async_smem();
                 }
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive_expect_tx(full_bar(s), have_tile ? Cfg::kGatherBytes : 0u);
-                prefetch_values();  // the next tile's, whose slot landed an iteration ago (see the wait below)
+                if (lane == 0) ptx::mbar_arrive_expect_tx(full_bar(s), gather_here * Cfg::kGatherBytes);
+                prefetch_values();  // the next iteration's, whose slot landed an iteration ago (see the wait below)
             }
             if (kTma) {
                 B200_PROF_T0();
-                if (have_tile && lane < Cfg::kGatherOps) {
-                    const uint4 rows4 = *reinterpret_cast<const uint4 *>(list + op_quad * 4);
+                if (half < gather_here && hl < (uint32_t)Cfg::kGatherOps) {
+                    const uint4 rows4 = *reinterpret_cast<const uint4 *>(slot_words + half * Cfg::kCW + op_quad * 4);
                     // padded slots hold 0xFFFFFFFF: clamp to the first row past the end, which reads zeros
-                    ptx::tma_gather4_2d(tile_area + op_dst, &tmap_b, (int32_t)(slab * kNs + op_x),
+                    ptx::tma_gather4_2d(gather_addr + (first_slot + half) * Cfg::kGatherBytes + op_dst, &tmap_b,
+                                        (int32_t)(slab * kNs + op_x),
                                         (int32_t)min(rows4.x, p.cols), (int32_t)min(rows4.y, p.cols),
                                         (int32_t)min(rows4.z, p.cols), (int32_t)min(rows4.w, p.cols), full_bar(s));
                 }
@@ -646,14 +668,19 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 {
                     B200_PROF_T0();
                     const uint32_t slab_byte0 = slab * kNs * Cfg::kEsz;
-                    if (have_tile) {
 #pragma unroll
-                        for (int i = 0; i < kCopies; ++i) {
-                            const uint32_t col = list[k_of[i]];
-                            const uint32_t in_row = slab_byte0 + src_off[i];
-                            const bool live = col < p.cols && in_row < n_bytes;  // padded slots hold 0xFFFFFFFF
-                            const uint8_t *src = live ? Bbytes + (uint64_t)col * row_pitch + in_row : Bbytes;
-                            ptx::cp_async_16(tile_area + dst_off[i], src, live ? 16u : 0u);
+                    for (uint32_t j = 0; j < kTpw; ++j) {
+                        if (j < gather_here) {
+                            const uint32_t *list = slot_words + j * Cfg::kCW;
+                            const uint32_t tile_area = gather_addr + (first_slot + j) * Cfg::kGatherBytes;
+#pragma unroll
+                            for (int i = 0; i < kCopies; ++i) {
+                                const uint32_t col = list[k_of[i]];
+                                const uint32_t in_row = slab_byte0 + src_off[i];
+                                const bool live = col < p.cols && in_row < n_bytes;  // padded slots hold 0xFFFFFFFF
+                                const uint8_t *src = live ? Bbytes + (uint64_t)col * row_pitch + in_row : Bbytes;
+                                ptx::cp_async_16(tile_area + dst_off[i], src, live ? 16u : 0u);
+                            }
                         }
                     }
                     fetch_list();  // rides in the same group as this tile's rows
