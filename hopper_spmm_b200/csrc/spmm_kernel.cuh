@@ -17,21 +17,23 @@
 // A single GPU thread retires roughly one dependent instruction every ten cycles, so the kernel
 // is organised around instruction counts on each role's critical path, not only around bytes.
 //
-// Roles in a CTA (544 threads for feature slabs up to 128, where two CTAs share an SM and give it
-// two MMA-issuing threads; 672 threads, one CTA per SM, for wider slabs):
+// Roles in a CTA of 544 threads (for feature slabs up to 128 two CTAs share an SM and give it two
+// MMA-issuing threads; wider slabs need the whole SM's shared memory for one CTA):
 //   warps 0-7  epilogue, two sets of four warps; set e drains accumulator buffer e, i.e. every
 //              other window.  Warp q of a set owns TMEM lanes 32q..32q+31 (32 features): after
 //              tcgen05.ld lane l holds one feature of the 16 window rows and stores them straight
 //              to C, 32 lanes covering one 128-byte line of a row per instruction; no barrier
 //              between warps.  Also zero-fills rows that belong to windows without entries
 //   warp  8    lane 0 issues tcgen05.mma / tcgen05.commit; the warp owns the TMEM allocation
-//   warps 9-   producers, two or three groups of four warps.  A ring stage holds four consecutive
-//              tiles; group g fills stages g, g+G, g+2G, ... - one tile per warp.  The first warp of
-//              the group brings the stage's four 512-byte A tiles with one TMA load; every warp
-//              fetches the CW rows of B its tile selects with TMA tile::gather4 (four rows per
-//              instruction, one instruction per lane, landing in the swizzled operand layout;
-//              a cp.async variant exists for comparison and for very narrow B).  Column lists
-//              are fetched several iterations ahead into a per-warp ring.
+//   warps 9-16 producers, two groups of four warps.  A ring stage holds eight consecutive tiles;
+//              group g fills stages g, g+2, g+4, ... - two tiles per warp, 16 lanes each.  The first
+//              warp of the group brings the stage's eight 512-byte A tiles with one TMA load; every
+//              half-warp fetches the CW rows of B its tile selects with TMA tile::gather4 (four rows
+//              per instruction, one instruction per lane, landing in the swizzled operand layout;
+//              a cp.async variant exists for comparison and for very narrow B).  Column lists are
+//              fetched a few iterations ahead into a per-warp ring.  Two tiles per warp and
+//              iteration halve the producers' instructions per tile; eight tiles per stage halve
+//              the barrier round trips of the MMA issuer.
 //
 // The schedule cuts the tile stream, not the window list, so a window heavier than a CTA's share
 // is computed in pieces by several CTAs; pieces go to fp32 slots and spmm_fixup_kernel adds them.
@@ -132,10 +134,9 @@ struct SpmmCfg {
     static constexpr int kFullChunks = kNs / 128;        // M = 128 MMAs per tile
     static constexpr bool kHalfChunk = (kNs % 128) != 0; // plus one M = 64 MMA
     static constexpr int kChunks = kFullChunks + (kHalfChunk ? 1 : 0);
-    // Ring depth, and how many stages' cp.async groups a producer warp keeps in flight before it
-    // reports the oldest as landed: 4 * (kLag + 1) tiles are in flight per SM (90-100 KB); the
-    // rest of the ring absorbs the round trip through the MMA issuer.  One barrier pair serves
-    // four tiles, which keeps the per-tile cost of waits, fences and commits low.
+    // Ring depth: 24-40 tiles (about 110 KB for two CTAs per SM, 210 KB for one) are in flight per
+    // CTA.  One barrier pair serves eight tiles, which keeps the per-tile cost of waits, fences and
+    // commits low.  (With compressed tiles the wider list slots leave room for two stages only.)
     static constexpr int kStages = kNs == 64 ? 5 : kNs == 128 ? (kBitmap ? 2 : 3) : kNs == 192 ? 4 : 3;
     // cp.async variant only: groups a warp keeps in flight before it reports the oldest as landed
     static constexpr int kLag = kStages / kProducerGroups >= 3 ? kStages / kProducerGroups - 2 : 0;
@@ -185,8 +186,8 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
     uint8_t *base = smem_raw + pad;
-    const uint32_t gather_addr = raw_addr + pad;                                    // kStages x 4 x kGatherBytes
-    const uint32_t atile_addr = gather_addr + kStages * kTps * Cfg::kGatherBytes;    // kStages x 4 x 512
+    const uint32_t gather_addr = raw_addr + pad;                                    // kStages x 8 x kGatherBytes
+    const uint32_t atile_addr = gather_addr + kStages * kTps * Cfg::kGatherBytes;    // kStages x 8 x 512
     uint32_t *idx_ring = reinterpret_cast<uint32_t *>(base + kStages * Cfg::kStageBytes);
     const uint32_t idx_ring_addr = atile_addr + kStages * kTps * kATileBytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(base + kStages * Cfg::kStageBytes + Cfg::kIdxBytes);
@@ -216,7 +217,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     // that gets through its tiles faster (warmer columns of B, or simply the better share of the
     // SM it lives on) ends up with more chunks, and all CTAs finish together.  Which CTA ran a
     // chunk has no influence on the result.
-    // A chunk's tiles are streamed once per feature slab; a pass is cut into stages of four
+    // A chunk's tiles are streamed once per feature slab; a pass is cut into stages of eight
     // consecutive tiles (the last stage of a pass may be short).  Ring stages, barrier phases and
     // accumulator buffers simply carry on from one pass and chunk to the next.
     // The schedule may cut inside a window: then the chunk computes a piece of it, which goes to
@@ -738,7 +739,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     } else if (warp == kMmaWarp && lane == 0) {
         // =========================================================== MMA issuer (warp 4, lane 0)
         // A single thread: every instruction it executes per tile is on the critical path, so the
-        // loop is kept to a wait per four tiles, one or two MMAs per tile and a commit per four
+        // loop is kept to a wait per eight tiles, one or two MMAs per tile and a commit per eight
         // tiles.  The tile counts of the next kWinAhead windows are prefetched into shared memory
         // with 4-byte cp.async copies, one group per window.
         constexpr uint32_t fmt = kTf32 ? ptx::kFmtTF32 : ptx::kFmtF16;
@@ -826,10 +827,10 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     }
                     const uint32_t d = tmem_base + a * kAccCols;
                     uint32_t accumulate = 0;
-                    // A segment is the run of tiles that share a ring stage and a window: at most four.
+                    // A segment is the run of tiles that share a ring stage and a window: at most eight.
                     // Branches are what a lone thread can least afford, so the window is walked as
                     //   head - the rest of a stage the previous window left partly used (predicated MMAs),
-                    //   body - whole stages: wait, four MMAs, commit; ring bookkeeping by selects,
+                    //   body - whole stages: wait, eight MMAs, commit; ring bookkeeping by selects,
                     //   tail - the first tiles of a stage the next window will finish (predicated MMAs).
                     auto partial = [&](uint32_t k) {  // k tiles starting at (s, slot), 0 < k < 4 or closing a stage
                         B200_PROF_T0();
