@@ -80,6 +80,7 @@ SIGNATURES = {
     "b200spmm_shard_rows_weighted": (C.c_int, [u64, vp, C.c_int, C.c_int, u64, vp]),
     "b200spmm_build_schedule": (C.c_int, [vp, u64, C.c_int, vp]),
     "b200spmm_build_tile_schedule": (C.c_int, [vp, u64, C.c_int, vp, vp, vp, vp]),
+    "b200spmm_build_row_bands": (C.c_int, [vp, vp, u64, u64, C.c_int, C.c_int, vp, vp, C.POINTER(C.c_int)]),
     "b200spmm_plan_create": (C.c_int, [vp, C.c_int, C.c_int, C.POINTER(vp)]),
     "b200spmm_plan_create_device": (C.c_int, [C.POINTER(BtcfInfo), vp, vp, vp, vp, C.c_int, C.c_int, C.POINTER(vp)]),
     "b200spmm_plan_destroy": (None, [vp]),

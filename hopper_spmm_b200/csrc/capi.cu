@@ -51,7 +51,15 @@ struct b200spmm_plan {
         SplitWindow *d_splits = nullptr;
         uint32_t *d_piece_slots = nullptr;
         uint32_t n_splits = 0, n_slots = 0;
+        // Bands: the chunk table cut into a few runs of whole windows, so that a caller can launch
+        // band after band and start copying a band's rows of C out while the next one is computed.
+        // Band k covers chunks [band_chunk[k], band_chunk[k+1]), rows [band_row[k], band_row[k+1])
+        // and the split windows [band_split[k], band_split[k+1]).
+        std::vector<uint32_t> band_chunk, band_split;
+        std::vector<uint64_t> band_row;
     } sched[2];
+    cudaStream_t copy_stream = nullptr;       // host-buffer call: C goes out on this one
+    std::vector<cudaEvent_t> band_done;
     const Sched *launch_sched = nullptr;  // the one the next launch uses
     CompressedTiles comp;                 // the tiles as bitmap + stored values (empty: dense tiles only)
     float *d_partial = nullptr;  // [n_slots][16][n] fp32, grown to the largest need seen
@@ -99,6 +107,7 @@ int launch_one(b200spmm_plan *p, const SpmmParams &prm, const CUtensorMap &tmap_
 
 // Feature slab a launch uses for B of width n, and how many CTAs of that kernel share an SM.
 constexpr uint64_t kMaxChunksPerCta = 16;
+constexpr uint32_t kRowBands = 8;  // bands of the host-buffer call (large matrices only)
 inline uint32_t slab_for(uint32_t n) { return std::min(256u, (n + 63u) / 64u * 64u); }
 inline int ctas_per_sm_for(uint32_t n) { return slab_for(n) <= 128 ? 2 : 1; }
 
@@ -156,7 +165,7 @@ int encode_tile_map(b200spmm_plan *p) {
     return B200SPMM_OK;
 }
 
-int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, int n_ctas) {
+int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, const uint32_t *h_rowIdx, int n_ctas) {
     const auto &info = p->info;
     if (info.row_window != kRowWindow) return B200SPMM_ERR_UNSUPPORTED;
     const int cw = info.dtype == B200SPMM_F16 ? 16 : 8;
@@ -194,6 +203,11 @@ int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, int n_ctas) {
         if (st_up != B200SPMM_OK) return st_up;
         ps.n_splits = (uint32_t)splits.size();
         ps.n_slots = sc.n_slots;
+        RowBands bands;  // only schedules with many chunks are worth launching in bands
+        build_row_bands(sc, h_rowIdx, info.rows, ps.n_chunks >= (uint32_t)ps.n_ctas * 8u ? kRowBands : 1u, &bands);
+        ps.band_chunk = bands.chunk;
+        ps.band_row = bands.row;
+        ps.band_split = bands.split;
     }
     // status word, then the two counters of the chunk hand-out (the kernel leaves them at zero)
     B200_CUDA_TRY(cudaMalloc(&p->d_status, 4 * sizeof(uint32_t)));
@@ -377,6 +391,20 @@ int b200spmm_build_tile_schedule(const uint32_t *rowOffset, uint64_t eff_row_win
     return B200SPMM_OK;
 }
 
+int b200spmm_build_row_bands(const uint32_t *rowOffset, const uint32_t *rowIdx, uint64_t eff_row_windows, uint64_t rows,
+                             int n_parts, int max_bands, uint32_t *band_chunk, uint64_t *band_row, int *n_bands) {
+    if (!rowOffset || !band_chunk || !band_row || !n_bands || n_parts < 1 || max_bands < 1 || (eff_row_windows && !rowIdx))
+        return B200SPMM_ERR_INVALID_ARG;
+    TileSchedule sc;
+    build_tile_schedule(rowOffset, eff_row_windows, n_parts, /*allow_split=*/true, &sc);
+    RowBands bands;
+    build_row_bands(sc, rowIdx, rows, (uint32_t)max_bands, &bands);
+    *n_bands = (int)bands.chunk.size() - 1;
+    std::memcpy(band_chunk, bands.chunk.data(), bands.chunk.size() * sizeof(uint32_t));
+    std::memcpy(band_row, bands.row.data(), bands.row.size() * sizeof(uint64_t));
+    return B200SPMM_OK;
+}
+
 void b200spmm_plan_destroy(b200spmm_plan_t *p) {
     if (!p) return;
     cudaSetDevice(p->device);
@@ -396,6 +424,8 @@ void b200spmm_plan_destroy(b200spmm_plan_t *p) {
         cudaFree(ps.d_piece_slots);
     }
     free_compressed_tiles(&p->comp);
+    for (cudaEvent_t e : p->band_done) cudaEventDestroy(e);
+    if (p->copy_stream) cudaStreamDestroy(p->copy_stream);
     cudaFree(p->d_partial);
     cudaFree(p->d_status);
     cudaFree(p->d_B);
@@ -427,7 +457,7 @@ int b200spmm_plan_create(const b200spmm_btcf_t *h, int device, int n_ctas, b200s
     if (st == B200SPMM_OK) st = upload((void **)&p->d_tcA2B, f.tcA2B.data(), f.tcA2B.size() * 4);
     if (st == B200SPMM_OK) st = upload((void **)&p->d_rowIdx, f.rowIdx.data(), f.rowIdx.size() * 4);
     if (st == B200SPMM_OK) st = upload(&p->d_data, f.data.data(), f.data.size());
-    if (st == B200SPMM_OK) st = plan_finish(p, f.rowOffset.data(), n_ctas);
+    if (st == B200SPMM_OK) st = plan_finish(p, f.rowOffset.data(), f.rowIdx.data(), n_ctas);
     if (st != B200SPMM_OK) {
         b200spmm_plan_destroy(p);
         return st;
@@ -465,7 +495,13 @@ int b200spmm_plan_create_device(const b200spmm_btcf_info_t *info, const uint32_t
         st = B200SPMM_ERR_CUDA;
     }
     if (st == B200SPMM_OK && h_rowOffset[info->eff_row_windows] != info->total_tiles) st = B200SPMM_ERR_INVALID_ARG;
-    if (st == B200SPMM_OK) st = plan_finish(p, h_rowOffset.data(), n_ctas);
+    std::vector<uint32_t> h_rowIdx(info->eff_row_windows);
+    if (st == B200SPMM_OK && info->eff_row_windows &&
+        cudaMemcpy(h_rowIdx.data(), d_rowIdx, h_rowIdx.size() * 4, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        record_cuda_error(cudaGetLastError(), "cudaMemcpy(rowIdx)");
+        st = B200SPMM_ERR_CUDA;
+    }
+    if (st == B200SPMM_OK) st = plan_finish(p, h_rowOffset.data(), h_rowIdx.data(), n_ctas);
     if (st != B200SPMM_OK) {
         b200spmm_plan_destroy(p);
         return st;
@@ -486,8 +522,14 @@ int b200spmm_plan_launch_info(const b200spmm_plan_t *p, b200spmm_launch_info_t *
     return B200SPMM_OK;
 }
 
-int b200spmm_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, void *d_C, int64_t ldc, int c_dtype,
-                  void *stream_v) {
+}  // extern "C"
+
+namespace {
+
+// The product, or one band of it (band < 0: every chunk; otherwise the chunks, rows and split
+// windows of that band of the schedule the launch selects - see b200spmm_plan::Sched).
+int spmm_launch(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, void *d_C, int64_t ldc, int c_dtype,
+                void *stream_v, int band) {
     if (!p || !d_B || !d_C || n <= 0 || ldb < n || ldc < n) return B200SPMM_ERR_INVALID_ARG;
     if (c_dtype != B200SPMM_C_F32 && c_dtype != B200SPMM_C_F16) return B200SPMM_ERR_INVALID_ARG;
     const int esz = p->info.elt_size, csz = c_dtype == B200SPMM_C_F32 ? 4 : 2;
@@ -512,7 +554,11 @@ int b200spmm_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, v
     prm.chunk_wlast = sc.d_wlast;
     prm.chunk_head_slot = sc.d_head_slot;
     prm.chunk_tail_slot = sc.d_tail_slot;
-    prm.n_chunks = sc.n_chunks;
+    if (band >= 0 && (size_t)band + 1 >= sc.band_chunk.size()) return B200SPMM_ERR_INVALID_ARG;
+    prm.chunk_begin = band < 0 ? 0u : sc.band_chunk[band];
+    prm.chunk_end = band < 0 ? sc.n_chunks : sc.band_chunk[band + 1];
+    const uint32_t split_begin = band < 0 ? 0u : sc.band_split[band];
+    const uint32_t split_end = band < 0 ? sc.n_splits : sc.band_split[band + 1];
     prm.sched_counter = sc.n_chunks > (uint32_t)sc.n_ctas ? p->d_status + 1 : nullptr;
     if (sc.n_slots) {  // slots for the pieces of windows that span chunks
         const size_t need = (size_t)sc.n_slots * kRowWindow * (size_t)n;
@@ -543,13 +589,22 @@ int b200spmm_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, v
 #endif
     if (const char *dbg = std::getenv("B200SPMM_DEBUG")) prm.debug = (uint32_t)std::atoi(dbg);  // measurement aid, results invalid
     int st = p->info.dtype == B200SPMM_F16 ? launch_dtype<false>(p, prm, stream) : launch_dtype<true>(p, prm, stream);
-    if (st != B200SPMM_OK || !sc.n_splits) return st;
+    if (st != B200SPMM_OK || split_end == split_begin) return st;
     // windows shared out over several CTAs: sum their pieces
-    spmm_fixup_kernel<<<sc.n_splits, 256, 0, stream>>>(sc.d_splits, sc.d_piece_slots, p->d_partial, p->d_rowIdx, d_C, ldc,
-                                                       prm.rows, prm.n, prm.c_is_half);
+    spmm_fixup_kernel<<<split_end - split_begin, 256, 0, stream>>>(sc.d_splits + split_begin, sc.d_piece_slots, p->d_partial,
+                                                                   p->d_rowIdx, d_C, ldc, prm.rows, prm.n, prm.c_is_half);
     B200_CUDA_TRY(cudaGetLastError());
     p->last.kernel_launches = 2;
     return B200SPMM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200spmm_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, void *d_C, int64_t ldc, int c_dtype,
+                  void *stream_v) {
+    return spmm_launch(p, d_B, ldb, n, d_C, ldc, c_dtype, stream_v, -1);
 }
 
 int b200spmm_fp16_spmm(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, void *d_C, int64_t ldc, int c_dtype,
@@ -600,9 +655,36 @@ int b200spmm_spmm_host(b200spmm_plan_t *p, const void *h_B, int64_t n, void *h_C
         p->d_C_bytes = c_bytes;
     }
     B200_CUDA_TRY(cudaMemcpyAsync(p->d_B, h_B, b_bytes, cudaMemcpyHostToDevice, nullptr));
-    int st = b200spmm_spmm(p, p->d_B, n, n, p->d_C, n, c_dtype, nullptr);
-    if (st != B200SPMM_OK) return st;
-    B200_CUDA_TRY(cudaMemcpyAsync(h_C, p->d_C, c_bytes, cudaMemcpyDeviceToHost, nullptr));
+    const b200spmm_plan::Sched &sc = p->sched[ctas_per_sm_for((uint32_t)n) - 1];
+    const size_t bands = sc.band_chunk.size() > 1 ? sc.band_chunk.size() - 1 : 1;
+    if (bands == 1 || p->info.eff_row_windows == 0) {
+        int st = b200spmm_spmm(p, p->d_B, n, n, p->d_C, n, c_dtype, nullptr);
+        if (st != B200SPMM_OK) return st;
+        B200_CUDA_TRY(cudaMemcpyAsync(h_C, p->d_C, c_bytes, cudaMemcpyDeviceToHost, nullptr));
+        return b200spmm_plan_sync(p, nullptr);
+    }
+    // Large matrix: band after band on the compute stream; as soon as a band is done its rows of C
+    // leave on a second stream while the next band is computed.
+    if (!p->copy_stream) B200_CUDA_TRY(cudaStreamCreateWithFlags(&p->copy_stream, cudaStreamNonBlocking));
+    while (p->band_done.size() < bands) {
+        cudaEvent_t e;
+        B200_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        p->band_done.push_back(e);
+    }
+    const size_t row_bytes = (size_t)n * (c_dtype == B200SPMM_C_F32 ? 4 : 2);
+    int64_t launches = 0;
+    for (size_t k = 0; k < bands; ++k) {
+        int st = spmm_launch(p, p->d_B, n, n, p->d_C, n, c_dtype, nullptr, (int)k);
+        if (st != B200SPMM_OK) return st;
+        launches += p->last.kernel_launches;
+        B200_CUDA_TRY(cudaEventRecord(p->band_done[k], nullptr));
+        B200_CUDA_TRY(cudaStreamWaitEvent(p->copy_stream, p->band_done[k], 0));
+        const uint64_t r0 = sc.band_row[k], r1 = sc.band_row[k + 1];
+        B200_CUDA_TRY(cudaMemcpyAsync(static_cast<char *>(h_C) + r0 * row_bytes, static_cast<char *>(p->d_C) + r0 * row_bytes,
+                                      (r1 - r0) * row_bytes, cudaMemcpyDeviceToHost, p->copy_stream));
+    }
+    p->last.kernel_launches = launches;
+    B200_CUDA_TRY(cudaStreamSynchronize(p->copy_stream));
     return b200spmm_plan_sync(p, nullptr);
 }
 
@@ -693,7 +775,8 @@ int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_ro
     prm.chunk_wfirst = scratch + kNoAllocWfirst;
     prm.chunk_wlast = scratch + kNoAllocWlast;
     prm.chunk_head_slot = prm.chunk_tail_slot = nullptr;  // cuts lie on window boundaries: no shared windows
-    prm.n_chunks = (uint32_t)n_ctas;
+    prm.chunk_begin = 0;
+    prm.chunk_end = (uint32_t)n_ctas;
     prm.sched_counter = nullptr;
     prm.partial = nullptr;
     prm.B = d_B;

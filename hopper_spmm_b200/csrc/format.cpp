@@ -274,4 +274,28 @@ void build_tile_schedule(const uint32_t *rowOffset, uint64_t eff, int n_ctas, bo
     }
 }
 
+void build_row_bands(const TileSchedule &sc, const uint32_t *rowIdx, uint64_t rows, uint32_t want, RowBands *out) {
+    RowBands &b = *out;
+    const uint32_t n_chunks = (uint32_t)sc.wfirst.size();
+    b.chunk.assign(1, 0);
+    for (uint32_t k = 1; k < want; ++k) {
+        uint32_t c = (uint32_t)((uint64_t)n_chunks * k / want);
+        // a band starts with a chunk that holds tiles and begins its first window
+        while (c < n_chunks && (sc.head_slot[c] != kNoSlot || sc.tile[c + 1] == sc.tile[c])) ++c;
+        if (c < n_chunks && c > b.chunk.back()) b.chunk.push_back(c);
+    }
+    b.chunk.push_back(n_chunks);
+    b.row.clear();
+    b.split.clear();
+    uint32_t first_split = 0;  // the splits are ordered by window
+    for (size_t k = 0; k + 1 < b.chunk.size(); ++k) {
+        const uint32_t c = b.chunk[k];
+        b.row.push_back(k == 0 ? 0 : rowIdx[sc.wfirst[c]]);
+        while (k != 0 && first_split < sc.splits.size() && sc.splits[first_split].window < sc.wfirst[c]) ++first_split;
+        b.split.push_back(first_split);
+    }
+    b.row.push_back(rows);
+    b.split.push_back((uint32_t)sc.splits.size());
+}
+
 }  // namespace b200spmm

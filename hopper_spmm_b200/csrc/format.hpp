@@ -64,4 +64,15 @@ struct TileSchedule {
 void build_tile_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_parts, bool allow_split,
                          TileSchedule *out);
 
+// Bands of a schedule: up to `want` runs of consecutive chunks with about the same number of
+// chunks each, cut only where a chunk starts on a window boundary, so that no window is shared
+// between two bands.  Band k covers chunks [chunk[k], chunk[k+1]), rows [row[k], row[k+1]) of C
+// (the rows of its windows and of the empty windows after them; band 0 also the rows before the
+// first window) and the split windows [split[k], split[k+1]) of the schedule.
+struct RowBands {
+    std::vector<uint32_t> chunk, split;
+    std::vector<uint64_t> row;
+};
+void build_row_bands(const TileSchedule &sc, const uint32_t *rowIdx, uint64_t rows, uint32_t want, RowBands *out);
+
 }  // namespace b200spmm

@@ -80,14 +80,14 @@ struct SpmmParams {
     const uint32_t *rowOffset;   // [eff+1] tiles
     const uint32_t *tcA2B;       // [tiles*CW]
     const uint32_t *rowIdx;      // [eff]
-    // schedule: chunk c holds tiles [chunk_tile[c], chunk_tile[c+1]); CTA b starts with chunk b and takes
-    // further chunks, from gridDim.x on, in the order in which the CTAs ask for them
+    // schedule: chunk c holds tiles [chunk_tile[c], chunk_tile[c+1]); CTA b starts with chunk chunk_begin + b and
+    // takes further chunks, from chunk_begin + gridDim.x on, in the order in which the CTAs ask for them
     const uint32_t *chunk_tile;       // [n_chunks+1]
     const uint32_t *chunk_wfirst;     // [n_chunks] window holding the chunk's first tile
     const uint32_t *chunk_wlast;      // [n_chunks] window holding the chunk's last tile
     const uint32_t *chunk_head_slot;  // [n_chunks] slot for the piece at the chunk's head, or kNoSlot (null: no pieces)
     const uint32_t *chunk_tail_slot;  // [n_chunks] slot for the piece at the chunk's tail, or kNoSlot
-    uint32_t n_chunks;
+    uint32_t chunk_begin, chunk_end;  // the chunks this launch covers (the whole table, or one band of rows)
     uint32_t *sched_counter;     // [2] chunks handed out beyond the first gridDim.x, CTAs finished; both zero
                                  // at launch and again at exit (null: every CTA runs its first chunk only)
     float *partial;              // [slots][16][n] fp32 pieces of windows cut at a chunk boundary (may be null)
@@ -264,7 +264,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
         *abort_flag = 0;
         *mma_done = 0;
-        chunk_list[0] = blockIdx.x < p.n_chunks ? blockIdx.x : kNoChunk;
+        chunk_list[0] = p.chunk_begin + blockIdx.x < p.chunk_end ? p.chunk_begin + blockIdx.x : kNoChunk;
         *chunk_avail = 1;
         ptx::fence_mbar_init();
         if (!kBitmap) ptx::prefetch_tensormap(&tmap_a);
@@ -475,8 +475,8 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 if (lane == 0) {
                     uint32_t next = kNoChunk;
                     if (p.sched_counter && c.round + 1 < (uint32_t)Cfg::kChunkSlots) {
-                        next = gridDim.x + atomicAdd(p.sched_counter, 1u);
-                        if (next >= p.n_chunks) next = kNoChunk;
+                        next = p.chunk_begin + gridDim.x + atomicAdd(p.sched_counter, 1u);
+                        if (next >= p.chunk_end) next = kNoChunk;
                     }
                     chunk_list[c.round] = next;
                     __threadfence_block();

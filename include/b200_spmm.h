@@ -153,6 +153,17 @@ int b200spmm_build_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows,
 int b200spmm_build_tile_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_parts, uint32_t *cta_tile,
                                  uint32_t *cta_wfirst, uint32_t *cta_wlast, uint32_t *slot_window);
 
+/*
+ * Bands of that schedule, as the host-buffer SpMM uses them on large matrices: at most max_bands
+ * runs of consecutive chunks, cut only where a chunk starts on a window boundary, so a band's rows
+ * of C are complete when its chunks are done and can be copied out while the next band is
+ * computed.  band_chunk[n_bands+1] and band_row[n_bands+1] (arrays of max_bands+1 elements)
+ * receive the chunk and row cuts; band k covers chunks [band_chunk[k], band_chunk[k+1]) and rows
+ * [band_row[k], band_row[k+1]).  No counterpart in the reference.
+ */
+int b200spmm_build_row_bands(const uint32_t *rowOffset, const uint32_t *rowIdx, uint64_t eff_row_windows, uint64_t rows,
+                             int n_parts, int max_bands, uint32_t *band_chunk, uint64_t *band_row, int *n_bands);
+
 /* ------------------------------------------------------------------ the reference's other formats */
 
 /*

@@ -180,3 +180,36 @@ def test_tile_schedule_covers_every_tile_once_and_accounts_for_every_piece():
             share = (total + charge * eff) / n_ctas
             slack = max(32, total // n_ctas // 16) + 3 * charge
             assert load.max() <= share + slack, (eff, n_ctas, load.max(), share)
+
+
+def test_row_bands_cut_only_between_windows_and_cover_all_rows():
+    rng = np.random.default_rng(5)
+    for eff, n_parts, want in ((0, 8, 4), (3, 16, 8), (5000, 148 * 16, 8), (5000, 7, 8), (40000, 296 * 16, 8)):
+        tiles = rng.integers(1, 40, eff)
+        if eff > 10:
+            tiles[:3] = (30000, 2000, 700)
+        row_offset = np.concatenate([[0], np.cumsum(tiles)]).astype(np.uint32)
+        # windows 16 rows apart with some empty windows in between
+        row_idx = (np.cumsum(rng.integers(1, 3, eff)) * 16).astype(np.uint32) if eff else np.zeros(0, np.uint32)
+        rows = int(row_idx[-1]) + 40 if eff else 100
+        band_chunk = np.zeros(want + 1, np.uint32)
+        band_row = np.zeros(want + 1, np.uint64)
+        n_bands = C.c_int()
+        st = capi.lib().b200spmm_build_row_bands(row_offset.ctypes.data, row_idx.ctypes.data, eff, rows, n_parts, want,
+                                                 band_chunk.ctypes.data, band_row.ctypes.data, C.byref(n_bands))
+        assert st == capi.OK and 1 <= n_bands.value <= want
+        nb = n_bands.value
+        bc, br = band_chunk[:nb + 1].astype(np.int64), band_row[:nb + 1].astype(np.int64)
+        assert bc[0] == 0 and bc[-1] == n_parts and np.all(np.diff(bc) > 0)
+        assert br[0] == 0 and br[-1] == rows and np.all(np.diff(br) > 0)
+        cta_tile = np.zeros(n_parts + 1, np.uint32)
+        wfirst, wlast = np.zeros(n_parts, np.uint32), np.zeros(n_parts, np.uint32)
+        slot_window = np.zeros(2 * n_parts, np.uint32)
+        capi.lib().b200spmm_build_tile_schedule(row_offset.ctypes.data, eff, n_parts, cta_tile.ctypes.data,
+                                                wfirst.ctypes.data, wlast.ctypes.data, slot_window.ctypes.data)
+        for k in range(1, nb):
+            c = int(bc[k])
+            assert cta_tile[c] == row_offset[wfirst[c]], "a band starts at the first tile of a window"
+            assert slot_window[2 * c] == 0xFFFFFFFF and br[k] == row_idx[wfirst[c]]
+        if eff >= 5000 and n_parts >= 148 * 16:
+            assert nb == want

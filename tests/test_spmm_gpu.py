@@ -191,6 +191,14 @@ def test_rmat_rows_sum_to_one_at_scale():
     want = (deg > 0).to(torch.float32)[:, None].expand(-1, 128)
     err = (Cd - want).abs().max().item()
     assert err < 2e-3, err  # 1/deg is rounded to fp16: relative 2^-11 per term
+    # The host-buffer call of a matrix this large runs band after band and copies each band's rows of
+    # C out while the next is computed: same bits as the device-resident call, for fp32 and fp16 C.
+    Bn = torch.rand((csr.cols, 128), dtype=torch.float32, device="cuda").sub_(0.5).to(torch.float16)
+    for c_half in (False, True):
+        want_c = plan.spmm(Bn, c_half=c_half).cpu().numpy()
+        got_c = plan.spmm_host(Bn.cpu().numpy(), c_half=c_half)
+        assert plan.launch_info().kernel_launches > 2, "expected one launch per band"
+        assert np.array_equal(got_c.view(np.uint16 if c_half else np.uint32), want_c.view(np.uint16 if c_half else np.uint32))
     plan.close()
 
 
