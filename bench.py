@@ -268,22 +268,41 @@ def main():
         hC = torch.empty(C_dev.shape, dtype=torch.float16 if c_half else torch.float32, pin_memory=True)
         torch.cuda.synchronize()
         hBn, hCn = hB.numpy(), hC.numpy()
-        plan.spmm_host(hBn, hCn, c_half=c_half)  # warm-up: allocates the plan's device buffers
+        if world == 1:
+            step = lambda: plan.spmm_host(hBn, hCn, c_half=c_half)
+            h2d_bytes = int(hB.numel() * hB.element_size())
+        else:
+            # N ranks behind one host: every rank uploads 1/N of the replicated B and the parts are
+            # exchanged GPU to GPU (sharded.upload_replicated); then the rank's product, then its rows
+            # of C back to the host.  Bytes are whole-job sums.
+            dB = torch.empty_like(B)
+            dC = torch.empty(C_dev.shape, dtype=hC.dtype, device=dev)
+
+            def step():
+                sharded.upload_replicated(hB, dB)
+                plan.spmm(dB, dC, c_half=c_half, sync=False)
+                hC.copy_(dC, non_blocking=True)
+                plan.sync()
+            h2d_bytes = int(hB.numel() * hB.element_size())
+        step()  # warm-up: allocates the plan's device buffers
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.steps):
-            plan.spmm_host(hBn, hCn, c_half=c_half)
+            step()
         e1.record()
         barrier()
         t_e = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        d2h = torch.tensor([float(hC.numel() * hC.element_size())], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
+            dist.all_reduce(d2h, op=dist.ReduceOp.SUM)
         e_ms = float(t_e.item()) / args.steps
         e2e = {"value": flops / (e_ms * 1e-3) / 1e9, "unit": "GFLOP/s", "ms_per_step": e_ms,
-               "h2d_bytes_per_step": int(hB.numel() * hB.element_size()),
-               "d2h_bytes_per_step": int(hC.numel() * hC.element_size()),
-               "c_dtype": "f16" if c_half else "f32", "call": "b200spmm_spmm_host (fp16_spmm / tf32_spmm with host B and C)"}
+               "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": int(d2h.item()),
+               "c_dtype": "f16" if c_half else "f32",
+               "call": ("b200spmm_spmm_host (fp16_spmm / tf32_spmm with host B and C)" if world == 1 else
+                        "per rank: 1/N of host B in + GPU-to-GPU exchange, b200spmm_spmm, its rows of C out to the host")}
         assert bool(torch.isfinite(hC[:: max(1, hC.shape[0] // 4096)]).all())
 
     # ---- roofline of the SpMM kernel on this rank's launch

@@ -50,3 +50,27 @@ def allgather_rows(C_local, cuts, group=None):
     for w in work:
         w.wait()
     return full
+
+
+def upload_replicated(B_host, B_dev, group=None):
+    """Brings a host B (the same on every rank, pinned) into every rank's B_dev with one trip over
+    the host link per element: rank p copies rows [p*K/N, (p+1)*K/N) host -> device and then
+    broadcasts them to the other ranks, GPU to GPU.  With N ranks behind one host the replicated
+    operand crosses PCIe once instead of N times.  Works on CUDA tensors (NCCL) and CPU tensors
+    (gloo).  Returns the number of bytes this rank copied from the host."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    K = B_host.shape[0]
+    cuts = [K * p // world for p in range(world + 1)]
+    mine = B_dev[cuts[rank]:cuts[rank + 1]]
+    mine.copy_(B_host[cuts[rank]:cuts[rank + 1]], non_blocking=True)
+    work = []
+    for p in range(world):
+        part = B_dev[cuts[p]:cuts[p + 1]]
+        if part.numel():
+            src = dist.get_global_rank(group, p) if group is not None else p
+            work.append(dist.broadcast(part, src=src, group=group, async_op=True))
+    for w in work:
+        w.wait()
+    return mine.numel() * mine.element_size()

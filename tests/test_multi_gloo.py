@@ -42,6 +42,13 @@ def _worker(rank, world, port, out_dir):
         full = sharded.allgather_rows(C_local, cuts)
         want = oracle.spmm_csr(csr.rows, rp, ci, v, B.numpy())
         assert np.array_equal(full.numpy(), want)  # same per-row order of additions: bit-identical
+        # the replicated operand: every rank brings 1/N of it in, the rest arrives from the other ranks
+        B_dev = torch.full_like(B, float("nan"))
+        moved = sharded.upload_replicated(B, B_dev)
+        assert torch.equal(B_dev, B)
+        total = torch.tensor([moved], dtype=torch.int64)
+        dist.all_reduce(total)
+        assert int(total) == B.numel() * B.element_size()  # the operand crossed the host link once
         nnz = torch.tensor([len(pci)], dtype=torch.int64)
         dist.all_reduce(nnz)
         assert int(nnz) == csr.nnz
