@@ -39,11 +39,9 @@ struct b200spmm_plan {
     bool owns_format = false;
     uint32_t *d_rowOffset = nullptr, *d_tcA2B = nullptr, *d_rowIdx = nullptr;
     void *d_data = nullptr;
-    // A schedule: the tile stream cut into chunks (tile cuts, first / last window and the
-    // partial-result slots of each chunk), which the CTAs take in turn - CTA b runs chunks b,
-    // b + n_ctas, ... - plus the split windows and their slots for the fix-up kernel.  The plan
-    // keeps one for the kernels that run one CTA per SM (wide feature slabs) and one for those
-    // that run two, and the launch picks by the width of B.
+    // The schedule: the tile stream cut into chunks (tile cuts, first / last window and the
+    // partial-result slots of each chunk), which the CTAs claim at run time, plus the split
+    // windows and their slots for the fix-up kernel.
     struct Sched {
         int n_ctas = 0;
         uint32_t n_chunks = 0;
@@ -57,7 +55,7 @@ struct b200spmm_plan {
         // and the split windows [band_split[k], band_split[k+1]).
         std::vector<uint32_t> band_chunk, band_split;
         std::vector<uint64_t> band_row;
-    } sched[2];
+    } sched;
     cudaStream_t copy_stream = nullptr;       // host-buffer call: C goes out on this one
     std::vector<cudaEvent_t> band_done;
     const Sched *launch_sched = nullptr;  // the one the next launch uses
@@ -108,8 +106,11 @@ int launch_one(b200spmm_plan *p, const SpmmParams &prm, const CUtensorMap &tmap_
 // Feature slab a launch uses for B of width n, and how many CTAs of that kernel share an SM.
 constexpr uint64_t kMaxChunksPerCta = 16;
 constexpr uint32_t kRowBands = 8;  // bands of the host-buffer call (large matrices only)
-inline uint32_t slab_for(uint32_t n) { return std::min(256u, (n + 63u) / 64u * 64u); }
-inline int ctas_per_sm_for(uint32_t n) { return slab_for(n) <= 128 ? 2 : 1; }
+// Up to 128 features per pass: a CTA of that width leaves room for a second one on the SM, and two
+// MMA-issuing threads per SM outweigh streaming the tiles once more per extra pass (n = 2048:
+// 4.27 ms in sixteen passes of 128 against 4.65 ms in eight of 256).
+inline uint32_t slab_for(uint32_t n) { return std::min(128u, (n + 63u) / 64u * 64u); }
+constexpr int kCtasPerSm = 2;  // every kernel variant in use is sized for two resident CTAs per SM
 
 template <bool kTf32, bool kTma, bool kBitmap>
 int launch_slab(b200spmm_plan *p, SpmmParams &prm, const CUtensorMap &tmap_b, cudaStream_t stream) {
@@ -117,9 +118,7 @@ int launch_slab(b200spmm_plan *p, SpmmParams &prm, const CUtensorMap &tmap_b, cu
     prm.n_slabs = (prm.n + ns - 1) / ns;
     switch (ns) {
         case 64: return launch_one<kTf32, 64, kTma, kBitmap>(p, prm, tmap_b, stream);
-        case 128: return launch_one<kTf32, 128, kTma, kBitmap>(p, prm, tmap_b, stream);
-        case 192: return launch_one<kTf32, 192, kTma, kBitmap>(p, prm, tmap_b, stream);
-        default: return launch_one<kTf32, 256, kTma, kBitmap>(p, prm, tmap_b, stream);
+        default: return launch_one<kTf32, 128, kTma, kBitmap>(p, prm, tmap_b, stream);
     }
 }
 
@@ -180,9 +179,9 @@ int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, const uint32_t *h
         if (!v.empty()) B200_CUDA_TRY(cudaMemcpy(*dst, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice));
         return B200SPMM_OK;
     };
-    for (int k = 0; k < 2; ++k) {  // k + 1 resident CTAs per SM
-        b200spmm_plan::Sched &ps = p->sched[k];
-        ps.n_ctas = n_ctas > 0 ? n_ctas : prop.multiProcessorCount * (k + 1);
+    {
+        b200spmm_plan::Sched &ps = p->sched;
+        ps.n_ctas = n_ctas > 0 ? n_ctas : prop.multiProcessorCount * kCtasPerSm;
         // Several chunks per CTA, taken from all over the matrix, even out regions whose tiles
         // cost more than the schedule's model says; a chunk stays long enough (512 tiles or
         // more) for the hand-over at its start not to matter.
@@ -414,7 +413,8 @@ void b200spmm_plan_destroy(b200spmm_plan_t *p) {
         cudaFree(p->d_rowIdx);
         cudaFree(p->d_data);
     }
-    for (auto &ps : p->sched) {
+    {
+        auto &ps = p->sched;
         cudaFree(ps.d_tile);
         cudaFree(ps.d_wfirst);
         cudaFree(ps.d_wlast);
@@ -547,7 +547,7 @@ int spmm_launch(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, voi
     prm.rowOffset = p->d_rowOffset;
     prm.tcA2B = p->d_tcA2B;
     prm.rowIdx = p->d_rowIdx;
-    const b200spmm_plan::Sched &sc = p->sched[ctas_per_sm_for((uint32_t)n) - 1];
+    const b200spmm_plan::Sched &sc = p->sched;
     p->launch_sched = &sc;
     prm.chunk_tile = sc.d_tile;
     prm.chunk_wfirst = sc.d_wfirst;
@@ -655,7 +655,7 @@ int b200spmm_spmm_host(b200spmm_plan_t *p, const void *h_B, int64_t n, void *h_C
         p->d_C_bytes = c_bytes;
     }
     B200_CUDA_TRY(cudaMemcpyAsync(p->d_B, h_B, b_bytes, cudaMemcpyHostToDevice, nullptr));
-    const b200spmm_plan::Sched &sc = p->sched[ctas_per_sm_for((uint32_t)n) - 1];
+    const b200spmm_plan::Sched &sc = p->sched;
     const size_t bands = sc.band_chunk.size() > 1 ? sc.band_chunk.size() - 1 : 1;
     if (bands == 1 || p->info.eff_row_windows == 0) {
         int st = b200spmm_spmm(p, p->d_B, n, n, p->d_C, n, c_dtype, nullptr);
@@ -738,7 +738,7 @@ int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_ro
     B200_CUDA_TRY(cudaSetDevice(device));
     if (n_ctas <= 0) {
         B200_CUDA_TRY(cudaDeviceGetAttribute(&n_ctas, cudaDevAttrMultiProcessorCount, device));
-        n_ctas *= ctas_per_sm_for((uint32_t)n);
+        n_ctas *= kCtasPerSm;
         if (n_ctas > kNoAllocMaxCtas) n_ctas = kNoAllocMaxCtas;
     }
     if (info->eff_row_windows == 0) {  // nothing stored: C is all zeros
@@ -752,8 +752,8 @@ int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_ro
     b200spmm_plan tmp;  // lives on the stack; owns nothing
     tmp.info = *info;
     tmp.device = device;
-    tmp.sched[0].n_ctas = n_ctas;  // the tables themselves are in the built-in array
-    tmp.launch_sched = &tmp.sched[0];
+    tmp.sched.n_ctas = n_ctas;  // the tables themselves are in the built-in array
+    tmp.launch_sched = &tmp.sched;
     tmp.d_rowOffset = const_cast<uint32_t *>(d_rowOffset);
     tmp.d_tcA2B = const_cast<uint32_t *>(d_tcA2B);
     tmp.d_rowIdx = const_cast<uint32_t *>(d_rowIdx);

@@ -17,8 +17,8 @@
 // A single GPU thread retires roughly one dependent instruction every ten cycles, so the kernel
 // is organised around instruction counts on each role's critical path, not only around bytes.
 //
-// Roles in a CTA of 544 threads (for feature slabs up to 128 two CTAs share an SM and give it two
-// MMA-issuing threads; wider slabs need the whole SM's shared memory for one CTA):
+// Roles in a CTA of 544 threads (a pass covers at most 128 features, so that two CTAs share an SM
+// and give it two MMA-issuing threads; wider B is multiplied in several passes):
 //   warps 0-7  epilogue, two sets of four warps; set e drains accumulator buffer e, i.e. every
 //              other window.  Warp q of a set owns TMEM lanes 32q..32q+31 (32 features): after
 //              tcgen05.ld lane l holds one feature of the 16 window rows and stores them straight
@@ -119,7 +119,7 @@ struct SpmmParams {
 template <bool kTf32, int kNs, bool kTma = true, bool kBitmap = false>
 struct SpmmCfg {
     static_assert(kTma || !kBitmap, "compressed tiles go with the TMA gather");
-    static_assert(kNs == 64 || kNs == 128 || kNs == 192 || kNs == 256, "feature slab");
+    static_assert(kNs == 64 || kNs == 128 || kNs == 192 || kNs == 256, "feature slab");  // in use: 64 and 128
     // One thread issues a CTA's MMAs, and with 16-row windows every MMA is small: the issuing
     // thread, not the tensor core, sets the pace.  Up to 128 features a CTA is small enough for
     // two to share an SM, which gives the SM two issuing threads and two rings to keep full.

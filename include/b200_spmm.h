@@ -246,8 +246,8 @@ typedef struct b200spmm_plan b200spmm_plan_t;
 /*
  * Uploads a converted matrix to `device` and builds the schedule: contiguous runs of row
  * windows per persistent CTA, balanced on tile count.  row_window must be 16.
- * n_ctas = 0 selects one CTA per SM for B wider than 128 columns and two per SM up to 128
- * (the plan holds a schedule for each; a launch picks by the width of B).
+ * n_ctas = 0 selects two CTAs per SM (the kernels are sized for two resident CTAs; B wider than
+ * 128 columns is multiplied in passes of 128 features).
  */
 int b200spmm_plan_create(const b200spmm_btcf_t *f, int device, int n_ctas, b200spmm_plan_t **out);
 
@@ -317,7 +317,7 @@ int b200spmm_bench(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, 
  * The kernel still needs working memory: the schedule table (one cut per CTA) and its status
  * word.  Both live in a 16 KiB array that is part of the library image on every GPU that loads
  * the library.  Consequences:
- *   - n_ctas may be at most 1024 (0 = one CTA per SM, two when n <= 128); more is refused with
+ *   - n_ctas may be at most 1024 (0 = two CTAs per SM); more is refused with
  *     B200SPMM_ERR_UNSUPPORTED and a message in b200spmm_last_cuda_error().
  *   - The first call on a device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current) and keeps it; make that first call
