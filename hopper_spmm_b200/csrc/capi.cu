@@ -82,12 +82,6 @@ int launch_one(b200spmm_plan *p, const SpmmParams &prm, const CUtensorMap &tmap_
         // all of the SM's shared-memory/L1 array as shared memory: two CTAs of the narrow slabs fit only then
         B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         configured_device = p->device;
-        if (std::getenv("B200SPMM_VERBOSE")) {
-            int occ = 0;
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, Cfg::kThreads, Cfg::kSmemBytes);
-            std::fprintf(stderr, "[b200spmm] slab %d stages %d smem %zu: %d CTAs per SM\n", kNs, Cfg::kStages,
-                         (size_t)Cfg::kSmemBytes, occ);
-        }
     }
     kernel<<<p->launch_sched->n_ctas, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p->tmap_a, tmap_b, prm);
     B200_CUDA_TRY(cudaGetLastError());
