@@ -116,12 +116,12 @@ def cpu_sample_rows(row_ptr_host: np.ndarray, target_nnz: int):
     return lo, max(hi, lo + 1)
 
 
-def time_cpu_oracle(rp, ci, v, B_host, steps, warmup, budget_s=12.0):
-    """GFLOP/s of the oracle's CSR SpMM (all host threads) on a row sample sized to the budget."""
+def time_cpu_oracle(rp, ci, v, B_host, steps, warmup, budget_s=12.0, threads=0):
+    """GFLOP/s of the oracle's CSR SpMM (all host threads, or `threads`) on a row sample sized to the budget."""
     import oracle
     rows = len(rp) - 1
     n = B_host.shape[1]
-    threads = oracle.max_threads()
+    threads = threads or oracle.max_threads()
     lo, hi = cpu_sample_rows(rp, 1 << 20)  # probe
     t0 = time.perf_counter()
     oracle.spmm_csr(rows, rp, ci, v, B_host, n_threads=threads, row_begin=lo, row_end=hi)
@@ -154,6 +154,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--scale-down", type=int, default=0)
+    ap.add_argument("--allgather", action="store_true", help="also time the all-gather of the row-sharded C (N > 1)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -257,6 +258,47 @@ def main():
     flops = 2.0 * total_nnz * n_feat
     value = flops / (ms_per_step * 1e-3) / 1e9
 
+    # ---- the same launches replayed from a CUDA graph (what a launch-latency-bound product costs
+    # without the per-launch host work); small workloads only
+    graph_ms = None
+    if ms_per_step < 0.2:
+        try:
+            g = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                plan.spmm(B, C_dev, sync=False)
+                with torch.cuda.graph(g, stream=side):
+                    for _ in range(args.steps):
+                        plan.spmm(B, C_dev, sync=False)
+            torch.cuda.current_stream().wait_stream(side)
+            g.replay()
+            torch.cuda.synchronize()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record()
+            g.replay()
+            g1.record()
+            torch.cuda.synchronize()
+            graph_ms = g0.elapsed_time(g1) / args.steps
+            del g
+        except RuntimeError as e:  # reported, not fatal: the figure is an extra
+            log(f"rank {rank}: CUDA-graph replay not measured: {e}")
+
+    # ---- optional collective: all-gather of the row-sharded C, timed on its own
+    allgather_ms = None
+    if world > 1 and args.allgather:
+        barrier()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        full = sharded.allgather_rows(C_dev, cuts)
+        a1.record()
+        barrier()
+        t_a = torch.tensor([a0.elapsed_time(a1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t_a, op=dist.ReduceOp.MAX)
+        allgather_ms = float(t_a.item())
+        del full
+        torch.cuda.empty_cache()
+
     # ---- end to end: B from pinned host memory in, C out to pinned host memory, every step
     e2e = None
     if not args.no_e2e:
@@ -325,11 +367,16 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu, _ = time_cpu_oracle(*host_csr, B.cpu().numpy(), 2, 1, budget_s=15.0)
+        one, _ = time_cpu_oracle(*host_csr, B.cpu().numpy(), 1, 1, budget_s=6.0, threads=1)  # the reference is single-threaded
+        cpu["one_core"] = {"value": one["value"], "unit": one["unit"], "sample": one["sample"]}
 
     if rank == 0:
         config.update(rows=int(cuts[-1]), cols=int(B.shape[0]), nnz=int(total_nnz), tiles_rank0=int(tiles_local),
                       fill_rank0=fill, n_ctas=info.n_ctas, feature_slab=info.feature_slab, stages=info.stages,
-                      convert_s_rank0=t_conv, rank_ms=[round(x, 4) for x in rank_ms])
+                      convert_s_rank0=t_conv, rank_ms=[round(x, 4) for x in rank_ms],
+                      # what the tensor cores execute: every tile is a dense 16 x CW x n product
+                      executed_mma_gflop_rank0=2.0 * tiles_local * 16 * btcf.col_window * n_feat / 1e9,
+                      graph_replay_ms_per_step=graph_ms, allgather_c_ms=allgather_ms)
         line = {"metric": "SpMM effective GFLOP/s (2*nnz*N)", "value": value, "unit": "GFLOP/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f16" if dtype_name == "f16" else "tf32",
