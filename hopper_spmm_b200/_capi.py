@@ -44,6 +44,7 @@ SIGNATURES = {
     "b200spmm_btcf_data": (vp, [vp]),
     "b200spmm_btcf_rowIdx": (vp, [vp]),
     "b200spmm_btcf_destroy": (None, [vp]),
+    "b200spmm_btcf_rewindow": (C.c_int, [C.POINTER(BtcfInfo), vp, vp, vp, vp, C.c_int, C.c_int, C.POINTER(vp)]),
     "b200spmm_csr2btcf_nobitmap_device": (C.c_int, [u64, u64, u64, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp,
                                                     C.POINTER(vp)]),
     "b200spmm_dbtcf_info": (C.c_int, [vp, C.POINTER(BtcfInfo)]),
@@ -98,6 +99,7 @@ SIGNATURES = {
     "b200spmm_kat_instr_desc": (u32, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "b200spmm_kat_tma": (C.c_int, [vp, u64, u64, u64, C.c_int, u32, u32, C.c_int, vp, C.c_int, u32, vp, u32,
                                     C.c_int]),
+    "b200spmm_kat_umma_rate": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double), C.c_int]),
 }
 
 _lib = None

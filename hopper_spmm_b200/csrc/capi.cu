@@ -330,6 +330,25 @@ int b200spmm_csr2btcf_nobitmap(uint64_t rows, uint64_t cols, uint64_t nnz, const
     return B200SPMM_OK;
 }
 
+int b200spmm_btcf_rewindow(const b200spmm_btcf_info_t *info, const uint32_t *rowOffset, const uint32_t *tcA2B,
+                           const void *data, const uint32_t *rowIdx, int row_window, int n_threads,
+                           b200spmm_btcf_t **out) {
+    if (!out) return B200SPMM_ERR_INVALID_ARG;
+    *out = nullptr;
+    if (!info || !rowOffset) return B200SPMM_ERR_INVALID_ARG;
+    if (rowOffset[info->eff_row_windows] != info->total_tiles) return B200SPMM_ERR_INVALID_ARG;
+    b200spmm_btcf *h = new (std::nothrow) b200spmm_btcf();
+    if (!h) return B200SPMM_ERR_NO_MEMORY;
+    int st = rewindow_btcf(info->rows, info->cols, info->nnzs, info->dtype, info->row_window, info->col_window,
+                           info->eff_row_windows, rowOffset, tcA2B, data, rowIdx, row_window, n_threads, &h->f);
+    if (st != B200SPMM_OK) {
+        delete h;
+        return st;
+    }
+    *out = h;
+    return B200SPMM_OK;
+}
+
 int b200spmm_btcf_info(const b200spmm_btcf_t *h, b200spmm_btcf_info_t *info) {
     if (!h || !info) return B200SPMM_ERR_INVALID_ARG;
     const Btcf &f = h->f;

@@ -159,6 +159,113 @@ int convert_csr_to_btcf(uint64_t rows, uint64_t cols, uint64_t nnz, const uint32
     return B200SPMM_OK;
 }
 
+int rewindow_btcf(uint64_t rows, uint64_t cols, uint64_t nnz, int dtype, int rw_in, int col_window,
+                  uint64_t eff_row_windows, const uint32_t *in_rowOffset, const uint32_t *in_tcA2B,
+                  const void *in_data, const uint32_t *in_rowIdx, int rw_out, int n_threads, Btcf *out) {
+    if (!out || !in_rowOffset) return B200SPMM_ERR_INVALID_ARG;
+    if (dtype != B200SPMM_F16 && dtype != B200SPMM_TF32) return B200SPMM_ERR_INVALID_ARG;
+    if (rw_in < 1 || rw_out < rw_in || rw_out % rw_in || (rw_out != 8 && rw_out != 16)) return B200SPMM_ERR_INVALID_ARG;
+    if (col_window != 4 && col_window != 8 && col_window != 16) return B200SPMM_ERR_INVALID_ARG;
+    if (rows >= 0xFFFFFFFFull || cols > 0xFFFFFFFFull) return B200SPMM_ERR_UNSUPPORTED;
+    const uint64_t eff_in = eff_row_windows, RWI = (uint64_t)rw_in, RWO = (uint64_t)rw_out, CW = (uint64_t)col_window;
+    const uint64_t tiles_in = in_rowOffset[eff_in];
+    if (in_rowOffset[0] != 0 || (eff_in && (!in_rowIdx || !in_tcA2B || !in_data))) return B200SPMM_ERR_INVALID_ARG;
+    const int esz = dtype == B200SPMM_F16 ? 2 : 4;
+
+    // Input windows are listed by ascending first row; a run of them that falls into one output
+    // window is a group.  group_first[g] = first input window of group g.
+    std::vector<uint64_t> group_first;
+    for (uint64_t i = 0; i < eff_in; ++i) {
+        const uint64_t r = in_rowIdx[i];
+        if (r >= rows || r % RWI || in_rowOffset[i + 1] <= in_rowOffset[i] || in_rowOffset[i + 1] > tiles_in)
+            return B200SPMM_ERR_INVALID_ARG;
+        if (i && r <= in_rowIdx[i - 1]) return B200SPMM_ERR_INVALID_ARG;
+        if (i == 0 || r / RWO != in_rowIdx[i - 1] / RWO) group_first.push_back(i);
+    }
+    const uint64_t eff = group_first.size();
+    group_first.push_back(eff_in);
+
+    // Sorted union of a group's column lists (each list ascending, padded with kIdxMax at its end).
+    std::atomic<int> bad{0};
+    auto group_columns = [&](uint64_t g, std::vector<uint32_t> *u) {
+        u->clear();
+        for (uint64_t i = group_first[g]; i < group_first[g + 1]; ++i) {
+            const uint32_t *lo = in_tcA2B + (uint64_t)in_rowOffset[i] * CW, *hi = in_tcA2B + (uint64_t)in_rowOffset[i + 1] * CW;
+            const uint32_t *end = hi;
+            while (end > lo && end[-1] == kIdxMax) --end;
+            if ((uint64_t)(hi - end) >= CW || end == lo) bad = 1;  // padding fills the last tile only
+            for (const uint32_t *p = lo; p < end; ++p)
+                if (*p >= cols || (p > lo && *p <= p[-1])) bad = 1;
+            const size_t mid = u->size();
+            u->insert(u->end(), lo, end);
+            std::inplace_merge(u->begin(), u->begin() + mid, u->end());
+        }
+        u->erase(std::unique(u->begin(), u->end()), u->end());
+    };
+
+    std::vector<uint32_t> group_tiles(eff);
+    parallel_chunks(eff, 256, n_threads, [&](uint64_t lo, uint64_t hi) {
+        std::vector<uint32_t> u;
+        for (uint64_t g = lo; g < hi; ++g) {
+            group_columns(g, &u);
+            group_tiles[g] = (uint32_t)((u.size() + CW - 1) / CW);
+        }
+    });
+    if (bad) return B200SPMM_ERR_INVALID_ARG;
+    uint64_t tiles = 0;
+    for (uint64_t g = 0; g < eff; ++g) tiles += group_tiles[g];
+    if (tiles > 0xFFFFFFFFull) return B200SPMM_ERR_UNSUPPORTED;
+
+    Btcf &f = *out;
+    f = Btcf();
+    f.rows = rows;
+    f.cols = cols;
+    f.nnzs = nnz;
+    f.row_window = rw_out;
+    f.col_window = col_window;
+    f.dtype = dtype;
+    f.elt_size = esz;
+    f.total_row_windows = (rows + RWO - 1) / RWO;
+    f.eff_row_windows = eff;
+    f.total_tiles = tiles;
+    try {
+        f.rowOffset.assign(eff + 1, 0);
+        f.rowIdx.assign(eff, 0);
+        f.tcA2B.assign(tiles * CW, kIdxMax);
+        f.data.assign(tiles * RWO * CW * esz, 0);
+    } catch (const std::bad_alloc &) {
+        return B200SPMM_ERR_NO_MEMORY;
+    }
+    for (uint64_t g = 0; g < eff; ++g) {
+        f.rowOffset[g + 1] = f.rowOffset[g] + group_tiles[g];
+        f.rowIdx[g] = (uint32_t)(in_rowIdx[group_first[g]] / RWO * RWO);
+    }
+    const uint8_t *src = static_cast<const uint8_t *>(in_data);
+    parallel_chunks(eff, 256, n_threads, [&](uint64_t lo, uint64_t hi) {
+        std::vector<uint32_t> u;
+        for (uint64_t g = lo; g < hi; ++g) {
+            group_columns(g, &u);
+            const uint64_t tile0 = f.rowOffset[g];
+            std::copy(u.begin(), u.end(), f.tcA2B.begin() + tile0 * CW);
+            for (uint64_t i = group_first[g]; i < group_first[g + 1]; ++i) {
+                const uint64_t row_shift = in_rowIdx[i] - f.rowIdx[g];  // rows of this input window inside the group
+                size_t s = 0;  // position in u; the input list is ascending, so s only moves forward
+                for (uint64_t t = in_rowOffset[i]; t < in_rowOffset[i + 1]; ++t)
+                    for (uint64_t lc = 0; lc < CW; ++lc) {
+                        const uint32_t c = in_tcA2B[t * CW + lc];
+                        if (c == kIdxMax) break;
+                        while (u[s] != c) ++s;
+                        const uint64_t ot = tile0 + s / CW, olc = s % CW;
+                        for (uint64_t lr = 0; lr < RWI; ++lr)
+                            std::memcpy(&f.data[((ot * RWO + row_shift + lr) * CW + olc) * esz],
+                                        src + ((t * RWI + lr) * CW + lc) * esz, esz);
+                    }
+            }
+        }
+    });
+    return B200SPMM_OK;
+}
+
 int shard_rows(uint64_t rows, const uint32_t *row_ptr, int row_window, int parts, uint64_t row_charge,
                uint64_t *row_begin) {
     if (!row_ptr || !row_begin || parts < 1 || row_window < 1) return B200SPMM_ERR_INVALID_ARG;

@@ -35,6 +35,16 @@ int convert_csr_to_btcf(uint64_t rows, uint64_t cols, uint64_t nnz, const uint32
                         const uint32_t *col_idx, const void *values, int dtype, int row_window, int col_window,
                         int n_threads, Btcf *out);
 
+// Re-windows a condensed format: `in_*` describe a format with row windows of rw_in rows (the
+// reference builds 8, src/common.h:17); the result has windows of rw_out rows (a multiple of
+// rw_in) and is, bit for bit, what convert_csr_to_btcf gives at rw_out for the same matrix: the
+// column list of an output window is the union of the lists of the input windows it covers, and
+// every stored tile entry moves to its row and column slot there.  Lets a format produced by the
+// reference's own CSR2BTCFNOBITMAP feed the 16-row kernels without going back to the CSR.
+int rewindow_btcf(uint64_t rows, uint64_t cols, uint64_t nnz, int dtype, int rw_in, int col_window,
+                  uint64_t eff_row_windows, const uint32_t *in_rowOffset, const uint32_t *in_tcA2B,
+                  const void *in_data, const uint32_t *in_rowIdx, int rw_out, int n_threads, Btcf *out);
+
 int shard_rows(uint64_t rows, const uint32_t *row_ptr, int row_window, int parts, uint64_t row_charge,
                uint64_t *row_begin);
 

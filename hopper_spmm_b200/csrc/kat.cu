@@ -118,6 +118,71 @@ kat_tma_kernel(const __grid_constant__ CUtensorMap tmap, const int32_t *__restri
         *reinterpret_cast<uint32_t *>(dump + i) = *reinterpret_cast<const uint32_t *>(area + i);
 }
 
+// Issue-rate probe: `issuers` threads (lane 0 of warps 1 and 2) each issue `count` MMAs of
+// M = m, N = n, K = 32 bytes back to back into their own accumulator, operands rotating over
+// eight positions of a zero-filled image laid out as the SpMM kernel lays them out (operand A
+// MN-major under the 128-byte swizzle, operand B K-major under the 32-byte swizzle).
+// cycles[0] = clocks the first issuer spent issuing, cycles[1] = issuing plus draining.
+__global__ void __launch_bounds__(128, 1)
+kat_umma_rate_kernel(int tf32, uint32_t idesc, int count, int issuers, long long *__restrict__ cycles,
+                     uint32_t *__restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t done_bar[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ uint32_t abort_flag;
+    constexpr uint32_t kImageBytes = 64u * 1024u, kBOff = 32u * 1024u, kCols = 512;
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t *area = smem_raw + pad;
+    const uint32_t area_addr = raw_addr + pad;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (uint32_t i = tid * 16u; i < kImageBytes; i += blockDim.x * 16u) *reinterpret_cast<uint4 *>(area + i) = make_uint4(0, 0, 0, 0);
+    if (tid == 0) {
+        abort_flag = 0;
+        ptx::mbar_init(ptx::smem_u32(&done_bar[0]), 1);
+        ptx::mbar_init(ptx::smem_u32(&done_bar[1]), 1);
+        ptx::fence_mbar_init();
+    }
+    ptx::fence_proxy_async_smem();
+    if (warp == 0) {
+        ptx::tmem_alloc(ptx::smem_u32(&tmem_base_slot), kCols);
+        ptx::tmem_relinquish_alloc_permit();
+    }
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    ptx::tcgen05_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+    if (warp >= 1 && warp <= issuers && lane == 0) {
+        const int w = warp - 1;
+        const uint64_t a0 = tf32 ? ptx::make_smem_desc(area_addr, 1024, 512, ptx::kSwizzle128BBase32B)
+                                 : ptx::make_smem_desc(area_addr, 2048, 1024, ptx::kSwizzle128B);
+        const uint64_t b0 = ptx::make_smem_desc(area_addr + kBOff, 16, 256, ptx::kSwizzle32B);
+        const uint32_t a_hi = (uint32_t)(a0 >> 32), b_hi = (uint32_t)(b0 >> 32), a_lo = (uint32_t)a0, b_lo = (uint32_t)b0;
+        const uint32_t acc = tmem_base + (uint32_t)w * 256u;
+        const long long t0 = clock64();
+        for (int i = 0; i < count; ++i) {
+            // operand A advances by 4 KB (one gathered tile), operand B by 512 bytes (one sparse tile)
+            if (tf32)
+                ptx::umma_tf32_ss_lohi(acc, a_lo + (uint32_t)(i & 7) * 256u, a_hi, b_lo + (uint32_t)(i & 7) * 32u, b_hi, idesc, i > 0);
+            else
+                ptx::umma_f16_ss_lohi(acc, a_lo + (uint32_t)(i & 7) * 256u, a_hi, b_lo + (uint32_t)(i & 7) * 32u, b_hi, idesc, i > 0);
+        }
+        const long long t1 = clock64();
+        ptx::umma_commit(ptx::smem_u32(&done_bar[w]));
+        const bool ok = ptx::mbar_wait(ptx::smem_u32(&done_bar[w]), 0, &abort_flag, kDeviceWaitLimitNs);
+        const long long t2 = clock64();
+        if (!ok) atomicOr(status, kDevStatusTimeout);
+        if (w == 0) {
+            cycles[0] = t1 - t0;
+            cycles[1] = t2 - t0;
+        }
+    }
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    ptx::tcgen05_fence_after_sync();
+    if (warp == 0) ptx::tmem_dealloc(tmem_base, kCols);
+}
+
 struct DevBuf {
     void *p = nullptr;
     ~DevBuf() { if (p) cudaFree(p); }
@@ -212,5 +277,31 @@ extern "C" int b200spmm_kat_tma(const void *tensor, uint64_t inner_elems, uint64
     uint32_t status = 0;
     B200_CUDA_TRY(cudaMemcpy(&status, d_status.p, 4, cudaMemcpyDeviceToHost));
     B200_CUDA_TRY(cudaMemcpy(dump, d_dump.p, dump_bytes, cudaMemcpyDeviceToHost));
+    return (status & kDevStatusTimeout) ? B200SPMM_ERR_DEVICE_TIMEOUT : B200SPMM_OK;
+}
+
+extern "C" int b200spmm_kat_umma_rate(int tf32, int m, int n, int count, int issuers, double *cycles_per_mma, int device) {
+    if (!cycles_per_mma || (m != 64 && m != 128) || n < 16 || n > 256 || n % 16 || count < 1 || count > (1 << 20) ||
+        issuers < 1 || issuers > 2)
+        return B200SPMM_ERR_INVALID_ARG;
+    int st = check_device(device);
+    if (st != B200SPMM_OK) return st;
+    DevBuf d_cycles, d_status;
+    B200_CUDA_TRY(cudaMalloc(&d_cycles.p, 2 * sizeof(long long)));
+    B200_CUDA_TRY(cudaMemset(d_cycles.p, 0, 2 * sizeof(long long)));
+    B200_CUDA_TRY(cudaMalloc(&d_status.p, 4));
+    B200_CUDA_TRY(cudaMemset(d_status.p, 0, 4));
+    const uint32_t idesc = ptx::make_instr_desc(tf32 ? ptx::kFmtTF32 : ptx::kFmtF16, (uint32_t)m, (uint32_t)n, true, false);
+    const size_t smem = 64 * 1024 + 1024 + 4096;
+    B200_CUDA_TRY(cudaFuncSetAttribute(kat_umma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kat_umma_rate_kernel<<<1, 128, smem>>>(tf32 ? 1 : 0, idesc, count, issuers, (long long *)d_cycles.p, (uint32_t *)d_status.p);
+    B200_CUDA_TRY(cudaGetLastError());
+    B200_CUDA_TRY(cudaDeviceSynchronize());
+    uint32_t status = 0;
+    long long cycles[2] = {0, 0};
+    B200_CUDA_TRY(cudaMemcpy(&status, d_status.p, 4, cudaMemcpyDeviceToHost));
+    B200_CUDA_TRY(cudaMemcpy(cycles, d_cycles.p, sizeof(cycles), cudaMemcpyDeviceToHost));
+    cycles_per_mma[0] = (double)cycles[0] / count;
+    cycles_per_mma[1] = (double)cycles[1] / count;
     return (status & kDevStatusTimeout) ? B200SPMM_ERR_DEVICE_TIMEOUT : B200SPMM_OK;
 }

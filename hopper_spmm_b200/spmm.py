@@ -126,6 +126,38 @@ def CSR2BTCFNOBITMAP(csr: CSR_MTX, btcf: BTCF_MTX_NO_BITMAP | None = None, row_w
     return btcf
 
 
+def rewindow(rows: int, cols: int, nnzs: int, rowOffset, tcA2B, data, rowIdx, row_window_in: int = 8,
+             row_window: int = ROW_WINDOW, n_threads: int = 0) -> BTCF_MTX_NO_BITMAP:
+    """A BTCF_MTX_NO_BITMAP given as its arrays - e.g. one the reference's own CSR2BTCFNOBITMAP built
+    with its fixed 8-row windows (src/common.h:17, src/utils/convert.h:146-225) - brought to the
+    ``row_window`` the kernels consume.  Bit-identical to converting the matrix at that height."""
+    data = np.ascontiguousarray(data)
+    if data.dtype not in (np.float16, np.float32):
+        raise TypeError("data must be float16 or float32")
+    rowOffset = np.ascontiguousarray(rowOffset, np.uint32)
+    tcA2B = np.ascontiguousarray(tcA2B, np.uint32)
+    rowIdx = np.ascontiguousarray(rowIdx, np.uint32)
+    if rowOffset.size < 1 or rowIdx.size != rowOffset.size - 1:
+        raise ValueError("rowOffset holds one entry more than rowIdx")
+    tiles = int(rowOffset[-1])
+    if tiles and (tcA2B.size % tiles or data.size != tiles * row_window_in * (tcA2B.size // tiles)):
+        raise ValueError("tcA2B and data do not describe rowOffset[-1] tiles of row_window_in rows")
+    info = capi.BtcfInfo()
+    info.rows, info.cols, info.nnzs = rows, cols, nnzs
+    info.total_row_windows = (rows + row_window_in - 1) // row_window_in
+    info.eff_row_windows, info.total_tiles = rowIdx.size, tiles
+    info.row_window = row_window_in
+    info.col_window = tcA2B.size // tiles if tiles else (16 if data.dtype == np.float16 else 8)
+    info.dtype, info.elt_size = _dtype_code(data.dtype), data.dtype.itemsize
+    h = C.c_void_p()
+    st = capi.lib().b200spmm_btcf_rewindow(C.byref(info), rowOffset.ctypes.data, tcA2B.ctypes.data, data.ctypes.data,
+                                           rowIdx.ctypes.data, row_window, n_threads, C.byref(h))
+    capi.check(st, "b200spmm_btcf_rewindow")
+    out = BTCF_MTX_NO_BITMAP()
+    out._adopt(h)
+    return out
+
+
 class DeviceBtcf:
     """BTCF_MTX_NO_BITMAP (src/utils/class.h:74-85) resident on the GPU, made by the device-side
     converter from CSR tensors that already live there."""

@@ -86,6 +86,21 @@ const uint32_t *b200spmm_btcf_rowOffset(const b200spmm_btcf_t *f); /* [eff_row_w
 const uint32_t *b200spmm_btcf_tcA2B(const b200spmm_btcf_t *f);     /* [total_tiles * col_window]         */
 const void *b200spmm_btcf_data(const b200spmm_btcf_t *f);          /* [total_tiles * row_window * col_window] */
 const uint32_t *b200spmm_btcf_rowIdx(const b200spmm_btcf_t *f);    /* [eff_row_windows]                  */
+/*
+ * Re-windows a BTCF_MTX_NO_BITMAP given as its host arrays (src/utils/class.h:74-85; `info`
+ * carries rows, cols, nnzs, eff_row_windows, total_tiles, row_window, col_window, dtype): the
+ * result has windows of `row_window` rows, a multiple of info->row_window, and is bit-identical
+ * to converting the same matrix directly at that height.  The reference's converter is fixed at
+ * 8-row windows (ROW_WINDOW, src/common.h:17) while the sm_100a kernels consume 16: this is how a
+ * format built by the reference's own CSR2BTCFNOBITMAP (src/utils/convert.h:146-225) reaches
+ * b200spmm_plan_create, in place of handing it to fp16_spmm (src/fp16.cu:221).  The input is
+ * validated (ascending aligned windows, ascending columns below cols, padding only at the end of
+ * a window's last tile); anything else fails with B200SPMM_ERR_INVALID_ARG.
+ */
+int b200spmm_btcf_rewindow(const b200spmm_btcf_info_t *info, const uint32_t *rowOffset, const uint32_t *tcA2B,
+                           const void *data, const uint32_t *rowIdx, int row_window, int n_threads,
+                           b200spmm_btcf_t **out);
+
 /* The reference's structs are freed by going out of scope (std::vector members). */
 void b200spmm_btcf_destroy(b200spmm_btcf_t *f);
 

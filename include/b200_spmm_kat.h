@@ -53,6 +53,19 @@ int b200spmm_kat_tma(const void *tensor, uint64_t inner_elems, uint64_t rows, ui
                      uint32_t box_inner, uint32_t box_rows, int swizzle, const int32_t *loads, int n_loads,
                      uint32_t expect_bytes, void *dump, uint32_t dump_bytes, int device);
 
+/*
+ * Issue-rate probe for the SpMM's MMA shape.  `issuers` (1 or 2) threads of one CTA each issue
+ * `count` tcgen05.mma of M = m (64 or 128), N = n (16..256, multiple of 16), K = 32 bytes back to
+ * back into their own TMEM accumulator, with the operand layouts of the SpMM kernel (operand A
+ * MN-major, 128-byte swizzle; operand B K-major, 32-byte swizzle; zero-filled).
+ * cycles_per_mma[0] = SM clocks per MMA the first issuer spent in its issue loop,
+ * cycles_per_mma[1] = the same including the wait for the last MMA to retire.
+ * It measures what one condensed tile costs the tensor pipe whatever its fill.  The reference
+ * times its MMA chain only as part of a whole kernel (the consumer loop of
+ * test/03.warp_specialized/main.cu:87-100 inside the event window of its main).
+ */
+int b200spmm_kat_umma_rate(int tf32, int m, int n, int count, int issuers, double *cycles_per_mma, int device);
+
 #ifdef __cplusplus
 }
 #endif

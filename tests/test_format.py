@@ -213,3 +213,68 @@ def test_row_bands_cut_only_between_windows_and_cover_all_rows():
             assert slot_window[2 * c] == 0xFFFFFFFF and br[k] == row_idx[wfirst[c]]
         if eff >= 5000 and n_parts >= 148 * 16:
             assert nb == want
+
+
+def rewound(f, rw_out=16, rows=None, threads=0):
+    return hs.rewindow(f.rows if rows is None else rows, f.cols, f.nnzs, f.rowOffset, f.tcA2B, f.data, f.rowIdx,
+                       row_window_in=f.row_window, row_window=rw_out, n_threads=threads)
+
+
+@pytest.mark.parametrize("flavour", ["fp16", "tf32"])
+@pytest.mark.parametrize("case", ["hand", "rand_a", "rand_b"])
+def test_reference_built_format_rewindows_to_the_direct_conversion(flavour, case):
+    # the arrays the reference's own CSR2BTCFNOBITMAP produced (8-row windows), brought to 16 rows
+    g = np.load(os.path.join(GOLDEN, f"format_ref_{flavour}.npz"))
+    rows, cols = (int(x) for x in g[f"{case}_shape"])
+    rp, ci, v = g[f"{case}_row_ptr"], g[f"{case}_col_idx"], g[f"{case}_values"]
+    f16 = hs.rewindow(rows, cols, len(ci), g[f"{case}_rowOffset"], g[f"{case}_tcA2B"], g[f"{case}_data"],
+                      g[f"{case}_rowIdx"], row_window_in=8, row_window=16)
+    direct = convert(rows, cols, rp, ci, v, rw=16)
+    assert same_format(f16, direct)
+    assert (f16.row_window, f16.col_window, f16.total_row_windows) == (16, direct.col_window, (rows + 15) // 16)
+    assert same_format(f16, oracle.csr2btcf_nobitmap(rows, cols, rp, ci, v, 16, direct.col_window))
+
+
+@pytest.mark.parametrize("dt,cw", [(np.float16, 16), (np.float32, 8), (np.float32, 4)])
+def test_rewindow_random_matrices(dt, cw):
+    shapes = [(1, 1, 1.0), (9, 40, 0.3), (16, 16, 0.5), (23, 33, 0.2), (203, 517, 0.03), (500, 70000, 0.0005), (96, 7, 0.6)]
+    for seed, (rows, cols, dens) in enumerate(shapes):
+        rows, cols, rp, ci, v = random_csr(rows, cols, dens, seed, dt,
+                                           empty_rows=[(16, 48), (56, 64), (96, 104)] if rows > 104 else (),
+                                           dense_rows=[3] if cols < 1000 and rows > 3 else ())
+        v = v.copy()
+        v[::7] = 0  # stored zeros keep their column
+        f8 = convert(rows, cols, rp, ci, v, 8, cw)
+        assert same_format(rewound(f8, 16, threads=seed % 3), convert(rows, cols, rp, ci, v, 16, cw))
+        assert same_format(rewound(f8, 8), f8)
+
+
+def test_rewindow_of_an_empty_format_and_bad_input():
+    f8 = convert(40, 10, np.zeros(41, np.uint32), np.zeros(0, np.uint32), np.zeros(0, np.float16), rw=8)
+    f16 = rewound(f8)
+    assert (f16.eff_row_windows, f16.total_tiles, f16.total_row_windows) == (0, 0, 3)
+    rows, cols, rp, ci, v = random_csr(64, 50, 0.1, 5)
+    f8 = convert(rows, cols, rp, ci, v, rw=8)
+
+    def broken(**kw):
+        a = {k: np.array(getattr(f8, k)) for k in FORMAT_FIELDS}
+        for k, fn in kw.items():
+            fn(a[k])
+        with pytest.raises(RuntimeError):
+            hs.rewindow(rows, cols, f8.nnzs, a["rowOffset"], a["tcA2B"], a["data"], a["rowIdx"], 8, 16)
+
+    def swap_first_two(x):
+        x[[0, 1]] = x[[1, 0]]
+
+    def set_first(value):
+        def fn(x):
+            x[0] = value
+        return fn
+
+    broken(tcA2B=swap_first_two)              # columns of a window must ascend
+    broken(tcA2B=set_first(cols))             # column past the matrix
+    broken(rowIdx=set_first(3))               # windows start on multiples of the input height
+    broken(rowIdx=swap_first_two)             # windows must ascend
+    broken(rowOffset=set_first(1))            # rowOffset starts at zero
+    with pytest.raises(RuntimeError):         # 16 -> 8 is not a re-windowing
+        rewound(convert(rows, cols, rp, ci, v, rw=16), 8)

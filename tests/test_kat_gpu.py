@@ -120,3 +120,24 @@ def test_tma_gather4_lands_in_operand_layout(dt):
         if r < K:
             gathered[k] = B[r]
     assert dump.tobytes() == ku.pack_gathered(np.ascontiguousarray(gathered.T))
+
+
+@pytest.mark.parametrize("tf32", [False, True])
+def test_mma_issue_rate_of_the_spmm_shape(tf32):
+    # One MMA per condensed tile and 128-feature chunk: its cost does not depend on the tile's fill
+    # and, up to N = 64, not on N either - the 4 KB operand of gathered rows sets it.  The bounds
+    # are loose sanity limits (measured: ~59 SM clocks with one issuing thread, ~78 per thread
+    # with two, i.e. ~39 per MMA and SM).
+    import ctypes as C
+    from hopper_spmm_b200 import _capi as capi
+    lib = capi.lib()
+    out = (C.c_double * 2)()
+    seen = {}
+    for n, issuers in ((16, 1), (64, 1), (16, 2)):
+        assert lib.b200spmm_kat_umma_rate(int(tf32), 128, n, 512, issuers, out, 0) == 0
+        seen[(n, issuers)] = (out[0], out[1])
+        assert 4.0 < out[0] <= out[1] < 2000.0, seen
+    # two issuing threads together get more MMAs through the SM than one
+    assert seen[(16, 2)][1] / 2 < seen[(16, 1)][1] * 1.05, seen
+    assert lib.b200spmm_kat_umma_rate(0, 128, 24, 16, 1, out, 0) == capi.ERR_INVALID_ARG
+    assert lib.b200spmm_kat_umma_rate(0, 128, 16, 16, 3, out, 0) == capi.ERR_INVALID_ARG

@@ -214,6 +214,29 @@ def test_bitmap_format_feeds_the_spmm_after_expansion():
         plan.close()
 
 
+@pytest.mark.parametrize("flavour", ["fp16", "tf32"])
+def test_format_built_by_the_reference_converter_feeds_the_spmm(flavour):
+    # The committed arrays are the output of the reference's own CSR2BTCFNOBITMAP (8-row windows);
+    # re-windowed to 16 rows they go through the plan like a format converted here, and the product
+    # has the bits of the product from the direct conversion.
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", f"format_ref_{flavour}.npz"))
+    for case in ("hand", "rand_a", "rand_b"):
+        rows, cols = (int(x) for x in g[f"{case}_shape"])
+        rp, ci, v = g[f"{case}_row_ptr"], g[f"{case}_col_idx"], g[f"{case}_values"]
+        f = hs.rewindow(rows, cols, len(ci), g[f"{case}_rowOffset"], g[f"{case}_tcA2B"], g[f"{case}_data"],
+                        g[f"{case}_rowIdx"], row_window_in=8)
+        B = dense_b(cols, 72, 13, v.dtype)
+        plan = hs.SpmmPlan(f)
+        try:
+            out = plan.spmm_host(B)
+        finally:
+            plan.close()
+        parity.check(out, rows, rp, ci, v, B)
+        direct, _ = run_host(rows, cols, rp, ci, v, B)
+        assert np.array_equal(out.view(np.uint8), direct.view(np.uint8))
+
+
 @pytest.mark.parametrize("kind", ["fp16", "tf32"])
 def test_command_line_run_on_a_matrix_market_file(kind, tmp_path):
     # spmm_test <file> <N>: the reference's main (src/fp16.cu:283-319) with a result check added
