@@ -47,6 +47,22 @@ def test_converter_matches_live_reference(flavour, dt):
         assert same_format(mine, ref)
 
 
+@pytest.mark.parametrize("flavour,dt", [("fp16", np.float16), ("tf32", np.float32)])
+def test_live_reference_output_rewindows_to_the_sixteen_row_format(flavour, dt):
+    # the reference's converter runs here (8-row windows); its arrays, re-windowed by the library,
+    # must equal the restated converter's 16-row output
+    if not oracle.ref_available(flavour):
+        pytest.skip("reference harness not built (needs the reference sources)")
+    import hopper_spmm_b200 as hs
+    for seed in range(5):
+        rows, cols = [(17, 40), (64, 64), (333, 1000), (9, 5), (250, 77)][seed]
+        rows, cols, rp, ci, v = random_csr(rows, cols, [0.05, 0.3, 0.01, 0.5, 0.08][seed], seed, dt,
+                                           empty_rows=[(8, 24), (40, 48)] if rows > 48 else ())
+        ref = oracle.ref_convert(flavour, rows, cols, rp, ci, v)
+        f16 = hs.rewindow(rows, cols, len(ci), ref.rowOffset, ref.tcA2B, ref.data, ref.rowIdx, row_window_in=8)
+        assert same_format(f16, oracle.csr2btcf_nobitmap(rows, cols, rp, ci, v, 16, ref.col_window))
+
+
 def test_kat1_fp16_single_tile():
     # src/test_fp16.cu:407-415: A[i] = half(i+1) (64x16, K-major), B = 1 (8x16) -> C[r][c] = 256 r + 136
     A = np.arange(1, 64 * 16 + 1, dtype=np.float32).astype(np.float16).astype(np.float32).reshape(64, 16)
