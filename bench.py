@@ -212,6 +212,15 @@ def main():
     total_nnz = csr.nnz
     cols = B.shape[0]
     host_csr = part.numpy() if (rank == 0 and world == 1 and not args.no_cpu) else None  # only the CPU baseline needs it
+    # The end-to-end step on several GPUs sends every rank's rows of C to the host, so its row
+    # ranges are cut with the rows charged for those bytes (nearly equal row counts); the ranges
+    # of the device-resident measurement balance the product alone.
+    part_e2e = None
+    if world > 1 and not args.no_e2e:
+        c_item = 2 if dtype_name == "f16" else 4
+        e2e_charge = sharded.e2e_row_charge(n_feat, c_item)
+        _, q0, q1 = sharded.my_rows(csr.rows, rp_full, world, rank, row_charge=e2e_charge)
+        part_e2e = csr.row_slice(q0, q1)
     del csr
     torch.cuda.empty_cache()
     # conversion on the device: CSR tensors -> condensed tiles, all in HBM
@@ -307,7 +316,8 @@ def main():
         # the reference's operator keeps C in the matrix's element type (DENSE_MTX.values is MAT_VAL_TYPE,
         # src/utils/class.h:44-48: fp16 in the fp16 build): the host-buffer call is made the same way
         c_half = dtype_name == "f16"
-        hC = torch.empty(C_dev.shape, dtype=torch.float16 if c_half else torch.float32, pin_memory=True)
+        c_rows = C_dev.shape[0] if world == 1 else q1 - q0
+        hC = torch.empty((c_rows, n_feat), dtype=torch.float16 if c_half else torch.float32, pin_memory=True)
         torch.cuda.synchronize()
         hBn, hCn = hB.numpy(), hC.numpy()
         if world == 1:
@@ -317,14 +327,19 @@ def main():
             # N ranks behind one host: every rank uploads 1/N of the replicated B and the parts are
             # exchanged GPU to GPU (sharded.upload_replicated); then the rank's product, then its rows
             # of C back to the host.  Bytes are whole-job sums.
+            btcf_e = hs.DeviceBtcf(q1 - q0, cols, part_e2e.row_ptr.to(torch.int32), part_e2e.col_idx, part_e2e.values,
+                                   device=local_rank)
+            del part_e2e
+            plan_e = hs.SpmmPlan(btcf_e, device=local_rank)
+            log(f"rank {rank}: end-to-end rows [{q0},{q1}) (row charge {e2e_charge}) tiles={btcf_e.total_tiles}")
             dB = torch.empty_like(B)
-            dC = torch.empty(C_dev.shape, dtype=hC.dtype, device=dev)
+            dC = torch.empty((q1 - q0, n_feat), dtype=hC.dtype, device=dev)
 
             def step():
                 sharded.upload_replicated(hB, dB)
-                plan.spmm(dB, dC, c_half=c_half, sync=False)
+                plan_e.spmm(dB, dC, c_half=c_half, sync=False)
                 hC.copy_(dC, non_blocking=True)
-                plan.sync()
+                plan_e.sync()
             h2d_bytes = int(hB.numel() * hB.element_size())
         step()  # warm-up: allocates the plan's device buffers
         barrier()
@@ -345,6 +360,8 @@ def main():
                "c_dtype": "f16" if c_half else "f32",
                "call": ("b200spmm_spmm_host (fp16_spmm / tf32_spmm with host B and C)" if world == 1 else
                         "per rank: 1/N of host B in + GPU-to-GPU exchange, b200spmm_spmm, its rows of C out to the host")}
+        if world > 1:
+            e2e["row_charge"] = e2e_charge  # rows charged for their bytes of C over the host link
         assert bool(torch.isfinite(hC[:: max(1, hC.shape[0] // 4096)]).all())
 
     # ---- roofline of the SpMM kernel on this rank's launch

@@ -15,6 +15,19 @@ from . import spmm as _spmm
 
 ROW_CHARGE = 6  # entries a row is charged on top of its own when the ranks' shares are cut
 
+# The fit behind ROW_CHARGE (default workload, one B200): a rank's product takes about 0.0253 ms per
+# million entries plus 0.153 ms per million rows.
+_MS_PER_M_ENTRIES = 0.0253
+
+
+def e2e_row_charge(n: int, c_itemsize: int, host_link_gbs: float = 52.0, row_charge: int = ROW_CHARGE) -> int:
+    """Row charge for cuts that balance a rank's whole step when its rows of C go back to the host
+    every step: a row then also costs its n * c_itemsize bytes over the rank's host link
+    (about 52 GB/s measured device to host), which outweighs the product itself - the cuts
+    become nearly equal row counts."""
+    ms_per_m_rows = n * c_itemsize / (host_link_gbs * 1e9) * 1e3 * 1e6
+    return row_charge + int(round(ms_per_m_rows / _MS_PER_M_ENTRIES))
+
 
 def my_rows(rows: int, row_ptr, world: int, rank: int, row_charge: int = ROW_CHARGE):
     """(cuts, r0, r1): the cuts for `world` ranks, balanced on nnz + row_charge per row, and this
