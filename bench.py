@@ -155,6 +155,9 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--scale-down", type=int, default=0)
     ap.add_argument("--allgather", action="store_true", help="also time the all-gather of the row-sharded C (N > 1)")
+    ap.add_argument("--e2e-row-charge", type=int, default=-1,
+                    help="entries a row is charged when the end-to-end step gets row ranges of its own (N > 1); "
+                         "-1 = the ranges of the device-resident measurement")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -212,14 +215,11 @@ def main():
     total_nnz = csr.nnz
     cols = B.shape[0]
     host_csr = part.numpy() if (rank == 0 and world == 1 and not args.no_cpu) else None  # only the CPU baseline needs it
-    # The end-to-end step on several GPUs sends every rank's rows of C to the host, so its row
-    # ranges are cut with the rows charged for those bytes (nearly equal row counts); the ranges
-    # of the device-resident measurement balance the product alone.
-    part_e2e = None
-    if world > 1 and not args.no_e2e:
-        c_item = 2 if dtype_name == "f16" else 4
-        e2e_charge = sharded.e2e_row_charge(n_feat, c_item)
-        _, q0, q1 = sharded.my_rows(csr.rows, rp_full, world, rank, row_charge=e2e_charge)
+    # The end-to-end step on several GPUs uses the same row ranges unless --e2e-row-charge asks for
+    # ranges of its own (rows charged more: more even row counts, i.e. bytes of C per rank).
+    part_e2e, q0, q1 = None, r0, r1
+    if world > 1 and not args.no_e2e and args.e2e_row_charge >= 0:
+        _, q0, q1 = sharded.my_rows(csr.rows, rp_full, world, rank, row_charge=args.e2e_row_charge)
         part_e2e = csr.row_slice(q0, q1)
     del csr
     torch.cuda.empty_cache()
@@ -298,6 +298,9 @@ def main():
     if world > 1 and args.allgather:
         barrier()
         a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        full = sharded.allgather_rows(C_dev, cuts)  # untimed: the first exchange sets up the peer connections
+        del full
+        barrier()
         a0.record()
         full = sharded.allgather_rows(C_dev, cuts)
         a1.record()
@@ -327,11 +330,13 @@ def main():
             # N ranks behind one host: every rank uploads 1/N of the replicated B and the parts are
             # exchanged GPU to GPU (sharded.upload_replicated); then the rank's product, then its rows
             # of C back to the host.  Bytes are whole-job sums.
-            btcf_e = hs.DeviceBtcf(q1 - q0, cols, part_e2e.row_ptr.to(torch.int32), part_e2e.col_idx, part_e2e.values,
-                                   device=local_rank)
-            del part_e2e
-            plan_e = hs.SpmmPlan(btcf_e, device=local_rank)
-            log(f"rank {rank}: end-to-end rows [{q0},{q1}) (row charge {e2e_charge}) tiles={btcf_e.total_tiles}")
+            plan_e = plan
+            if part_e2e is not None:
+                btcf_e = hs.DeviceBtcf(q1 - q0, cols, part_e2e.row_ptr.to(torch.int32), part_e2e.col_idx, part_e2e.values,
+                                       device=local_rank)
+                del part_e2e
+                plan_e = hs.SpmmPlan(btcf_e, device=local_rank)
+                log(f"rank {rank}: end-to-end rows [{q0},{q1}) (row charge {args.e2e_row_charge}) tiles={btcf_e.total_tiles}")
             dB = torch.empty_like(B)
             dC = torch.empty((q1 - q0, n_feat), dtype=hC.dtype, device=dev)
 
@@ -361,7 +366,7 @@ def main():
                "call": ("b200spmm_spmm_host (fp16_spmm / tf32_spmm with host B and C)" if world == 1 else
                         "per rank: 1/N of host B in + GPU-to-GPU exchange, b200spmm_spmm, its rows of C out to the host")}
         if world > 1:
-            e2e["row_charge"] = e2e_charge  # rows charged for their bytes of C over the host link
+            e2e["row_charge"] = args.e2e_row_charge if args.e2e_row_charge >= 0 else sharded.ROW_CHARGE
         assert bool(torch.isfinite(hC[:: max(1, hC.shape[0] // 4096)]).all())
 
     # ---- roofline of the SpMM kernel on this rank's launch

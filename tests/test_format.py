@@ -279,17 +279,3 @@ def test_rewindow_of_an_empty_format_and_bad_input():
     with pytest.raises(RuntimeError):         # 16 -> 8 is not a re-windowing
         rewound(convert(rows, cols, rp, ci, v, rw=16), 8)
 
-
-def test_row_charge_for_steps_that_send_c_to_the_host_evens_out_the_row_counts():
-    from hopper_spmm_b200 import sharded
-    charge = sharded.e2e_row_charge(128, 2)
-    assert 150 < charge < 300 and sharded.e2e_row_charge(128, 4) > charge > sharded.e2e_row_charge(64, 2)
-    rows, parts = 4096, 4
-    per_row = np.full(rows, 2)
-    per_row[:256] = 200  # hub rows first, as in an R-MAT matrix
-    rp = np.concatenate([[0], np.cumsum(per_row)]).astype(np.uint32)
-    by_product = np.diff(hs.shard_rows(rows, rp, parts, row_charge=sharded.ROW_CHARGE))
-    by_step = np.diff(hs.shard_rows(rows, rp, parts, row_charge=charge))
-    assert by_product.sum() == by_step.sum() == rows
-    assert by_product.min() < 0.15 * rows / parts      # balanced on entries: the hub rank holds few rows
-    assert by_step.min() > 0.5 * rows / parts and by_step.max() < 1.3 * rows / parts
