@@ -1,10 +1,13 @@
-// spmm_test <matrix_file> <feature_dim> [fp16|tf32]
+// spmm_test <matrix_file> <feature_dim> [fp16|tf32] [rw8]
 //
 // The command-line run of the reference's main (src/fp16.cu:283-319) on top of the C ABI: load a
 // MatrixMarket file, convert it to the condensed format, fill B with rand() / RAND_MAX as the
 // reference does, time the SpMM with its protocol (3 warm-up launches, 5 timed ones) and print
 // the matrix summary and the timing block.  Unlike the reference, whose "result check" is an
 // empty comment, it then checks a sample of C's rows against a plain CSR product on the host.
+// With "rw8" the matrix is first converted with the reference's own 8-row windows (ROW_WINDOW,
+// src/common.h:17) and that format is re-windowed to the 16 rows the kernels consume - the route a
+// format built by the reference's converter takes.
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
@@ -31,13 +34,21 @@ float element(const void *values, bool f16, uint64_t i) {
 }  // namespace
 
 int main(int argc, char *argv[]) {
-    if (argc != 3 && argc != 4) {
-        std::printf("Usage: %s <matrix_file> <feature_dim> [fp16|tf32]\n", argv[0]);
+    if (argc < 3 || argc > 5) {
+        std::printf("Usage: %s <matrix_file> <feature_dim> [fp16|tf32] [rw8]\n", argv[0]);
         return 1;
     }
     const char *matrix_file = argv[1];
     const int64_t n = std::atoll(argv[2]);
-    const bool f16 = argc == 3 || std::strcmp(argv[3], "tf32") != 0;
+    bool f16 = true, via_rw8 = false;
+    for (int i = 3; i < argc; ++i) {
+        if (std::strcmp(argv[i], "tf32") == 0) f16 = false;
+        else if (std::strcmp(argv[i], "rw8") == 0) via_rw8 = true;
+        else if (std::strcmp(argv[i], "fp16") != 0) {
+            std::fprintf(stderr, "unknown option %s\n", argv[i]);
+            return 1;
+        }
+    }
     const int dtype = f16 ? B200SPMM_F16 : B200SPMM_TF32;
     if (n <= 0 || n % 8) {
         std::fprintf(stderr, "feature_dim must be a positive multiple of 8\n");
@@ -54,10 +65,21 @@ int main(int argc, char *argv[]) {
     const void *values = b200spmm_csr_values(csr);
 
     b200spmm_btcf_t *btcf = nullptr;
-    st = b200spmm_csr2btcf_nobitmap(rows, cols, nnz, row_ptr, col_idx, values, dtype, 16, 0, 0, &btcf);
+    st = b200spmm_csr2btcf_nobitmap(rows, cols, nnz, row_ptr, col_idx, values, dtype, via_rw8 ? 8 : 16, 0, 0, &btcf);
     if (st) return fail("CSR2BTCFNOBITMAP", st);
     b200spmm_btcf_info_t info;
     b200spmm_btcf_info(btcf, &info);
+    if (via_rw8) {  // the 8-row format, as the reference builds it, brought to 16-row windows
+        std::printf("8-row format: %llu non-empty row windows, %llu tiles\n", (unsigned long long)info.eff_row_windows,
+                    (unsigned long long)info.total_tiles);
+        b200spmm_btcf_t *wide = nullptr;
+        st = b200spmm_btcf_rewindow(&info, b200spmm_btcf_rowOffset(btcf), b200spmm_btcf_tcA2B(btcf), b200spmm_btcf_data(btcf),
+                                    b200spmm_btcf_rowIdx(btcf), 16, 0, &wide);
+        if (st) return fail("btcf_rewindow", st);
+        b200spmm_btcf_destroy(btcf);
+        btcf = wide;
+        b200spmm_btcf_info(btcf, &info);
+    }
     std::printf("=== BTCF matrix ===\n");
     std::printf("rows: %llu\n", (unsigned long long)info.rows);
     std::printf("cols: %llu\n", (unsigned long long)info.cols);

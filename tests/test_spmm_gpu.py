@@ -237,7 +237,7 @@ def test_format_built_by_the_reference_converter_feeds_the_spmm(flavour):
         assert np.array_equal(out.view(np.uint8), direct.view(np.uint8))
 
 
-@pytest.mark.parametrize("kind", ["fp16", "tf32"])
+@pytest.mark.parametrize("kind", ["fp16", "tf32", "fp16 rw8", "tf32 rw8"])
 def test_command_line_run_on_a_matrix_market_file(kind, tmp_path):
     # spmm_test <file> <N>: the reference's main (src/fp16.cu:283-319) with a result check added
     import os
@@ -250,6 +250,7 @@ def test_command_line_run_on_a_matrix_market_file(kind, tmp_path):
             for p in range(rp[r], rp[r + 1]):
                 fh.write("%d %d %.6f\n" % (r + 1, ci[p] + 1, v[p]))
     exe = os.path.join(os.path.dirname(hs.__file__), "spmm_test")
-    out = subprocess.run([exe, str(path), "64", kind], capture_output=True, text=True, timeout=300)
+    out = subprocess.run([exe, str(path), "64"] + kind.split(), capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stdout + out.stderr
     assert "nonzeros: %d" % len(ci) in out.stdout and "SPMM mean time" in out.stdout and "(ok," in out.stdout
+    assert ("8-row format:" in out.stdout) == kind.endswith("rw8") and "tiles (16x" in out.stdout
