@@ -215,11 +215,17 @@ def main():
     total_nnz = csr.nnz
     cols = B.shape[0]
     host_csr = part.numpy() if (rank == 0 and world == 1 and not args.no_cpu) else None  # only the CPU baseline needs it
-    # The end-to-end step on several GPUs uses the same row ranges unless --e2e-row-charge asks for
-    # ranges of its own (rows charged more: more even row counts, i.e. bytes of C per rank).
+    # Row ranges of the end-to-end step on several GPUs: the product's own, unless --e2e-row-charge
+    # asks for others.  Charging the rows for their bytes of C over the rank's host link (201
+    # entries per row at 128 fp16 features: 52 GB/s against 0.0253 ms per million entries) evens
+    # out the row counts, but did not pay reliably: ms per step with the product's ranges / with
+    # 201 per row, same box each pair: 109.5 / 97.7 on two GPUs (on other boxes 110 / 112-114 and
+    # 112 / 90), 105.1 / 103.6 on four, 67.6 / 78.4 on eight, where the host's memory system, not
+    # a rank's own link, limits the copies.
+    e2e_charge = args.e2e_row_charge
     part_e2e, q0, q1 = None, r0, r1
-    if world > 1 and not args.no_e2e and args.e2e_row_charge >= 0:
-        _, q0, q1 = sharded.my_rows(csr.rows, rp_full, world, rank, row_charge=args.e2e_row_charge)
+    if world > 1 and not args.no_e2e and e2e_charge >= 0:
+        _, q0, q1 = sharded.my_rows(csr.rows, rp_full, world, rank, row_charge=e2e_charge)
         part_e2e = csr.row_slice(q0, q1)
     del csr
     torch.cuda.empty_cache()
@@ -336,7 +342,7 @@ def main():
                                        device=local_rank)
                 del part_e2e
                 plan_e = hs.SpmmPlan(btcf_e, device=local_rank)
-                log(f"rank {rank}: end-to-end rows [{q0},{q1}) (row charge {args.e2e_row_charge}) tiles={btcf_e.total_tiles}")
+                log(f"rank {rank}: end-to-end rows [{q0},{q1}) (row charge {e2e_charge}) tiles={btcf_e.total_tiles}")
             dB = torch.empty_like(B)
             dC = torch.empty((q1 - q0, n_feat), dtype=hC.dtype, device=dev)
 
@@ -366,7 +372,7 @@ def main():
                "call": ("b200spmm_spmm_host (fp16_spmm / tf32_spmm with host B and C)" if world == 1 else
                         "per rank: 1/N of host B in + GPU-to-GPU exchange, b200spmm_spmm, its rows of C out to the host")}
         if world > 1:
-            e2e["row_charge"] = args.e2e_row_charge if args.e2e_row_charge >= 0 else sharded.ROW_CHARGE
+            e2e["row_charge"] = e2e_charge if e2e_charge >= 0 else sharded.ROW_CHARGE
         assert bool(torch.isfinite(hC[:: max(1, hC.shape[0] // 4096)]).all())
 
     # ---- roofline of the SpMM kernel on this rank's launch
