@@ -2,10 +2,10 @@
 """Benchmark of the SpMM hot path: effective GFLOP/s (2*nnz*N) on seeded synthetic inputs.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload NAME] [--scale-down k]
+                    [--workload NAME] [--scale-down k] [--no-workloads]
 
 One "step" is one SpMM of the whole matrix.  With N > 1 (launched by torch.distributed.run, one
-rank per GPU) the matrix is cut into N nnz-balanced row-window ranges, B is replicated and every
+rank per GPU) the matrix is cut into N time-balanced row-window ranges, B is replicated and every
 rank multiplies its own range; there is no data-path collective, total work is fixed (strong
 scaling).  Rank 0 prints ONE JSON line.
 
@@ -14,7 +14,11 @@ scaling).  Rank 0 prints ONE JSON line.
               copied back inside the timed region (the converted matrix stays resident, like
               weights)
   roofline    algorithmic bytes of one launch / its duration against the measured HBM peak
-  cpu_baseline  the CPU oracle's CSR SpMM on a bounded row sample, all host threads
+  cpu_baseline  the CPU oracle's CSR SpMM on a bounded row sample, all host cores
+  parity      the timed result itself against the CPU oracle (a row sample holding the heaviest
+              rows, the first and the last window; every rank checks its own rows)
+  workloads   (1 GPU) the four other benchmark configurations at full size, each with its time
+              (L2 flushed between timed launches), roofline fraction, CPU baseline and parity record
 
 --impl reference times that CPU path alone (the reference project has no CSR-level SpMM and
 its GPU kernel is sm_90a-only and unfinished, so its own verifier arithmetic, restated in
@@ -34,20 +38,33 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))  # parity.py: the tolerance rules of the parity tests
 
 DEFAULT_WORKLOAD = "rmat24_sharded_fp16"
+OTHER_WORKLOADS = ("uniform_4096_fp16", "blocks_16384_tf32", "rmat20_gnn_fp16", "pruned_llm_fp16")
+L2_FLUSH_BYTES = 512 << 20  # written between timed launches of the smaller workloads (L2 is 126 MB)
 
 
 def log(*a):
     print("[bench]", *a, file=sys.stderr, flush=True)
 
 
+def host_cores() -> int:
+    """Cores this process may run on.  Taken from the machine, not from OMP_NUM_THREADS, which
+    torch.distributed.run sets to 1 for every rank."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def measured_peaks():
+    """(HBM GB/s, fp16/bf16 dense TFLOP/s, where they come from)."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         d = json.load(open(path))
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
 
 
 class ClockSampler:
@@ -117,24 +134,26 @@ def cpu_sample_rows(row_ptr_host: np.ndarray, target_nnz: int):
 
 
 def time_cpu_oracle(rp, ci, v, B_host, steps, warmup, budget_s=12.0, threads=0):
-    """GFLOP/s of the oracle's CSR SpMM (all host threads, or `threads`) on a row sample sized to the budget."""
+    """GFLOP/s of the oracle's CSR SpMM on `threads` host threads (0: every core of the machine) on a
+    row sample sized to the budget."""
     import oracle
     rows = len(rp) - 1
     n = B_host.shape[1]
-    threads = threads or oracle.max_threads()
+    threads = threads or host_cores()
     lo, hi = cpu_sample_rows(rp, 1 << 20)  # probe
     t0 = time.perf_counter()
-    oracle.spmm_csr(rows, rp, ci, v, B_host, n_threads=threads, row_begin=lo, row_end=hi)
+    oracle.spmm_csr(hi - lo, *slice_rows(rp, ci, v, lo, hi), B_host, n_threads=threads)
     probe = max(time.perf_counter() - t0, 1e-4)
     probe_nnz = int(rp[hi]) - int(rp[lo])
     per_step = budget_s / max(1, steps + warmup)
     target = int(min(int(rp[-1]), max(1 << 20, probe_nnz * per_step / probe)))
     lo, hi = cpu_sample_rows(rp, target)
-    nnz_s = int(rp[hi]) - int(rp[lo])
+    srp, sci, sv = slice_rows(rp, ci, v, lo, hi)
+    nnz_s = int(srp[-1])
     times = []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        oracle.spmm_csr(rows, rp, ci, v, B_host, n_threads=threads, row_begin=lo, row_end=hi)
+        oracle.spmm_csr(hi - lo, srp, sci, sv, B_host, n_threads=threads)
         if i >= warmup:
             times.append(time.perf_counter() - t0)
     t = float(np.mean(times))
@@ -143,7 +162,197 @@ def time_cpu_oracle(rp, ci, v, B_host, steps, warmup, budget_s=12.0, threads=0):
                       f"{t * 1e3:.1f} ms each"}, t
 
 
+def slice_rows(rp, ci, v, lo, hi):
+    a, b = int(rp[lo]), int(rp[hi])
+    return (np.asarray(rp[lo:hi + 1], dtype=np.int64) - a).astype(np.uint32), ci[a:b], v[a:b]
+
+
+def parity_ranges(rows: int, rp, want_rows: int = 1 << 15):
+    """Row ranges of the parity sample: the first rows (window 0; on the R-MAT matrices also the
+    heaviest rows, which the generator puts at the low indices), the rows around the heaviest row if
+    it lies elsewhere, a block from the middle and the last rows (the last, possibly ragged, window)."""
+    if rows <= 4 * want_rows:
+        return [(0, rows)]
+    w = want_rows
+    ranges = [(0, w), (rows // 2 // 16 * 16, rows // 2 // 16 * 16 + w), (rows - w, rows)]
+    deg = np.diff(np.asarray(rp).astype(np.int64))
+    hub = int(np.argmax(deg))
+    if not any(a <= hub < b for a, b in ranges):
+        a = max(0, min(rows - 64, hub // 16 * 16))
+        ranges.append((a, a + 64))
+    return sorted(ranges)
+
+
+def parity_record(get_rows, rows, rp, ci, v, B_host):
+    """Parity of a result against the CPU oracle on the sample rows; get_rows(a, b) returns C[a:b] as numpy."""
+    import parity
+    ranges = parity_ranges(rows, rp)
+    got = np.concatenate([np.asarray(get_rows(a, b), dtype=np.float32) for a, b in ranges])
+    try:
+        st = parity.check_rows(got, rp, ci, v, B_host, ranges, threads=host_cores())
+        st["ok"] = True
+    except AssertionError as e:  # reported in the line; the bench exits non-zero at the end
+        st = {"ok": False, "error": str(e), "checked_rows": int(got.shape[0])}
+    st["rows_sampled"] = [[int(a), int(b)] for a, b in ranges]
+    return st
+
+
+def tf32_peak_tflops(dev):
+    """Dense tf32 matmul throughput of this GPU (cuBLAS through torch, 8192^3, best of 5): the tensor
+    peak of the tf32 workload, measured in the same run as the kernel it bounds."""
+    import torch
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        m = 8192
+        a = torch.randn((m, m), device=dev)
+        b = torch.randn((m, m), device=dev)
+        for _ in range(2):
+            torch.matmul(a, b)
+        best = float("inf")
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch.matmul(a, b)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        return 2.0 * m ** 3 / (best * 1e-3) / 1e12
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+
+
+def roofline_record(nnz, rows, cols, n, esz, kernel_ms, hbm_gbs, tensor_tflops, peak_kind, tensor_note):
+    """Fraction of the slower of the two rooflines: t_roof = max(bytes / HBM, flops / tensor peak)."""
+    alg = algorithmic_bytes(nnz, rows, cols, n, esz, esz, 4)
+    flops = 2.0 * nnz * n
+    t_hbm = alg / (hbm_gbs * 1e9)
+    t_tensor = flops / (tensor_tflops * 1e12)
+    bound = "hbm" if t_hbm >= t_tensor else "tensor"
+    t = kernel_ms * 1e-3
+    if bound == "hbm":
+        achieved, peak, unit = alg / t / 1e9, hbm_gbs, "GB/s"
+    else:
+        achieved, peak, unit = flops / t / 1e12, tensor_tflops, "TFLOP/s"
+    return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+            "peak_source": f"of {peak_kind}" + (f"; tensor: {tensor_note}" if tensor_note else ""),
+            "kernel_ms": kernel_ms, "algorithmic_bytes": alg, "t_hbm_us": t_hbm * 1e6, "t_tensor_us": t_tensor * 1e6}
+
+
+def dram_traffic(workload, tiles, n_slabs):
+    tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if os.path.exists(tpath):
+        per_tile = json.load(open(tpath)).get(workload, {}).get("dram_bytes_per_tile")
+        if per_tile:
+            return float(per_tile) * tiles * n_slabs
+    return None
+
+
+def graph_replay_ms(plan, B, C_dev, steps):
+    """The same launches replayed from a CUDA graph: what a launch-latency-bound product costs without
+    the per-launch host work."""
+    import torch
+    try:
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            plan.spmm(B, C_dev, sync=False)
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(steps):
+                    plan.spmm(B, C_dev, sync=False)
+        torch.cuda.current_stream().wait_stream(side)
+        g.replay()
+        torch.cuda.synchronize()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        g.replay()
+        g1.record()
+        torch.cuda.synchronize()
+        ms = g0.elapsed_time(g1) / steps
+        del g
+        return ms
+    except RuntimeError as e:  # reported, not fatal: the figure is an extra
+        log(f"CUDA-graph replay not measured: {e}")
+        return None
+
+
+def run_other_workload(name, dev, steps, warmup, hbm_gbs, f16_tflops, tf32_tflops, peak_kind, flush_buf):
+    """One of the smaller configurations at full size on one GPU: time (L2 flushed between the timed
+    launches), roofline, CPU baseline, and the timed result checked whole against the CPU oracle."""
+    import torch
+    import hopper_spmm_b200 as hs
+    from hopper_spmm_b200 import synth
+    import parity
+    dtype_name, n_feat, desc = synth.CONFIGS[name]
+    csr, B = synth.make_config(name, 0, dev, 0)
+    btcf = hs.DeviceBtcf(csr.rows, csr.cols, csr.row_ptr.to(torch.int32), csr.col_idx, csr.values, device=dev.index)
+    plan = hs.SpmmPlan(btcf, device=dev.index)
+    C_dev = torch.full((csr.rows, n_feat), float("nan"), dtype=torch.float32, device=dev)
+    for _ in range(warmup):
+        plan.spmm(B, C_dev, sync=False)
+    plan.sync()
+    cold = []
+    for _ in range(steps):
+        flush_buf.zero_()  # evicts operands and result from L2
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        plan.spmm(B, C_dev, sync=False)
+        e1.record()
+        plan.sync()
+        cold.append(e0.elapsed_time(e1))
+    h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    h0.record()
+    for _ in range(steps):
+        plan.spmm(B, C_dev, sync=False)
+    h1.record()
+    plan.sync()
+    ms = float(np.mean(cold))
+    ms_hot = h0.elapsed_time(h1) / steps
+    info = plan.launch_info()
+    esz = 2 if dtype_name == "f16" else 4
+    tensor = f16_tflops if dtype_name == "f16" else tf32_tflops
+    note = "" if dtype_name == "f16" else "tf32 matmul measured in this run"
+    roof = roofline_record(csr.nnz, csr.rows, csr.cols, n_feat, esz, ms, hbm_gbs, tensor, peak_kind, note)
+    flops = 2.0 * csr.nnz * n_feat
+    rec = {"workload": name, "description": desc, "rows": csr.rows, "cols": csr.cols, "nnz": csr.nnz, "features": n_feat,
+           "dtype": "f16" if dtype_name == "f16" else "tf32", "tiles": int(btcf.total_tiles),
+           "fill": csr.nnz / max(1, btcf.total_tiles * 16 * btcf.col_window),
+           "ms": ms, "ms_l2_warm": ms_hot, "l2": f"flushed between timed launches ({L2_FLUSH_BYTES >> 20} MB written)",
+           "value": flops / (ms * 1e-3) / 1e9, "unit": "GFLOP/s", "roofline": roof,
+           "kernel": {"n_ctas": info.n_ctas, "feature_slab": info.feature_slab, "n_slabs": info.n_slabs,
+                      "stages": info.stages, "launches_per_step": int(info.kernel_launches),
+                      "row_window": int(getattr(info, "row_window", 16) or 16)},
+           "graph_replay_ms": graph_replay_ms(plan, B, C_dev, steps) if ms_hot < 0.2 else None}
+    rp, ci, v = csr.numpy()
+    B_host = B.cpu().numpy()
+    got = C_dev.cpu().numpy()
+    try:
+        st = parity.check(got, csr.rows, rp, ci, v, B_host, threads=host_cores())
+        st.update(ok=True, checked_rows=csr.rows)
+    except AssertionError as e:
+        st = {"ok": False, "error": str(e), "checked_rows": csr.rows}
+    rec["parity"] = st
+    cpu, _ = time_cpu_oracle(rp, ci, v, B_host, 2, 1, budget_s=4.0)
+    rec["cpu_baseline"] = cpu
+    rec["vs_cpu"] = rec["value"] / cpu["value"]
+    plan.close()
+    btcf.close()
+    del C_dev, B, csr
+    torch.cuda.empty_cache()
+    return rec
+
+
 from hopper_spmm_b200.sharded import ROW_CHARGE as sharded_charge
+
+
+def static_config(args, world, dtype_name, n_feat, desc, rows, cols, nnz):
+    """What names the workload; the same keys and values in both arms."""
+    return {"workload": args.workload, "description": desc, "scale_down": args.scale_down, "features": n_feat,
+            "row_window": 16, "c_dtype": "f32", "rows": int(rows), "cols": int(cols), "nnz": int(nnz),
+            "parallelism": f"row-window shards x{world} (balanced on nnz + {sharded_charge} per row), B replicated",
+            "l2": "operands larger than L2 (no flush needed)" if args.scale_down == 0 and args.workload == DEFAULT_WORKLOAD
+                  else "see workloads[].l2 / operands may fit L2 at this scale"}
 
 
 def main():
@@ -154,12 +363,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--scale-down", type=int, default=0)
-    ap.add_argument("--allgather", action="store_true", help="also time the all-gather of the row-sharded C (N > 1)")
+    ap.add_argument("--no-allgather", action="store_true", help="skip the timing of the all-gather of the row-sharded C (N > 1)")
     ap.add_argument("--e2e-row-charge", type=int, default=-1,
                     help="entries a row is charged when the end-to-end step gets row ranges of its own (N > 1); "
                          "-1 = the ranges of the device-resident measurement")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--no-workloads", action="store_true", help="skip the four other configurations (1 GPU, default workload only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -169,9 +380,6 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     dtype_name, n_feat, desc = synth.CONFIGS[args.workload]
-    config = {"workload": args.workload, "description": desc, "scale_down": args.scale_down, "features": n_feat,
-              "row_window": 16, "c_dtype": "f32", "parallelism": f"row-window shards x{world} (balanced on nnz + {sharded_charge} per row), B replicated",
-              "l2": "operands larger than L2 (no flush needed)"}
 
     if args.impl == "reference":
         if rank != 0:
@@ -179,13 +387,15 @@ def main():
         dev = "cuda" if torch.cuda.is_available() else "cpu"
         csr, B = synth.make_config(args.workload, 0, dev, args.scale_down)
         rp, ci, v = csr.numpy()
-        base, t = time_cpu_oracle(rp, ci, v, B.cpu().numpy(), args.steps, args.warmup, budget_s=60.0)
-        config.update(rows=csr.rows, cols=csr.cols, nnz=csr.nnz)
+        cores = host_cores()
+        base, t = time_cpu_oracle(rp, ci, v, B.cpu().numpy(), args.steps, args.warmup, budget_s=60.0, threads=cores)
+        config = static_config(args, max(world, args.gpus), dtype_name, n_feat, desc, csr.rows, csr.cols, csr.nnz)
         line = {"impl": "reference", "metric": "SpMM effective GFLOP/s (2*nnz*N)", "value": base["value"],
                 "unit": "GFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "f16" if dtype_name == "f16" else "f32", "data": "synthetic", "config": config,
-                "cpu_baseline": base, "gpu_launches": 0,
+                "dtype": "f16" if dtype_name == "f16" else "tf32", "data": "synthetic", "config": config,
+                "cpu_baseline": base, "gpu_launches": 0, "host_cores": cores,
+                "omp_num_threads_env": os.environ.get("OMP_NUM_THREADS"),
                 "e2e": {"value": base["value"], "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line), flush=True)
         return
@@ -212,9 +422,12 @@ def main():
     from hopper_spmm_b200 import sharded
     cuts, r0, r1 = sharded.my_rows(csr.rows, rp_full, world, rank)
     part = csr.row_slice(r0, r1)
-    total_nnz = csr.nnz
+    total_nnz, total_rows = csr.nnz, csr.rows
     cols = B.shape[0]
-    host_csr = part.numpy() if (rank == 0 and world == 1 and not args.no_cpu) else None  # only the CPU baseline needs it
+    config = static_config(args, world, dtype_name, n_feat, desc, csr.rows, csr.cols, csr.nnz)
+    # this rank's rows on the host: the parity sample and (1 GPU) the CPU baseline read them
+    need_host = (not args.no_parity) or (rank == 0 and world == 1 and not args.no_cpu)
+    host_csr = part.numpy() if need_host else None
     # Row ranges of the end-to-end step on several GPUs: the product's own, unless --e2e-row-charge
     # asks for others.  Charging the rows for their bytes of C over the rank's host link (201
     # entries per row at 128 fp16 features: 52 GB/s against 0.0253 ms per million entries) evens
@@ -242,7 +455,7 @@ def main():
     log(f"rank {rank}: rows [{r0},{r1}) nnz={nnz_local} tiles={btcf.total_tiles} device convert {t_conv:.2f}s")
     tiles_local, rows_local = btcf.total_tiles, r1 - r0
     fill = nnz_local / max(1, tiles_local * 16 * btcf.col_window)
-    C_dev = torch.empty((rows_local, n_feat), dtype=torch.float32, device=dev)
+    C_dev = torch.full((rows_local, n_feat), float("nan"), dtype=torch.float32, device=dev)  # every row must be written
 
     # ---- device-resident timing (clocks are sampled from the warm-up to the end of the run)
     clocks = ClockSampler(local_rank)
@@ -273,35 +486,18 @@ def main():
     flops = 2.0 * total_nnz * n_feat
     value = flops / (ms_per_step * 1e-3) / 1e9
 
-    # ---- the same launches replayed from a CUDA graph (what a launch-latency-bound product costs
-    # without the per-launch host work); small workloads only
-    graph_ms = None
-    if ms_per_step < 0.2:
-        try:
-            g = torch.cuda.CUDAGraph()
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                plan.spmm(B, C_dev, sync=False)
-                with torch.cuda.graph(g, stream=side):
-                    for _ in range(args.steps):
-                        plan.spmm(B, C_dev, sync=False)
-            torch.cuda.current_stream().wait_stream(side)
-            g.replay()
-            torch.cuda.synchronize()
-            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            g0.record()
-            g.replay()
-            g1.record()
-            torch.cuda.synchronize()
-            graph_ms = g0.elapsed_time(g1) / args.steps
-            del g
-        except RuntimeError as e:  # reported, not fatal: the figure is an extra
-            log(f"rank {rank}: CUDA-graph replay not measured: {e}")
+    # ---- parity of the timed result: this rank's rows against the CPU oracle (sample rows)
+    B_host = B.cpu().numpy() if need_host else None
+    parity_dev = None
+    if not args.no_parity:
+        parity_dev = parity_record(lambda a, b: C_dev[a:b].cpu().numpy(), rows_local, *host_csr, B_host)
+        log(f"rank {rank}: parity of the device-resident result: {parity_dev}")
 
-    # ---- optional collective: all-gather of the row-sharded C, timed on its own
-    allgather_ms = None
-    if world > 1 and args.allgather:
+    graph_ms = graph_replay_ms(plan, B, C_dev, args.steps) if ms_per_step < 0.2 else None
+
+    # ---- the collective: all-gather of the row-sharded C, timed on its own
+    allgather_ms, allgather_bytes = None, None
+    if world > 1 and not args.no_allgather:
         barrier()
         a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         full = sharded.allgather_rows(C_dev, cuts)  # untimed: the first exchange sets up the peer connections
@@ -314,11 +510,14 @@ def main():
         t_a = torch.tensor([a0.elapsed_time(a1)], dtype=torch.float64, device=dev)
         dist.all_reduce(t_a, op=dist.ReduceOp.MAX)
         allgather_ms = float(t_a.item())
+        allgather_bytes = int(full.numel() * full.element_size())
+        # the gathered result holds this rank's rows where they belong
+        assert torch.equal(full[r0:r1], C_dev), "all-gather misplaced this rank's rows"
         del full
         torch.cuda.empty_cache()
 
     # ---- end to end: B from pinned host memory in, C out to pinned host memory, every step
-    e2e = None
+    e2e, parity_e2e = None, None
     if not args.no_e2e:
         hB = torch.empty(B.shape, dtype=B.dtype, pin_memory=True)
         hB.copy_(B)
@@ -373,47 +572,97 @@ def main():
                         "per rank: 1/N of host B in + GPU-to-GPU exchange, b200spmm_spmm, its rows of C out to the host")}
         if world > 1:
             e2e["row_charge"] = e2e_charge if e2e_charge >= 0 else sharded.ROW_CHARGE
-        assert bool(torch.isfinite(hC[:: max(1, hC.shape[0] // 4096)]).all())
+        if not args.no_parity and (q0, q1) == (r0, r1):  # the host-buffer result, same rows as above
+            parity_e2e = parity_record(lambda a, b: hCn[a:b], rows_local, *host_csr, B_host)
+            log(f"rank {rank}: parity of the end-to-end result: {parity_e2e}")
+        else:
+            assert bool(torch.isfinite(hC[:: max(1, hC.shape[0] // 4096)]).all())
 
     # ---- roofline of the SpMM kernel on this rank's launch
-    peak, peak_kind = measured_peaks()
+    hbm_gbs, f16_tflops, peak_kind = measured_peaks()
     esz = 2 if dtype_name == "f16" else 4
-    alg = algorithmic_bytes(nnz_local, rows_local, B.shape[0], n_feat, esz, esz, 4)
+    tf32_tflops = None
+    if dtype_name != "f16" or (world == 1 and not args.no_workloads and args.workload == DEFAULT_WORKLOAD):
+        tf32_tflops = tf32_peak_tflops(dev)
     kernel_ms = float(np.mean(step_ms))
-    achieved = alg / (kernel_ms * 1e-3) / 1e9
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
-    if os.path.exists(tpath):
-        per_tile = json.load(open(tpath)).get(args.workload, {}).get("dram_bytes_per_tile")
-        if per_tile:
-            traffic = float(per_tile) * tiles_local * info.n_slabs
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": traffic, "peak_source": f"of {peak_kind}", "kernel": "spmm_sm100_kernel",
-                "kernel_ms": kernel_ms, "algorithmic_bytes": alg}
+    roofline = roofline_record(nnz_local, rows_local, cols, n_feat, esz, kernel_ms, hbm_gbs,
+                               f16_tflops if dtype_name == "f16" else tf32_tflops, peak_kind,
+                               "" if dtype_name == "f16" else "tf32 matmul measured in this run")
+    roofline["kernel"] = "spmm_sm100_kernel"
+    roofline["traffic"] = dram_traffic(args.workload, tiles_local, info.n_slabs)
+    # whole job: every rank's A and C bytes once, B once (it is replicated, not re-read by the algorithm),
+    # against N GPUs' bandwidth
+    alg_job = algorithmic_bytes(total_nnz, total_rows, cols, n_feat, esz, esz, 4)
+    roofline["whole_job"] = {"algorithmic_bytes": alg_job, "achieved": alg_job / (ms_per_step * 1e-3) / 1e9,
+                             "peak": hbm_gbs * world, "frac": alg_job / (ms_per_step * 1e-3) / 1e9 / (hbm_gbs * world)}
+    if world > 1:
+        roofline["note"] = "achieved/frac: rank 0's launch with the replicated B counted in full; whole_job counts B once"
 
     clocks.__exit__(None, None, None)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        cpu, _ = time_cpu_oracle(*host_csr, B.cpu().numpy(), 2, 1, budget_s=15.0)
-        one, _ = time_cpu_oracle(*host_csr, B.cpu().numpy(), 1, 1, budget_s=6.0, threads=1)  # the reference is single-threaded
+        cpu, _ = time_cpu_oracle(*host_csr, B_host, 2, 1, budget_s=15.0)
+        one, _ = time_cpu_oracle(*host_csr, B_host, 1, 1, budget_s=6.0, threads=1)  # the reference is single-threaded
         cpu["one_core"] = {"value": one["value"], "unit": one["unit"], "sample": one["sample"]}
 
+    # ---- every rank's parity record goes to rank 0, which reports the worst
+    def worst(rec):
+        if rec is None:
+            return None
+        mine = [float(rec.get("ok", False)), float(rec.get("scaled_err", float("inf"))), float(rec.get("rule_failures", -1)),
+                float(rec.get("checked_rows", 0))]
+        if world == 1:
+            return dict(rec, ranks=1)
+        t = torch.tensor(mine, dtype=torch.float64, device=dev)
+        allr = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(allr, t)
+        rows_ = [[float(x) for x in a.tolist()] for a in allr]
+        return {"ok": all(r_[0] == 1.0 for r_ in rows_), "scaled_err": max(r_[1] for r_ in rows_),
+                "rule_failures": int(max(r_[2] for r_ in rows_)), "checked_rows": int(sum(r_[3] for r_ in rows_)),
+                "ranks": world, "rank0": rec}
+    parity_dev, parity_e2e = worst(parity_dev), worst(parity_e2e)
+
+    # ---- the other four configurations, full size, one GPU
+    plan.close()
+    btcf.close()
+    del C_dev
+    workloads = None
+    if world == 1 and not args.no_workloads and args.workload == DEFAULT_WORKLOAD and args.scale_down == 0:
+        del B
+        torch.cuda.empty_cache()
+        flush_buf = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+        workloads = []
+        for name in OTHER_WORKLOADS:
+            t0 = time.perf_counter()
+            rec = run_other_workload(name, dev, args.steps, args.warmup, hbm_gbs, f16_tflops, tf32_tflops, peak_kind, flush_buf)
+            log(f"{name}: {rec['ms'] * 1e3:.1f} us ({rec['ms_l2_warm'] * 1e3:.1f} us L2-warm), {rec['value']:.0f} GFLOP/s, "
+                f"frac {rec['roofline']['frac']:.3f} ({rec['roofline']['bound']}), x{rec['vs_cpu']:.0f} CPU, "
+                f"parity {rec['parity']}, {time.perf_counter() - t0:.1f}s")
+            workloads.append(rec)
+
+    failed = False
     if rank == 0:
-        config.update(rows=int(cuts[-1]), cols=int(B.shape[0]), nnz=int(total_nnz), tiles_rank0=int(tiles_local),
-                      fill_rank0=fill, n_ctas=info.n_ctas, feature_slab=info.feature_slab, stages=info.stages,
-                      convert_s_rank0=t_conv, rank_ms=[round(x, 4) for x in rank_ms],
-                      # what the tensor cores execute: every tile is a dense 16 x CW x n product
-                      executed_mma_gflop_rank0=2.0 * tiles_local * 16 * btcf.col_window * n_feat / 1e9,
-                      graph_replay_ms_per_step=graph_ms, allgather_c_ms=allgather_ms)
+        details = dict(tiles_rank0=int(tiles_local), fill_rank0=fill, n_ctas=info.n_ctas, feature_slab=info.feature_slab,
+                       stages=info.stages, convert_s_rank0=t_conv, rank_ms=[round(x, 4) for x in rank_ms],
+                       # what the tensor cores execute: every tile is a dense 16 x CW x n product
+                       executed_mma_gflop_rank0=2.0 * tiles_local * 16 * btcf.col_window * n_feat / 1e9,
+                       graph_replay_ms_per_step=graph_ms, allgather_c_ms=allgather_ms, allgather_c_bytes=allgather_bytes,
+                       tf32_tflops_measured=tf32_tflops, host_cores=host_cores())
         line = {"metric": "SpMM effective GFLOP/s (2*nnz*N)", "value": value, "unit": "GFLOP/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f16" if dtype_name == "f16" else "tf32",
-                "data": "synthetic", "config": config, "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+                "data": "synthetic", "config": config, "details": details, "roofline": roofline, "cpu_baseline": cpu,
+                "e2e": e2e, "parity": {"device_resident": parity_dev, "e2e": parity_e2e},
+                "allgather_c_ms": allgather_ms, "workloads": workloads,
                 "gpu_launches": int(args.steps * info.kernel_launches), "clocks": clocks.summary()}
         print(json.dumps(line), flush=True)
-    plan.close()
+        recs = [parity_dev, parity_e2e] + [w["parity"] for w in (workloads or [])]
+        failed = any(r is not None and not r.get("ok", False) for r in recs)
     if world > 1:
         dist.destroy_process_group()
+    if failed:
+        log("PARITY FAILED - see the parity records in the line above")
+        sys.exit(1)
 
 
 if __name__ == "__main__":

@@ -96,6 +96,8 @@ SIGNATURES = {
                                         C.c_int, vp]),
     "b200spmm_plan_launch_info": (C.c_int, [vp, C.POINTER(LaunchInfo)]),
     "b200spmm_kat_umma": (C.c_int, [vp, u32, C.POINTER(KatMma), C.c_int, C.c_int, vp, C.c_int]),
+    "b200spmm_kat_wait_limit": (C.c_uint64, [C.c_uint64]),
+    "b200spmm_kat_spmm_starved": (C.c_int, [vp, vp, i64, i64, vp, i64, C.c_uint64, vp]),
     "b200spmm_kat_instr_desc": (u32, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "b200spmm_kat_tma": (C.c_int, [vp, u64, u64, u64, C.c_int, u32, u32, C.c_int, vp, C.c_int, u32, vp, u32,
                                     C.c_int]),

@@ -20,13 +20,19 @@
 namespace b200spmm {
 
 namespace {
+// The last error of the calling thread: either a composed text (CUDA failures: the failing call
+// and the runtime's message) or a pointer to a fixed message, which needs no allocation.
 thread_local std::string g_last_cuda_error;
+thread_local const char *g_last_static_error = nullptr;
 }
 
 void record_cuda_error(cudaError_t e, const char *what) {
+    g_last_static_error = nullptr;
     g_last_cuda_error = std::string(what) + ": " + cudaGetErrorString(e);
     cudaGetLastError();  // clear the sticky-free error so later calls start clean
 }
+
+void set_last_error_static(const char *message) { g_last_static_error = message; }
 
 }  // namespace b200spmm
 
@@ -64,6 +70,15 @@ struct b200spmm_plan {
     size_t partial_floats = 0;
     uint32_t *d_status = nullptr;
     CUtensorMap tmap_a{};
+    // Tensor map over B, kept between launches: B's address, pitch and width rarely change from call
+    // to call, and encoding a map costs the host several microseconds of a 10-microsecond launch.
+    CUtensorMap tmap_b{};
+    const void *tmap_b_ptr = nullptr;
+    int64_t tmap_b_ldb = 0;
+    uint32_t tmap_b_n = 0;
+    bool gather_cpasync = false;  // B200SPMM_GATHER=cpasync, read when the plan is made
+    unsigned long long wait_limit_ns = kDeviceWaitLimitNs;  // how long a wait inside the kernel may last
+    bool starve_gathers = false;  // b200spmm_kat_spmm_starved only: B's tensor map delivers half the bytes
     // buffers of the host-pointer entry point, grown on demand
     void *d_B = nullptr, *d_C = nullptr;
     size_t d_B_bytes = 0, d_C_bytes = 0;
@@ -116,24 +131,44 @@ int launch_slab(b200spmm_plan *p, SpmmParams &prm, const CUtensorMap &tmap_b, cu
     }
 }
 
-// How the rows of B are gathered: TMA tile::gather4 unless the caller asks for the cp.async
-// path (B200SPMM_GATHER=cpasync) or B is narrower than one 128-byte TMA box.
+// The environment is consulted when a plan is made (and once per process for the plan-less
+// allocation-free call), never on a launch.
+bool env_is(const char *name, const char *value) {
+    const char *v = std::getenv(name);
+    return v && std::strcmp(v, value) == 0;
+}
+
+// Tensor map over B seen as [cols][n] with its real row pitch; a box is 128 bytes of one row.
+// Rows or features past the end read as zeros.  Re-encoded only when B's address, pitch or width
+// differ from the previous launch of this plan.
+int b_tensor_map(b200spmm_plan *p, const SpmmParams &prm, bool tf32) {
+    if (p->tmap_b_ptr == prm.B && p->tmap_b_ldb == prm.ldb && p->tmap_b_n == prm.n) return B200SPMM_OK;
+    const uint32_t esz = tf32 ? 4 : 2, box = (p->starve_gathers ? 64 : 128) / esz;
+    p->tmap_b_ptr = nullptr;
+    if (!encode_2d(&p->tmap_b, tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, prm.B, prm.n,
+                   prm.cols, (uint64_t)prm.ldb * esz, box, 1,
+                   tf32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) {
+        set_last_error_static("cuTensorMapEncodeTiled failed for B");
+        return B200SPMM_ERR_CUDA;
+    }
+    p->tmap_b_ptr = prm.B;
+    p->tmap_b_ldb = prm.ldb;
+    p->tmap_b_n = prm.n;
+    return B200SPMM_OK;
+}
+
+// How the rows of B are gathered: TMA tile::gather4 unless the plan was made with
+// B200SPMM_GATHER=cpasync or B is narrower than one 128-byte TMA box.
 template <bool kTf32>
 int launch_dtype(b200spmm_plan *p, SpmmParams &prm, cudaStream_t stream) {
     constexpr uint32_t esz = kTf32 ? 4 : 2, box = 128 / esz;
-    const char *mode = std::getenv("B200SPMM_GATHER");
-    const bool want_cpasync = mode && std::strcmp(mode, "cpasync") == 0;
-    CUtensorMap tmap_b{};
-    if (want_cpasync || prm.n < box) return launch_slab<kTf32, false, false>(p, prm, tmap_b, stream);
-    // B seen as [cols][n] with its real row pitch; a box is 128 bytes of one row.  Rows or
-    // features past the end read as zeros.
-    if (!encode_2d(&tmap_b, kTf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, prm.B, prm.n,
-                   prm.cols, (uint64_t)prm.ldb * esz, box, 1,
-                   kTf32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) {
-        g_last_cuda_error = "cuTensorMapEncodeTiled failed for B";
-        return B200SPMM_ERR_CUDA;
+    if (p->gather_cpasync || prm.n < box) return launch_slab<kTf32, false, false>(p, prm, p->tmap_b, stream);
+    {
+        int st = b_tensor_map(p, prm, kTf32);
+        if (st != B200SPMM_OK) return st;
     }
+    const CUtensorMap &tmap_b = p->tmap_b;
     if (p->comp.tcBit) {  // stream the compressed tiles
         prm.tcBit = p->comp.tcBit;
         prm.nnzOffset = p->comp.nnzOffset;
@@ -144,7 +179,7 @@ int launch_dtype(b200spmm_plan *p, SpmmParams &prm, cudaStream_t stream) {
 }
 
 // Tensor map over `data` seen as rows of 32 bytes: one tile is 16 consecutive rows, one box is
-// the four consecutive tiles of a ring stage.
+// the eight consecutive tiles of a ring stage.
 int encode_tile_map(b200spmm_plan *p) {
     const auto &info = p->info;
     if (!info.total_tiles) return B200SPMM_OK;
@@ -152,7 +187,7 @@ int encode_tile_map(b200spmm_plan *p) {
     if (!encode_2d(&p->tmap_a, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p->d_data,
                    f16 ? 16 : 8, info.total_tiles * kRowWindow, 32, f16 ? 16 : 8, kRowWindow * kTilesPerStage,
                    CU_TENSOR_MAP_SWIZZLE_32B)) {
-        g_last_cuda_error = "cuTensorMapEncodeTiled failed for the tile array";
+        set_last_error_static("cuTensorMapEncodeTiled failed for the tile array");
         return B200SPMM_ERR_CUDA;
     }
     return B200SPMM_OK;
@@ -214,8 +249,8 @@ int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, const uint32_t *h
     // give the same C bit for bit.  The compressed form moves an eighth of the tile bytes at a
     // few per cent fill but costs the producer warps more instructions per tile than they can
     // spare today, so dense tiles are the default.
-    const char *tiles_mode = std::getenv("B200SPMM_TILES");
-    if (info.total_tiles && tiles_mode && std::strcmp(tiles_mode, "bitmap") == 0) {
+    p->gather_cpasync = env_is("B200SPMM_GATHER", "cpasync");
+    if (info.total_tiles && env_is("B200SPMM_TILES", "bitmap")) {
         int st = compress_tiles_device(p->d_data, info.total_tiles, info.dtype, &p->comp);
         if (st != B200SPMM_OK) return st;
     }
@@ -310,7 +345,7 @@ const char *b200spmm_status_string(int status) {
     }
 }
 
-const char *b200spmm_last_cuda_error(void) { return g_last_cuda_error.c_str(); }
+const char *b200spmm_last_cuda_error(void) { return g_last_static_error ? g_last_static_error : g_last_cuda_error.c_str(); }
 
 int b200spmm_version(void) { return 100; }
 
@@ -594,13 +629,13 @@ int spmm_launch(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, voi
     prm.eff_row_windows = (uint32_t)p->info.eff_row_windows;
     prm.c_is_half = c_dtype == B200SPMM_C_F16;
     prm.status = p->d_status;
-    prm.wait_limit_ns = kDeviceWaitLimitNs;
+    prm.wait_limit_ns = p->wait_limit_ns;
 #ifdef B200SPMM_PROFILE
     if (!g_prof) cudaMalloc(&g_prof, 1024 * 24 * 8);
     cudaMemsetAsync(g_prof, 0, 1024 * 24 * 8, stream);
     prm.prof = g_prof;
+    if (const char *dbg = std::getenv("B200SPMM_DEBUG")) prm.debug = (uint32_t)std::atoi(dbg);  // results invalid
 #endif
-    if (const char *dbg = std::getenv("B200SPMM_DEBUG")) prm.debug = (uint32_t)std::atoi(dbg);  // measurement aid, results invalid
     int st = p->info.dtype == B200SPMM_F16 ? launch_dtype<false>(p, prm, stream) : launch_dtype<true>(p, prm, stream);
     if (st != B200SPMM_OK || split_end == split_begin) return st;
     // windows shared out over several CTAs: sum their pieces
@@ -727,6 +762,21 @@ int b200spmm_bench(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, 
     return st;
 }
 
+/* Declared in b200_spmm_kat.h: the product launched so that its stage barriers can never complete. */
+int b200spmm_kat_spmm_starved(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, void *d_C, int64_t ldc,
+                              unsigned long long limit_ns, void *stream) {
+    if (!p || limit_ns == 0 || limit_ns > kDeviceWaitLimitNs) return B200SPMM_ERR_INVALID_ARG;
+    if (p->gather_cpasync || n * p->info.elt_size < 128) return B200SPMM_ERR_UNSUPPORTED;  // needs the TMA gathers
+    p->starve_gathers = true;
+    p->wait_limit_ns = limit_ns;
+    p->tmap_b_ptr = nullptr;  // a map encoded for a normal launch must not be reused, nor this one later
+    const int st = spmm_launch(p, d_B, ldb, n, d_C, ldc, B200SPMM_C_F32, stream, -1);
+    p->starve_gathers = false;
+    p->wait_limit_ns = kDeviceWaitLimitNs;
+    p->tmap_b_ptr = nullptr;
+    return st;
+}
+
 int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_rowOffset, const uint32_t *d_tcA2B,
                           const void *d_data, const uint32_t *d_rowIdx, const void *d_B, int64_t ldb, int64_t n,
                           void *d_C, int64_t ldc, int c_dtype, int device, int n_ctas, void *stream_v) {
@@ -737,7 +787,7 @@ int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_ro
     if (info->row_window != kRowWindow || info->col_window != (info->dtype == B200SPMM_F16 ? 16 : 8))
         return B200SPMM_ERR_UNSUPPORTED;
     if (n_ctas > kNoAllocMaxCtas) {
-        g_last_cuda_error = "b200spmm_spmm_noalloc: n_ctas exceeds the 1024 CTAs the built-in schedule table holds";
+        set_last_error_static("b200spmm_spmm_noalloc: n_ctas exceeds the 1024 CTAs the built-in schedule table holds");
         return B200SPMM_ERR_UNSUPPORTED;
     }
     if (info->total_tiles * (uint64_t)kRowWindow >= 0x7FFFFFFFull || info->cols > 0x7FFFFFFFull || n > 0x7FFFFFFF || n % 8)
@@ -763,6 +813,8 @@ int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_ro
     if (st != B200SPMM_OK) return st;
 
     b200spmm_plan tmp;  // lives on the stack; owns nothing
+    static const bool cpasync = env_is("B200SPMM_GATHER", "cpasync");  // read once per process
+    tmp.gather_cpasync = cpasync;
     tmp.info = *info;
     tmp.device = device;
     tmp.sched.n_ctas = n_ctas;  // the tables themselves are in the built-in array

@@ -11,6 +11,8 @@ namespace b200spmm {
 
 // Remembers `what: cudaGetErrorString(e)` for b200spmm_last_cuda_error().
 void record_cuda_error(cudaError_t e, const char *what);
+// Same, for a fixed message: keeps the pointer, allocates nothing.
+void set_last_error_static(const char *message);
 
 // How long a device-side wait may spin before the kernel gives up (nanoseconds).
 constexpr unsigned long long kDeviceWaitLimitNs = 2000000000ull;

@@ -15,11 +15,15 @@
 namespace b200spmm {
 namespace {
 
-constexpr uint32_t kKatTmemCols = 128;
+constexpr uint32_t kKatTmemCols = 256;
+
+// Wait limit of the known-answer kernels; a test shortens it to see a bounded wait run out.
+unsigned long long g_kat_wait_limit_ns = kDeviceWaitLimitNs;
 
 __global__ void __launch_bounds__(128, 1)
 kat_umma_kernel(const uint8_t *__restrict__ image, uint32_t image_bytes, const b200spmm_kat_mma_t *__restrict__ mmas,
-                int n_mmas, int n_cols, float *__restrict__ out, uint32_t *__restrict__ status) {
+                int n_mmas, int n_cols, float *__restrict__ out, uint32_t *__restrict__ status,
+                unsigned long long limit_ns) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t done_bar;
     __shared__ uint32_t tmem_base_slot;
@@ -62,7 +66,7 @@ kat_umma_kernel(const uint8_t *__restrict__ image, uint32_t image_bytes, const b
         ptx::umma_commit(ptx::smem_u32(&done_bar));
     }
     __syncwarp();
-    const bool ok = ptx::mbar_wait(ptx::smem_u32(&done_bar), 0, &abort_flag, kDeviceWaitLimitNs);
+    const bool ok = ptx::mbar_wait(ptx::smem_u32(&done_bar), 0, &abort_flag, limit_ns);
     ptx::tcgen05_fence_after_sync();
     if (!ok && tid == 0) atomicOr(status, kDevStatusTimeout);
 
@@ -81,7 +85,8 @@ kat_umma_kernel(const uint8_t *__restrict__ image, uint32_t image_bytes, const b
 
 __global__ void __launch_bounds__(32, 1)
 kat_tma_kernel(const __grid_constant__ CUtensorMap tmap, const int32_t *__restrict__ loads, int n_loads,
-               uint32_t expect_bytes, uint8_t *__restrict__ dump, uint32_t dump_bytes, uint32_t *__restrict__ status) {
+               uint32_t expect_bytes, uint8_t *__restrict__ dump, uint32_t dump_bytes, uint32_t *__restrict__ status,
+               unsigned long long limit_ns) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar;
     __shared__ uint32_t abort_flag;
@@ -111,7 +116,9 @@ kat_tma_kernel(const __grid_constant__ CUtensorMap tmap, const int32_t *__restri
         }
     }
     __syncwarp();
-    const bool ok = ptx::mbar_wait(ptx::smem_u32(&bar), 0, &abort_flag, kDeviceWaitLimitNs / 4);
+    // Every load that was issued is given its bytes' worth of waiting even when the barrier expects
+    // more than the loads deliver: nothing is still writing shared memory when the dump is read.
+    const bool ok = ptx::mbar_wait(ptx::smem_u32(&bar), 0, &abort_flag, limit_ns);
     if (!ok && tid == 0) atomicOr(status, kDevStatusTimeout);
     __syncwarp();
     for (uint32_t i = tid * 4u; i < dump_bytes; i += 32u * 4u)
@@ -206,6 +213,12 @@ int check_device(int device) {
 
 using namespace b200spmm;
 
+extern "C" unsigned long long b200spmm_kat_wait_limit(unsigned long long limit_ns) {
+    const unsigned long long before = g_kat_wait_limit_ns;
+    g_kat_wait_limit_ns = limit_ns ? limit_ns : kDeviceWaitLimitNs;
+    return before;
+}
+
 extern "C" uint32_t b200spmm_kat_instr_desc(int fmt, int m, int n, int a_mn_major, int b_mn_major) {
     return ptx::make_instr_desc((uint32_t)fmt, (uint32_t)m, (uint32_t)n, a_mn_major != 0, b_mn_major != 0);
 }
@@ -231,7 +244,7 @@ extern "C" int b200spmm_kat_umma(const void *image, uint32_t image_bytes, const 
     const size_t smem = (size_t)padded + 1024 + 4096;  // slack so descriptor strides never leave the allocation
     B200_CUDA_TRY(cudaFuncSetAttribute(kat_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kat_umma_kernel<<<1, 128, smem>>>((const uint8_t *)d_img.p, padded, (const b200spmm_kat_mma_t *)d_mma.p, n_mmas,
-                                      n_cols, (float *)d_out.p, (uint32_t *)d_status.p);
+                                      n_cols, (float *)d_out.p, (uint32_t *)d_status.p, g_kat_wait_limit_ns);
     B200_CUDA_TRY(cudaGetLastError());
     B200_CUDA_TRY(cudaDeviceSynchronize());
     uint32_t status = 0;
@@ -271,7 +284,7 @@ extern "C" int b200spmm_kat_tma(const void *tensor, uint64_t inner_elems, uint64
     const size_t smem = (size_t)dump_bytes + 1024;
     B200_CUDA_TRY(cudaFuncSetAttribute(kat_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kat_tma_kernel<<<1, 32, smem>>>(map, (const int32_t *)d_loads.p, n_loads, expect_bytes, (uint8_t *)d_dump.p,
-                                    dump_bytes, (uint32_t *)d_status.p);
+                                    dump_bytes, (uint32_t *)d_status.p, g_kat_wait_limit_ns);
     B200_CUDA_TRY(cudaGetLastError());
     B200_CUDA_TRY(cudaDeviceSynchronize());
     uint32_t status = 0;

@@ -90,6 +90,17 @@ B200_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abo
     }
 }
 
+// The same wait without an abort flag: for the teardown after a failure, where the flag is already
+// up and the waiter only wants its own outstanding work to finish (or the time to run out).
+B200_DEVICE bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 0 && global_timer_ns() - t0 > limit_ns) return false;
+    }
+}
+
 // ------------------------------------------------------------------ proxies and fences
 
 // Orders this thread's generic-proxy shared-memory accesses with async-proxy accesses

@@ -56,11 +56,13 @@
 #define B200_PROF_T0() const long long prof_t0__ = clock64()
 #define B200_PROF_ADD(name) name += clock64() - prof_t0__
 #define B200_PROF_STORE(slot, value) p.prof[(size_t)blockIdx.x * 24 + (slot)] = (unsigned long long)(value)
+#define B200_DEBUG_BITS(p) ((p).debug)
 #else
 #define B200_PROF_DECL(name)
 #define B200_PROF_T0()
 #define B200_PROF_ADD(name)
 #define B200_PROF_STORE(slot, value)
+#define B200_DEBUG_BITS(p) 0u
 #endif
 
 namespace b200spmm {
@@ -75,6 +77,7 @@ constexpr int kFirstProducerWarp = 9;
 constexpr int kATileBytes = 512;     // 16 rows x 32 bytes
 constexpr uint32_t kAccCols = 32;    // TMEM columns per accumulator buffer (2 chunks x 16)
 constexpr uint32_t kTmemCols = 64;   // two accumulator buffers
+constexpr uint64_t kAbortLingerNs = 200000;  // failure path: how long a CTA lingers before it exits
 
 struct SpmmParams {
     const uint32_t *rowOffset;   // [eff+1] tiles
@@ -103,11 +106,12 @@ struct SpmmParams {
     uint32_t n_slabs;            // ceil(n / kNs)
     uint32_t c_is_half;          // 0: fp32 C, 1: fp16 C
     uint32_t *status;            // device status word
-    uint32_t debug;              // measurement aid: bit 0 skips the B gathers, bit 1 the MMAs, bit 2 the A tiles,
-                                 // bit 3 the loads of a compressed tile's stored values
     unsigned long long wait_limit_ns;
 #ifdef B200SPMM_PROFILE
-    unsigned long long *prof;    // [gridDim.x][16] cycle counters
+    // measurement builds only: bit 0 skips the B gathers, bit 1 the MMAs, bit 2 the A tiles, bit 3 the
+    // loads of a compressed tile's stored values (results are then invalid)
+    uint32_t debug;
+    unsigned long long *prof;    // [gridDim.x][24] cycle counters
 #endif
 };
 
@@ -164,7 +168,7 @@ struct SpmmCfg {
         kBitmap ? (kTilesPerWarp * (kCW * 4 + kBitWords * 8) + (kTilesPerWarp + 1) * 4 + 15) / 16 * 16 : kTilesPerWarp * kCW * 4;
     static_assert(kTilesPerWarp == 2 && kGatherOps <= 16, "a producer warp splits into two halves of 16 lanes, one per tile");
     static constexpr int kIdxBytes = kProducerWarps * kProducerGroups * kIdxSlots * kSlotBytes;
-    static constexpr int kBarrierBytes = (2 * kStages + 4) * 8 + 16;
+    static constexpr int kBarrierBytes = (2 * kStages + 5) * 8 + 16;
     static constexpr int kWinBytes = kWinSlots * 4;
     static constexpr int kChunkSlots = 32;  // chunks one CTA may take; the last entry always ends the list
     static constexpr int kChunkBytes = kChunkSlots * 4 + 8;
@@ -196,11 +200,12 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     auto empty_bar = [&](uint32_t s) { return bars_addr + 8u * ((uint32_t)kStages + s); };
     auto acc_full_bar = [&](uint32_t a) { return bars_addr + 8u * (uint32_t)(2 * kStages + a); };
     auto acc_empty_bar = [&](uint32_t a) { return bars_addr + 8u * (uint32_t)(2 * kStages + 2 + a); };
-    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(bars + 2 * kStages + 4);
+    const uint32_t drain_bar = bars_addr + 8u * (uint32_t)(2 * kStages + 4);  // failure path only, see the MMA issuer
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(bars + 2 * kStages + 5);
     uint32_t *tmem_slot = const_cast<uint32_t *>(abort_flag) + 1;
     volatile uint32_t *mma_done = abort_flag + 2;
-    volatile uint32_t *win_ends = reinterpret_cast<volatile uint32_t *>(bars + 2 * kStages + 4 + 2);
-    const uint32_t win_ends_addr = bars_addr + 8u * (uint32_t)(2 * kStages + 4 + 2);
+    volatile uint32_t *win_ends = reinterpret_cast<volatile uint32_t *>(bars + 2 * kStages + 5 + 2);
+    const uint32_t win_ends_addr = bars_addr + 8u * (uint32_t)(2 * kStages + 5 + 2);
     volatile uint32_t *chunk_list = win_ends + Cfg::kWinSlots;          // chunks this CTA runs, in order
     volatile uint32_t *chunk_avail = chunk_list + Cfg::kChunkSlots;     // entries of chunk_list written so far
 
@@ -262,6 +267,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             ptx::mbar_init(acc_full_bar(a), 1);
             ptx::mbar_init(acc_empty_bar(a), 4);
         }
+        ptx::mbar_init(drain_bar, 1);
         *abort_flag = 0;
         *mma_done = 0;
         chunk_list[0] = p.chunk_begin + blockIdx.x < p.chunk_end ? p.chunk_begin + blockIdx.x : kNoChunk;
@@ -405,7 +411,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     } else if (warp >= kFirstProducerWarp) {
         // =========================================================== producer warps
         const uint32_t pid = (uint32_t)(warp - kFirstProducerWarp);
-        const uint32_t grp = pid / kProducerWarps;  // fills stages grp, grp + 3, grp + 6, ...
+        const uint32_t grp = pid / kProducerWarps;  // fills stages grp, grp + 2, grp + 4, ...
         const uint32_t pw = pid % kProducerWarps;   // with tile slots 2*pw and 2*pw + 1 of each of them
         constexpr uint32_t kTpw = kTilesPerWarp;
         const uint32_t half = (uint32_t)lane >> 4, hl = (uint32_t)lane & 15u;  // TMA gathers: lanes 16*j.. serve tile j of the warp
@@ -555,7 +561,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             if (!kBitmap) return;
             const uint32_t *slot_words = my_idx + (it_v % Cfg::kIdxSlots) * kSlotWords;
             const uint32_t tpos0 = vc.sp * kTps + pw * kTpw;
-            const uint32_t here = (!vc.done && tpos0 < vc.n_tiles && !(p.debug & 8u)) ? min(kTpw, vc.n_tiles - tpos0) : 0u;
+            const uint32_t here = (!vc.done && tpos0 < vc.n_tiles && !(B200_DEBUG_BITS(p) & 8u)) ? min(kTpw, vc.n_tiles - tpos0) : 0u;
 #pragma unroll
             for (uint32_t j = 0; j < kTpw; ++j) {
 #pragma unroll
@@ -597,7 +603,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             const uint32_t tpos0 = sp * kTps + pw * kTpw;
             // the warp's tiles in this stage (the last stage of a pass may be short), and those it gathers rows for
             const uint32_t here = tpos0 < cur.n_tiles ? min(kTpw, cur.n_tiles - tpos0) : 0u;
-            const uint32_t gather_here = (p.debug & 1u) ? 0u : here;
+            const uint32_t gather_here = (B200_DEBUG_BITS(p) & 1u) ? 0u : here;
             const uint32_t *slot_words = my_idx + (it % Cfg::kIdxSlots) * kSlotWords;
             const uint32_t first_slot = s * kTps + pw * kTpw;  // the warp's first tile slot of the ring
 
@@ -611,7 +617,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     B200_PROF_ADD(prof_wait_empty);
                 }
                 if (ok && !kBitmap) {
-                    const bool a_tiles = pw == 0 && !(p.debug & 4u);
+                    const bool a_tiles = pw == 0 && !(B200_DEBUG_BITS(p) & 4u);
                     if (kTma) {
                         // this warp's arrival, announcing the bytes its TMA loads will deliver
                         const uint32_t bytes = gather_here * Cfg::kGatherBytes + (a_tiles ? kTps * kATileBytes : 0u);
@@ -628,7 +634,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             if (!ok) { failed = true; break; }
             if (kBitmap) {
                 // expand this warp's tiles into their 512 bytes of the stage, then announce the gathers' bytes
-                if (here && !(p.debug & 4u)) {
+                if (here && !(B200_DEBUG_BITS(p) & 4u)) {
 #pragma unroll
                     for (uint32_t j = 0; j < kTpw; ++j) {
                         if (j < here) {
@@ -737,7 +743,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
         (void)failed; (void)n_bytes; (void)Bbytes; (void)row_pitch; (void)op_dst; (void)op_x; (void)op_quad; (void)s_arrive;
     } else if (warp == kMmaWarp && lane == 0) {
-        // =========================================================== MMA issuer (warp 4, lane 0)
+        // =========================================================== MMA issuer (warp 8, lane 0)
         // A single thread: every instruction it executes per tile is on the critical path, so the
         // loop is kept to a wait per eight tiles, one or two MMAs per tile and a commit per eight
         // tiles.  The tile counts of the next kWinAhead windows are prefetched into shared memory
@@ -764,7 +770,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         uint32_t ad_lo = a_lo0, bd_lo = b_lo0;  // low descriptor words of tile (s, slot)
         uint32_t acc_it = 0;
         bool alive = true;
-        const bool do_mma = !(p.debug & 2u);
+        const bool do_mma = !(B200_DEBUG_BITS(p) & 2u);
         B200_PROF_DECL(prof_wait_full);
         B200_PROF_DECL(prof_wait_acc);
         B200_PROF_DECL(prof_mma);
@@ -832,7 +838,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     //   head - the rest of a stage the previous window left partly used (predicated MMAs),
                     //   body - whole stages: wait, eight MMAs, commit; ring bookkeeping by selects,
                     //   tail - the first tiles of a stage the next window will finish (predicated MMAs).
-                    auto partial = [&](uint32_t k) {  // k tiles starting at (s, slot), 0 < k < 4 or closing a stage
+                    auto partial = [&](uint32_t k) {  // k tiles starting at (s, slot), 0 < k < 8 or closing a stage
                         B200_PROF_T0();
 #pragma unroll
                         for (int q = 0; q < kTps; ++q) {
@@ -895,7 +901,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                             B200_PROF_ADD(prof_commit);
                         }
                     }
-                    if (nt != 0 && alive) {  // tail: slot == 0, 0 < nt < 4
+                    if (nt != 0 && alive) {  // tail: slot == 0, 0 < nt < 8
                         await_stage();
                         if (alive) partial(nt);
                     }
@@ -914,6 +920,14 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             }
         }  // chunks
         ptx::cp_async_wait_group<0>();
+        if (!alive || *abort_flag) {
+            // Gave up, possibly in the middle of a window: MMAs may have been issued that no commit covers yet.
+            // They read shared memory and write TMEM, so they must be finished before the CTA frees
+            // either: one more commit, and a wait (bounded like every other) for its arrival.
+            ptx::umma_commit(drain_bar);
+            ptx::mbar_wait_bounded(drain_bar, 0, limit);
+            ptx::tcgen05_fence_after_sync();
+        }
 #ifdef B200SPMM_PROFILE
         B200_PROF_STORE(4, clock64() - prof_start);
         B200_PROF_STORE(5, prof_wait_full);
@@ -937,6 +951,15 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         __syncwarp();
     }
     // ---- teardown: every role ends up here, on success and on timeout alike
+    if (*abort_flag) {
+        // After a failure TMA loads may still be on their way into this CTA's shared memory: the
+        // producers stop at their next wait, which can be right after an issue, and a load whose
+        // barrier phase never completes offers nothing to wait on.  The thread that gave up has
+        // already waited the full limit; everybody else stays this long after its last instruction,
+        // many times the latency of a load, before the CTA lets go of its shared memory.
+        const uint64_t t0 = ptx::global_timer_ns();
+        while (ptx::global_timer_ns() - t0 < kAbortLingerNs) __nanosleep(1000);
+    }
     ptx::tcgen05_fence_before_sync();
     __syncthreads();
     if (warp == kMmaWarp) {

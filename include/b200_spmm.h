@@ -325,8 +325,9 @@ int b200spmm_bench(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, 
  * host thread inside a latency budget where cudaMalloc's implicit device synchronisation is not
  * acceptable, or a component that is simply not allowed to grow the process's footprint after
  * start-up.  b200spmm_plan_create allocates (the device copy of the matrix, the schedule table,
- * a status word); this entry point allocates nothing, on the host heap or on the device, and
- * calls no allocating library routine.  The caller passes the converted matrix as four arrays
+ * a status word); this entry point allocates no device memory and calls no allocating library
+ * routine (on the host it allocates nothing either unless a CUDA call fails, when the runtime's
+ * message is composed into a string for b200spmm_last_cuda_error()).  The caller passes the converted matrix as four arrays
  * that already live on `device` (for example carved out of its own pool), B and C.
  *
  * The kernel still needs working memory: the schedule table (one cut per CTA) and its status

@@ -31,11 +31,35 @@ typedef struct {
 /*
  * Copies `image` (image_bytes <= 96 KiB) into 1024-byte-aligned shared memory, issues the listed
  * MMAs in order from one thread, then dumps TMEM lanes 0..127 x columns 0..n_cols-1 as fp32 into
- * out[128 * n_cols].  n_cols is a multiple of 16, at most 128.
+ * out[128 * n_cols].  n_cols is a multiple of 16, at most 256.
  * Replaces tma_wgmma_kernel + test_result_cpu (src/test_fp16.cu:238-315).
  */
 int b200spmm_kat_umma(const void *image, uint32_t image_bytes, const b200spmm_kat_mma_t *mmas, int n_mmas,
                       int n_cols, float *out, int device);
+
+/*
+ * Sets how long a wait inside the known-answer kernels may last, in nanoseconds (0 restores the
+ * default of two seconds), and returns the previous value.  A test shortens it, hands
+ * b200spmm_kat_tma an expect_bytes larger than its loads deliver and must get
+ * B200SPMM_ERR_DEVICE_TIMEOUT back - the bounded wait that replaces the reference's endless
+ * mbarrier spin (src/ptx/barrier.h:29-41) - with the device still usable afterwards.
+ */
+unsigned long long b200spmm_kat_wait_limit(unsigned long long limit_ns);
+
+/*
+ * The whole SpMM kernel with a failure made on the host: the product of `plan` (b200_spmm.h) is
+ * launched with a tensor map over B whose box is half as wide as the kernel counts on, so every ring
+ * stage receives fewer bytes than its barrier expects and no stage ever completes.  Every load that
+ * is issued still lands, inside its own slot.  With waits limited to limit_ns (at most two seconds)
+ * the kernel must unwind by itself - all warp roles leave their loops, pending MMAs are waited for,
+ * tensor memory is released - and b200spmm_plan_sync must then report B200SPMM_ERR_DEVICE_TIMEOUT
+ * and leave the plan ready for a normal launch.  C receives nothing meaningful.  This is the bounded
+ * replacement of the reference's endless waits (src/ptx/barrier.h:29-41, 72-86) under test; fp32 C,
+ * n at least one 128-byte box wide.  The plan type is declared in b200_spmm.h.
+ */
+struct b200spmm_plan;
+int b200spmm_kat_spmm_starved(struct b200spmm_plan *plan, const void *d_B, int64_t ldb, int64_t n, void *d_C,
+                              int64_t ldc, unsigned long long limit_ns, void *stream);
 
 /* Builds an instruction descriptor: fmt 0 = f16, 1 = bf16, 2 = tf32; fp32 accumulate. */
 uint32_t b200spmm_kat_instr_desc(int fmt, int m, int n, int a_mn_major, int b_mn_major);

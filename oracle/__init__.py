@@ -21,10 +21,16 @@ _i64 = C.c_int64
 _p = C.c_void_p
 
 
+def reference_dir() -> str:
+    """Where the reference project's sources are mounted: $HOPPER_SPMM_REFERENCE, else the default
+    mount point.  Only the build of the harness reads it; nothing needs it at run time."""
+    return os.environ.get("HOPPER_SPMM_REFERENCE", "/root/reference")
+
+
 def build(with_ref: bool = False) -> None:
     """Compile the oracle with make; ``with_ref`` also builds the reference harness."""
     targets = ["all"] + (["ref"] if with_ref else [])
-    subprocess.run(["make", "-s", "-C", _HERE] + targets, check=True)
+    subprocess.run(["make", "-s", "-C", _HERE, "REF=" + reference_dir()] + targets, check=True)
 
 
 def _load() -> C.CDLL:

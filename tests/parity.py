@@ -31,3 +31,26 @@ def check(got, rows, rp, ci, v, B, tf32_mode=1, threads=0):
     bad, max_rel, max_abs = oracle.compare(got, tight, tol)
     assert bad <= 1e-3 * got.size, f"{bad} of {got.size} elements fail the reference's rule (max rel {max_rel:.3e})"
     return {"scaled_err": scaled, "rule_failures": bad, "max_rel": max_rel, "max_abs": max_abs}
+
+
+def rows_subset(rp, ci, v, ranges):
+    """CSR (row_ptr rebased to zero) of the rows in `ranges`, a list of [begin, end) pairs, stacked in order."""
+    rp = np.asarray(rp)
+    counts, cols, vals = [], [], []
+    for a, b in ranges:
+        lo, hi = int(rp[a]), int(rp[b])
+        counts.append(np.diff(rp[a:b + 1].astype(np.int64)))
+        cols.append(ci[lo:hi])
+        vals.append(v[lo:hi])
+    sub_rp = np.concatenate([[0], np.cumsum(np.concatenate(counts))]).astype(np.uint32)
+    return sub_rp, np.concatenate(cols), np.concatenate(vals)
+
+
+def check_rows(got_rows, rp, ci, v, B, ranges, threads=0):
+    """The same two measurements on a sample of rows: `got_rows` holds C's rows of `ranges`, stacked in
+    order.  For results too large to recompute whole on the host; the sample should hold the heaviest
+    rows, the first window and the last one."""
+    sub_rp, sub_ci, sub_v = rows_subset(rp, ci, v, ranges)
+    stats = check(got_rows, len(sub_rp) - 1, sub_rp, sub_ci, sub_v, B, threads=threads)
+    stats["checked_rows"] = len(sub_rp) - 1
+    return stats

@@ -141,3 +141,24 @@ def test_mma_issue_rate_of_the_spmm_shape(tf32):
     assert seen[(16, 2)][1] / 2 < seen[(16, 1)][1] * 1.05, seen
     assert lib.b200spmm_kat_umma_rate(0, 128, 24, 16, 1, out, 0) == capi.ERR_INVALID_ARG
     assert lib.b200spmm_kat_umma_rate(0, 128, 16, 16, 3, out, 0) == capi.ERR_INVALID_ARG
+
+
+def test_a_wait_that_cannot_complete_runs_out_and_the_device_stays_usable():
+    # The reference's mbarrier_wait spins for ever (src/ptx/barrier.h:29-41); every wait here is
+    # bounded.  The barrier is told to expect 16 bytes more than the one load delivers, so its phase
+    # can never complete: the kernel must come back on its own with the time-out status, the load
+    # that was issued must have landed all the same, and the next kernel on the device must work.
+    from hopper_spmm_b200 import _capi as capi
+    lib = capi.lib()
+    data = np.arange(64 * 16, dtype=np.uint16).reshape(64, 16)
+    loads = [[0, 0, 0, 16, 0, 0, 0]]
+    expect = ku.pack_tile(data[16:32].view(np.float16))
+    before = lib.b200spmm_kat_wait_limit(5_000_000)  # 5 ms
+    try:
+        st, dump = ku.run_tma(data, 16, 16, 1, loads, 512 + 16, 512)
+        assert st == capi.ERR_DEVICE_TIMEOUT
+        assert dump.tobytes() == expect
+    finally:
+        assert lib.b200spmm_kat_wait_limit(before) == 5_000_000
+    st, dump = ku.run_tma(data, 16, 16, 1, loads, 512, 512)
+    assert st == 0 and dump.tobytes() == expect

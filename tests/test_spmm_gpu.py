@@ -91,6 +91,56 @@ def test_hub_windows_are_shared_between_ctas(dt, n, c_half):
         assert np.all(C_out[64:96] == 0)
 
 
+def test_hub_windows_leave_no_row_unwritten():
+    # the same kind of matrix through the device-pointer call into a C full of NaN: the rows of split
+    # windows come from the fix-up kernel, the gaps after them from the epilogue's zero fill
+    import torch
+    rows, cols, rp, ci, v = random_csr(203, 6000, 0.004, 21, empty_rows=[(64, 96), (128, 144)], dense_rows=[3, 120, 200])
+    B = dense_b(cols, 128, 4)
+    plan = hs.SpmmPlan(hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v)), n_ctas=37)
+    try:
+        dC = torch.full((rows, 128), float("nan"), device="cuda")
+        plan.spmm(torch.from_numpy(B).cuda(), dC)
+        assert plan.launch_info().kernel_launches == 2
+        parity.check(dC.cpu().numpy(), rows, rp, ci, v, B)
+    finally:
+        plan.close()
+
+
+@pytest.mark.parametrize("case", ["small fp16", "small tf32", "chunks handed out at run time"])
+def test_starved_pipeline_times_out_and_the_plan_recovers(case):
+    # A failure made on the host: B's tensor map delivers half the bytes every stage barrier expects,
+    # so no stage ever completes.  With waits limited to 5 ms the kernel has to unwind by itself (the
+    # reference would spin for ever, src/ptx/barrier.h:29-41); the status says so, and the next launch
+    # of the same plan is a normal, correct product.
+    import time
+    import torch
+    if case.startswith("small"):
+        dt = np.float16 if case.endswith("fp16") else np.float32
+        rows, cols, rp, ci, v = random_csr(203, 517, 0.03, 11, dt, dense_rows=[7])
+        B = torch.from_numpy(dense_b(cols, 128, 3, dt)).cuda()
+    else:
+        csr, B = synth.make_config("rmat24_sharded_fp16", 0, "cuda", 6)  # enough tiles for several chunks per CTA
+        rows, cols = csr.rows, csr.cols
+        rp, ci, v = csr.numpy()
+    plan = hs.SpmmPlan(hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v)))
+    try:
+        n = B.shape[1]
+        dC = torch.zeros((rows, n), device="cuda")
+        s = torch.cuda.current_stream().cuda_stream
+        lib = capi.lib()
+        assert lib.b200spmm_kat_spmm_starved(plan._p, B.data_ptr(), n, n, dC.data_ptr(), n, 5_000_000, s) == 0
+        t0 = time.perf_counter()
+        assert lib.b200spmm_plan_sync(plan._p, s) == capi.ERR_DEVICE_TIMEOUT
+        assert time.perf_counter() - t0 < 5.0
+        for _ in range(2):  # tensor memory was released and the hand-out counters are back at zero
+            dC = torch.full((rows, n), float("nan"), device="cuda")
+            plan.spmm(B, dC)
+            parity.check(dC.cpu().numpy(), rows, rp, ci, v, B.cpu().numpy())
+    finally:
+        plan.close()
+
+
 def test_more_ctas_than_windows_and_one_cta():
     rows, cols, rp, ci, v = random_csr(96, 300, 0.1, 8)
     B = dense_b(cols, 64, 4)
@@ -168,13 +218,16 @@ def test_reference_operator_names():
         hs.tf32_spmm(btcf, hs.DENSE_MTX(cols, 128, B), Cm)
 
 
-@pytest.mark.parametrize("name,k", [("uniform_4096_fp16", 0), ("blocks_16384_tf32", 1), ("rmat20_gnn_fp16", 4),
-                                    ("pruned_llm_fp16", 3), ("rmat24_sharded_fp16", 8)])
+@pytest.mark.parametrize("name,k", [("uniform_4096_fp16", 0), ("blocks_16384_tf32", 0), ("rmat20_gnn_fp16", 0),
+                                    ("pruned_llm_fp16", 0), ("rmat24_sharded_fp16", 5)])
 def test_benchmark_configurations(name, k):
-    csr, B = synth.make_config(name, 0, "cpu", k)
+    # the first four at their full size, whole result against the CPU oracle; the 2^24-node graph is
+    # checked at full size, on a row sample, by the benchmark itself and here at 2^19 nodes
+    csr, B = synth.make_config(name, 0, "cuda", k)
     rp, ci, v = csr.numpy()
-    C_out, _ = run_host(csr.rows, csr.cols, rp, ci, v, B.numpy())
-    stats = parity.check(C_out, csr.rows, rp, ci, v, B.numpy())
+    Bn = B.cpu().numpy()
+    C_out, _ = run_host(csr.rows, csr.cols, rp, ci, v, Bn)
+    stats = parity.check(C_out, csr.rows, rp, ci, v, Bn)
     print(name, stats)
 
 
