@@ -23,7 +23,8 @@ class BtcfInfo(C.Structure):
 
 class LaunchInfo(C.Structure):
     _fields_ = [("n_ctas", i32), ("threads", i32), ("stages", i32), ("feature_slab", i32), ("n_slabs", i32),
-                ("smem_bytes", i64), ("kernel_launches", i64), ("tma_gather", i32), ("bitmap_tiles", i32)]
+                ("smem_bytes", i64), ("kernel_launches", i64), ("tma_gather", i32), ("bitmap_tiles", i32),
+                ("row_window", i32)]
 
 
 class KatMma(C.Structure):
@@ -94,6 +95,8 @@ SIGNATURES = {
     "b200spmm_bench": (C.c_int, [vp, vp, i64, i64, vp, i64, C.c_int, C.c_int, C.c_int, vp, C.POINTER(C.c_float)]),
     "b200spmm_spmm_noalloc": (C.c_int, [C.POINTER(BtcfInfo), vp, vp, vp, vp, vp, i64, i64, vp, i64, C.c_int, C.c_int,
                                         C.c_int, vp]),
+    "b200spmm_plan_tall_info": (C.c_int, [vp, C.POINTER(BtcfInfo)]),
+    "b200spmm_plan_tall_copy_to_host": (C.c_int, [vp, vp, vp, vp, vp]),
     "b200spmm_plan_launch_info": (C.c_int, [vp, C.POINTER(LaunchInfo)]),
     "b200spmm_kat_umma": (C.c_int, [vp, u32, C.POINTER(KatMma), C.c_int, C.c_int, vp, C.c_int]),
     "b200spmm_kat_wait_limit": (C.c_uint64, [C.c_uint64]),

@@ -15,6 +15,8 @@
 #include "format.hpp"
 #include "handles.hpp"
 #include "spmm_kernel.cuh"
+#include "spmm_tall_kernel.cuh"
+#include "tall_gpu.hpp"
 #include "tensormap.hpp"
 
 namespace b200spmm {
@@ -66,6 +68,12 @@ struct b200spmm_plan {
     std::vector<cudaEvent_t> band_done;
     const Sched *launch_sched = nullptr;  // the one the next launch uses
     CompressedTiles comp;                 // the tiles as bitmap + stored values (empty: dense tiles only)
+    // The same matrix in 128-row super-windows, built when merging eight windows shortens the tile
+    // stream enough for the wide-MMA kernel (spmm_tall_kernel.cuh) to win; empty otherwise.
+    TallFormat tall;
+    bool tall_forced = false;  // B200SPMM_WINDOW=128: use it whatever the launch's size
+    CUtensorMap tmap_tall{};
+    int n_sms = 0;
     float *d_partial = nullptr;  // [n_slots][16][n] fp32, grown to the largest need seen
     size_t partial_floats = 0;
     uint32_t *d_status = nullptr;
@@ -109,6 +117,7 @@ int launch_one(b200spmm_plan *p, const SpmmParams &prm, const CUtensorMap &tmap_
     p->last.kernel_launches = 1;
     p->last.tma_gather = kTma ? 1 : 0;
     p->last.bitmap_tiles = kBitmap ? 1 : 0;
+    p->last.row_window = kRowWindow;
     return B200SPMM_OK;
 }
 
@@ -141,20 +150,20 @@ bool env_is(const char *name, const char *value) {
 // Tensor map over B seen as [cols][n] with its real row pitch; a box is 128 bytes of one row.
 // Rows or features past the end read as zeros.  Re-encoded only when B's address, pitch or width
 // differ from the previous launch of this plan.
-int b_tensor_map(b200spmm_plan *p, const SpmmParams &prm, bool tf32) {
-    if (p->tmap_b_ptr == prm.B && p->tmap_b_ldb == prm.ldb && p->tmap_b_n == prm.n) return B200SPMM_OK;
+int b_tensor_map(b200spmm_plan *p, const void *B, int64_t ldb, uint32_t n, uint32_t cols, bool tf32) {
+    if (p->tmap_b_ptr == B && p->tmap_b_ldb == ldb && p->tmap_b_n == n) return B200SPMM_OK;
     const uint32_t esz = tf32 ? 4 : 2, box = (p->starve_gathers ? 64 : 128) / esz;
     p->tmap_b_ptr = nullptr;
-    if (!encode_2d(&p->tmap_b, tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, prm.B, prm.n,
-                   prm.cols, (uint64_t)prm.ldb * esz, box, 1,
+    if (!encode_2d(&p->tmap_b, tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, B, n,
+                   cols, (uint64_t)ldb * esz, box, 1,
                    tf32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) {
         set_last_error_static("cuTensorMapEncodeTiled failed for B");
         return B200SPMM_ERR_CUDA;
     }
-    p->tmap_b_ptr = prm.B;
-    p->tmap_b_ldb = prm.ldb;
-    p->tmap_b_n = prm.n;
+    p->tmap_b_ptr = B;
+    p->tmap_b_ldb = ldb;
+    p->tmap_b_n = n;
     return B200SPMM_OK;
 }
 
@@ -165,7 +174,7 @@ int launch_dtype(b200spmm_plan *p, SpmmParams &prm, cudaStream_t stream) {
     constexpr uint32_t esz = kTf32 ? 4 : 2, box = 128 / esz;
     if (p->gather_cpasync || prm.n < box) return launch_slab<kTf32, false, false>(p, prm, p->tmap_b, stream);
     {
-        int st = b_tensor_map(p, prm, kTf32);
+        int st = b_tensor_map(p, prm.B, prm.ldb, prm.n, prm.cols, kTf32);
         if (st != B200SPMM_OK) return st;
     }
     const CUtensorMap &tmap_b = p->tmap_b;
@@ -193,6 +202,97 @@ int encode_tile_map(b200spmm_plan *p) {
     return B200SPMM_OK;
 }
 
+// ---- 128-row super-windows
+template <bool kTf32, int kNs>
+int launch_tall_one(b200spmm_plan *p, TallParams &prm, cudaStream_t stream) {
+    using Cfg = TallCfg<kTf32, kNs>;
+    auto kernel = spmm_tall_kernel<kTf32, kNs>;
+    static thread_local int configured_device = -1;
+    if (configured_device != p->device) {
+        B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes));
+        configured_device = p->device;
+    }
+    prm.n_slabs = (prm.n + kNs - 1) / kNs;
+    prm.n_items = prm.eff_row_windows * prm.n_slabs;
+    const int n_ctas = (int)std::min<uint32_t>(prm.n_items, (uint32_t)p->n_sms);
+    kernel<<<n_ctas, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p->tmap_tall, p->tmap_b, prm);
+    B200_CUDA_TRY(cudaGetLastError());
+    p->last.n_ctas = n_ctas;
+    p->last.threads = Cfg::kThreads;
+    p->last.stages = Cfg::kStages;
+    p->last.feature_slab = kNs;
+    p->last.n_slabs = (int)prm.n_slabs;
+    p->last.smem_bytes = (int64_t)Cfg::kSmemBytes;
+    p->last.kernel_launches = 1;
+    p->last.tma_gather = 1;
+    p->last.bitmap_tiles = 0;
+    p->last.row_window = kTallRows;
+    return B200SPMM_OK;
+}
+
+// Does this launch go to the super-window kernel?  Only with the TMA gathers (B at least one
+// 128-byte box wide), and - unless forced - only when there are enough (window, slab) items to
+// occupy every SM.
+bool use_tall(const b200spmm_plan *p, int64_t n) {
+    if (!p->tall.tiles || p->gather_cpasync || p->starve_gathers) return false;
+    if (n * p->info.elt_size < 128) return false;
+    if (p->tall_forced) return true;
+    const int64_t slab = n <= 128 ? 128 : 256;
+    return (int64_t)p->tall.eff * ((n + slab - 1) / slab) >= p->n_sms;
+}
+
+int launch_tall(b200spmm_plan *p, const void *d_B, int64_t ldb, int64_t n, void *d_C, int64_t ldc, int c_dtype,
+                cudaStream_t stream) {
+    const bool tf32 = p->info.dtype == B200SPMM_TF32;
+    int st = b_tensor_map(p, d_B, ldb, (uint32_t)n, (uint32_t)p->info.cols, tf32);
+    if (st != B200SPMM_OK) return st;
+    TallParams prm{};
+    prm.rowOffset = p->tall.d_rowOffset;
+    prm.tcA2B = p->tall.d_tcA2B;
+    prm.rowIdx = p->tall.d_rowIdx;
+    prm.sched_counter = p->d_status + 1;
+    prm.C = d_C;
+    prm.ldc = ldc;
+    prm.rows = (uint32_t)p->info.rows;
+    prm.cols = (uint32_t)p->info.cols;
+    prm.n = (uint32_t)n;
+    prm.eff_row_windows = (uint32_t)p->tall.eff;
+    prm.c_is_half = c_dtype == B200SPMM_C_F16;
+    prm.status = p->d_status;
+    prm.wait_limit_ns = p->wait_limit_ns;
+    if (n <= 128) return tf32 ? launch_tall_one<true, 128>(p, prm, stream) : launch_tall_one<false, 128>(p, prm, stream);
+    return tf32 ? launch_tall_one<true, 256>(p, prm, stream) : launch_tall_one<false, 256>(p, prm, stream);
+}
+
+// Builds the super-window copy of the matrix when it pays.  The 16-row kernel spends about 100 SM
+// clocks per tile and 128 features whatever the tile holds; the super-window kernel about 70 per
+// 128-row tile and 128 features.  So the merge pays when it leaves fewer than ~0.7 of the tiles -
+// i.e. when the parts of a super-window share most of their columns (a pruned weight matrix: 0.15;
+// a power-law graph: ~0.9, stays with 16 rows).  B200SPMM_WINDOW=16 / 128 overrides the choice.
+int plan_build_tall(b200spmm_plan *p, const uint32_t *h_rowOffset, const uint32_t *h_rowIdx) {
+    const auto &info = p->info;
+    if (!info.total_tiles || env_is("B200SPMM_WINDOW", "16")) return B200SPMM_OK;
+    p->tall_forced = env_is("B200SPMM_WINDOW", "128");
+    if (!p->tall_forced) {
+        double ratio = 1.0;
+        uint64_t n_super = 0;
+        int st = estimate_tall_tile_ratio(info, h_rowOffset, h_rowIdx, p->d_tcA2B, 48, &ratio, &n_super);
+        if (st != B200SPMM_OK) return st;
+        // fewer super-windows than SMs / 16 can never fill the GPU, however wide B is
+        if (ratio > 0.7 || n_super * 16 < (uint64_t)p->n_sms) return B200SPMM_OK;
+    }
+    int st = build_tall_device(info, h_rowOffset, h_rowIdx, p->d_rowOffset, p->d_tcA2B, p->d_data, p->d_rowIdx, &p->tall);
+    if (st == B200SPMM_ERR_UNSUPPORTED) return B200SPMM_OK;  // too large for one tile tensor map: 16-row kernel
+    if (st != B200SPMM_OK || !p->tall.tiles) return st;
+    const bool f16 = info.dtype == B200SPMM_F16;
+    if (!encode_2d(&p->tmap_tall, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p->tall.d_data,
+                   f16 ? 16 : 8, p->tall.tiles * kTallRows, 32, f16 ? 16 : 8, kTallRows, CU_TENSOR_MAP_SWIZZLE_32B)) {
+        set_last_error_static("cuTensorMapEncodeTiled failed for the super-window tile array");
+        return B200SPMM_ERR_CUDA;
+    }
+    return B200SPMM_OK;
+}
+
 int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, const uint32_t *h_rowIdx, int n_ctas) {
     const auto &info = p->info;
     if (info.row_window != kRowWindow) return B200SPMM_ERR_UNSUPPORTED;
@@ -202,6 +302,7 @@ int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, const uint32_t *h
     cudaDeviceProp prop;
     B200_CUDA_TRY(cudaGetDeviceProperties(&prop, p->device));
     if (prop.major != 10) return B200SPMM_ERR_NO_DEVICE;
+    p->n_sms = prop.multiProcessorCount;
     auto upload = [](auto **dst, const auto &v) -> int {
         using T = typename std::remove_reference<decltype(v)>::type::value_type;
         B200_CUDA_TRY(cudaMalloc(dst, std::max<size_t>(v.size() * sizeof(T), 16)));
@@ -252,6 +353,10 @@ int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, const uint32_t *h
     p->gather_cpasync = env_is("B200SPMM_GATHER", "cpasync");
     if (info.total_tiles && env_is("B200SPMM_TILES", "bitmap")) {
         int st = compress_tiles_device(p->d_data, info.total_tiles, info.dtype, &p->comp);
+        if (st != B200SPMM_OK) return st;
+    }
+    if (n_ctas <= 0 && !p->comp.tcBit) {  // an explicit CTA count or compressed tiles ask for the 16-row kernel
+        int st = plan_build_tall(p, h_rowOffset, h_rowIdx);
         if (st != B200SPMM_OK) return st;
     }
     return B200SPMM_OK;
@@ -472,6 +577,7 @@ void b200spmm_plan_destroy(b200spmm_plan_t *p) {
         cudaFree(ps.d_piece_slots);
     }
     free_compressed_tiles(&p->comp);
+    free_tall(&p->tall);
     for (cudaEvent_t e : p->band_done) cudaEventDestroy(e);
     if (p->copy_stream) cudaStreamDestroy(p->copy_stream);
     cudaFree(p->d_partial);
@@ -564,6 +670,29 @@ int b200spmm_plan_info(const b200spmm_plan_t *p, b200spmm_btcf_info_t *info) {
     return B200SPMM_OK;
 }
 
+int b200spmm_plan_tall_info(const b200spmm_plan_t *p, b200spmm_btcf_info_t *info) {
+    if (!p || !info) return B200SPMM_ERR_INVALID_ARG;
+    *info = p->info;
+    info->row_window = p->tall.tiles ? kTallRows : 0;
+    info->total_row_windows = (p->info.rows + kTallRows - 1) / kTallRows;
+    info->eff_row_windows = p->tall.eff;
+    info->total_tiles = p->tall.tiles;
+    return B200SPMM_OK;
+}
+
+int b200spmm_plan_tall_copy_to_host(const b200spmm_plan_t *p, uint32_t *rowOffset, uint32_t *tcA2B, void *data,
+                                    uint32_t *rowIdx) {
+    if (!p || !rowOffset || !tcA2B || !data || !rowIdx) return B200SPMM_ERR_INVALID_ARG;
+    if (!p->tall.tiles) return B200SPMM_ERR_UNSUPPORTED;
+    B200_CUDA_TRY(cudaSetDevice(p->device));
+    const uint64_t cw = (uint64_t)p->info.col_window;
+    B200_CUDA_TRY(cudaMemcpy(rowOffset, p->tall.d_rowOffset, (p->tall.eff + 1) * 4, cudaMemcpyDeviceToHost));
+    B200_CUDA_TRY(cudaMemcpy(rowIdx, p->tall.d_rowIdx, p->tall.eff * 4, cudaMemcpyDeviceToHost));
+    B200_CUDA_TRY(cudaMemcpy(tcA2B, p->tall.d_tcA2B, p->tall.tiles * cw * 4, cudaMemcpyDeviceToHost));
+    B200_CUDA_TRY(cudaMemcpy(data, p->tall.d_data, p->tall.tiles * kTallRows * cw * p->info.elt_size, cudaMemcpyDeviceToHost));
+    return B200SPMM_OK;
+}
+
 int b200spmm_plan_launch_info(const b200spmm_plan_t *p, b200spmm_launch_info_t *info) {
     if (!p || !info) return B200SPMM_ERR_INVALID_ARG;
     *info = p->last;
@@ -591,6 +720,7 @@ int spmm_launch(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, voi
         B200_CUDA_TRY(cudaMemset2DAsync(d_C, (size_t)ldc * csz, 0, (size_t)n * csz, p->info.rows, stream));
         return B200SPMM_OK;
     }
+    if (band < 0 && use_tall(p, n)) return launch_tall(p, d_B, ldb, n, d_C, ldc, c_dtype, stream);
     SpmmParams prm{};
     prm.rowOffset = p->d_rowOffset;
     prm.tcA2B = p->d_tcA2B;
@@ -704,7 +834,7 @@ int b200spmm_spmm_host(b200spmm_plan_t *p, const void *h_B, int64_t n, void *h_C
     }
     B200_CUDA_TRY(cudaMemcpyAsync(p->d_B, h_B, b_bytes, cudaMemcpyHostToDevice, nullptr));
     const b200spmm_plan::Sched &sc = p->sched;
-    const size_t bands = sc.band_chunk.size() > 1 ? sc.band_chunk.size() - 1 : 1;
+    const size_t bands = sc.band_chunk.size() > 1 && !use_tall(p, n) ? sc.band_chunk.size() - 1 : 1;
     if (bands == 1 || p->info.eff_row_windows == 0) {
         int st = b200spmm_spmm(p, p->d_B, n, n, p->d_C, n, c_dtype, nullptr);
         if (st != B200SPMM_OK) return st;

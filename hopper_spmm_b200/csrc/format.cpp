@@ -164,7 +164,8 @@ int rewindow_btcf(uint64_t rows, uint64_t cols, uint64_t nnz, int dtype, int rw_
                   const void *in_data, const uint32_t *in_rowIdx, int rw_out, int n_threads, Btcf *out) {
     if (!out || !in_rowOffset) return B200SPMM_ERR_INVALID_ARG;
     if (dtype != B200SPMM_F16 && dtype != B200SPMM_TF32) return B200SPMM_ERR_INVALID_ARG;
-    if (rw_in < 1 || rw_out < rw_in || rw_out % rw_in || (rw_out != 8 && rw_out != 16)) return B200SPMM_ERR_INVALID_ARG;
+    if (rw_in < 1 || rw_out < rw_in || rw_out % rw_in) return B200SPMM_ERR_INVALID_ARG;
+    if (rw_out != 8 && rw_out != 16 && rw_out != 32 && rw_out != 64 && rw_out != 128) return B200SPMM_ERR_INVALID_ARG;
     if (col_window != 4 && col_window != 8 && col_window != 16) return B200SPMM_ERR_INVALID_ARG;
     if (rows >= 0xFFFFFFFFull || cols > 0xFFFFFFFFull) return B200SPMM_ERR_UNSUPPORTED;
     const uint64_t eff_in = eff_row_windows, RWI = (uint64_t)rw_in, RWO = (uint64_t)rw_out, CW = (uint64_t)col_window;

@@ -1,0 +1,436 @@
+// SpMM kernel for 128-row super-windows: the variant for matrices whose 16-row windows already touch
+// most columns (a pruned weight matrix: 10 % unstructured density puts 81 % of all columns into every
+// 16-row window), where the condensed tile stream is as long as a dense one.
+//
+// The 16-row kernel (spmm_kernel.cuh) keeps the reference's transposition (src/fp16.cu:147): the
+// gathered rows of B are the wide operand and the window's 16 rows are the MMA's N.  An N = 16 MMA
+// holds the tensor pipe for the ~40 clocks it takes to read its 4 KB operand from shared memory and
+// does 8 clocks of arithmetic.  Here eight windows are merged (plan-internal, the format handed to
+// callers stays the reference's) and the transposition is undone:
+//     D[128 window rows x kNs features] += Atile[128 x CW] * Bgather[CW x kNs]
+// The sparse tile is the UMMA A operand (M = 128, K-major, 32-byte swizzle: as it lies in `data`,
+// 128 rows of 32 bytes), the gathered rows of B are the UMMA B operand (N = kNs = 128 or 256 features,
+// MN-major, 128-byte swizzle: as TMA tile::gather4 lays B's rows down).  One MMA per tile does
+// 128 x kNs x CW multiply-adds at the pipe's full rate, and the accumulator's lane is the window row,
+// so an epilogue thread holds consecutive features of one row and stores them as 16-byte vectors.
+//
+// A work item is (super-window, feature slab); items are numbered window-major, so the CTAs that
+// run at the same time work on the slabs of the same few windows and share their tiles in L2.  CTA b
+// starts with item b and claims further items from a global counter.
+//
+// Roles in a CTA of 416 threads, one CTA per SM:
+//   warps 0-7   epilogue: warp w drains TMEM lanes 32 (w % 4) .. +31 (32 window rows), columns half
+//               w / 4 of the accumulator; tcgen05.ld 32x32b.x32 gives a thread 32 consecutive features
+//               of its row
+//   warp  8     lane 0 issues tcgen05.mma / tcgen05.commit; the warp owns the TMEM allocation
+//               (two accumulators of kNs columns)
+//   warps 9-12  producers: warp g fills ring stages g, g + 4, ...; a stage is two consecutive tiles
+//               (2 x 4 KB of A by two TMA boxes, 2 x CW rows of B by tile::gather4, one instruction per lane)
+// Every wait is bounded, as in the 16-row kernel.
+#pragma once
+
+#include "spmm_kernel.cuh"
+
+namespace b200spmm {
+
+constexpr int kTallRows = 128;                  // rows of a super-window
+constexpr int kTallTileBytes = kTallRows * 32;  // one tile of it: 128 rows x 32 bytes
+
+struct TallParams {
+    const uint32_t *rowOffset;  // [eff+1] tiles
+    const uint32_t *tcA2B;      // [tiles*CW]
+    const uint32_t *rowIdx;     // [eff] first row of each super-window (a multiple of 128)
+    uint32_t *sched_counter;    // [2] items handed out beyond the first gridDim.x, CTAs finished; zero at launch and at exit
+    void *C;                    // [rows, n] row-major
+    int64_t ldc;                // elements
+    uint32_t rows, cols, n;
+    uint32_t eff_row_windows;
+    uint32_t n_slabs;           // ceil(n / kNs)
+    uint32_t n_items;           // eff_row_windows * n_slabs
+    uint32_t c_is_half;
+    uint32_t *status;
+    unsigned long long wait_limit_ns;
+};
+
+template <bool kTf32, int kNs>
+struct TallCfg {
+    static_assert(kNs == 128 || kNs == 256, "feature slab");
+    static constexpr int kCW = kTf32 ? 8 : 16;
+    static constexpr int kEsz = kTf32 ? 4 : 2;
+    static constexpr int kTps = 2;                          // tiles per ring stage
+    static constexpr int kGatherBytes = 32 * kNs;           // CW rows x kNs features
+    static constexpr int kStageBytes = kTps * (kGatherBytes + kTallTileBytes);
+    static constexpr int kProducerWarps = 4;
+    static constexpr int kStages = kNs == 256 ? 8 : 12;     // a multiple of kProducerWarps: 192 KB of operands
+    static_assert(kStages % kProducerWarps == 0, "every producer warp owns a fixed set of ring stages");
+    static constexpr int kEpilogueWarps = 8;
+    static constexpr int kMmaWarp = 8;
+    static constexpr int kFirstProducerWarp = 9;
+    static constexpr int kThreads = 32 * (kFirstProducerWarp + kProducerWarps);  // 416
+    static constexpr int kBoxFeatures = 128 / kEsz;         // features in one 128-byte TMA box
+    static constexpr int kRowQuads = kCW / 4;
+    static constexpr int kGatherOps = kRowQuads * (kNs / kBoxFeatures);  // gather4 instructions per tile: 16 or 8
+    static_assert(kGatherOps <= 16, "16 lanes serve one tile");
+    static constexpr int kIdxSlots = 4;                     // per producer warp: column lists of its next stages
+    static constexpr int kIdxAhead = kIdxSlots - 1;
+    static constexpr int kSlotBytes = kTps * kCW * 4;
+    static constexpr int kIdxBytes = kProducerWarps * kIdxSlots * kSlotBytes;
+    static constexpr int kBarriers = 2 * kStages + 5;       // full, empty, 2 x acc_full, 2 x acc_empty, drain
+    static constexpr int kItemSlots = 64;                   // circular list of the items this CTA runs
+    static constexpr uint32_t kTmemCols = 2 * kNs;          // two accumulators
+    static constexpr size_t kSmemBytes =
+        1024 + (size_t)kStages * kStageBytes + kIdxBytes + kBarriers * 8 + 16 + kItemSlots * 4 + 8;
+};
+
+template <bool kTf32, int kNs>
+__global__ void __launch_bounds__((TallCfg<kTf32, kNs>::kThreads), 1)
+spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const TallParams p) {
+    using Cfg = TallCfg<kTf32, kNs>;
+    constexpr int kStages = Cfg::kStages;
+    constexpr int kTps = Cfg::kTps;
+    extern __shared__ uint8_t smem_raw[];
+
+    // ---- shared memory carve-up (1024-byte aligned: swizzle patterns follow address bits)
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t *base = smem_raw + pad;
+    const uint32_t gather_addr = raw_addr + pad;                                      // kStages x 2 x kGatherBytes
+    const uint32_t atile_addr = gather_addr + kStages * kTps * Cfg::kGatherBytes;      // kStages x 2 x 4 KB
+    uint32_t *idx_ring = reinterpret_cast<uint32_t *>(base + kStages * Cfg::kStageBytes);
+    const uint32_t idx_ring_addr = atile_addr + kStages * kTps * kTallTileBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(base + kStages * Cfg::kStageBytes + Cfg::kIdxBytes);
+    const uint32_t bars_addr = idx_ring_addr + Cfg::kIdxBytes;
+    auto full_bar = [&](uint32_t s) { return bars_addr + 8u * s; };
+    auto empty_bar = [&](uint32_t s) { return bars_addr + 8u * ((uint32_t)kStages + s); };
+    auto acc_full_bar = [&](uint32_t a) { return bars_addr + 8u * (uint32_t)(2 * kStages + a); };
+    auto acc_empty_bar = [&](uint32_t a) { return bars_addr + 8u * (uint32_t)(2 * kStages + 2 + a); };
+    const uint32_t drain_bar = bars_addr + 8u * (uint32_t)(2 * kStages + 4);
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(bars + Cfg::kBarriers);
+    uint32_t *tmem_slot = const_cast<uint32_t *>(abort_flag) + 1;
+    volatile uint32_t *mma_done = abort_flag + 2;
+    volatile uint32_t *item_list = abort_flag + 4;                 // items this CTA runs, in order (circular)
+    volatile uint32_t *item_avail = item_list + Cfg::kItemSlots;   // entries written so far
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint64_t limit = p.wait_limit_ns;
+
+    // ---- this CTA's items.  Every role follows the list at its own pace; the roles are never further
+    // apart than the ring and the two accumulators allow (far fewer than kItemSlots items), so a slot
+    // is not rewritten while a slower role still has to read it.
+    constexpr uint32_t kNoItem = 0xFFFFFFFFu;
+    auto item_id = [&](uint32_t k) -> uint32_t {
+        if (*item_avail <= k) {
+            const uint64_t t0 = ptx::global_timer_ns();
+            while (*item_avail <= k) {
+                __nanosleep(100);
+                if (*abort_flag) return kNoItem;
+                if (ptx::global_timer_ns() - t0 > limit) {
+                    *abort_flag = 1;
+                    return kNoItem;
+                }
+            }
+        }
+        __threadfence_block();
+        return item_list[k % Cfg::kItemSlots];
+    };
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {
+            ptx::mbar_init(full_bar(s), 1);   // lane 0 of the stage's producer warp (+ the bytes of its loads)
+            ptx::mbar_init(empty_bar(s), 1);  // tcgen05.commit of the MMA issuer
+        }
+        for (uint32_t a = 0; a < 2; ++a) {
+            ptx::mbar_init(acc_full_bar(a), 1);
+            ptx::mbar_init(acc_empty_bar(a), Cfg::kEpilogueWarps);
+        }
+        ptx::mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        *mma_done = 0;
+        item_list[0] = blockIdx.x < p.n_items ? blockIdx.x : kNoItem;
+        *item_avail = 1;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+    }
+    if (warp == Cfg::kMmaWarp) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_slot), Cfg::kTmemCols);
+        ptx::tmem_relinquish_alloc_permit();
+    }
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    ptx::tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < Cfg::kEpilogueWarps) {
+        // =========================================================== epilogue warps
+        const uint32_t q = (uint32_t)warp & 3u;      // TMEM lane quarter: window rows 32q .. 32q + 31
+        const uint32_t hsel = (uint32_t)warp >> 2;   // which half of the accumulator's columns
+        constexpr uint32_t kHalf = kNs / 2;
+        bool epi_alive = true;
+        for (uint32_t round = 0; epi_alive; ++round) {
+            const uint32_t item = item_id(round);
+            if (item == kNoItem) break;
+            const uint32_t w = item / p.n_slabs, slab = item - w * p.n_slabs;
+            const uint32_t row0 = p.rowIdx[w];
+            const uint32_t gap_hi = w + 1 < p.eff_row_windows ? p.rowIdx[w + 1] : p.rows;
+            const uint32_t a = round & 1u;
+            uint32_t ok = 1;
+            if (lane == 0) ok = ptx::mbar_wait(acc_full_bar(a), (round >> 1) & 1u, abort_flag, limit) ? 1u : 0u;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) { epi_alive = false; break; }
+            ptx::tcgen05_fence_after_sync();
+            const uint32_t row = row0 + q * 32u + (uint32_t)lane;
+            const uint32_t f_slab = slab * kNs;
+#pragma unroll 1
+            for (uint32_t c = 0; c < kHalf / 32u; ++c) {
+                const uint32_t col0 = hsel * kHalf + c * 32u;
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(tmem_base + ((q * 32u) << 16) + a * kNs + col0, r);
+                ptx::tmem_ld_wait();
+                if (c + 1 == kHalf / 32u) {  // the last read of this buffer: it may be overwritten from here on
+                    ptx::tcgen05_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(acc_empty_bar(a));
+                }
+                const uint32_t feat0 = f_slab + col0;  // this thread: features feat0 .. feat0 + 31 of its row
+                if (row < p.rows && feat0 < p.n) {
+                    if (p.c_is_half) {
+                        __half *dst = static_cast<__half *>(p.C) + (int64_t)row * p.ldc + feat0;
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {  // 8 features = 16 bytes per store (n is a multiple of 8)
+                            if (feat0 + v * 8 < p.n) {
+                                uint4 pk;
+                                __half2 h0 = __floats2half2_rn(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                                __half2 h1 = __floats2half2_rn(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                                __half2 h2 = __floats2half2_rn(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                                __half2 h3 = __floats2half2_rn(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                                pk.x = *reinterpret_cast<uint32_t *>(&h0);
+                                pk.y = *reinterpret_cast<uint32_t *>(&h1);
+                                pk.z = *reinterpret_cast<uint32_t *>(&h2);
+                                pk.w = *reinterpret_cast<uint32_t *>(&h3);
+                                *reinterpret_cast<uint4 *>(dst + v * 8) = pk;
+                            }
+                        }
+                    } else {
+                        float *dst = static_cast<float *>(p.C) + (int64_t)row * p.ldc + feat0;
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)  // 4 features = 16 bytes per store
+                            if (feat0 + v * 4 < p.n)
+                                *reinterpret_cast<uint4 *>(dst + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+                    }
+                }
+            }
+            // Rows of super-windows without entries are absent from the format: clear the gap after this
+            // window (and the rows before the very first one), this slab's features.  Warp w takes every
+            // eighth row.
+            const bool lead = w == 0 && row0 > 0;
+            if (gap_hi > row0 + kTallRows || lead) {
+                const uint32_t slab_feats = min((uint32_t)kNs, p.n - f_slab);
+                const uint32_t vec_per_row = slab_feats / 4;
+                for (int pass = 0; pass < 2; ++pass) {
+                    const uint32_t lo = pass == 0 ? row0 + kTallRows : 0u;
+                    const uint32_t hi = pass == 0 ? min(gap_hi, p.rows) : (lead ? row0 : 0u);
+                    for (uint32_t rr = lo + (uint32_t)warp; rr < hi; rr += Cfg::kEpilogueWarps) {
+                        for (uint32_t v4 = lane; v4 < vec_per_row; v4 += 32) {
+                            const uint32_t feat = f_slab + v4 * 4;
+                            if (p.c_is_half)
+                                *reinterpret_cast<uint2 *>(static_cast<__half *>(p.C) + (int64_t)rr * p.ldc + feat) = make_uint2(0, 0);
+                            else
+                                *reinterpret_cast<float4 *>(static_cast<float *>(p.C) + (int64_t)rr * p.ldc + feat) = make_float4(0, 0, 0, 0);
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp >= Cfg::kFirstProducerWarp) {
+        // =========================================================== producer warps
+        const uint32_t pid = (uint32_t)(warp - Cfg::kFirstProducerWarp);  // fills stages pid, pid + 4, ...
+        const uint32_t half = (uint32_t)lane >> 4, hl = (uint32_t)lane & 15u;  // lanes 16j .. serve tile j of the stage
+        constexpr uint32_t kSlotWords = Cfg::kSlotBytes / 4;
+        uint32_t *my_idx = idx_ring + pid * Cfg::kIdxSlots * kSlotWords;
+        const uint32_t my_idx_addr = idx_ring_addr + pid * Cfg::kIdxSlots * Cfg::kSlotBytes;
+        constexpr int kIdxLanes = Cfg::kCW * 4 / 16;  // lanes that copy one column list (16 bytes each)
+        // lane o of a half issues gather instruction o of its tile: row quad g = o % kRowQuads of
+        // 128-byte column block h = o / kRowQuads
+        const uint32_t g = hl % Cfg::kRowQuads, h = hl / Cfg::kRowQuads;
+        const uint32_t op_quad = g, op_x = h * Cfg::kBoxFeatures;
+        // fp16: block (h, rows 8j..8j+7) is 1 KiB, a quad is half of it; tf32: block (h, quad) is 512 B
+        const uint32_t op_dst = kTf32 ? (h * 2 + g) * 512u : (h * 2 + (g >> 1)) * 1024u + (g & 1u) * 512u;
+
+        struct Cursor {
+            uint32_t round, sp, tile_begin, n_tiles, stages, slab, done;
+        };
+        uint32_t grabbed = 1;  // first producer warp: entries of the CTA's item list written so far
+        auto open_item = [&](Cursor &c) {
+            if (pid == 0 && c.round == grabbed) {  // nobody has asked for this one yet: claim the next item
+                if (lane == 0) {
+                    uint32_t next = gridDim.x + atomicAdd(p.sched_counter, 1u);
+                    if (next >= p.n_items) next = kNoItem;
+                    item_list[c.round % Cfg::kItemSlots] = next;
+                    __threadfence_block();
+                    *item_avail = c.round + 1;
+                }
+                ++grabbed;
+                __syncwarp();
+            }
+            const uint32_t item = item_id(c.round);
+            if (item == kNoItem) {
+                c.done = 1;
+                return;
+            }
+            const uint32_t w = item / p.n_slabs;
+            c.slab = item - w * p.n_slabs;
+            c.tile_begin = p.rowOffset[w];
+            c.n_tiles = p.rowOffset[w + 1] - c.tile_begin;
+            c.stages = (c.n_tiles + kTps - 1) / kTps;
+        };
+        auto normalise = [&](Cursor &c) {  // stage cursor past the end of an item: next item
+            while (!c.done && c.sp >= c.stages) {
+                c.sp -= c.stages;
+                ++c.round;
+                open_item(c);
+            }
+        };
+        Cursor cur{0, pid, 0, 0, 0, 0, 0};
+        open_item(cur);
+        normalise(cur);
+        Cursor fc = cur;
+        uint32_t it = 0, it_f = 0;
+        auto fetch_list = [&]() {  // column lists of the fetch cursor's stage -> its ring slot; then advance
+            if (!fc.done) {
+                const uint32_t tpos0 = fc.sp * kTps;
+                const uint32_t here = min((uint32_t)kTps, fc.n_tiles - tpos0);
+                const uint32_t slot_addr = my_idx_addr + (it_f % Cfg::kIdxSlots) * Cfg::kSlotBytes;
+                const uint64_t t = (uint64_t)fc.tile_begin + tpos0;
+                if ((uint32_t)lane < kIdxLanes * kTps && (uint32_t)lane / kIdxLanes < here)
+                    ptx::cp_async_16(slot_addr + lane * 16, p.tcA2B + t * Cfg::kCW + lane * 4, 16u);
+                fc.sp += Cfg::kProducerWarps;
+                normalise(fc);
+            }
+            ++it_f;
+        };
+        for (int i = 0; i < Cfg::kIdxAhead; ++i) fetch_list();
+        ptx::cp_async_commit();
+        ptx::cp_async_wait_group<0>();
+        __syncwarp();
+
+        uint32_t s = pid, use = 0;
+        while (!cur.done) {
+            const uint32_t tpos0 = cur.sp * kTps;
+            const uint32_t here = min((uint32_t)kTps, cur.n_tiles - tpos0);
+            const uint32_t *slot_words = my_idx + (it % Cfg::kIdxSlots) * kSlotWords;
+            uint32_t ok = 1;
+            if (lane == 0) {
+                ok = ptx::mbar_wait(empty_bar(s), (use & 1u) ^ 1u, abort_flag, limit) ? 1u : 0u;
+                if (ok) {
+                    ptx::mbar_arrive_expect_tx(full_bar(s), here * (uint32_t)(Cfg::kGatherBytes + kTallTileBytes));
+                    for (uint32_t j = 0; j < here; ++j)  // the stage's tiles of A: 128 rows of 32 bytes each
+                        ptx::tma_load_2d(atile_addr + (s * kTps + j) * kTallTileBytes, &tmap_a, 0,
+                                         (int32_t)((cur.tile_begin + tpos0 + j) * kTallRows), full_bar(s));
+                }
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            if (half < here && hl < (uint32_t)Cfg::kGatherOps) {
+                const uint4 rows4 = *reinterpret_cast<const uint4 *>(slot_words + half * Cfg::kCW + op_quad * 4);
+                // padded slots hold 0xFFFFFFFF: clamp to the first row past the end, which reads zeros
+                ptx::tma_gather4_2d(gather_addr + (s * kTps + half) * Cfg::kGatherBytes + op_dst, &tmap_b,
+                                    (int32_t)(cur.slab * kNs + op_x),
+                                    (int32_t)min(rows4.x, p.cols), (int32_t)min(rows4.y, p.cols),
+                                    (int32_t)min(rows4.z, p.cols), (int32_t)min(rows4.w, p.cols), full_bar(s));
+            }
+            fetch_list();
+            ptx::cp_async_commit();
+            // the list needed next iteration was fetched kIdxAhead groups ago
+            ptx::cp_async_wait_group<Cfg::kIdxAhead - 1>();
+            __syncwarp();
+            ++it;
+            cur.sp += Cfg::kProducerWarps;
+            normalise(cur);
+            s += Cfg::kProducerWarps;
+            if (s >= (uint32_t)kStages) { s -= kStages; ++use; }
+        }
+        ptx::cp_async_wait_group<0>();
+        __syncwarp();
+    } else if (warp == Cfg::kMmaWarp && lane == 0) {
+        // =========================================================== MMA issuer (warp 8, lane 0)
+        constexpr uint32_t fmt = kTf32 ? ptx::kFmtTF32 : ptx::kFmtF16;
+        // A = the sparse tile, K-major; B = the gathered rows, MN-major
+        constexpr uint32_t idesc = ptx::make_instr_desc(fmt, kTallRows, kNs, false, true);
+        // sparse tile: K-major rows of 32 bytes, 32-byte swizzle, 8-row groups 256 bytes apart
+        const uint64_t a_desc0 = ptx::make_smem_desc(atile_addr, 16, 256, ptx::kSwizzle32B);
+        // gathered rows: MN-major, 128-byte swizzle.  fp16: 64-feature blocks 2 KiB apart, 8-row groups
+        // 1 KiB apart; tf32: 32-feature blocks 1 KiB apart, 4-row groups 512 B apart
+        constexpr uint32_t b_lbo = kTf32 ? 1024u : 2048u, b_sbo = kTf32 ? 512u : 1024u;
+        const uint64_t b_desc0 =
+            ptx::make_smem_desc(gather_addr, b_lbo, b_sbo, kTf32 ? ptx::kSwizzle128BBase32B : ptx::kSwizzle128B);
+        const uint32_t a_hi = (uint32_t)(a_desc0 >> 32), b_hi = (uint32_t)(b_desc0 >> 32);
+        const uint32_t a_lo0 = (uint32_t)a_desc0, b_lo0 = (uint32_t)b_desc0;
+        constexpr uint32_t kATile16 = kTallTileBytes >> 4, kGather16 = Cfg::kGatherBytes >> 4;
+        uint32_t s = 0, phase = 0;
+        bool alive = true;
+        for (uint32_t round = 0; alive; ++round) {
+            const uint32_t item = item_id(round);
+            if (item == kNoItem) break;
+            const uint32_t w = item / p.n_slabs;
+            uint32_t nt = p.rowOffset[w + 1] - p.rowOffset[w];
+            const uint32_t a = round & 1u;
+            alive = ptx::mbar_wait(acc_empty_bar(a), ((round >> 1) & 1u) ^ 1u, abort_flag, limit);
+            ptx::tcgen05_fence_after_sync();
+            const uint32_t d = tmem_base + a * kNs;
+            uint32_t accumulate = 0;
+            while (nt != 0 && alive) {
+                alive = ptx::mbar_wait(full_bar(s), phase, abort_flag, limit);
+                ptx::tcgen05_fence_after_sync();
+                if (!alive) break;
+                const uint32_t alo = a_lo0 + s * kTps * kATile16, blo = b_lo0 + s * kTps * kGather16;
+                if (kTf32) ptx::umma_tf32_ss_lohi(d, alo, a_hi, blo, b_hi, idesc, accumulate);
+                else ptx::umma_f16_ss_lohi(d, alo, a_hi, blo, b_hi, idesc, accumulate);
+                const uint32_t second = nt > 1 ? 1u : 0u;
+                if (kTf32) ptx::umma_tf32_ss_lohi_if(second, d, alo + kATile16, a_hi, blo + kGather16, b_hi, idesc, 1u);
+                else ptx::umma_f16_ss_lohi_if(second, d, alo + kATile16, a_hi, blo + kGather16, b_hi, idesc, 1u);
+                accumulate = 1;
+                nt -= 1u + second;
+                ptx::umma_commit(empty_bar(s));
+                if (++s == (uint32_t)kStages) { s = 0; phase ^= 1u; }
+            }
+            if (alive) ptx::umma_commit(acc_full_bar(a));
+        }
+        if (!alive || *abort_flag) {  // MMAs may be in flight that no awaited commit covers: see the 16-row kernel
+            ptx::umma_commit(drain_bar);
+            ptx::mbar_wait_bounded(drain_bar, 0, limit);
+            ptx::tcgen05_fence_after_sync();
+        }
+    }
+
+    if (warp == Cfg::kMmaWarp) {  // the idle lanes of the MMA warp sleep until lane 0 is done
+        if (lane == 0) {
+            *mma_done = 1;
+        } else {
+            while (*mma_done == 0) __nanosleep(2000);
+        }
+        __syncwarp();
+    }
+    // ---- teardown: every role ends up here, on success and on timeout alike
+    if (*abort_flag) {  // loads may still be on their way into shared memory: see the 16-row kernel
+        const uint64_t t0 = ptx::global_timer_ns();
+        while (ptx::global_timer_ns() - t0 < kAbortLingerNs) __nanosleep(1000);
+    }
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    if (warp == Cfg::kMmaWarp) {
+        ptx::tcgen05_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+    if (tid == 0 && *abort_flag) atomicOr(p.status, kDevStatusTimeout);
+    if (tid == 0) {  // the last CTA to finish leaves both counters at zero for the next launch
+        __threadfence();
+        if (atomicAdd(p.sched_counter + 1, 1u) == gridDim.x - 1u) {
+            p.sched_counter[0] = 0;
+            p.sched_counter[1] = 0;
+        }
+    }
+}
+
+}  // namespace b200spmm

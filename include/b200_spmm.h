@@ -89,8 +89,8 @@ const uint32_t *b200spmm_btcf_rowIdx(const b200spmm_btcf_t *f);    /* [eff_row_w
 /*
  * Re-windows a BTCF_MTX_NO_BITMAP given as its host arrays (src/utils/class.h:74-85; `info`
  * carries rows, cols, nnzs, eff_row_windows, total_tiles, row_window, col_window, dtype): the
- * result has windows of `row_window` rows, a multiple of info->row_window, and is bit-identical
- * to converting the same matrix directly at that height.  The reference's converter is fixed at
+ * result has windows of `row_window` rows (8, 16, 32, 64 or 128, a multiple of info->row_window) and
+ * is bit-identical to converting the same matrix directly at that height.  The reference's converter is fixed at
  * 8-row windows (ROW_WINDOW, src/common.h:17) while the sm_100a kernels consume 16: this is how a
  * format built by the reference's own CSR2BTCFNOBITMAP (src/utils/convert.h:146-225) reaches
  * b200spmm_plan_create, in place of handing it to fp16_spmm (src/fp16.cu:221).  The input is
@@ -351,6 +351,24 @@ int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_ro
                           const void *d_data, const uint32_t *d_rowIdx, const void *d_B, int64_t ldb, int64_t n,
                           void *d_C, int64_t ldc, int c_dtype, int device, int n_ctas, void *stream);
 
+/*
+ * Super-windows.  When the 16-row windows of a matrix already touch most of its columns (a pruned
+ * weight matrix: at 10 % unstructured density a 16-row window holds 81 % of all columns) the plan
+ * also keeps the matrix in windows of 128 rows - eight windows merged, column lists united, the
+ * converter's algorithm (src/utils/convert.h:146-225) at ROW_WINDOW = 128 - and multiplies it with a
+ * kernel whose MMA is 128 window rows x 128/256 features instead of 128 features x 16 rows.  The choice
+ * is made when the plan is created (the merge must leave fewer than ~0.7 of the tiles, estimated on a
+ * sample of windows; B200SPMM_WINDOW=16 or =128 in the environment overrides it) and per launch (B at
+ * least 128 bytes wide, enough windows x feature slabs to occupy every SM).  The format handed to
+ * callers is unchanged.  b200spmm_plan_tall_info reports the merged format (row_window 128, or 0 when
+ * the plan has none); b200spmm_plan_tall_copy_to_host copies its four arrays out (buffers sized from
+ * that info) so that it can be compared with a conversion at 128 rows.  No counterpart in the
+ * reference, which fixes ROW_WINDOW at 8 (src/common.h:17).
+ */
+int b200spmm_plan_tall_info(const b200spmm_plan_t *p, b200spmm_btcf_info_t *info);
+int b200spmm_plan_tall_copy_to_host(const b200spmm_plan_t *p, uint32_t *rowOffset, uint32_t *tcA2B, void *data,
+                                    uint32_t *rowIdx);
+
 /* Per-launch facts of the most recent b200spmm_spmm on this plan. */
 typedef struct {
     int32_t n_ctas, threads, stages;
@@ -360,6 +378,7 @@ typedef struct {
     int64_t kernel_launches; /* launches issued by that call */
     int32_t tma_gather;      /* 1: rows of B fetched by TMA tile::gather4, 0: by cp.async copies */
     int32_t bitmap_tiles;    /* 1: tiles streamed as bitmap + stored values and expanded in the kernel, 0: dense tiles */
+    int32_t row_window;      /* rows per window the launched kernel consumed: 16, or 128 (super-windows) */
 } b200spmm_launch_info_t;
 int b200spmm_plan_launch_info(const b200spmm_plan_t *p, b200spmm_launch_info_t *info);
 

@@ -279,3 +279,16 @@ def test_rewindow_of_an_empty_format_and_bad_input():
     with pytest.raises(RuntimeError):         # 16 -> 8 is not a re-windowing
         rewound(convert(rows, cols, rp, ci, v, rw=16), 8)
 
+
+
+@pytest.mark.parametrize("dt", [np.float16, np.float32])
+@pytest.mark.parametrize("rw_out", [32, 64, 128])
+def test_rewindow_to_taller_windows_equals_a_direct_conversion(dt, rw_out):
+    # the merge the plan applies on the device for its 128-row kernel, here on the host: the same arrays as
+    # the converter's algorithm (src/utils/convert.h:146-225) at that window height
+    rows, cols, rp, ci, v = random_csr(715, 900, 0.02, 5, dt, empty_rows=[(0, 130), (256, 384), (600, 640)], dense_rows=[140, 700])
+    cw = 16 if dt == np.float16 else 8
+    f16 = convert(rows, cols, rp, ci, v, rw=16)
+    tall = hs.rewindow(rows, cols, len(ci), f16.rowOffset, f16.tcA2B, f16.data, f16.rowIdx, row_window_in=16, row_window=rw_out)
+    want = oracle.csr2btcf_nobitmap(rows, cols, rp, ci, v, rw_out, cw)
+    assert same_format(tall, want) and tall.row_window == rw_out

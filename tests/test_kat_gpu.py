@@ -31,6 +31,28 @@ def test_single_tile_product(tf32, m):
     assert np.array_equal(got, feats.astype(np.float32) @ tile.astype(np.float32).T)  # small integers: exact
 
 
+@pytest.mark.parametrize("tf32", [False, True])
+@pytest.mark.parametrize("n", [128, 256])
+def test_super_window_tile_product(tf32, n):
+    # The MMA of the 128-row kernel: the sparse tile (128 window rows x CW, K-major, 32-byte swizzle) is
+    # operand A, the gathered rows of B (n features x CW, MN-major, 128-byte swizzle) operand B - the
+    # reference's transposition (src/fp16.cu:147) undone.  D[row][feature], row = TMEM lane.
+    from hopper_spmm_b200 import _capi as capi
+    dt, cw = (np.float32, 8) if tf32 else (np.float16, 16)
+    rng = np.random.default_rng(n + tf32)
+    tile = rng.integers(-8, 9, (128, cw)).astype(dt)
+    feats = rng.integers(-8, 9, (n, cw)).astype(dt)   # gathered rows of B, [feature][k]
+    gathered = ku.pack_gathered(feats)
+    img = ku.pack_tile(tile) + gathered + bytes(8192)
+    idesc = capi.lib().b200spmm_kat_instr_desc(2 if tf32 else 0, 128, n, 0, 1)
+    mma = capi.KatMma(a_off=0, a_lbo=16, a_sbo=256, a_swizzle=6, b_off=4096, b_lbo=1024 if tf32 else 2048,
+                      b_sbo=512 if tf32 else 1024, b_swizzle=1 if tf32 else 2, idesc=idesc, d_col=0, accumulate=0,
+                      kind=1 if tf32 else 0)
+    st, d = ku.run_umma(img, [mma], n_cols=n)
+    assert st == 0
+    assert np.array_equal(d, tile.astype(np.float32) @ feats.astype(np.float32).T)  # small integers: exact
+
+
 def test_kat1_fp16_values():
     # src/test_fp16.cu:407-415 re-expressed for the transposed mapping: the 64x16 operand
     # A[i] = half(i+1) plays the feature side (M = 64), the all-ones operand the window side.
