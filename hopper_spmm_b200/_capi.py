@@ -80,6 +80,14 @@ SIGNATURES = {
     "b200spmm_csr_destroy": (None, [vp]),
     "b200spmm_shard_rows": (C.c_int, [u64, vp, C.c_int, C.c_int, vp]),
     "b200spmm_shard_rows_weighted": (C.c_int, [u64, vp, C.c_int, C.c_int, u64, vp]),
+    "b200spmm_sharded_create": (C.c_int, [u64, u64, u64, vp, vp, vp, C.c_int, vp, C.c_int, u64, C.POINTER(vp)]),
+    "b200spmm_sharded_info": (C.c_int, [vp, C.POINTER(C.c_int), vp]),
+    "b200spmm_sharded_stream": (vp, [vp, C.c_int]),
+    "b200spmm_spmm_sharded": (C.c_int, [vp, vp, i64, i64, vp, i64, C.c_int]),
+    "b200spmm_sharded_sync": (C.c_int, [vp]),
+    "b200spmm_spmm_sharded_host": (C.c_int, [vp, vp, i64, vp, C.c_int]),
+    "b200spmm_allgather_c": (C.c_int, [vp, vp, i64, C.c_int]),
+    "b200spmm_sharded_destroy": (None, [vp]),
     "b200spmm_build_schedule": (C.c_int, [vp, u64, C.c_int, vp]),
     "b200spmm_build_tile_schedule": (C.c_int, [vp, u64, C.c_int, vp, vp, vp, vp]),
     "b200spmm_build_row_bands": (C.c_int, [vp, vp, u64, u64, C.c_int, C.c_int, vp, vp, C.POINTER(C.c_int)]),

@@ -8,10 +8,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200spmm.so")
 CLI = os.path.join(HERE, "spmm_test")  # spmm_test <matrix.mtx> <feature_dim> [fp16|tf32]
-SOURCES = ["capi.cu", "kat.cu", "convert_gpu.cu", "compress_gpu.cu", "tall_gpu.cu", "formats_ext.cu", "capi_formats.cpp", "format.cpp"]
+SOURCES = ["capi.cu", "kat.cu", "convert_gpu.cu", "compress_gpu.cu", "tall_gpu.cu", "sharded.cu", "formats_ext.cu", "capi_formats.cpp", "format.cpp"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",  # -arch=sm_100a would add a generic PTX pass that rejects tcgen05
-    "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared",
+    "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-ldl",
 ]
 
 

@@ -72,7 +72,6 @@ struct b200spmm_plan {
     // stream enough for the wide-MMA kernel (spmm_tall_kernel.cuh) to win; empty otherwise.
     TallFormat tall;
     bool tall_forced = false;  // B200SPMM_WINDOW=128: use it whatever the launch's size
-    CUtensorMap tmap_tall{};
     int n_sms = 0;
     float *d_partial = nullptr;  // [n_slots][16][n] fp32, grown to the largest need seen
     size_t partial_floats = 0;
@@ -215,7 +214,7 @@ int launch_tall_one(b200spmm_plan *p, TallParams &prm, cudaStream_t stream) {
     prm.n_slabs = (prm.n + kNs - 1) / kNs;
     prm.n_items = prm.eff_row_windows * prm.n_slabs;
     const int n_ctas = (int)std::min<uint32_t>(prm.n_items, (uint32_t)p->n_sms);
-    kernel<<<n_ctas, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p->tmap_tall, p->tmap_b, prm);
+    kernel<<<n_ctas, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p->tmap_b, prm);
     B200_CUDA_TRY(cudaGetLastError());
     p->last.n_ctas = n_ctas;
     p->last.threads = Cfg::kThreads;
@@ -250,6 +249,7 @@ int launch_tall(b200spmm_plan *p, const void *d_B, int64_t ldb, int64_t n, void 
     prm.rowOffset = p->tall.d_rowOffset;
     prm.tcA2B = p->tall.d_tcA2B;
     prm.rowIdx = p->tall.d_rowIdx;
+    prm.data = static_cast<const uint8_t *>(p->tall.d_data);
     prm.sched_counter = p->d_status + 1;
     prm.C = d_C;
     prm.ldc = ldc;
@@ -260,6 +260,9 @@ int launch_tall(b200spmm_plan *p, const void *d_B, int64_t ldb, int64_t n, void 
     prm.c_is_half = c_dtype == B200SPMM_C_F16;
     prm.status = p->d_status;
     prm.wait_limit_ns = p->wait_limit_ns;
+#ifdef B200SPMM_PROFILE
+    if (const char *dbg = std::getenv("B200SPMM_DEBUG")) prm.debug = (uint32_t)std::atoi(dbg);  // results invalid
+#endif
     if (n <= 128) return tf32 ? launch_tall_one<true, 128>(p, prm, stream) : launch_tall_one<false, 128>(p, prm, stream);
     return tf32 ? launch_tall_one<true, 256>(p, prm, stream) : launch_tall_one<false, 256>(p, prm, stream);
 }
@@ -282,15 +285,8 @@ int plan_build_tall(b200spmm_plan *p, const uint32_t *h_rowOffset, const uint32_
         if (ratio > 0.7 || n_super * 16 < (uint64_t)p->n_sms) return B200SPMM_OK;
     }
     int st = build_tall_device(info, h_rowOffset, h_rowIdx, p->d_rowOffset, p->d_tcA2B, p->d_data, p->d_rowIdx, &p->tall);
-    if (st == B200SPMM_ERR_UNSUPPORTED) return B200SPMM_OK;  // too large for one tile tensor map: 16-row kernel
-    if (st != B200SPMM_OK || !p->tall.tiles) return st;
-    const bool f16 = info.dtype == B200SPMM_F16;
-    if (!encode_2d(&p->tmap_tall, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p->tall.d_data,
-                   f16 ? 16 : 8, p->tall.tiles * kTallRows, 32, f16 ? 16 : 8, kTallRows, CU_TENSOR_MAP_SWIZZLE_32B)) {
-        set_last_error_static("cuTensorMapEncodeTiled failed for the super-window tile array");
-        return B200SPMM_ERR_CUDA;
-    }
-    return B200SPMM_OK;
+    if (st == B200SPMM_ERR_UNSUPPORTED) return B200SPMM_OK;  // too many tiles for 32-bit offsets: 16-row kernel
+    return st;
 }
 
 int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, const uint32_t *h_rowIdx, int n_ctas) {
@@ -690,6 +686,10 @@ int b200spmm_plan_tall_copy_to_host(const b200spmm_plan_t *p, uint32_t *rowOffse
     B200_CUDA_TRY(cudaMemcpy(rowIdx, p->tall.d_rowIdx, p->tall.eff * 4, cudaMemcpyDeviceToHost));
     B200_CUDA_TRY(cudaMemcpy(tcA2B, p->tall.d_tcA2B, p->tall.tiles * cw * 4, cudaMemcpyDeviceToHost));
     B200_CUDA_TRY(cudaMemcpy(data, p->tall.d_data, p->tall.tiles * kTallRows * cw * p->info.elt_size, cudaMemcpyDeviceToHost));
+    // the device copy is the kernel's shared-memory image: put the halves of the swizzled rows back
+    uint8_t *bytes = static_cast<uint8_t *>(data);
+    for (uint64_t r = 0; r < p->tall.tiles * kTallRows; ++r)
+        if ((r >> 2) & 1u) std::swap_ranges(bytes + r * 32, bytes + r * 32 + 16, bytes + r * 32 + 16);
     return B200SPMM_OK;
 }
 

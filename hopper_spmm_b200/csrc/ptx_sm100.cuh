@@ -129,6 +129,15 @@ B200_DEVICE void tma_load_2d(uint32_t dst, const void *tmap, int32_t x, int32_t 
         : "memory");
 }
 
+// Plain bulk copy global -> shared of `bytes` contiguous bytes (a multiple of 16, both addresses
+// 16-byte aligned), completion counted in bytes on `bar`.  One request whatever the size, where a
+// tiled load of narrow rows costs the TMA unit one request per row.
+B200_DEVICE void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 // Gather of four rows y0..y3 of a 2-D tensor, box width taken from the tensor map, starting at
 // column x.  The four rows land one after another in shared memory.
 B200_DEVICE void tma_gather4_2d(uint32_t dst, const void *tmap, int32_t x, int32_t y0, int32_t y1, int32_t y2,

@@ -8,9 +8,11 @@
 // does 8 clocks of arithmetic.  Here eight windows are merged (plan-internal, the format handed to
 // callers stays the reference's) and the transposition is undone:
 //     D[128 window rows x kNs features] += Atile[128 x CW] * Bgather[CW x kNs]
-// The sparse tile is the UMMA A operand (M = 128, K-major, 32-byte swizzle: as it lies in `data`,
-// 128 rows of 32 bytes), the gathered rows of B are the UMMA B operand (N = kNs = 128 or 256 features,
-// MN-major, 128-byte swizzle: as TMA tile::gather4 lays B's rows down).  One MMA per tile does
+// The sparse tile is the UMMA A operand (M = 128, K-major, 32-byte swizzle: 128 rows of 32 bytes; the
+// plan stores the merged tiles already in that shared-memory image, so a tile arrives by one plain
+// 4 KB bulk copy instead of a tiled load of 128 narrow rows), the gathered rows of B are the UMMA B
+// operand (N = kNs = 128 or 256 features, MN-major, 128-byte swizzle: as TMA tile::gather4 lays B's
+// rows down).  One MMA per tile does
 // 128 x kNs x CW multiply-adds at the pipe's full rate, and the accumulator's lane is the window row,
 // so an epilogue thread holds consecutive features of one row and stores them as 16-byte vectors.
 //
@@ -25,7 +27,7 @@
 //   warp  8     lane 0 issues tcgen05.mma / tcgen05.commit; the warp owns the TMEM allocation
 //               (two accumulators of kNs columns)
 //   warps 9-12  producers: warp g fills ring stages g, g + 4, ...; a stage is two consecutive tiles
-//               (2 x 4 KB of A by two TMA boxes, 2 x CW rows of B by tile::gather4, one instruction per lane)
+//               (2 x 4 KB of A by one bulk copy, 2 x CW rows of B by tile::gather4, one instruction per lane)
 // Every wait is bounded, as in the 16-row kernel.
 #pragma once
 
@@ -40,6 +42,8 @@ struct TallParams {
     const uint32_t *rowOffset;  // [eff+1] tiles
     const uint32_t *tcA2B;      // [tiles*CW]
     const uint32_t *rowIdx;     // [eff] first row of each super-window (a multiple of 128)
+    const uint8_t *data;        // [tiles][4 KB] tiles as they lie in shared memory: row r of a tile at r * 32 bytes,
+                                // its two 16-byte halves swapped when (r / 4) is odd (the 32-byte swizzle)
     uint32_t *sched_counter;    // [2] items handed out beyond the first gridDim.x, CTAs finished; zero at launch and at exit
     void *C;                    // [rows, n] row-major
     int64_t ldc;                // elements
@@ -50,6 +54,9 @@ struct TallParams {
     uint32_t c_is_half;
     uint32_t *status;
     unsigned long long wait_limit_ns;
+#ifdef B200SPMM_PROFILE
+    uint32_t debug;  // measurement builds only: bit 0 skips the B gathers, bit 1 the MMAs, bit 2 the A tiles
+#endif
 };
 
 template <bool kTf32, int kNs>
@@ -84,8 +91,7 @@ struct TallCfg {
 
 template <bool kTf32, int kNs>
 __global__ void __launch_bounds__((TallCfg<kTf32, kNs>::kThreads), 1)
-spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const TallParams p) {
+spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_b, const TallParams p) {
     using Cfg = TallCfg<kTf32, kNs>;
     constexpr int kStages = Cfg::kStages;
     constexpr int kTps = Cfg::kTps;
@@ -150,7 +156,6 @@ spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         item_list[0] = blockIdx.x < p.n_items ? blockIdx.x : kNoItem;
         *item_avail = 1;
         ptx::fence_mbar_init();
-        ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
     }
     if (warp == Cfg::kMmaWarp) {
@@ -324,15 +329,18 @@ spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (lane == 0) {
                 ok = ptx::mbar_wait(empty_bar(s), (use & 1u) ^ 1u, abort_flag, limit) ? 1u : 0u;
                 if (ok) {
-                    ptx::mbar_arrive_expect_tx(full_bar(s), here * (uint32_t)(Cfg::kGatherBytes + kTallTileBytes));
-                    for (uint32_t j = 0; j < here; ++j)  // the stage's tiles of A: 128 rows of 32 bytes each
-                        ptx::tma_load_2d(atile_addr + (s * kTps + j) * kTallTileBytes, &tmap_a, 0,
-                                         (int32_t)((cur.tile_begin + tpos0 + j) * kTallRows), full_bar(s));
+                    const uint32_t gather_bytes = (B200_DEBUG_BITS(p) & 1u) ? 0u : (uint32_t)Cfg::kGatherBytes;
+                    const uint32_t tile_bytes = (B200_DEBUG_BITS(p) & 4u) ? 0u : (uint32_t)kTallTileBytes;
+                    ptx::mbar_arrive_expect_tx(full_bar(s), here * (gather_bytes + tile_bytes));
+                    // the stage's tiles of A are neighbours in memory and in the ring: one copy
+                    if (tile_bytes)
+                        ptx::bulk_load(atile_addr + s * kTps * kTallTileBytes,
+                                       p.data + (uint64_t)(cur.tile_begin + tpos0) * kTallTileBytes, here * kTallTileBytes, full_bar(s));
                 }
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
-            if (half < here && hl < (uint32_t)Cfg::kGatherOps) {
+            if (half < here && hl < (uint32_t)Cfg::kGatherOps && !(B200_DEBUG_BITS(p) & 1u)) {
                 const uint4 rows4 = *reinterpret_cast<const uint4 *>(slot_words + half * Cfg::kCW + op_quad * 4);
                 // padded slots hold 0xFFFFFFFF: clamp to the first row past the end, which reads zeros
                 ptx::tma_gather4_2d(gather_addr + (s * kTps + half) * Cfg::kGatherBytes + op_dst, &tmap_b,
@@ -385,13 +393,14 @@ spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 ptx::tcgen05_fence_after_sync();
                 if (!alive) break;
                 const uint32_t alo = a_lo0 + s * kTps * kATile16, blo = b_lo0 + s * kTps * kGather16;
-                if (kTf32) ptx::umma_tf32_ss_lohi(d, alo, a_hi, blo, b_hi, idesc, accumulate);
-                else ptx::umma_f16_ss_lohi(d, alo, a_hi, blo, b_hi, idesc, accumulate);
-                const uint32_t second = nt > 1 ? 1u : 0u;
+                const uint32_t first = (B200_DEBUG_BITS(p) & 2u) ? 0u : 1u;
+                if (kTf32) ptx::umma_tf32_ss_lohi_if(first, d, alo, a_hi, blo, b_hi, idesc, accumulate);
+                else ptx::umma_f16_ss_lohi_if(first, d, alo, a_hi, blo, b_hi, idesc, accumulate);
+                const uint32_t second = nt > 1 ? first : 0u;
                 if (kTf32) ptx::umma_tf32_ss_lohi_if(second, d, alo + kATile16, a_hi, blo + kGather16, b_hi, idesc, 1u);
                 else ptx::umma_f16_ss_lohi_if(second, d, alo + kATile16, a_hi, blo + kGather16, b_hi, idesc, 1u);
                 accumulate = 1;
-                nt -= 1u + second;
+                nt -= nt > 1 ? 2u : 1u;
                 ptx::umma_commit(empty_bar(s));
                 if (++s == (uint32_t)kStages) { s = 0; phase ^= 1u; }
             }

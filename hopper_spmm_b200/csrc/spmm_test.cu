@@ -1,4 +1,4 @@
-// spmm_test <matrix_file> <feature_dim> [fp16|tf32] [rw8]
+// spmm_test <matrix_file> <feature_dim> [fp16|tf32] [rw8] [gpus=N]
 //
 // The command-line run of the reference's main (src/fp16.cu:283-319) on top of the C ABI: load a
 // MatrixMarket file, convert it to the condensed format, fill B with rand() / RAND_MAX as the
@@ -7,7 +7,8 @@
 // empty comment, it then checks a sample of C's rows against a plain CSR product on the host.
 // With "rw8" the matrix is first converted with the reference's own 8-row windows (ROW_WINDOW,
 // src/common.h:17) and that format is re-windowed to the 16 rows the kernels consume - the route a
-// format built by the reference's converter takes.
+// format built by the reference's converter takes.  With "gpus=N" the product is also run row-sharded
+// over N GPUs through the sharded operator (host B in, host C out) and compared with the one-GPU result.
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
@@ -34,16 +35,18 @@ float element(const void *values, bool f16, uint64_t i) {
 }  // namespace
 
 int main(int argc, char *argv[]) {
-    if (argc < 3 || argc > 5) {
-        std::printf("Usage: %s <matrix_file> <feature_dim> [fp16|tf32] [rw8]\n", argv[0]);
+    if (argc < 3 || argc > 6) {
+        std::printf("Usage: %s <matrix_file> <feature_dim> [fp16|tf32] [rw8] [gpus=N]\n", argv[0]);
         return 1;
     }
     const char *matrix_file = argv[1];
     const int64_t n = std::atoll(argv[2]);
     bool f16 = true, via_rw8 = false;
+    int gpus = 1;
     for (int i = 3; i < argc; ++i) {
         if (std::strcmp(argv[i], "tf32") == 0) f16 = false;
         else if (std::strcmp(argv[i], "rw8") == 0) via_rw8 = true;
+        else if (std::strncmp(argv[i], "gpus=", 5) == 0 && std::atoi(argv[i] + 5) >= 1) gpus = std::atoi(argv[i] + 5);
         else if (std::strcmp(argv[i], "fp16") != 0) {
             std::fprintf(stderr, "unknown option %s\n", argv[i]);
             return 1;
@@ -135,6 +138,26 @@ int main(int argc, char *argv[]) {
     const double tol = f16 ? 1e-2 : 5e-3;
     std::printf("check: largest error relative to the magnitude sum %.3e (%s, tolerance %.0e)\n", worst,
                 worst <= tol ? "ok" : "FAILED", tol);
+
+    if (gpus > 1) {  // the same product row-sharded over several GPUs, host buffers in and out
+        std::vector<int> devices(gpus);
+        for (int d = 0; d < gpus; ++d) devices[d] = d;
+        b200spmm_sharded_t *sh = nullptr;
+        st = b200spmm_sharded_create(rows, cols, nnz, row_ptr, col_idx, values, dtype, devices.data(), gpus, 6, &sh);
+        if (st) return fail("sharded_create", st);
+        std::vector<uint64_t> cuts(gpus + 1);
+        b200spmm_sharded_info(sh, nullptr, cuts.data());
+        std::vector<float> hC2((size_t)rows * n);
+        st = b200spmm_spmm_sharded_host(sh, hB.data(), n, hC2.data(), B200SPMM_C_F32);
+        if (st) return fail("spmm_sharded_host", st);
+        double diff = 0.0;
+        for (size_t i = 0; i < hC.size(); ++i) diff = std::fmax(diff, std::fabs((double)hC[i] - hC2[i]));
+        std::printf("sharded over %d GPUs (row cuts:", gpus);
+        for (uint64_t c : cuts) std::printf(" %llu", (unsigned long long)c);
+        std::printf("): largest difference to the one-GPU result %.3e\n", diff);
+        b200spmm_sharded_destroy(sh);
+        if (diff > 1e-3) worst = 1.0;
+    }
 
     cudaFree(dB);
     cudaFree(dC);

@@ -8,7 +8,8 @@
 //   3. per super-window: first distinct key and count (binary search) -> tiles -> rowOffset
 //   4. column lists scattered into tcA2B (pre-filled with 0xFFFFFFFF)
 //   5. every (16-row tile, column slot) finds its slot in the super-window's list and its sixteen
-//      values move into the zero-filled 128-row tiles
+//      values move into the zero-filled 128-row tiles, which are stored as the kernel's shared-memory
+//      image (the two 16-byte halves of a tile row swapped when row / 4 is odd: the 32-byte swizzle)
 #include <algorithm>
 #include <cub/cub.cuh>
 #include <vector>
@@ -111,9 +112,13 @@ __global__ void tall_scatter_values_kernel(const uint32_t *__restrict__ rowOffse
         const uint64_t ot = (uint64_t)t_rowOffset[g] + lo / cw;
         const uint32_t olc = lo % cw, row_shift = rowIdx[i] - t_rowIdx[g];
         const T *src = data + ((uint64_t)t * kShort) * cw + lc;
-        T *dst = t_data + (ot * kTall + row_shift) * cw + olc;
+        T *dst = t_data + (ot * kTall + row_shift) * cw;
+        const uint32_t half = cw / 2;  // elements per 16-byte half of a tile row
 #pragma unroll 4
-        for (uint32_t lr = 0; lr < kShort; ++lr) dst[(uint64_t)lr * cw] = src[(uint64_t)lr * cw];
+        for (uint32_t lr = 0; lr < kShort; ++lr) {
+            const uint32_t flip = ((row_shift + lr) >> 2) & 1u;  // the 32-byte swizzle of the shared-memory image
+            dst[(uint64_t)lr * cw + (((olc / half) ^ flip) * half + olc % half)] = src[(uint64_t)lr * cw];
+        }
     }
 }
 
@@ -215,7 +220,7 @@ int build_tall_device(const b200spmm_btcf_info_t &info, const uint32_t *h_rowOff
         t_tiles += ((uint64_t)(ubase[g + 1] - ubase[g]) + cw - 1) / cw;
         t_rowOffset[g + 1] = (uint32_t)t_tiles;
     }
-    if (t_tiles * kTall >= 0x7FFFFFFFull) return B200SPMM_ERR_UNSUPPORTED;  // TMA row coordinate of the tile array
+    if (t_tiles > 0xFFFFFFFFull) return B200SPMM_ERR_UNSUPPORTED;  // rowOffset is 32-bit
 
     TallFormat t;
     t.eff = n_groups;

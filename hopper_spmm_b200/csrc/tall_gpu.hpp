@@ -11,7 +11,8 @@ namespace b200spmm {
 struct TallFormat {
     uint64_t eff = 0, tiles = 0;  // super-windows holding entries, their tiles (128 rows x CW each)
     uint32_t *d_rowOffset = nullptr, *d_tcA2B = nullptr, *d_rowIdx = nullptr;
-    void *d_data = nullptr;
+    void *d_data = nullptr;  // tiles in the kernel's shared-memory image: row r of a tile has its two 16-byte
+                             // halves swapped when (r / 4) is odd
 };
 
 // How many tiles the matrix would have with 128-row windows, as a fraction of its 16-row tiles,
@@ -26,7 +27,8 @@ int estimate_tall_tile_ratio(const b200spmm_btcf_info_t &info, const uint32_t *h
 // sorted union of theirs (padded with 0xFFFFFFFF to whole tiles), and every stored tile entry moves
 // to its row and column slot in tiles of 128 rows - bit for bit what the converter gives at a window
 // height of 128 (src/utils/convert.h:146-225 with ROW_WINDOW = 128).  All arrays in device memory of
-// the current device; synchronous.
+// the current device; synchronous.  Only the order of the two halves of a tile row differs from that
+// conversion (see TallFormat::d_data).
 int build_tall_device(const b200spmm_btcf_info_t &info, const uint32_t *h_rowOffset, const uint32_t *h_rowIdx,
                       const uint32_t *d_rowOffset, const uint32_t *d_tcA2B, const void *d_data, const uint32_t *d_rowIdx,
                       TallFormat *out);

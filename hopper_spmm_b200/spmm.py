@@ -338,6 +338,59 @@ class SpmmPlan:
         return li
 
 
+class ShardedSpmm:
+    """The sharded operator of the C ABI (b200spmm_sharded_*): one process, several GPUs, the matrix cut
+    into time-balanced row ranges, B replicated, C row-sharded.  Host arrays in, host arrays out, like
+    fp16_spmm (src/fp16.cu:221-281); the device-pointer calls are reachable through ``_s``."""
+
+    def __init__(self, csr: CSR_MTX, devices, row_charge: int = 6):
+        lib = capi.lib()
+        self._s = C.c_void_p()
+        devs = (C.c_int * len(devices))(*devices)
+        capi.check(lib.b200spmm_sharded_create(csr.rows, csr.cols, csr.nnzs, csr.row_ptr.ctypes.data, csr.col_idx.ctypes.data,
+                                               csr.values.ctypes.data, _dtype_code(csr.values.dtype), devs, len(devices),
+                                               row_charge, C.byref(self._s)), "b200spmm_sharded_create")
+        self.devices = list(devices)
+        self.rows, self.cols = csr.rows, csr.cols
+        self.dtype = csr.values.dtype
+        cuts = np.zeros(len(devices) + 1, np.uint64)
+        n = C.c_int()
+        capi.check(lib.b200spmm_sharded_info(self._s, C.byref(n), cuts.ctypes.data), "b200spmm_sharded_info")
+        self.row_begin = cuts.astype(np.int64)
+
+    def spmm_host(self, B: np.ndarray, c_half: bool = False) -> np.ndarray:
+        B = np.ascontiguousarray(B, dtype=self.dtype)
+        out = np.empty((self.rows, B.shape[1]), np.float16 if c_half else np.float32)
+        capi.check(capi.lib().b200spmm_spmm_sharded_host(self._s, B.ctypes.data, B.shape[1], out.ctypes.data,
+                                                         capi.C_F16 if c_half else capi.C_F32), "b200spmm_spmm_sharded_host")
+        return out
+
+    def spmm_allgather(self, B_per_device, C_full_per_device):
+        """Device tensors: B_per_device[p] is B on devices[p]; C_full_per_device[p] is a [rows, n] fp32 tensor
+        there.  Every shard writes its rows in place, then the all-gather completes every copy."""
+        n = B_per_device[0].shape[1]
+        ptr = lambda xs: (C.c_void_p * len(xs))(*xs)
+        dB = ptr([b.data_ptr() for b in B_per_device])
+        dC = ptr([c.data_ptr() + int(self.row_begin[p]) * c.stride(0) * c.element_size() for p, c in enumerate(C_full_per_device)])
+        full = ptr([c.data_ptr() for c in C_full_per_device])
+        lib = capi.lib()
+        capi.check(lib.b200spmm_spmm_sharded(self._s, dB, B_per_device[0].stride(0), n, dC, C_full_per_device[0].stride(0),
+                                             capi.C_F32), "b200spmm_spmm_sharded")
+        capi.check(lib.b200spmm_allgather_c(self._s, full, n, capi.C_F32), "b200spmm_allgather_c")
+        capi.check(lib.b200spmm_sharded_sync(self._s), "b200spmm_sharded_sync")
+
+    def close(self):
+        if self._s:
+            capi.lib().b200spmm_sharded_destroy(self._s)
+            self._s = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def _operator(btcf: BTCF_MTX_NO_BITMAP, B: DENSE_MTX, C_mtx: DENSE_MTX, want) -> PERF_RESULT:
     if btcf.dtype != want:
         raise TypeError("matrix element type does not match the operator")

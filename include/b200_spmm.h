@@ -144,6 +144,44 @@ int b200spmm_shard_rows_weighted(uint64_t rows, const uint32_t *row_ptr, int row
                                  uint64_t row_charge, uint64_t *row_begin);
 
 /*
+ * The sharded operator: the same blocking host call as fp16_spmm (src/fp16.cu:221-281), over several
+ * GPUs of this process.  b200spmm_sharded_create cuts the rows with b200spmm_shard_rows_weighted
+ * (row_charge: 6 balances the GPUs' times on power-law graphs, 0 is plain nnz balance), gives every
+ * device its rows of the CSR, converts them there and plans them.  devices[] lists distinct CUDA device
+ * ordinals; shard p lives on devices[p] and owns rows [row_begin[p], row_begin[p+1]).
+ *   b200spmm_spmm_sharded       every shard's product on its own device and stream: d_B[p] is B
+ *                               (replicated: a device pointer on devices[p]), d_C[p] receives the
+ *                               shard's rows of C.  Asynchronous; b200spmm_sharded_sync waits for all
+ *                               shards and returns the first kernel status that is not OK.
+ *   b200spmm_spmm_sharded_host  B [cols, n] and C [rows, n] in host memory (pinned for full speed):
+ *                               every device copies 1/N of B in and the parts are exchanged GPU to GPU
+ *                               (NCCL all-gather over NVLink), so B crosses the host link once, not N
+ *                               times; then the products; then every shard's rows of C go back to
+ *                               their place in h_C.  Blocking.
+ *   b200spmm_allgather_c        the optional collective: d_C_full[p] is a [rows, n] array on
+ *                               devices[p] that already holds shard p's rows in place (let
+ *                               b200spmm_spmm_sharded write them there: d_C[p] = d_C_full[p] +
+ *                               row_begin[p] * ldc); on return, in stream order, every device holds
+ *                               all rows.  One grouped NCCL exchange; the ranges may differ in length.
+ *   b200spmm_sharded_stream     the cudaStream_t shard p's work is queued on.
+ * NCCL (libnccl.so.2) is loaded when the first collective is needed; without it the two collective
+ * calls fail with B200SPMM_ERR_UNSUPPORTED on more than one device and everything else works.  Every
+ * buffer a kernel or NCCL sees is memory of the device it runs on.  One call at a time per handle.
+ */
+typedef struct b200spmm_sharded b200spmm_sharded_t;
+int b200spmm_sharded_create(uint64_t rows, uint64_t cols, uint64_t nnz, const uint32_t *row_ptr, const uint32_t *col_idx,
+                            const void *values, int dtype, const int *devices, int n_devices, uint64_t row_charge,
+                            b200spmm_sharded_t **out);
+int b200spmm_sharded_info(const b200spmm_sharded_t *s, int *n_devices, uint64_t *row_begin /* [n_devices + 1] */);
+void *b200spmm_sharded_stream(const b200spmm_sharded_t *s, int shard);
+int b200spmm_spmm_sharded(b200spmm_sharded_t *s, const void *const *d_B, int64_t ldb, int64_t n, void *const *d_C,
+                          int64_t ldc, int c_dtype);
+int b200spmm_sharded_sync(b200spmm_sharded_t *s);
+int b200spmm_spmm_sharded_host(b200spmm_sharded_t *s, const void *h_B, int64_t n, void *h_C, int c_dtype);
+int b200spmm_allgather_c(b200spmm_sharded_t *s, void *const *d_C_full, int64_t n, int c_dtype);
+void b200spmm_sharded_destroy(b200spmm_sharded_t *s);
+
+/*
  * Persistent schedule: cta_window[n_ctas+1] receives the cuts of the effective row windows
  * over n_ctas persistent CTAs; CTA c streams windows [cta_window[c], cta_window[c+1]).  Cuts
  * follow the running tile count (rowOffset), so every CTA gets about the same number of tiles

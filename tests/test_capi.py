@@ -64,3 +64,25 @@ def test_no_device_is_an_error_not_a_fallback():
     with pytest.raises(capi.SpmmError) as e:
         hs.SpmmPlan(f)
     assert e.value.status == capi.ERR_NO_DEVICE
+
+
+def test_sharded_operator_argument_checks_need_no_device():
+    import numpy as np
+    lib = capi.lib()
+    rp = np.array([0, 1, 2], np.uint32)
+    ci = np.array([0, 1], np.uint32)
+    v = np.ones(2, np.float16)
+    out = C.c_void_p()
+    two = (C.c_int * 2)(0, 0)  # the same device twice
+    args = (2, 2, 2, rp.ctypes.data, ci.ctypes.data, v.ctypes.data, capi.F16)
+    assert lib.b200spmm_sharded_create(*args, two, 2, 6, C.byref(out)) == capi.ERR_INVALID_ARG
+    assert lib.b200spmm_sharded_create(*args, None, 1, 6, C.byref(out)) == capi.ERR_INVALID_ARG
+    bad = np.array([0, 5], np.uint32)  # a column past the end is caught before any device is touched
+    one = (C.c_int * 1)(0)
+    assert lib.b200spmm_sharded_create(2, 2, 2, rp.ctypes.data, bad.ctypes.data, v.ctypes.data, capi.F16, one, 1, 6,
+                                       C.byref(out)) == capi.ERR_BAD_CSR
+    assert lib.b200spmm_sharded_sync(None) == capi.ERR_INVALID_ARG
+    assert lib.b200spmm_allgather_c(None, None, 8, 0) == capi.ERR_INVALID_ARG
+    import torch
+    if not torch.cuda.is_available():
+        assert lib.b200spmm_sharded_create(*args, one, 1, 6, C.byref(out)) == capi.ERR_NO_DEVICE
