@@ -79,7 +79,8 @@ struct b200spmm_plan {
     CUtensorMap tmap_a{};
     // Tensor map over B, kept between launches: B's address, pitch and width rarely change from call
     // to call, and encoding a map costs the host several microseconds of a 10-microsecond launch.
-    CUtensorMap tmap_b{};
+    CUtensorMap tmap_b{};   // box: 128 bytes of one row (the unit of tile::gather4)
+    CUtensorMap tmap_bt{};  // box: 128 bytes of CW consecutive rows (tiles whose columns are neighbours)
     const void *tmap_b_ptr = nullptr;
     int64_t tmap_b_ldb = 0;
     uint32_t tmap_b_n = 0;
@@ -160,6 +161,13 @@ int b_tensor_map(b200spmm_plan *p, const void *B, int64_t ldb, uint32_t n, uint3
         set_last_error_static("cuTensorMapEncodeTiled failed for B");
         return B200SPMM_ERR_CUDA;
     }
+    if (p->tall.tiles &&
+        !encode_2d(&p->tmap_bt, tf32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, B, n, cols,
+                   (uint64_t)ldb * esz, 128 / esz, std::min<uint32_t>((uint32_t)p->info.col_window, cols),
+                   tf32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) {
+        set_last_error_static("cuTensorMapEncodeTiled failed for B (row boxes)");
+        return B200SPMM_ERR_CUDA;
+    }
     p->tmap_b_ptr = B;
     p->tmap_b_ldb = ldb;
     p->tmap_b_n = n;
@@ -201,6 +209,10 @@ int encode_tile_map(b200spmm_plan *p) {
     return B200SPMM_OK;
 }
 
+#ifdef B200SPMM_PROFILE
+unsigned long long *g_prof = nullptr;
+#endif
+
 // ---- 128-row super-windows
 template <bool kTf32, int kNs>
 int launch_tall_one(b200spmm_plan *p, TallParams &prm, cudaStream_t stream) {
@@ -214,7 +226,7 @@ int launch_tall_one(b200spmm_plan *p, TallParams &prm, cudaStream_t stream) {
     prm.n_slabs = (prm.n + kNs - 1) / kNs;
     prm.n_items = prm.eff_row_windows * prm.n_slabs;
     const int n_ctas = (int)std::min<uint32_t>(prm.n_items, (uint32_t)p->n_sms);
-    kernel<<<n_ctas, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p->tmap_b, prm);
+    kernel<<<n_ctas, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p->tmap_b, p->tmap_bt, prm);
     B200_CUDA_TRY(cudaGetLastError());
     p->last.n_ctas = n_ctas;
     p->last.threads = Cfg::kThreads;
@@ -262,6 +274,9 @@ int launch_tall(b200spmm_plan *p, const void *d_B, int64_t ldb, int64_t n, void 
     prm.wait_limit_ns = p->wait_limit_ns;
 #ifdef B200SPMM_PROFILE
     if (const char *dbg = std::getenv("B200SPMM_DEBUG")) prm.debug = (uint32_t)std::atoi(dbg);  // results invalid
+    if (!g_prof) cudaMalloc(&g_prof, 1024 * 24 * 8);
+    cudaMemsetAsync(g_prof, 0, 1024 * 24 * 8, stream);
+    prm.prof = g_prof;
 #endif
     if (n <= 128) return tf32 ? launch_tall_one<true, 128>(p, prm, stream) : launch_tall_one<false, 128>(p, prm, stream);
     return tf32 ? launch_tall_one<true, 256>(p, prm, stream) : launch_tall_one<false, 256>(p, prm, stream);
@@ -424,7 +439,6 @@ int noalloc_scratch_address(int device, uint32_t **out) {
 using namespace noalloc;
 
 #ifdef B200SPMM_PROFILE
-static unsigned long long *g_prof = nullptr;
 extern "C" int b200spmm_debug_read_profile(unsigned long long *out, int n_ctas) {
     return cudaMemcpy(out, g_prof, (size_t)n_ctas * 24 * 8, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -5;
 }

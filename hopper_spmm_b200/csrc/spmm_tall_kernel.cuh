@@ -26,8 +26,10 @@
 //               of its row
 //   warp  8     lane 0 issues tcgen05.mma / tcgen05.commit; the warp owns the TMEM allocation
 //               (two accumulators of kNs columns)
-//   warps 9-12  producers: warp g fills ring stages g, g + 4, ...; a stage is two consecutive tiles
-//               (2 x 4 KB of A by one bulk copy, 2 x CW rows of B by tile::gather4, one instruction per lane)
+//   warps 9-12  producers: warp g fills every fourth stage of the tile stream; a stage is four consecutive
+//               tiles: their 4 x 4 KB of A by one bulk copy, their rows of B by tiled TMA boxes where a
+//               tile's columns are neighbours (CW rows x 128 bytes per instruction) and by tile::gather4
+//               elsewhere (four rows per instruction)
 // Every wait is bounded, as in the 16-row kernel.
 #pragma once
 
@@ -56,6 +58,7 @@ struct TallParams {
     unsigned long long wait_limit_ns;
 #ifdef B200SPMM_PROFILE
     uint32_t debug;  // measurement builds only: bit 0 skips the B gathers, bit 1 the MMAs, bit 2 the A tiles
+    unsigned long long *prof;  // [gridDim.x][24] cycle counters
 #endif
 };
 
@@ -64,20 +67,24 @@ struct TallCfg {
     static_assert(kNs == 128 || kNs == 256, "feature slab");
     static constexpr int kCW = kTf32 ? 8 : 16;
     static constexpr int kEsz = kTf32 ? 4 : 2;
-    static constexpr int kTps = 2;                          // tiles per ring stage
+    // Four tiles per ring stage: the MMA-issuing thread pays its wait, its commit and its ring
+    // bookkeeping (about 330 SM clocks, measured) once per stage, and four MMAs keep the tensor pipe
+    // busy for 512 clocks.  With two tiles per stage that thread, not the pipe, set the pace.
+    static constexpr int kTps = 4;                          // tiles per ring stage
     static constexpr int kGatherBytes = 32 * kNs;           // CW rows x kNs features
     static constexpr int kStageBytes = kTps * (kGatherBytes + kTallTileBytes);
     static constexpr int kProducerWarps = 4;
-    static constexpr int kStages = kNs == 256 ? 8 : 12;     // a multiple of kProducerWarps: 192 KB of operands
-    static_assert(kStages % kProducerWarps == 0, "every producer warp owns a fixed set of ring stages");
+    static constexpr int kStages = kNs == 256 ? 4 : 6;      // 192 KB of operands in flight
     static constexpr int kEpilogueWarps = 8;
     static constexpr int kMmaWarp = 8;
     static constexpr int kFirstProducerWarp = 9;
     static constexpr int kThreads = 32 * (kFirstProducerWarp + kProducerWarps);  // 416
     static constexpr int kBoxFeatures = 128 / kEsz;         // features in one 128-byte TMA box
     static constexpr int kRowQuads = kCW / 4;
-    static constexpr int kGatherOps = kRowQuads * (kNs / kBoxFeatures);  // gather4 instructions per tile: 16 or 8
-    static_assert(kGatherOps <= 16, "16 lanes serve one tile");
+    static constexpr int kBoxes = kNs / kBoxFeatures;       // 128-byte column blocks of a slab
+    static constexpr int kGatherOps = kRowQuads * kBoxes;   // gather4 instructions per tile: 16 or 8
+    static constexpr int kBoxBytes = kCW * 128;             // CW consecutive rows of B, one column block
+    static_assert(kGatherOps <= 16 && kTps % 2 == 0, "16 lanes serve one tile, a warp two tiles at a time");
     static constexpr int kIdxSlots = 4;                     // per producer warp: column lists of its next stages
     static constexpr int kIdxAhead = kIdxSlots - 1;
     static constexpr int kSlotBytes = kTps * kCW * 4;
@@ -91,7 +98,8 @@ struct TallCfg {
 
 template <bool kTf32, int kNs>
 __global__ void __launch_bounds__((TallCfg<kTf32, kNs>::kThreads), 1)
-spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_b, const TallParams p) {
+spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_bt,
+                 const TallParams p) {
     using Cfg = TallCfg<kTf32, kNs>;
     constexpr int kStages = Cfg::kStages;
     constexpr int kTps = Cfg::kTps;
@@ -157,6 +165,7 @@ spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_b, const TallParams p)
         *item_avail = 1;
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tmap_b);
+        ptx::prefetch_tensormap(&tmap_bt);
     }
     if (warp == Cfg::kMmaWarp) {
         ptx::tmem_alloc(ptx::smem_u32(tmem_slot), Cfg::kTmemCols);
@@ -321,13 +330,22 @@ spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_b, const TallParams p)
         __syncwarp();
 
         uint32_t s = pid, use = 0;
+        B200_PROF_DECL(prof_wait_empty);
+        B200_PROF_DECL(prof_issue);
+#ifdef B200SPMM_PROFILE
+        const long long prof_start = clock64();
+#endif
         while (!cur.done) {
             const uint32_t tpos0 = cur.sp * kTps;
             const uint32_t here = min((uint32_t)kTps, cur.n_tiles - tpos0);
             const uint32_t *slot_words = my_idx + (it % Cfg::kIdxSlots) * kSlotWords;
             uint32_t ok = 1;
             if (lane == 0) {
-                ok = ptx::mbar_wait(empty_bar(s), (use & 1u) ^ 1u, abort_flag, limit) ? 1u : 0u;
+                {
+                    B200_PROF_T0();
+                    ok = ptx::mbar_wait(empty_bar(s), (use & 1u) ^ 1u, abort_flag, limit) ? 1u : 0u;
+                    B200_PROF_ADD(prof_wait_empty);
+                }
                 if (ok) {
                     const uint32_t gather_bytes = (B200_DEBUG_BITS(p) & 1u) ? 0u : (uint32_t)Cfg::kGatherBytes;
                     const uint32_t tile_bytes = (B200_DEBUG_BITS(p) & 4u) ? 0u : (uint32_t)kTallTileBytes;
@@ -340,27 +358,54 @@ spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_b, const TallParams p)
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
-            if (half < here && hl < (uint32_t)Cfg::kGatherOps && !(B200_DEBUG_BITS(p) & 1u)) {
-                const uint4 rows4 = *reinterpret_cast<const uint4 *>(slot_words + half * Cfg::kCW + op_quad * 4);
-                // padded slots hold 0xFFFFFFFF: clamp to the first row past the end, which reads zeros
-                ptx::tma_gather4_2d(gather_addr + (s * kTps + half) * Cfg::kGatherBytes + op_dst, &tmap_b,
-                                    (int32_t)(cur.slab * kNs + op_x),
-                                    (int32_t)min(rows4.x, p.cols), (int32_t)min(rows4.y, p.cols),
-                                    (int32_t)min(rows4.z, p.cols), (int32_t)min(rows4.w, p.cols), full_bar(s));
+            B200_PROF_T0();
+#pragma unroll
+            for (uint32_t r = 0; r < (uint32_t)kTps / 2; ++r) {  // two tiles at a time, 16 lanes each
+                const uint32_t j = 2 * r + half;
+                if (j < here && !(B200_DEBUG_BITS(p) & 1u)) {
+                    const uint32_t *list = slot_words + j * Cfg::kCW;
+                    const uint32_t dst = gather_addr + (s * kTps + j) * Cfg::kGatherBytes;
+                    const uint32_t first = list[0];
+                    // A list is ascending and distinct (padding 0xFFFFFFFF at its end): when its last entry
+                    // is CW - 1 past its first, the tile's rows of B are neighbours and arrive as tiled
+                    // boxes of CW rows - the TMA unit moves those several times faster than four-row
+                    // gathers (about 39 bytes per clock and SM, measured).  In a matrix that takes this
+                    // kernel nearly every tile is of that kind.
+                    if (list[Cfg::kCW - 1] - first == (uint32_t)Cfg::kCW - 1u) {
+                        if (hl < (uint32_t)Cfg::kBoxes)
+                            ptx::tma_load_2d(dst + hl * Cfg::kBoxBytes, &tmap_bt, (int32_t)(cur.slab * kNs + hl * Cfg::kBoxFeatures),
+                                             (int32_t)first, full_bar(s));
+                    } else if (hl < (uint32_t)Cfg::kGatherOps) {
+                        const uint4 rows4 = *reinterpret_cast<const uint4 *>(list + op_quad * 4);
+                        // padded slots hold 0xFFFFFFFF: clamp to the first row past the end, which reads zeros
+                        ptx::tma_gather4_2d(dst + op_dst, &tmap_b, (int32_t)(cur.slab * kNs + op_x),
+                                            (int32_t)min(rows4.x, p.cols), (int32_t)min(rows4.y, p.cols),
+                                            (int32_t)min(rows4.z, p.cols), (int32_t)min(rows4.w, p.cols), full_bar(s));
+                    }
+                }
             }
             fetch_list();
             ptx::cp_async_commit();
             // the list needed next iteration was fetched kIdxAhead groups ago
             ptx::cp_async_wait_group<Cfg::kIdxAhead - 1>();
             __syncwarp();
+            B200_PROF_ADD(prof_issue);
             ++it;
             cur.sp += Cfg::kProducerWarps;
             normalise(cur);
             s += Cfg::kProducerWarps;
-            if (s >= (uint32_t)kStages) { s -= kStages; ++use; }
+            while (s >= (uint32_t)kStages) { s -= kStages; ++use; }
         }
         ptx::cp_async_wait_group<0>();
         __syncwarp();
+#ifdef B200SPMM_PROFILE
+        if (lane == 0 && pid == 1) {
+            B200_PROF_STORE(0, clock64() - prof_start);
+            B200_PROF_STORE(1, prof_wait_empty);
+            B200_PROF_STORE(3, it);
+            B200_PROF_STORE(11, prof_issue);
+        }
+#endif
     } else if (warp == Cfg::kMmaWarp && lane == 0) {
         // =========================================================== MMA issuer (warp 8, lane 0)
         constexpr uint32_t fmt = kTf32 ? ptx::kFmtTF32 : ptx::kFmtF16;
@@ -377,35 +422,65 @@ spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_b, const TallParams p)
         const uint32_t a_lo0 = (uint32_t)a_desc0, b_lo0 = (uint32_t)b_desc0;
         constexpr uint32_t kATile16 = kTallTileBytes >> 4, kGather16 = Cfg::kGatherBytes >> 4;
         uint32_t s = 0, phase = 0;
+        uint32_t alo = a_lo0, blo = b_lo0;  // low descriptor words of the first tile of stage s
         bool alive = true;
+        const uint32_t do_mma = (B200_DEBUG_BITS(p) & 2u) ? 0u : 1u;
+        B200_PROF_DECL(prof_wait_full);
+        B200_PROF_DECL(prof_wait_acc);
+#ifdef B200SPMM_PROFILE
+        const long long prof_start = clock64();
+        long long prof_stages = 0;
+#endif
         for (uint32_t round = 0; alive; ++round) {
             const uint32_t item = item_id(round);
             if (item == kNoItem) break;
             const uint32_t w = item / p.n_slabs;
             uint32_t nt = p.rowOffset[w + 1] - p.rowOffset[w];
             const uint32_t a = round & 1u;
-            alive = ptx::mbar_wait(acc_empty_bar(a), ((round >> 1) & 1u) ^ 1u, abort_flag, limit);
+            {
+                B200_PROF_T0();
+                alive = ptx::mbar_wait(acc_empty_bar(a), ((round >> 1) & 1u) ^ 1u, abort_flag, limit);
+                B200_PROF_ADD(prof_wait_acc);
+            }
             ptx::tcgen05_fence_after_sync();
             const uint32_t d = tmem_base + a * kNs;
             uint32_t accumulate = 0;
             while (nt != 0 && alive) {
-                alive = ptx::mbar_wait(full_bar(s), phase, abort_flag, limit);
+                {
+                    B200_PROF_T0();
+                    alive = ptx::mbar_wait(full_bar(s), phase, abort_flag, limit);
+                    B200_PROF_ADD(prof_wait_full);
+                }
+#ifdef B200SPMM_PROFILE
+                ++prof_stages;
+#endif
                 ptx::tcgen05_fence_after_sync();
                 if (!alive) break;
-                const uint32_t alo = a_lo0 + s * kTps * kATile16, blo = b_lo0 + s * kTps * kGather16;
-                const uint32_t first = (B200_DEBUG_BITS(p) & 2u) ? 0u : 1u;
-                if (kTf32) ptx::umma_tf32_ss_lohi_if(first, d, alo, a_hi, blo, b_hi, idesc, accumulate);
-                else ptx::umma_f16_ss_lohi_if(first, d, alo, a_hi, blo, b_hi, idesc, accumulate);
-                const uint32_t second = nt > 1 ? first : 0u;
-                if (kTf32) ptx::umma_tf32_ss_lohi_if(second, d, alo + kATile16, a_hi, blo + kGather16, b_hi, idesc, 1u);
-                else ptx::umma_f16_ss_lohi_if(second, d, alo + kATile16, a_hi, blo + kGather16, b_hi, idesc, 1u);
+                const uint32_t here = min(nt, (uint32_t)kTps);
+#pragma unroll
+                for (uint32_t q = 0; q < (uint32_t)kTps; ++q) {  // predicated, no branches: the last stage of an item may be short
+                    const uint32_t on = q < here ? do_mma : 0u;
+                    const uint32_t acc = q == 0 ? accumulate : 1u;
+                    if (kTf32) ptx::umma_tf32_ss_lohi_if(on, d, alo + q * kATile16, a_hi, blo + q * kGather16, b_hi, idesc, acc);
+                    else ptx::umma_f16_ss_lohi_if(on, d, alo + q * kATile16, a_hi, blo + q * kGather16, b_hi, idesc, acc);
+                }
                 accumulate = 1;
-                nt -= nt > 1 ? 2u : 1u;
+                nt -= here;
                 ptx::umma_commit(empty_bar(s));
-                if (++s == (uint32_t)kStages) { s = 0; phase ^= 1u; }
+                const bool wrap = s + 1 == (uint32_t)kStages;  // selects, no branch
+                s = wrap ? 0u : s + 1;
+                phase ^= wrap ? 1u : 0u;
+                alo = wrap ? a_lo0 : alo + kTps * kATile16;
+                blo = wrap ? b_lo0 : blo + kTps * kGather16;
             }
             if (alive) ptx::umma_commit(acc_full_bar(a));
         }
+#ifdef B200SPMM_PROFILE
+        B200_PROF_STORE(4, clock64() - prof_start);
+        B200_PROF_STORE(5, prof_wait_full);
+        B200_PROF_STORE(6, prof_wait_acc);
+        B200_PROF_STORE(7, prof_stages);
+#endif
         if (!alive || *abort_flag) {  // MMAs may be in flight that no awaited commit covers: see the 16-row kernel
             ptx::umma_commit(drain_bar);
             ptx::mbar_wait_bounded(drain_bar, 0, limit);
