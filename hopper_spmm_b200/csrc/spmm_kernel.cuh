@@ -42,6 +42,7 @@
 #pragma once
 
 #include <cstdint>
+#include <type_traits>
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -835,23 +836,34 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     uint32_t accumulate = 0;
                     // A segment is the run of tiles that share a ring stage and a window: at most eight.
                     // Branches are what a lone thread can least afford, so the window is walked as
-                    //   head - the rest of a stage the previous window left partly used (predicated MMAs),
+                    //   head - the rest of a stage the previous window left partly used,
                     //   body - whole stages: wait, eight MMAs, commit; ring bookkeeping by selects,
-                    //   tail - the first tiles of a stage the next window will finish (predicated MMAs).
-                    auto partial = [&](uint32_t k) {  // k tiles starting at (s, slot), 0 < k < 8 or closing a stage
-                        B200_PROF_T0();
+                    //   tail - the first tiles of a stage the next window will finish.
+                    // `count` MMAs (a compile-time number) for the tiles q0 .. of the current segment
+                    auto burst = [&](auto count_tag, uint32_t q0) {
+                        constexpr int kCount = decltype(count_tag)::value;
+                        const uint32_t alo0 = ad_lo + q0 * kGather16, blo0 = bd_lo + q0 * kATile16;
 #pragma unroll
-                        for (int q = 0; q < kTps; ++q) {
-                            const uint32_t on = (do_mma && (uint32_t)q < k) ? 1u : 0u;
+                        for (int q = 0; q < kCount; ++q) {
 #pragma unroll
                             for (int c = 0; c < Cfg::kChunks; ++c) {
                                 const bool half_chunk = Cfg::kHalfChunk && c == Cfg::kFullChunks;
-                                const uint32_t idesc = half_chunk ? idesc_half : idesc_full;
-                                const uint32_t acc = q == 0 ? accumulate : 1u;
-                                const uint32_t alo = ad_lo + q * kGather16 + c * 256u, blo = bd_lo + q * kATile16;
-                                if (kTf32) ptx::umma_tf32_ss_lohi_if(on, d + c * 16, alo, a_hi, blo, b_hi, idesc, acc);
-                                else ptx::umma_f16_ss_lohi_if(on, d + c * 16, alo, a_hi, blo, b_hi, idesc, acc);
+                                issue(d + c * 16, alo0 + q * kGather16 + c * 256u, blo0 + q * kATile16,
+                                      half_chunk ? idesc_half : idesc_full, q == 0 ? accumulate : 1u);
                             }
+                        }
+                        accumulate = 1;
+                    };
+                    // k tiles starting at (s, slot), 0 < k < 8: bursts of four, two and one.  (Eight predicated
+                    // MMAs, of which the dead ones still cost the thread 30-40 clocks each, were slower: on a
+                    // graph with 15 tiles per window 24 slots were walked for 15 MMAs.)
+                    auto partial = [&](uint32_t k) {
+                        B200_PROF_T0();
+                        if (do_mma) {
+                            uint32_t q0 = 0;
+                            if (k & 4u) { burst(std::integral_constant<int, 4>{}, q0); q0 = 4; }
+                            if (k & 2u) { burst(std::integral_constant<int, 2>{}, q0); q0 += 2; }
+                            if (k & 1u) burst(std::integral_constant<int, 1>{}, q0);
                         }
                         accumulate = 1;
                         nt -= k;
