@@ -307,29 +307,39 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             if (n_win == 0) continue;
             const uint32_t total = p.n_slabs * n_win;  // accumulators this chunk produces, in order
             const uint32_t first = (e ^ g0) & 1u;      // this set drains the accumulators whose running number is e mod 2
-            auto meta = [&](uint32_t it, uint32_t &row0, uint32_t &after) {
+            // accumulator `it` belongs to window (it mod n_win) of the chunk; the position is carried
+            // along (pf) instead of divided out
+            auto meta = [&](uint32_t it, uint32_t wi, uint32_t &row0, uint32_t &after) {
                 if (it < total) {
-                    const uint32_t w = w_begin + it % n_win;
+                    const uint32_t w = w_begin + wi;
                     row0 = p.rowIdx[w];
                     after = w + 1 < p.eff_row_windows ? p.rowIdx[w + 1] : p.rows;
                 }
             };
+            auto wrap = [&](uint32_t x) {
+                while (x >= n_win) x -= n_win;
+                return x;
+            };
             uint32_t row0_a = 0, after_a = 0, row0_b = 0, after_b = 0;
-            meta(first, row0_a, after_a);
-            meta(first + 2, row0_b, after_b);
+            uint32_t pf = wrap(first);
+            meta(first, pf, row0_a, after_a);
+            pf = wrap(pf + 2);
+            meta(first + 2, pf, row0_b, after_b);
+            pf = wrap(pf + 2);
             uint32_t slab = 0, i = first;  // position of accumulator `it`: window i of slab `slab`
             while (i >= n_win) { i -= n_win; ++slab; }
             for (uint32_t it = first; it < total; it += 2) {
                 const uint32_t row0 = row0_a, gap_hi = after_a;
                 row0_a = row0_b;
                 after_a = after_b;
-                meta(it + 4, row0_b, after_b);
+                meta(it + 4, pf, row0_b, after_b);
+                pf = wrap(pf + 2);
                 const uint32_t f0 = slab * kNs;  // first feature of the slab
                 // a piece of a window shared with a neighbouring CTA goes to a partial-result slot
                 const bool is_head_piece = i == 0 && ch.head_slot != kNoSlot;
                 const bool is_tail_piece = i + 1 == n_win && ch.tail_slot != kNoSlot;
                 const bool piece = is_head_piece || is_tail_piece;
-                float *slot_rows = p.partial + (size_t)(is_head_piece ? ch.head_slot : ch.tail_slot) * kRowWindow * p.n;
+                float *slot_rows = piece ? p.partial + (size_t)(is_head_piece ? ch.head_slot : ch.tail_slot) * kRowWindow * p.n : nullptr;
                 uint32_t ok = 1;
                 if (lane == 0) {  // one lane polls; every mbarrier operation costs a shared-memory slot per thread
                     B200_PROF_T0();
@@ -356,19 +366,42 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     const uint32_t width = half_chunk ? 16 : 32;  // features this warp owns in the chunk
                     const uint32_t feat = f0 + c * 128 + q * width + lane;
                     if (lane < width && feat < p.n) {
+                        // The address of row j is walked with one 64-bit add per store and the row check is
+                        // made once per window: the SM is short of issue slots, and sixteen multiplies and
+                        // sixteen comparisons per window and warp cost a fifth of the time on short windows.
                         if (piece) {
+                            float *dst = slot_rows + feat;
 #pragma unroll
-                            for (int j = 0; j < kRowWindow; ++j) slot_rows[(size_t)j * p.n + feat] = __uint_as_float(r[c][j]);
+                            for (int j = 0; j < kRowWindow; ++j) {
+                                *dst = __uint_as_float(r[c][j]);
+                                dst += p.n;
+                            }
                         } else if (p.c_is_half) {
                             __half *dst = static_cast<__half *>(p.C) + (int64_t)row0 * p.ldc + feat;
+                            if (row0 + kRowWindow <= p.rows) {
 #pragma unroll
-                            for (int j = 0; j < kRowWindow; ++j)
-                                if (row0 + j < p.rows) dst[(int64_t)j * p.ldc] = __float2half_rn(__uint_as_float(r[c][j]));
+                                for (int j = 0; j < kRowWindow; ++j) {
+                                    *dst = __float2half_rn(__uint_as_float(r[c][j]));
+                                    dst += p.ldc;
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < kRowWindow; ++j)
+                                    if (row0 + j < p.rows) dst[(int64_t)j * p.ldc] = __float2half_rn(__uint_as_float(r[c][j]));
+                            }
                         } else {
                             float *dst = static_cast<float *>(p.C) + (int64_t)row0 * p.ldc + feat;
+                            if (row0 + kRowWindow <= p.rows) {
 #pragma unroll
-                            for (int j = 0; j < kRowWindow; ++j)
-                                if (row0 + j < p.rows) dst[(int64_t)j * p.ldc] = __uint_as_float(r[c][j]);
+                                for (int j = 0; j < kRowWindow; ++j) {
+                                    *dst = __uint_as_float(r[c][j]);
+                                    dst += p.ldc;
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < kRowWindow; ++j)
+                                    if (row0 + j < p.rows) dst[(int64_t)j * p.ldc] = __uint_as_float(r[c][j]);
+                            }
                         }
                     }
                 }

@@ -163,7 +163,9 @@ int b200spmm_shard_rows_weighted(uint64_t rows, const uint32_t *row_ptr, int row
  *                               b200spmm_spmm_sharded write them there: d_C[p] = d_C_full[p] +
  *                               row_begin[p] * ldc); on return, in stream order, every device holds
  *                               all rows.  One grouped NCCL exchange; the ranges may differ in length.
- *   b200spmm_sharded_stream     the cudaStream_t shard p's work is queued on.
+ *   b200spmm_sharded_stream     the cudaStream_t shard p's work is queued on (a non-blocking stream of the
+ *                               handle's own: whatever produces d_B / d_C on other streams has to be
+ *                               complete, or ordered before this stream, when the calls above are made).
  * NCCL (libnccl.so.2) is loaded when the first collective is needed; without it the two collective
  * calls fail with B200SPMM_ERR_UNSUPPORTED on more than one device and everything else works.  Every
  * buffer a kernel or NCCL sees is memory of the device it runs on.  One call at a time per handle.

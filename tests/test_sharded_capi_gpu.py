@@ -60,6 +60,8 @@ def test_shards_on_several_devices_give_the_one_device_result(n_dev):
         # device-resident products written in place + the all-gather of C
         Bs = [B.to(f"cuda:{d}") for d in range(n_dev)]
         Cs = [torch.full((csr.rows, Bn.shape[1]), float("nan"), device=f"cuda:{d}") for d in range(n_dev)]
+        for d in range(n_dev):  # the shards run on streams of their own: what fills B and C must be done first
+            torch.cuda.synchronize(d)
         sh.spmm_allgather(Bs, Cs)
         for d in range(n_dev):
             assert np.array_equal(Cs[d].cpu().numpy().view(np.uint32), got.view(np.uint32)), d

@@ -160,10 +160,12 @@ def test_compressed_tiles_give_the_same_bits_as_dense_tiles(dt, n, monkeypatch):
     v[::7] = 0
     v[3::11] = -0.0
     B = dense_b(cols, n, 6, dt)
+    # the same CTA count for both: a window that is shared between CTAs is summed from its pieces, and
+    # where the cuts fall depends on the number of chunks
     monkeypatch.setenv("B200SPMM_TILES", "dense")
-    dense, info_d = run_host(rows, cols, rp, ci, v, B)
+    dense, info_d = run_host(rows, cols, rp, ci, v, B, n_ctas=296)
     monkeypatch.setenv("B200SPMM_TILES", "bitmap")
-    packed, info_b = run_host(rows, cols, rp, ci, v, B)
+    packed, info_b = run_host(rows, cols, rp, ci, v, B, n_ctas=296)
     assert info_d.bitmap_tiles == 0 and info_b.bitmap_tiles == 1
     assert np.array_equal(dense.view(np.uint32), packed.view(np.uint32))
     parity.check(packed, rows, rp, ci, v, B)
