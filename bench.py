@@ -309,6 +309,9 @@ def run_other_workload(name, dev, steps, warmup, hbm_gbs, f16_tflops, tf32_tflop
     plan.sync()
     ms = float(np.mean(cold))
     ms_hot = h0.elapsed_time(h1) / steps
+    # the reference's own protocol (src/common.h:48-49, src/fp16.cu:255-268): 3 warm-up launches, then 5
+    # back to back between two events, issued by the library's C loop (no Python between the launches)
+    proto = plan.bench(B, C_dev, hs.WARMUP_RUNS, hs.RUNS)
     info = plan.launch_info()
     esz = 2 if dtype_name == "f16" else 4
     tensor = f16_tflops if dtype_name == "f16" else tf32_tflops
@@ -318,7 +321,8 @@ def run_other_workload(name, dev, steps, warmup, hbm_gbs, f16_tflops, tf32_tflop
     rec = {"workload": name, "description": desc, "rows": csr.rows, "cols": csr.cols, "nnz": csr.nnz, "features": n_feat,
            "dtype": "f16" if dtype_name == "f16" else "tf32", "tiles": int(btcf.total_tiles),
            "fill": csr.nnz / max(1, btcf.total_tiles * 16 * btcf.col_window),
-           "ms": ms, "ms_l2_warm": ms_hot, "l2": f"flushed between timed launches ({L2_FLUSH_BYTES >> 20} MB written)",
+           "ms": ms, "ms_l2_warm": ms_hot, "ms_reference_protocol_3_5": proto.time / proto.runs,
+           "l2": f"flushed between timed launches ({L2_FLUSH_BYTES >> 20} MB written)",
            "value": flops / (ms * 1e-3) / 1e9, "unit": "GFLOP/s", "roofline": roof,
            "kernel": {"n_ctas": info.n_ctas, "feature_slab": info.feature_slab, "n_slabs": info.n_slabs,
                       "stages": info.stages, "launches_per_step": int(info.kernel_launches),

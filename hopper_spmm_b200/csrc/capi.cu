@@ -73,6 +73,10 @@ struct b200spmm_plan {
     TallFormat tall;
     bool tall_forced = false;  // B200SPMM_WINDOW=128: use it whatever the launch's size
     int n_sms = 0;
+    // The tiles as the kernel's shared-memory image (spmm_kernel.cuh, SpmmParams::tiles_image): the plan's own
+    // array swizzled in place when it owns the format, a swizzled copy when the arrays are the caller's.
+    void *d_tiles_image = nullptr;
+    bool image_is_copy = false;
     float *d_partial = nullptr;  // [n_slots][16][n] fp32, grown to the largest need seen
     size_t partial_floats = 0;
     uint32_t *d_status = nullptr;
@@ -92,6 +96,19 @@ struct b200spmm_plan {
     size_t d_B_bytes = 0, d_C_bytes = 0;
     b200spmm_launch_info_t last{};
 };
+
+namespace tileimage {
+// dst row r (32 bytes) = src row r with its 16-byte halves swapped when (r / 4) is odd; dst may be src.
+__global__ void swizzle_tiles_kernel(const uint4 *__restrict__ src, uint4 *__restrict__ dst, uint64_t n_rows) {
+    for (uint64_t r = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; r < n_rows; r += (uint64_t)gridDim.x * blockDim.x) {
+        const uint4 lo = src[2 * r], hi = src[2 * r + 1];
+        const bool flip = (r >> 2) & 1u;
+        dst[2 * r] = flip ? hi : lo;
+        dst[2 * r + 1] = flip ? lo : hi;
+    }
+}
+
+}  // namespace tileimage
 
 namespace {
 
@@ -304,6 +321,27 @@ int plan_build_tall(b200spmm_plan *p, const uint32_t *h_rowOffset, const uint32_
     return st;
 }
 
+// Gives the plan its tile image.  Called last in plan_finish: everything that reads the tiles in the
+// reference's layout (compression, the super-window merge) has run by then.
+int plan_build_tile_image(b200spmm_plan *p) {
+    const uint64_t n_rows = p->info.total_tiles * (uint64_t)kRowWindow;
+    if (!n_rows || p->comp.tcBit) return B200SPMM_OK;  // compressed tiles are expanded in the kernel
+    void *dst = p->d_data;
+    if (!p->owns_format) {
+        if (cudaMalloc(&dst, n_rows * 32) != cudaSuccess) {  // no room for a copy: the tiled loads still work
+            cudaGetLastError();
+            return B200SPMM_OK;
+        }
+        p->image_is_copy = true;
+    }
+    const int grid = (int)std::min<uint64_t>((n_rows + 255) / 256, 148 * 16);
+    tileimage::swizzle_tiles_kernel<<<grid, 256>>>(static_cast<const uint4 *>(p->d_data), static_cast<uint4 *>(dst), n_rows);
+    B200_CUDA_TRY(cudaGetLastError());
+    B200_CUDA_TRY(cudaDeviceSynchronize());
+    p->d_tiles_image = dst;
+    return B200SPMM_OK;
+}
+
 int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, const uint32_t *h_rowIdx, int n_ctas) {
     const auto &info = p->info;
     if (info.row_window != kRowWindow) return B200SPMM_ERR_UNSUPPORTED;
@@ -370,7 +408,7 @@ int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, const uint32_t *h
         int st = plan_build_tall(p, h_rowOffset, h_rowIdx);
         if (st != B200SPMM_OK) return st;
     }
-    return B200SPMM_OK;
+    return plan_build_tile_image(p);
 }
 
 }  // namespace
@@ -588,6 +626,7 @@ void b200spmm_plan_destroy(b200spmm_plan_t *p) {
     }
     free_compressed_tiles(&p->comp);
     free_tall(&p->tall);
+    if (p->image_is_copy) cudaFree(p->d_tiles_image);
     for (cudaEvent_t e : p->band_done) cudaEventDestroy(e);
     if (p->copy_stream) cudaStreamDestroy(p->copy_stream);
     cudaFree(p->d_partial);
@@ -763,6 +802,8 @@ int spmm_launch(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, voi
         }
     }
     prm.partial = p->d_partial;
+    prm.tiles_image = static_cast<const uint8_t *>(p->d_tiles_image);
+    prm.total_tiles = (uint32_t)p->info.total_tiles;
     prm.B = d_B;
     prm.C = d_C;
     prm.ldb = ldb;
@@ -988,6 +1029,8 @@ int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_ro
     prm.chunk_end = (uint32_t)n_ctas;
     prm.sched_counter = nullptr;
     prm.partial = nullptr;
+    prm.tiles_image = nullptr;  // the caller's tiles, as they are, through the tensor map
+    prm.total_tiles = (uint32_t)info->total_tiles;
     prm.B = d_B;
     prm.C = d_C;
     prm.ldb = ldb;

@@ -84,6 +84,13 @@ struct SpmmParams {
     const uint32_t *rowOffset;   // [eff+1] tiles
     const uint32_t *tcA2B;       // [tiles*CW]
     const uint32_t *rowIdx;      // [eff]
+    // The tiles as they lie in shared memory (the two 16-byte halves of a tile row swapped when row / 4 is
+    // odd: the 32-byte swizzle), or null.  With it a ring stage's eight tiles arrive by ONE plain 4 KB bulk
+    // copy; the tiled load of the caller's array costs the TMA unit a request per 32-byte row - 128 per
+    // stage, as many as half of the stage's gathers - and that unit's request rate is what bounds the
+    // kernel on matrices whose B fits L2.
+    const uint8_t *tiles_image;
+    uint32_t total_tiles;
     // schedule: chunk c holds tiles [chunk_tile[c], chunk_tile[c+1]); CTA b starts with chunk chunk_begin + b and
     // takes further chunks, from chunk_begin + gridDim.x on, in the order in which the CTAs ask for them
     const uint32_t *chunk_tile;       // [n_chunks+1]
@@ -652,16 +659,26 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 }
                 if (ok && !kBitmap) {
                     const bool a_tiles = pw == 0 && !(B200_DEBUG_BITS(p) & 4u);
+                    // the stage's eight A tiles (tiles past the chunk's end are fetched too, as long as the
+                    // array holds them: they are never multiplied)
+                    const uint32_t first_tile = tile_begin + sp * kTps;
+                    const uint32_t a_bytes = p.tiles_image ? min((uint32_t)kTps, p.total_tiles - first_tile) * kATileBytes
+                                                           : (uint32_t)kTps * kATileBytes;
                     if (kTma) {
                         // this warp's arrival, announcing the bytes its TMA loads will deliver
-                        const uint32_t bytes = gather_here * Cfg::kGatherBytes + (a_tiles ? kTps * kATileBytes : 0u);
+                        const uint32_t bytes = gather_here * Cfg::kGatherBytes + (a_tiles ? a_bytes : 0u);
                         ptx::mbar_arrive_expect_tx(full_bar(s), bytes);
                     } else if (a_tiles) {
-                        ptx::mbar_expect_tx(full_bar(s), kTps * kATileBytes);
+                        ptx::mbar_expect_tx(full_bar(s), a_bytes);
                     }
-                    if (a_tiles)  // the stage's eight A tiles: 128 rows of 32 bytes
-                        ptx::tma_load_2d(atile_addr + s * kTps * kATileBytes, &tmap_a, 0,
-                                         (int32_t)((tile_begin + sp * kTps) * kRowWindow), full_bar(s));
+                    if (a_tiles) {
+                        if (p.tiles_image)  // one bulk copy from the shared-memory image
+                            ptx::bulk_load(atile_addr + s * kTps * kATileBytes, p.tiles_image + (uint64_t)first_tile * kATileBytes,
+                                           a_bytes, full_bar(s));
+                        else  // the caller's array as it is: 128 rows of 32 bytes through the swizzling tensor map
+                            ptx::tma_load_2d(atile_addr + s * kTps * kATileBytes, &tmap_a, 0,
+                                             (int32_t)(first_tile * kRowWindow), full_bar(s));
+                    }
                 }
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
