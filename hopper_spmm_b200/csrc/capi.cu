@@ -72,6 +72,12 @@ struct b200spmm_plan {
     // stream enough for the wide-MMA kernel (spmm_tall_kernel.cuh) to win; empty otherwise.
     TallFormat tall;
     bool tall_forced = false;  // B200SPMM_WINDOW=128: use it whatever the launch's size
+    // Most tiles of the super-window format name one aligned group of CW consecutive rows of B: then B
+    // is re-laid as shared-memory images at every launch (scratch of the plan, as large as B) and such a
+    // tile's operand arrives by one bulk copy.
+    bool tall_pack_b = false;
+    void *d_b_packed = nullptr;
+    size_t b_packed_bytes = 0;
     int n_sms = 0;
     // The tiles as the kernel's shared-memory image (spmm_kernel.cuh, SpmmParams::tiles_image): the plan's own
     // array swizzled in place when it owns the format, a swizzled copy when the arrays are the caller's.
@@ -251,7 +257,7 @@ int launch_tall_one(b200spmm_plan *p, TallParams &prm, cudaStream_t stream) {
     p->last.feature_slab = kNs;
     p->last.n_slabs = (int)prm.n_slabs;
     p->last.smem_bytes = (int64_t)Cfg::kSmemBytes;
-    p->last.kernel_launches = 1;
+    p->last.kernel_launches = prm.b_packed ? 2 : 1;
     p->last.tma_gather = 1;
     p->last.bitmap_tiles = 0;
     p->last.row_window = kTallRows;
@@ -279,6 +285,29 @@ int launch_tall(b200spmm_plan *p, const void *d_B, int64_t ldb, int64_t n, void 
     prm.tcA2B = p->tall.d_tcA2B;
     prm.rowIdx = p->tall.d_rowIdx;
     prm.data = static_cast<const uint8_t *>(p->tall.d_data);
+    if (p->tall_pack_b) {
+        const uint32_t cw = (uint32_t)p->info.col_window, esz = (uint32_t)p->info.elt_size;
+        const uint32_t slab = n <= 128 ? 128u : 256u, n_slabs = (uint32_t)((n + slab - 1) / slab);
+        const uint32_t groups = (uint32_t)((p->info.cols + cw - 1) / cw);
+        const size_t need = (size_t)n_slabs * groups * 32u * slab;
+        if (need > p->b_packed_bytes) {
+            cudaFree(p->d_b_packed);
+            p->d_b_packed = nullptr;
+            p->b_packed_bytes = 0;
+            B200_CUDA_TRY(cudaMalloc(&p->d_b_packed, need));
+            p->b_packed_bytes = need;
+        }
+        const int grid = (int)std::min<size_t>((need / 16 + 255) / 256, (size_t)p->n_sms * 16);
+        if (tf32)
+            pack_b_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint8_t *>(d_B), ldb * esz, (uint32_t)p->info.cols,
+                                                          (uint32_t)n, slab, n_slabs, groups, static_cast<uint8_t *>(p->d_b_packed));
+        else
+            pack_b_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint8_t *>(d_B), ldb * esz, (uint32_t)p->info.cols,
+                                                           (uint32_t)n, slab, n_slabs, groups, static_cast<uint8_t *>(p->d_b_packed));
+        B200_CUDA_TRY(cudaGetLastError());
+        prm.b_packed = static_cast<const uint8_t *>(p->d_b_packed);
+        prm.b_groups = groups;
+    }
     prm.sched_counter = p->d_status + 1;
     prm.C = d_C;
     prm.ldc = ldc;
@@ -318,7 +347,20 @@ int plan_build_tall(b200spmm_plan *p, const uint32_t *h_rowOffset, const uint32_
     }
     int st = build_tall_device(info, h_rowOffset, h_rowIdx, p->d_rowOffset, p->d_tcA2B, p->d_data, p->d_rowIdx, &p->tall);
     if (st == B200SPMM_ERR_UNSUPPORTED) return B200SPMM_OK;  // too many tiles for 32-bit offsets: 16-row kernel
-    return st;
+    if (st != B200SPMM_OK || !p->tall.tiles) return st;
+    // how many tiles name one aligned row group of B (sampled on the host: every 16th tile's list ends)
+    {
+        const uint64_t cw = (uint64_t)info.col_window, step = 16, n_probe = (p->tall.tiles + step - 1) / step;
+        std::vector<uint32_t> probe(n_probe * 2);
+        // first and last entry of every 16th tile's column list: two strided copies
+        B200_CUDA_TRY(cudaMemcpy2D(probe.data(), 8, p->tall.d_tcA2B, step * cw * 4, 4, n_probe, cudaMemcpyDeviceToHost));
+        B200_CUDA_TRY(cudaMemcpy2D(probe.data() + 1, 8, p->tall.d_tcA2B + (cw - 1), step * cw * 4, 4, n_probe, cudaMemcpyDeviceToHost));
+        uint64_t aligned = 0;
+        for (uint64_t i = 0; i < n_probe; ++i)
+            aligned += (probe[2 * i] % cw == 0 && probe[2 * i + 1] - probe[2 * i] == cw - 1) ? 1 : 0;
+        p->tall_pack_b = aligned * 2 >= n_probe && !env_is("B200SPMM_PACK_B", "0");
+    }
+    return B200SPMM_OK;
 }
 
 // Gives the plan its tile image.  Called last in plan_finish: everything that reads the tiles in the
@@ -626,6 +668,7 @@ void b200spmm_plan_destroy(b200spmm_plan_t *p) {
     }
     free_compressed_tiles(&p->comp);
     free_tall(&p->tall);
+    cudaFree(p->d_b_packed);
     if (p->image_is_copy) cudaFree(p->d_tiles_image);
     for (cudaEvent_t e : p->band_done) cudaEventDestroy(e);
     if (p->copy_stream) cudaStreamDestroy(p->copy_stream);

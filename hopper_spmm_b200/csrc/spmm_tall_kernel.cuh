@@ -46,6 +46,11 @@ struct TallParams {
     const uint32_t *rowIdx;     // [eff] first row of each super-window (a multiple of 128)
     const uint8_t *data;        // [tiles][4 KB] tiles as they lie in shared memory: row r of a tile at r * 32 bytes,
                                 // its two 16-byte halves swapped when (r / 4) is odd (the 32-byte swizzle)
+    // B re-laid per launch as shared-memory images (pack_b_kernel), or null: block (slab, row group) holds
+    // the CW rows [group * CW, group * CW + CW) x the slab's kNs features exactly as the MMA's B operand
+    // lies in shared memory, so a tile whose columns are that row group arrives by one bulk copy.
+    const uint8_t *b_packed;
+    uint32_t b_groups;          // row groups of B: ceil(cols / CW)
     uint32_t *sched_counter;    // [2] items handed out beyond the first gridDim.x, CTAs finished; zero at launch and at exit
     void *C;                    // [rows, n] row-major
     int64_t ldc;                // elements
@@ -372,7 +377,14 @@ spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_consta
                     // gathers (about 39 bytes per clock and SM, measured).  In a matrix that takes this
                     // kernel nearly every tile is of that kind.
                     if (list[Cfg::kCW - 1] - first == (uint32_t)Cfg::kCW - 1u) {
-                        if (hl < (uint32_t)Cfg::kBoxes)
+                        // ... and when they are one aligned row group and B was packed for this launch, as
+                        // one bulk copy of the group's image: one request to the TMA unit instead of one per
+                        // row and column block (that unit's request rate, ~3 clocks per row, bounds this kernel)
+                        if (p.b_packed && first % (uint32_t)Cfg::kCW == 0u) {
+                            if (hl == 0)
+                                ptx::bulk_load(dst, p.b_packed + ((uint64_t)cur.slab * p.b_groups + first / (uint32_t)Cfg::kCW) * Cfg::kGatherBytes,
+                                               (uint32_t)Cfg::kGatherBytes, full_bar(s));
+                        } else if (hl < (uint32_t)Cfg::kBoxes)
                             ptx::tma_load_2d(dst + hl * Cfg::kBoxBytes, &tmap_bt, (int32_t)(cur.slab * kNs + hl * Cfg::kBoxFeatures),
                                              (int32_t)first, full_bar(s));
                     } else if (hl < (uint32_t)Cfg::kGatherOps) {
@@ -514,6 +526,42 @@ spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_consta
             p.sched_counter[0] = 0;
             p.sched_counter[1] = 0;
         }
+    }
+}
+
+// B [cols x n, leading dimension ldb] -> images of the MMA's B operand: block (slab, row group) of
+// 32 * kNs bytes holds rows [group * CW, +CW) x features [slab * kNs, +kNs) in the layout TMA lays a
+// gathered tile down - fp16: 64-feature column blocks of 2 KB (16 rows x 128 B, the 16-byte pieces of a
+// row XORed with row % 8 inside each 8-row half); tf32: 32-feature column blocks of 1 KB (8 rows x 128 B,
+// the 32-byte units XORed with row % 4 inside each 4-row half).  Rows past `cols` and features past n are
+// zeros.  One thread per 16-byte piece.
+template <bool kTf32>
+__global__ void __launch_bounds__(256)
+pack_b_kernel(const uint8_t *__restrict__ B, int64_t ldb_bytes, uint32_t cols, uint32_t n, uint32_t kNs, uint32_t n_slabs,
+              uint32_t n_groups, uint8_t *__restrict__ packed) {
+    constexpr uint32_t kCW = kTf32 ? 8 : 16, kEsz = kTf32 ? 4 : 2;
+    const uint32_t row_pieces = kNs * kEsz / 16;                       // 16-byte pieces of one row of a slab
+    const uint64_t total = (uint64_t)n_slabs * n_groups * kCW * row_pieces;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t piece = (uint32_t)(i % row_pieces);             // consecutive threads: consecutive pieces of a row
+        uint64_t rest = i / row_pieces;
+        const uint32_t k = (uint32_t)(rest % kCW);                     // row inside the group
+        rest /= kCW;
+        const uint32_t group = (uint32_t)(rest % n_groups), slab = (uint32_t)(rest / n_groups);
+        const uint32_t row = group * kCW + k;
+        const uint32_t feat_byte = (slab * kNs * kEsz) + piece * 16;   // byte offset inside the row of B
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < cols && feat_byte < n * kEsz) v = *reinterpret_cast<const uint4 *>(B + (uint64_t)row * ldb_bytes + feat_byte);
+        const uint32_t h = piece >> 3, cc = piece & 7u;                // 128-byte column block, piece inside it
+        uint32_t off;
+        if (kTf32) {
+            const uint32_t kr = k & 3u;
+            off = (h * 2 + (k >> 2)) * 512u + kr * 128u + ((((cc >> 1) ^ kr) << 5) | ((cc & 1u) << 4));
+        } else {
+            const uint32_t kr = k & 7u;
+            off = (h * 2 + (k >> 3)) * 1024u + kr * 128u + ((cc ^ kr) << 4);
+        }
+        *reinterpret_cast<uint4 *>(packed + ((uint64_t)slab * n_groups + group) * (32u * kNs) + off) = v;
     }
 }
 

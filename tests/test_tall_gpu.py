@@ -74,6 +74,28 @@ def test_narrow_b_and_explicit_cta_counts_stay_with_16_rows(tall):
 
 
 @pytest.mark.parametrize("dt", [np.float16, np.float32])
+@pytest.mark.parametrize("n", [128, 328])
+def test_dense_windows_take_packed_rows_of_b(dt, n, tall):
+    # every super-window holds a full row, so its column list is 0 .. cols - 1: all tiles but the ragged last
+    # one name an aligned group of rows of B and are fed from the per-launch images of B; both element types,
+    # one and two feature slabs (the second one partial), B with a larger leading dimension
+    import torch
+    rows, cols = 700, 1000 + (8 if dt == np.float32 else 16) // 2  # the last tile of every window is ragged
+    rows_, cols_, rp, ci, v = random_csr(rows, cols, 0.01, 23, dt, empty_rows=[(256, 384)], dense_rows=[5, 130, 400, 520, 650])
+    Bfull = torch.from_numpy(dense_b(cols, n + 72, 9, dt)).cuda()
+    Bv = Bfull[:, 8:8 + n]
+    plan = hs.SpmmPlan(hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v)))
+    try:
+        dC = torch.full((rows, n), float("nan"), device="cuda")
+        plan.spmm(Bv, dC)
+        info = plan.launch_info()
+        assert info.row_window == 128 and info.kernel_launches == 2
+        parity.check(dC.cpu().numpy(), rows, rp, ci, v, Bv.cpu().numpy())
+    finally:
+        plan.close()
+
+
+@pytest.mark.parametrize("dt", [np.float16, np.float32])
 def test_more_items_than_ctas_and_strided_operands(dt, tall):
     # 40 super-windows x 4 slabs = 160 work items on 148 CTAs: the run-time hand-out is used; B and C are
     # views with larger leading dimensions
@@ -95,7 +117,7 @@ def test_more_items_than_ctas_and_strided_operands(dt, tall):
         plan.close()
 
 
-def test_pruned_weight_matrix_chooses_super_windows_by_itself():
+def test_pruned_weight_matrix_chooses_super_windows_by_itself(monkeypatch):
     # a quarter-size pruned weight matrix: every 16-row window holds 81 % of the columns, eight of them
     # merged hardly more - the plan must pick the 128-row kernel without being told, a graph must not
     import torch
@@ -106,9 +128,22 @@ def test_pruned_weight_matrix_chooses_super_windows_by_itself():
     try:
         C_dev = plan.spmm(B)
         assert plan.launch_info().row_window == 128
+        # nearly every tile names one aligned group of 16 rows of B: B is re-laid per launch (a second kernel)
+        # and such tiles arrive by one bulk copy
+        assert plan.launch_info().kernel_launches == 2
         parity.check(C_dev.cpu().numpy(), csr.rows, rp, ci, v, B.cpu().numpy())
     finally:
         plan.close()
+    # the same product with B fetched through the tensor maps: where the rows come from changes no bit
+    monkeypatch.setenv("B200SPMM_PACK_B", "0")
+    plan = hs.SpmmPlan(btcf)
+    try:
+        C_maps = plan.spmm(B)
+        assert plan.launch_info().kernel_launches == 1
+        assert torch.equal(C_maps, C_dev)
+    finally:
+        plan.close()
+    monkeypatch.delenv("B200SPMM_PACK_B")
     csr, B = synth.make_config("rmat20_gnn_fp16", 0, "cuda", 4)
     btcf = hs.DeviceBtcf(csr.rows, csr.cols, csr.row_ptr.to(torch.int32), csr.col_idx, csr.values)
     plan = hs.SpmmPlan(btcf)
