@@ -103,10 +103,14 @@ SIGNATURES = {
     "b200spmm_bench": (C.c_int, [vp, vp, i64, i64, vp, i64, C.c_int, C.c_int, C.c_int, vp, C.POINTER(C.c_float)]),
     "b200spmm_spmm_noalloc": (C.c_int, [C.POINTER(BtcfInfo), vp, vp, vp, vp, vp, i64, i64, vp, i64, C.c_int, C.c_int,
                                         C.c_int, vp]),
+    "b200spmm_spmm_noalloc_status": (C.c_int, [C.c_int, vp]),
     "b200spmm_plan_tall_info": (C.c_int, [vp, C.POINTER(BtcfInfo)]),
     "b200spmm_plan_tall_copy_to_host": (C.c_int, [vp, vp, vp, vp, vp]),
+    "b200spmm_plan_pair_info": (C.c_int, [vp, C.POINTER(BtcfInfo)]),
+    "b200spmm_plan_pair_copy_to_host": (C.c_int, [vp, vp, vp, vp, vp]),
     "b200spmm_plan_launch_info": (C.c_int, [vp, C.POINTER(LaunchInfo)]),
     "b200spmm_kat_umma": (C.c_int, [vp, u32, C.POINTER(KatMma), C.c_int, C.c_int, vp, C.c_int]),
+    "b200spmm_kat_umma_pair": (C.c_int, [vp, u32, C.POINTER(KatMma), C.c_int, C.c_int, vp, C.c_int]),
     "b200spmm_kat_wait_limit": (C.c_uint64, [C.c_uint64]),
     "b200spmm_kat_spmm_starved": (C.c_int, [vp, vp, i64, i64, vp, i64, C.c_uint64, vp]),
     "b200spmm_kat_instr_desc": (u32, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),

@@ -15,6 +15,7 @@
 #include "format.hpp"
 #include "handles.hpp"
 #include "spmm_kernel.cuh"
+#include "spmm_pair_kernel.cuh"
 #include "spmm_tall_kernel.cuh"
 #include "tall_gpu.hpp"
 #include "tensormap.hpp"
@@ -71,7 +72,11 @@ struct b200spmm_plan {
     // The same matrix in 128-row super-windows, built when merging eight windows shortens the tile
     // stream enough for the wide-MMA kernel (spmm_tall_kernel.cuh) to win; empty otherwise.
     TallFormat tall;
-    bool tall_forced = false;  // B200SPMM_WINDOW=128: use it whatever the launch's size
+    bool tall_forced = false;  // B200SPMM_WINDOW=128 or 256: use it whatever the launch's size
+    // ... and in 256-row super-windows for the CTA-pair kernel (spmm_pair_kernel.cuh), which takes the
+    // launches wider than 128 features when doubling the window height again halves the tile count.
+    TallFormat pair;
+    int pair_clusters = 0;     // two-CTA clusters of that kernel the GPU runs at the same time
     // Most tiles of the super-window format name one aligned group of CW consecutive rows of B: then B
     // is re-laid as shared-memory images at every launch (scratch of the plan, as large as B) and such a
     // tile's operand arrives by one bulk copy.
@@ -264,6 +269,68 @@ int launch_tall_one(b200spmm_plan *p, TallParams &prm, cudaStream_t stream) {
     return B200SPMM_OK;
 }
 
+template <bool kTf32>
+int launch_pair_one(b200spmm_plan *p, TallParams &prm, cudaStream_t stream) {
+    using Cfg = PairCfg<kTf32>;
+    auto kernel = spmm_pair_kernel<kTf32>;
+    prm.n_slabs = (prm.n + Cfg::kNs - 1) / Cfg::kNs;
+    prm.n_items = prm.eff_row_windows * prm.n_slabs;
+    const int n_pairs = (int)std::min<uint32_t>(prm.n_items, (uint32_t)p->pair_clusters);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * n_pairs);
+    cfg.blockDim = dim3(Cfg::kThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p->tmap_b, p->tmap_bt, prm));
+    p->last.n_ctas = 2 * n_pairs;
+    p->last.threads = Cfg::kThreads;
+    p->last.stages = Cfg::kStages;
+    p->last.feature_slab = Cfg::kNs;
+    p->last.n_slabs = (int)prm.n_slabs;
+    p->last.smem_bytes = (int64_t)Cfg::kSmemBytes;
+    p->last.kernel_launches = prm.b_packed ? 2 : 1;
+    p->last.tma_gather = 1;
+    p->last.bitmap_tiles = 0;
+    p->last.row_window = kPairRows;
+    return B200SPMM_OK;
+}
+
+// How many two-CTA clusters of the pair kernel the device runs at once (0: it cannot run it).
+template <bool kTf32>
+int pair_max_clusters(int *out) {
+    using Cfg = PairCfg<kTf32>;
+    auto kernel = spmm_pair_kernel<kTf32>;
+    B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * 148);
+    cfg.blockDim = dim3(Cfg::kThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    B200_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+    *out = n;
+    return B200SPMM_OK;
+}
+
+bool use_pair(const b200spmm_plan *p, int64_t n) {
+    if (!p->pair.tiles || p->pair_clusters < 1 || n <= 128) return false;
+    if (p->tall_forced) return true;
+    return (int64_t)p->pair.eff * ((n + 255) / 256) >= p->pair_clusters;
+}
+
 // Does this launch go to the super-window kernel?  Only with the TMA gathers (B at least one
 // 128-byte box wide), and - unless forced - only when there are enough (window, slab) items to
 // occupy every SM.
@@ -280,14 +347,17 @@ int launch_tall(b200spmm_plan *p, const void *d_B, int64_t ldb, int64_t n, void 
     const bool tf32 = p->info.dtype == B200SPMM_TF32;
     int st = b_tensor_map(p, d_B, ldb, (uint32_t)n, (uint32_t)p->info.cols, tf32);
     if (st != B200SPMM_OK) return st;
+    const bool pair = use_pair(p, n);
+    const TallFormat &fmt = pair ? p->pair : p->tall;
     TallParams prm{};
-    prm.rowOffset = p->tall.d_rowOffset;
-    prm.tcA2B = p->tall.d_tcA2B;
-    prm.rowIdx = p->tall.d_rowIdx;
-    prm.data = static_cast<const uint8_t *>(p->tall.d_data);
+    prm.rowOffset = fmt.d_rowOffset;
+    prm.tcA2B = fmt.d_tcA2B;
+    prm.rowIdx = fmt.d_rowIdx;
+    prm.data = static_cast<const uint8_t *>(fmt.d_data);
     if (p->tall_pack_b) {
         const uint32_t cw = (uint32_t)p->info.col_window, esz = (uint32_t)p->info.elt_size;
-        const uint32_t slab = n <= 128 ? 128u : 256u, n_slabs = (uint32_t)((n + slab - 1) / slab);
+        // the pair kernel's CTAs fetch 128-feature halves of a 256-feature slab
+        const uint32_t slab = (n <= 128 || pair) ? 128u : 256u, n_slabs = (uint32_t)((n + slab - 1) / slab);
         const uint32_t groups = (uint32_t)((p->info.cols + cw - 1) / cw);
         const size_t need = (size_t)n_slabs * groups * 32u * slab;
         if (need > p->b_packed_bytes) {
@@ -314,7 +384,7 @@ int launch_tall(b200spmm_plan *p, const void *d_B, int64_t ldb, int64_t n, void 
     prm.rows = (uint32_t)p->info.rows;
     prm.cols = (uint32_t)p->info.cols;
     prm.n = (uint32_t)n;
-    prm.eff_row_windows = (uint32_t)p->tall.eff;
+    prm.eff_row_windows = (uint32_t)fmt.eff;
     prm.c_is_half = c_dtype == B200SPMM_C_F16;
     prm.status = p->d_status;
     prm.wait_limit_ns = p->wait_limit_ns;
@@ -324,6 +394,7 @@ int launch_tall(b200spmm_plan *p, const void *d_B, int64_t ldb, int64_t n, void 
     cudaMemsetAsync(g_prof, 0, 1024 * 24 * 8, stream);
     prm.prof = g_prof;
 #endif
+    if (pair) return tf32 ? launch_pair_one<true>(p, prm, stream) : launch_pair_one<false>(p, prm, stream);
     if (n <= 128) return tf32 ? launch_tall_one<true, 128>(p, prm, stream) : launch_tall_one<false, 128>(p, prm, stream);
     return tf32 ? launch_tall_one<true, 256>(p, prm, stream) : launch_tall_one<false, 256>(p, prm, stream);
 }
@@ -336,18 +407,30 @@ int launch_tall(b200spmm_plan *p, const void *d_B, int64_t ldb, int64_t n, void 
 int plan_build_tall(b200spmm_plan *p, const uint32_t *h_rowOffset, const uint32_t *h_rowIdx) {
     const auto &info = p->info;
     if (!info.total_tiles || env_is("B200SPMM_WINDOW", "16")) return B200SPMM_OK;
-    p->tall_forced = env_is("B200SPMM_WINDOW", "128");
+    const bool want_pair = env_is("B200SPMM_WINDOW", "256");
+    p->tall_forced = env_is("B200SPMM_WINDOW", "128") || want_pair;
     if (!p->tall_forced) {
         double ratio = 1.0;
         uint64_t n_super = 0;
-        int st = estimate_tall_tile_ratio(info, h_rowOffset, h_rowIdx, p->d_tcA2B, 48, &ratio, &n_super);
+        int st = estimate_tall_tile_ratio(info, h_rowOffset, h_rowIdx, p->d_tcA2B, kTallRows, 48, &ratio, &n_super);
         if (st != B200SPMM_OK) return st;
         // fewer super-windows than SMs / 16 can never fill the GPU, however wide B is
         if (ratio > 0.7 || n_super * 16 < (uint64_t)p->n_sms) return B200SPMM_OK;
     }
-    int st = build_tall_device(info, h_rowOffset, h_rowIdx, p->d_rowOffset, p->d_tcA2B, p->d_data, p->d_rowIdx, &p->tall);
+    int st = build_tall_device(info, h_rowOffset, h_rowIdx, p->d_rowOffset, p->d_tcA2B, p->d_data, p->d_rowIdx, kTallRows, &p->tall);
     if (st == B200SPMM_ERR_UNSUPPORTED) return B200SPMM_OK;  // too many tiles for 32-bit offsets: 16-row kernel
     if (st != B200SPMM_OK || !p->tall.tiles) return st;
+    // The pair kernel does twice the work per tile: it pays when a 256-row window has (about) the column
+    // list of its halves, i.e. half the tiles.  B200SPMM_WINDOW=256 forces it, =128 keeps it out.
+    if (!env_is("B200SPMM_WINDOW", "128")) {
+        st = info.dtype == B200SPMM_TF32 ? pair_max_clusters<true>(&p->pair_clusters) : pair_max_clusters<false>(&p->pair_clusters);
+        if (st != B200SPMM_OK) return st;
+        if (p->pair_clusters > 0) {
+            st = build_tall_device(info, h_rowOffset, h_rowIdx, p->d_rowOffset, p->d_tcA2B, p->d_data, p->d_rowIdx, kPairRows, &p->pair);
+            if (st != B200SPMM_OK && st != B200SPMM_ERR_UNSUPPORTED) return st;
+            if (!want_pair && (double)p->pair.tiles > 0.55 * (double)p->tall.tiles) free_tall(&p->pair);
+        }
+    }
     // how many tiles name one aligned row group of B (sampled on the host: every 16th tile's list ends)
     {
         const uint64_t cw = (uint64_t)info.col_window, step = 16, n_probe = (p->tall.tiles + step - 1) / step;
@@ -668,6 +751,7 @@ void b200spmm_plan_destroy(b200spmm_plan_t *p) {
     }
     free_compressed_tiles(&p->comp);
     free_tall(&p->tall);
+    free_tall(&p->pair);
     cudaFree(p->d_b_packed);
     if (p->image_is_copy) cudaFree(p->d_tiles_image);
     for (cudaEvent_t e : p->band_done) cudaEventDestroy(e);
@@ -762,31 +846,64 @@ int b200spmm_plan_info(const b200spmm_plan_t *p, b200spmm_btcf_info_t *info) {
     return B200SPMM_OK;
 }
 
-int b200spmm_plan_tall_info(const b200spmm_plan_t *p, b200spmm_btcf_info_t *info) {
+static int super_window_info(const b200spmm_plan_t *p, const TallFormat &f, int rows, b200spmm_btcf_info_t *info) {
     if (!p || !info) return B200SPMM_ERR_INVALID_ARG;
     *info = p->info;
-    info->row_window = p->tall.tiles ? kTallRows : 0;
-    info->total_row_windows = (p->info.rows + kTallRows - 1) / kTallRows;
-    info->eff_row_windows = p->tall.eff;
-    info->total_tiles = p->tall.tiles;
+    info->row_window = f.tiles ? rows : 0;
+    info->total_row_windows = (p->info.rows + rows - 1) / rows;
+    info->eff_row_windows = f.eff;
+    info->total_tiles = f.tiles;
     return B200SPMM_OK;
 }
 
+static int super_window_copy_to_host(const b200spmm_plan_t *p, const TallFormat &f, uint32_t *rowOffset, uint32_t *tcA2B,
+                                     void *data, uint32_t *rowIdx) {
+    if (!p || !rowOffset || !tcA2B || !data || !rowIdx) return B200SPMM_ERR_INVALID_ARG;
+    if (!f.tiles) return B200SPMM_ERR_UNSUPPORTED;
+    B200_CUDA_TRY(cudaSetDevice(p->device));
+    const uint64_t cw = (uint64_t)p->info.col_window, parts = f.rows / 128u;
+    B200_CUDA_TRY(cudaMemcpy(rowOffset, f.d_rowOffset, (f.eff + 1) * 4, cudaMemcpyDeviceToHost));
+    B200_CUDA_TRY(cudaMemcpy(rowIdx, f.d_rowIdx, f.eff * 4, cudaMemcpyDeviceToHost));
+    B200_CUDA_TRY(cudaMemcpy(tcA2B, f.d_tcA2B, f.tiles * cw * 4, cudaMemcpyDeviceToHost));
+    // The device copy holds 128-row images as they lie in shared memory (the halves of a row swapped when
+    // row / 4 is odd), for 256-row windows per window first rows 0-127 of all its tiles, then rows 128-255:
+    // put the halves back and the images where the converter would have them.
+    std::vector<uint8_t> img(f.tiles * parts * 4096);
+    B200_CUDA_TRY(cudaMemcpy(img.data(), f.d_data, img.size(), cudaMemcpyDeviceToHost));
+    uint8_t *bytes = static_cast<uint8_t *>(data);
+    for (uint64_t g = 0; g < f.eff; ++g) {
+        const uint64_t first = rowOffset[g], n_tiles = rowOffset[g + 1] - first;
+        for (uint64_t part = 0; part < parts; ++part)
+            for (uint64_t t = 0; t < n_tiles; ++t) {
+                const uint8_t *src = img.data() + (first * parts + part * n_tiles + t) * 4096;
+                uint8_t *dst = bytes + ((first + t) * parts + part) * 4096;
+                for (uint32_t r = 0; r < 128; ++r) {
+                    const uint32_t flip = (r >> 2) & 1u;
+                    std::memcpy(dst + r * 32, src + r * 32 + (flip ? 16 : 0), 16);
+                    std::memcpy(dst + r * 32 + 16, src + r * 32 + (flip ? 0 : 16), 16);
+                }
+            }
+    }
+    return B200SPMM_OK;
+}
+
+int b200spmm_plan_tall_info(const b200spmm_plan_t *p, b200spmm_btcf_info_t *info) {
+    if (!p) return B200SPMM_ERR_INVALID_ARG;
+    return super_window_info(p, p->tall, kTallRows, info);
+}
 int b200spmm_plan_tall_copy_to_host(const b200spmm_plan_t *p, uint32_t *rowOffset, uint32_t *tcA2B, void *data,
                                     uint32_t *rowIdx) {
-    if (!p || !rowOffset || !tcA2B || !data || !rowIdx) return B200SPMM_ERR_INVALID_ARG;
-    if (!p->tall.tiles) return B200SPMM_ERR_UNSUPPORTED;
-    B200_CUDA_TRY(cudaSetDevice(p->device));
-    const uint64_t cw = (uint64_t)p->info.col_window;
-    B200_CUDA_TRY(cudaMemcpy(rowOffset, p->tall.d_rowOffset, (p->tall.eff + 1) * 4, cudaMemcpyDeviceToHost));
-    B200_CUDA_TRY(cudaMemcpy(rowIdx, p->tall.d_rowIdx, p->tall.eff * 4, cudaMemcpyDeviceToHost));
-    B200_CUDA_TRY(cudaMemcpy(tcA2B, p->tall.d_tcA2B, p->tall.tiles * cw * 4, cudaMemcpyDeviceToHost));
-    B200_CUDA_TRY(cudaMemcpy(data, p->tall.d_data, p->tall.tiles * kTallRows * cw * p->info.elt_size, cudaMemcpyDeviceToHost));
-    // the device copy is the kernel's shared-memory image: put the halves of the swizzled rows back
-    uint8_t *bytes = static_cast<uint8_t *>(data);
-    for (uint64_t r = 0; r < p->tall.tiles * kTallRows; ++r)
-        if ((r >> 2) & 1u) std::swap_ranges(bytes + r * 32, bytes + r * 32 + 16, bytes + r * 32 + 16);
-    return B200SPMM_OK;
+    if (!p) return B200SPMM_ERR_INVALID_ARG;
+    return super_window_copy_to_host(p, p->tall, rowOffset, tcA2B, data, rowIdx);
+}
+int b200spmm_plan_pair_info(const b200spmm_plan_t *p, b200spmm_btcf_info_t *info) {
+    if (!p) return B200SPMM_ERR_INVALID_ARG;
+    return super_window_info(p, p->pair, kPairRows, info);
+}
+int b200spmm_plan_pair_copy_to_host(const b200spmm_plan_t *p, uint32_t *rowOffset, uint32_t *tcA2B, void *data,
+                                    uint32_t *rowIdx) {
+    if (!p) return B200SPMM_ERR_INVALID_ARG;
+    return super_window_copy_to_host(p, p->pair, rowOffset, tcA2B, data, rowIdx);
 }
 
 int b200spmm_plan_launch_info(const b200spmm_plan_t *p, b200spmm_launch_info_t *info) {
@@ -1003,6 +1120,17 @@ int b200spmm_kat_spmm_starved(b200spmm_plan_t *p, const void *d_B, int64_t ldb, 
     p->wait_limit_ns = kDeviceWaitLimitNs;
     p->tmap_b_ptr = nullptr;
     return st;
+}
+
+int b200spmm_spmm_noalloc_status(int device, void *stream_v) {
+    B200_CUDA_TRY(cudaSetDevice(device));
+    uint32_t *scratch = nullptr;
+    int st = noalloc_scratch_address(device, &scratch);
+    if (st != B200SPMM_OK) return st;
+    B200_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream_v)));
+    uint32_t status = 0;  // a copy into a stack word: nothing is allocated
+    B200_CUDA_TRY(cudaMemcpy(&status, scratch + kNoAllocStatusWord, sizeof(status), cudaMemcpyDeviceToHost));
+    return (status & kDevStatusTimeout) ? B200SPMM_ERR_DEVICE_TIMEOUT : B200SPMM_OK;
 }
 
 int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_rowOffset, const uint32_t *d_tcA2B,

@@ -190,6 +190,69 @@ kat_umma_rate_kernel(int tf32, uint32_t idesc, int count, int issuers, long long
     if (warp == 0) ptx::tmem_dealloc(tmem_base, kCols);
 }
 
+// Known answer for the MMA of a CTA pair (cta_group::2): two CTAs of one cluster each copy their own
+// image into shared memory, the even CTA issues the listed MMAs for both, each CTA dumps its 128 lanes of
+// tensor memory.  out[cta][128][n_cols].
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128, 1)
+kat_umma_pair_kernel(const uint8_t *__restrict__ images, uint32_t image_bytes, const b200spmm_kat_mma_t *__restrict__ mmas,
+                     int n_mmas, int n_cols, float *__restrict__ out, uint32_t *__restrict__ status, unsigned long long limit_ns) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t done_bar;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ uint32_t abort_flag;
+    const uint32_t rank = ptx::cluster_cta_rank();
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+    uint8_t *area = smem_raw + pad;
+    const uint32_t area_addr = raw_addr + pad;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const uint8_t *image = images + (size_t)rank * image_bytes;
+    for (uint32_t i = tid * 16u; i < image_bytes; i += blockDim.x * 16u)
+        *reinterpret_cast<uint4 *>(area + i) = *reinterpret_cast<const uint4 *>(image + i);
+    if (tid == 0) {
+        abort_flag = 0;
+        ptx::mbar_init(ptx::smem_u32(&done_bar), 1);
+        ptx::fence_mbar_init();
+    }
+    ptx::fence_proxy_async_smem();
+    if (warp == 0) {
+        ptx::tmem_alloc_pair(ptx::smem_u32(&tmem_base_slot), kKatTmemCols);
+        ptx::tmem_relinquish_alloc_permit_pair();
+    }
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_arrive();  // both images are in place and both barriers initialised before anything is issued
+    ptx::cluster_wait();
+    ptx::tcgen05_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+    if (rank == 0 && tid == 0) {
+        for (int i = 0; i < n_mmas; ++i) {
+            const b200spmm_kat_mma_t m = mmas[i];
+            const uint64_t ad = ptx::make_smem_desc(area_addr + m.a_off, m.a_lbo, m.a_sbo, m.a_swizzle);
+            const uint64_t bd = ptx::make_smem_desc(area_addr + m.b_off, m.b_lbo, m.b_sbo, m.b_swizzle);
+            ptx::umma_pair_ss_lohi_if(m.kind != 0, 1u, tmem_base + m.d_col, (uint32_t)ad, (uint32_t)(ad >> 32), (uint32_t)bd,
+                                      (uint32_t)(bd >> 32), m.idesc, m.accumulate);
+        }
+        ptx::umma_commit_pair(ptx::smem_u32(&done_bar));
+    }
+    __syncwarp();
+    const bool ok = ptx::mbar_wait(ptx::smem_u32(&done_bar), 0, &abort_flag, limit_ns);
+    ptx::tcgen05_fence_after_sync();
+    if (!ok && tid == 0) atomicOr(status, kDevStatusTimeout);
+    for (int c0 = 0; c0 < n_cols; c0 += 16) {  // every warp dumps its own 32 lanes
+        uint32_t r[16];
+        ptx::tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) out[((size_t)rank * 128 + tid) * n_cols + c0 + j] = __uint_as_float(r[j]);
+    }
+    ptx::tcgen05_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_arrive();  // neither CTA lets go of its shared or tensor memory while the other may still use it
+    ptx::cluster_wait();
+    if (warp == 0) ptx::tmem_dealloc_pair(tmem_base, kKatTmemCols);
+}
+
 struct DevBuf {
     void *p = nullptr;
     ~DevBuf() { if (p) cudaFree(p); }
@@ -250,6 +313,33 @@ extern "C" int b200spmm_kat_umma(const void *image, uint32_t image_bytes, const 
     uint32_t status = 0;
     B200_CUDA_TRY(cudaMemcpy(&status, d_status.p, 4, cudaMemcpyDeviceToHost));
     B200_CUDA_TRY(cudaMemcpy(out, d_out.p, sizeof(float) * 128 * n_cols, cudaMemcpyDeviceToHost));
+    return (status & kDevStatusTimeout) ? B200SPMM_ERR_DEVICE_TIMEOUT : B200SPMM_OK;
+}
+
+extern "C" int b200spmm_kat_umma_pair(const void *images, uint32_t image_bytes, const b200spmm_kat_mma_t *mmas, int n_mmas,
+                                      int n_cols, float *out, int device) {
+    if (!images || !mmas || !out || n_mmas < 1 || n_cols < 16 || n_cols > (int)kKatTmemCols || n_cols % 16) return B200SPMM_ERR_INVALID_ARG;
+    if (image_bytes > 96u * 1024u || image_bytes % 16) return B200SPMM_ERR_INVALID_ARG;
+    int st = check_device(device);
+    if (st != B200SPMM_OK) return st;
+    DevBuf d_img, d_mma, d_out, d_status;
+    B200_CUDA_TRY(cudaMalloc(&d_img.p, 2 * (size_t)image_bytes));
+    B200_CUDA_TRY(cudaMemcpy(d_img.p, images, 2 * (size_t)image_bytes, cudaMemcpyHostToDevice));
+    B200_CUDA_TRY(cudaMalloc(&d_mma.p, sizeof(b200spmm_kat_mma_t) * n_mmas));
+    B200_CUDA_TRY(cudaMemcpy(d_mma.p, mmas, sizeof(b200spmm_kat_mma_t) * n_mmas, cudaMemcpyHostToDevice));
+    B200_CUDA_TRY(cudaMalloc(&d_out.p, sizeof(float) * 256 * n_cols));
+    B200_CUDA_TRY(cudaMemset(d_out.p, 0, sizeof(float) * 256 * n_cols));
+    B200_CUDA_TRY(cudaMalloc(&d_status.p, 4));
+    B200_CUDA_TRY(cudaMemset(d_status.p, 0, 4));
+    const size_t smem = (size_t)image_bytes + 1024 + 4096;
+    B200_CUDA_TRY(cudaFuncSetAttribute(kat_umma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kat_umma_pair_kernel<<<2, 128, smem>>>((const uint8_t *)d_img.p, image_bytes, (const b200spmm_kat_mma_t *)d_mma.p, n_mmas,
+                                           n_cols, (float *)d_out.p, (uint32_t *)d_status.p, g_kat_wait_limit_ns);
+    B200_CUDA_TRY(cudaGetLastError());
+    B200_CUDA_TRY(cudaDeviceSynchronize());
+    uint32_t status = 0;
+    B200_CUDA_TRY(cudaMemcpy(&status, d_status.p, 4, cudaMemcpyDeviceToHost));
+    B200_CUDA_TRY(cudaMemcpy(out, d_out.p, sizeof(float) * 256 * n_cols, cudaMemcpyDeviceToHost));
     return (status & kDevStatusTimeout) ? B200SPMM_ERR_DEVICE_TIMEOUT : B200SPMM_OK;
 }
 

@@ -217,6 +217,101 @@ B200_DEVICE void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 B200_DEVICE void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ------------------------------------------------------------------ CTA pairs (cta_group::2)
+// A cluster of two CTAs on neighbouring SMs can run ONE tcgen05.mma of M = 256: CTA r holds rows
+// 128 r .. of A and of the accumulator and columns (N / 2) r .. of B in its own shared / tensor memory, at
+// the same offsets in both CTAs; the even CTA (rank 0) issues.  Every byte of B is then fetched from L2
+// by one of the two SMs only.
+
+B200_DEVICE uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+B200_DEVICE void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+B200_DEVICE void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// The address of `local_smem_addr` in the shared memory of CTA `rank` of this cluster.
+B200_DEVICE uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+    return r;
+}
+// One arrival on a barrier that may live in the other CTA of the cluster (address from map_to_cta).
+B200_DEVICE void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// The same without ordering of this thread's earlier memory operations (for data that another proxy wrote
+// and whose completion this thread has already observed).
+B200_DEVICE void mbar_arrive_cluster_relaxed(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+B200_DEVICE void tmem_alloc_pair(uint32_t dst_smem, uint32_t n_cols) {  // whole warp, the same warp in both CTAs
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(n_cols) : "memory");
+}
+B200_DEVICE void tmem_relinquish_alloc_permit_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+B200_DEVICE void tmem_dealloc_pair(uint32_t taddr, uint32_t n_cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(n_cols) : "memory");
+}
+// D (+)= A * B over the pair; issued by ONE thread of the even CTA.  `on` == 0 skips it.
+B200_DEVICE void umma_pair_ss_lohi_if(bool tf32, uint32_t on, uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                      uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    if (tf32)
+        asm volatile(
+            "{\n.reg .pred p, q;\n.reg .b64 da, db;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
+            "setp.ne.b32 p, %6, 0;\nsetp.ne.b32 q, %7, 0;\n"
+            "@q tcgen05.mma.cta_group::2.kind::tf32 [%0], da, db, %5, p;\n}\n"
+            ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(on) : "memory");
+    else
+        asm volatile(
+            "{\n.reg .pred p, q;\n.reg .b64 da, db;\nmov.b64 da, {%1, %2};\nmov.b64 db, {%3, %4};\n"
+            "setp.ne.b32 p, %6, 0;\nsetp.ne.b32 q, %7, 0;\n"
+            "@q tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}\n"
+            ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(on) : "memory");
+}
+// One arrival on the barrier at offset `bar` in BOTH CTAs of the pair (mask 0b11) when every MMA this
+// thread issued so far has finished.
+B200_DEVICE void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+// The same, arriving on the issuing CTA's barrier only.
+B200_DEVICE void umma_commit_pair_local(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+B200_DEVICE void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// mbar_wait for a barrier on which the other CTA of the cluster arrives: acquire at cluster scope.
+B200_DEVICE bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+B200_DEVICE bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, uint64_t limit_ns) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((it & 63u) == 0) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > limit_ns) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
 // ------------------------------------------------------------------ tcgen05.mma
 
 // Shared-memory matrix descriptor (64 bit):

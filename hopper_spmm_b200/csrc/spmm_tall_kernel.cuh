@@ -364,6 +364,27 @@ spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_consta
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             B200_PROF_T0();
+            // The whole stage at once: when its tiles name consecutive aligned row groups of B (the column
+            // list of a window that holds every column), their images are neighbours in the packed copy of B
+            // and in the ring, and one bulk copy brings them all.  A bulk copy holds the issuing warp for a
+            // couple of hundred clocks whatever its size, so fewer and larger ones keep the producers ahead.
+            bool stage_run = false;
+            if (p.b_packed) {
+                bool good = true;
+                if ((uint32_t)lane < here) {
+                    const uint32_t *l = slot_words + lane * Cfg::kCW;
+                    const uint32_t f = l[0];
+                    good = l[Cfg::kCW - 1] - f == (uint32_t)Cfg::kCW - 1u && f % (uint32_t)Cfg::kCW == 0u &&
+                           f == slot_words[0] + (uint32_t)lane * Cfg::kCW;
+                }
+                stage_run = __all_sync(0xffffffffu, good);
+            }
+            if (stage_run) {
+                if (lane == 0 && !(B200_DEBUG_BITS(p) & 1u))
+                    ptx::bulk_load(gather_addr + s * kTps * Cfg::kGatherBytes,
+                                   p.b_packed + ((uint64_t)cur.slab * p.b_groups + slot_words[0] / (uint32_t)Cfg::kCW) * Cfg::kGatherBytes,
+                                   here * (uint32_t)Cfg::kGatherBytes, full_bar(s));
+            } else
 #pragma unroll
             for (uint32_t r = 0; r < (uint32_t)kTps / 2; ++r) {  // two tiles at a time, 16 lanes each
                 const uint32_t j = 2 * r + half;

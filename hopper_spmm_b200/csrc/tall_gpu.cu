@@ -1,5 +1,5 @@
-// 16-row condensed format -> 128-row super-windows, on the device.  Same result as converting the
-// matrix at a window height of 128 with the reference's algorithm (src/utils/convert.h:146-225):
+// 16-row condensed format -> super-windows of 128 or 256 rows, on the device.  Same result as converting the
+// matrix at that window height with the reference's algorithm (src/utils/convert.h:146-225):
 // sorted distinct columns per window, padded to whole tiles; entries at (row % 128, column slot).
 //
 // Steps (integer work, bound by HBM traffic):
@@ -22,7 +22,7 @@ namespace b200spmm {
 namespace {
 
 constexpr int kBlock = 256;
-constexpr uint32_t kTall = 128, kShort = 16;
+constexpr uint32_t kShort = 16;
 
 struct Scratch {  // device buffers released on every exit path
     void *ptrs[16] = {};
@@ -96,7 +96,7 @@ __global__ void tall_scatter_values_kernel(const uint32_t *__restrict__ rowOffse
                                            const uint32_t *__restrict__ win_group, uint32_t eff, uint32_t cw,
                                            uint64_t n_entries, const uint32_t *__restrict__ ubase,
                                            const uint32_t *__restrict__ t_rowOffset, const uint32_t *__restrict__ t_tcA2B,
-                                           const uint32_t *__restrict__ t_rowIdx, T *__restrict__ t_data) {
+                                           const uint32_t *__restrict__ t_rowIdx, uint32_t tall_rows, T *__restrict__ t_data) {
     for (uint64_t e = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; e < n_entries; e += (uint64_t)gridDim.x * blockDim.x) {
         const uint32_t c = tcA2B[e];
         if (c == kIdxMax) continue;
@@ -109,10 +109,13 @@ __global__ void tall_scatter_values_kernel(const uint32_t *__restrict__ rowOffse
             const uint32_t mid = lo + (hi - lo) / 2;
             if (list[mid] < c) lo = mid + 1; else hi = mid;
         }
-        const uint64_t ot = (uint64_t)t_rowOffset[g] + lo / cw;
-        const uint32_t olc = lo % cw, row_shift = rowIdx[i] - t_rowIdx[g];
+        // A tile image is 128 rows.  Windows of 256 rows keep, per window, the images of rows 0-127 of all
+        // its tiles and then those of rows 128-255 (each CTA of a pair reads its own run).
+        const uint32_t olc = lo % cw, shift = rowIdx[i] - t_rowIdx[g], part = shift / 128u, row_shift = shift % 128u;
+        const uint64_t g_first = t_rowOffset[g], g_tiles = t_rowOffset[g + 1] - g_first;
+        const uint64_t ot = g_first * (tall_rows / 128u) + part * g_tiles + lo / cw;
         const T *src = data + ((uint64_t)t * kShort) * cw + lc;
-        T *dst = t_data + (ot * kTall + row_shift) * cw;
+        T *dst = t_data + (ot * 128u + row_shift) * cw;
         const uint32_t half = cw / 2;  // elements per 16-byte half of a tile row
 #pragma unroll 4
         for (uint32_t lr = 0; lr < kShort; ++lr) {
@@ -123,7 +126,8 @@ __global__ void tall_scatter_values_kernel(const uint32_t *__restrict__ rowOffse
 }
 
 // Runs of 16-row windows that fall into the same 128-row window.
-void group_windows(const uint32_t *h_rowIdx, uint64_t eff, std::vector<uint32_t> *win_group, std::vector<uint64_t> *group_first) {
+void group_windows(const uint32_t *h_rowIdx, uint64_t eff, uint32_t kTall, std::vector<uint32_t> *win_group,
+                   std::vector<uint64_t> *group_first) {
     win_group->resize(eff);
     group_first->clear();
     for (uint64_t i = 0; i < eff; ++i) {
@@ -136,11 +140,12 @@ void group_windows(const uint32_t *h_rowIdx, uint64_t eff, std::vector<uint32_t>
 }  // namespace
 
 int estimate_tall_tile_ratio(const b200spmm_btcf_info_t &info, const uint32_t *h_rowOffset, const uint32_t *h_rowIdx,
-                             const uint32_t *d_tcA2B, int max_samples, double *ratio, uint64_t *n_super_windows) {
+                             const uint32_t *d_tcA2B, uint32_t tall_rows, int max_samples, double *ratio,
+                             uint64_t *n_super_windows) {
     const uint64_t eff = info.eff_row_windows, cw = (uint64_t)info.col_window;
     std::vector<uint32_t> win_group;
     std::vector<uint64_t> group_first;
-    group_windows(h_rowIdx, eff, &win_group, &group_first);
+    group_windows(h_rowIdx, eff, tall_rows, &win_group, &group_first);
     const uint64_t n_groups = group_first.size() - 1;
     *n_super_windows = n_groups;
     *ratio = 1.0;
@@ -174,15 +179,16 @@ void free_tall(TallFormat *t) {
 
 int build_tall_device(const b200spmm_btcf_info_t &info, const uint32_t *h_rowOffset, const uint32_t *h_rowIdx,
                       const uint32_t *d_rowOffset, const uint32_t *d_tcA2B, const void *d_data, const uint32_t *d_rowIdx,
-                      TallFormat *out) {
+                      uint32_t tall_rows, TallFormat *out) {
     *out = TallFormat();
-    if (info.row_window != (int)kShort) return B200SPMM_ERR_UNSUPPORTED;
+    if (info.row_window != (int)kShort || (tall_rows != 128 && tall_rows != 256)) return B200SPMM_ERR_UNSUPPORTED;
+    const uint32_t kTall = tall_rows;
     const uint64_t eff = info.eff_row_windows, cw = (uint64_t)info.col_window, tiles = info.total_tiles;
     if (!eff || !tiles) return B200SPMM_OK;
     const uint64_t n_entries = tiles * cw;
     std::vector<uint32_t> win_group;
     std::vector<uint64_t> group_first;
-    group_windows(h_rowIdx, eff, &win_group, &group_first);
+    group_windows(h_rowIdx, eff, tall_rows, &win_group, &group_first);
     const uint64_t n_groups = group_first.size() - 1;
     std::vector<uint32_t> h_t_rowIdx(n_groups);
     for (uint64_t g = 0; g < n_groups; ++g) h_t_rowIdx[g] = h_rowIdx[group_first[g]] / kTall * kTall;
@@ -223,6 +229,7 @@ int build_tall_device(const b200spmm_btcf_info_t &info, const uint32_t *h_rowOff
     if (t_tiles > 0xFFFFFFFFull) return B200SPMM_ERR_UNSUPPORTED;  // rowOffset is 32-bit
 
     TallFormat t;
+    t.rows = kTall;
     t.eff = n_groups;
     t.tiles = t_tiles;
     struct Guard {
@@ -244,11 +251,11 @@ int build_tall_device(const b200spmm_btcf_info_t &info, const uint32_t *h_rowOff
     if (info.elt_size == 2)
         tall_scatter_values_kernel<uint16_t><<<grid_for(n_entries), kBlock>>>(
             d_rowOffset, d_tcA2B, static_cast<const uint16_t *>(d_data), d_rowIdx, d_group, (uint32_t)eff, (uint32_t)cw,
-            n_entries, d_ubase, t.d_rowOffset, t.d_tcA2B, t.d_rowIdx, static_cast<uint16_t *>(t.d_data));
+            n_entries, d_ubase, t.d_rowOffset, t.d_tcA2B, t.d_rowIdx, kTall, static_cast<uint16_t *>(t.d_data));
     else
         tall_scatter_values_kernel<uint32_t><<<grid_for(n_entries), kBlock>>>(
             d_rowOffset, d_tcA2B, static_cast<const uint32_t *>(d_data), d_rowIdx, d_group, (uint32_t)eff, (uint32_t)cw,
-            n_entries, d_ubase, t.d_rowOffset, t.d_tcA2B, t.d_rowIdx, static_cast<uint32_t *>(t.d_data));
+            n_entries, d_ubase, t.d_rowOffset, t.d_tcA2B, t.d_rowIdx, kTall, static_cast<uint32_t *>(t.d_data));
     B200_CUDA_TRY(cudaGetLastError());
     B200_CUDA_TRY(cudaDeviceSynchronize());
     *out = t;

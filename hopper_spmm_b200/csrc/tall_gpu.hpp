@@ -9,10 +9,12 @@
 namespace b200spmm {
 
 struct TallFormat {
-    uint64_t eff = 0, tiles = 0;  // super-windows holding entries, their tiles (128 rows x CW each)
+    uint32_t rows = 128;          // rows of a super-window: 128, or 256 for the CTA-pair kernel
+    uint64_t eff = 0, tiles = 0;  // super-windows holding entries, their tiles (rows x CW each)
     uint32_t *d_rowOffset = nullptr, *d_tcA2B = nullptr, *d_rowIdx = nullptr;
-    void *d_data = nullptr;  // tiles in the kernel's shared-memory image: row r of a tile has its two 16-byte
-                             // halves swapped when (r / 4) is odd
+    void *d_data = nullptr;  // tiles in the kernel's shared-memory image, 128 rows each: row r of an image has its
+                             // two 16-byte halves swapped when (r / 4) is odd.  rows == 256: per window the
+                             // images of rows 0-127 of all its tiles, then those of rows 128-255
 };
 
 // How many tiles the matrix would have with 128-row windows, as a fraction of its 16-row tiles,
@@ -21,7 +23,8 @@ struct TallFormat {
 // list of its fullest part (executed work unchanged); 1 means nothing was shared (work x 8).
 // h_rowOffset / h_rowIdx are host copies of the 16-row arrays.  Returns a B200SPMM status.
 int estimate_tall_tile_ratio(const b200spmm_btcf_info_t &info, const uint32_t *h_rowOffset, const uint32_t *h_rowIdx,
-                             const uint32_t *d_tcA2B, int max_samples, double *ratio, uint64_t *n_super_windows);
+                             const uint32_t *d_tcA2B, uint32_t tall_rows, int max_samples, double *ratio,
+                             uint64_t *n_super_windows);
 
 // Merges the 16-row windows that share a 128-row window: the column list of a super-window is the
 // sorted union of theirs (padded with 0xFFFFFFFF to whole tiles), and every stored tile entry moves
@@ -31,7 +34,7 @@ int estimate_tall_tile_ratio(const b200spmm_btcf_info_t &info, const uint32_t *h
 // conversion (see TallFormat::d_data).
 int build_tall_device(const b200spmm_btcf_info_t &info, const uint32_t *h_rowOffset, const uint32_t *h_rowIdx,
                       const uint32_t *d_rowOffset, const uint32_t *d_tcA2B, const void *d_data, const uint32_t *d_rowIdx,
-                      TallFormat *out);
+                      uint32_t tall_rows, TallFormat *out);
 void free_tall(TallFormat *t);
 
 }  // namespace b200spmm

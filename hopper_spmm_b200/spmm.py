@@ -316,19 +316,24 @@ class SpmmPlan:
                                                  capi.C_F16 if c_half else capi.C_F32), "b200spmm_spmm_host")
         return C_out
 
-    def tall_format(self):
-        """The plan's 128-row super-window copy of the matrix (b200spmm_plan_tall_*) as a dict of numpy
-        arrays plus its counts, or None when the plan keeps none."""
+    def tall_format(self, rows: int = 128):
+        """The plan's super-window copy of the matrix as a dict of numpy arrays plus its counts, or None
+        when the plan keeps none: rows=128 the one of the 128-row kernel (b200spmm_plan_tall_*), rows=256
+        the one of the CTA-pair kernel (b200spmm_plan_pair_*)."""
+        if rows not in (128, 256):
+            raise ValueError("super-windows have 128 or 256 rows")
+        kind = "tall" if rows == 128 else "pair"
+        get_info = getattr(capi.lib(), f"b200spmm_plan_{kind}_info")
+        copy_out = getattr(capi.lib(), f"b200spmm_plan_{kind}_copy_to_host")
         info = capi.BtcfInfo()
-        capi.check(capi.lib().b200spmm_plan_tall_info(self._p, C.byref(info)), "b200spmm_plan_tall_info")
+        capi.check(get_info(self._p, C.byref(info)), f"b200spmm_plan_{kind}_info")
         if info.row_window == 0:
             return None
         cw, dt = info.col_window, (np.float16 if self.is_f16 else np.float32)
         out = {"rowOffset": np.zeros(info.eff_row_windows + 1, np.uint32), "tcA2B": np.zeros(info.total_tiles * cw, np.uint32),
                "data": np.zeros(info.total_tiles * info.row_window * cw, dt), "rowIdx": np.zeros(info.eff_row_windows, np.uint32)}
-        capi.check(capi.lib().b200spmm_plan_tall_copy_to_host(self._p, out["rowOffset"].ctypes.data, out["tcA2B"].ctypes.data,
-                                                              out["data"].ctypes.data, out["rowIdx"].ctypes.data),
-                   "b200spmm_plan_tall_copy_to_host")
+        capi.check(copy_out(self._p, out["rowOffset"].ctypes.data, out["tcA2B"].ctypes.data, out["data"].ctypes.data,
+                            out["rowIdx"].ctypes.data), f"b200spmm_plan_{kind}_copy_to_host")
         out.update(row_window=info.row_window, eff_row_windows=info.eff_row_windows, total_tiles=info.total_tiles)
         return out
 

@@ -382,14 +382,17 @@ int b200spmm_bench(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, 
  *     kernel reads them, so nothing is carried over from the previous call - but all calls on
  *     a device share the one array: two calls whose kernels can overlap on the GPU (different
  *     streams, no dependency) race on it.  Serialise them.
- *   - The device-side timeout flag is not read back by this call; results after a suspected
- *     hang should be checked by the caller.
+ *   - The call is asynchronous and does not read the kernel's status word back;
+ *     b200spmm_spmm_noalloc_status(device, stream) waits for `stream` and returns
+ *     B200SPMM_ERR_DEVICE_TIMEOUT if a bounded wait inside the last allocation-free launch on that
+ *     device gave up (it allocates nothing either).
  * Same requirements on shapes and alignment as b200spmm_spmm; d_tcA2B and d_data 16-byte aligned.
  * Asynchronous on `stream`.
  */
 int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_rowOffset, const uint32_t *d_tcA2B,
                           const void *d_data, const uint32_t *d_rowIdx, const void *d_B, int64_t ldb, int64_t n,
                           void *d_C, int64_t ldc, int c_dtype, int device, int n_ctas, void *stream);
+int b200spmm_spmm_noalloc_status(int device, void *stream);
 
 /*
  * Super-windows.  When the 16-row windows of a matrix already touch most of its columns (a pruned
@@ -407,6 +410,17 @@ int b200spmm_spmm_noalloc(const b200spmm_btcf_info_t *info, const uint32_t *d_ro
  */
 int b200spmm_plan_tall_info(const b200spmm_plan_t *p, b200spmm_btcf_info_t *info);
 int b200spmm_plan_tall_copy_to_host(const b200spmm_plan_t *p, uint32_t *rowOffset, uint32_t *tcA2B, void *data,
+                                    uint32_t *rowIdx);
+/*
+ * Such a plan may keep the matrix a third time, in windows of 256 rows, for launches wider than 128
+ * features: a pair of CTAs on neighbouring SMs (a cluster of two) then shares one MMA of 256 window rows x
+ * 256 features, each CTA holding half of either operand, which halves what an SM fetches of B per tile.
+ * Kept when the 256-row windows have at most 0.55 of the 128-row tiles (B200SPMM_WINDOW=256 forces it,
+ * =128 keeps it out).  The two calls below are the counterparts of the two above for that copy
+ * (row_window 256, or 0 when the plan has none).
+ */
+int b200spmm_plan_pair_info(const b200spmm_plan_t *p, b200spmm_btcf_info_t *info);
+int b200spmm_plan_pair_copy_to_host(const b200spmm_plan_t *p, uint32_t *rowOffset, uint32_t *tcA2B, void *data,
                                     uint32_t *rowIdx);
 
 /* Per-launch facts of the most recent b200spmm_spmm on this plan. */

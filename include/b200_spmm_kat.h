@@ -38,6 +38,16 @@ int b200spmm_kat_umma(const void *image, uint32_t image_bytes, const b200spmm_ka
                       int n_cols, float *out, int device);
 
 /*
+ * The same for the MMA of a CTA pair (tcgen05.mma.cta_group::2, M = 256): `images` holds two images of
+ * image_bytes each, one per CTA of a two-CTA cluster (CTA r: rows 128 r .. of operand A and columns
+ * (N / 2) r .. of operand B, at the same offsets in both images); the even CTA issues the listed MMAs;
+ * out[2][128][n_cols] receives each CTA's 128 lanes of tensor memory (rows 128 r .. of D).  The reference
+ * has no counterpart (its wgmma tiles live in one SM: src/fp16.cu:147).
+ */
+int b200spmm_kat_umma_pair(const void *images, uint32_t image_bytes, const b200spmm_kat_mma_t *mmas, int n_mmas,
+                           int n_cols, float *out, int device);
+
+/*
  * Sets how long a wait inside the known-answer kernels may last, in nanoseconds (0 restores the
  * default of two seconds), and returns the previous value.  A test shortens it, hands
  * b200spmm_kat_tma an expect_bytes larger than its loads deliver and must get

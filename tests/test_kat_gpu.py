@@ -53,6 +53,32 @@ def test_super_window_tile_product(tf32, n):
     assert np.array_equal(d, tile.astype(np.float32) @ feats.astype(np.float32).T)  # small integers: exact
 
 
+@pytest.mark.parametrize("tf32", [False, True])
+def test_cta_pair_tile_product(tf32):
+    # One MMA over a pair of CTAs (cta_group::2): M = 256 window rows (128 per CTA), N = 256 features of
+    # which every CTA holds 128 in its own shared memory, K = one tile.  D rows 128 r .. come out of CTA r.
+    import ctypes as C
+    from hopper_spmm_b200 import _capi as capi
+    dt, cw = (np.float32, 8) if tf32 else (np.float16, 16)
+    rng = np.random.default_rng(7 + tf32)
+    tile = rng.integers(-8, 9, (256, cw)).astype(dt)
+    feats = rng.integers(-8, 9, (256, cw)).astype(dt)   # gathered rows of B, [feature][k]
+    images = b""
+    for r in range(2):
+        img = ku.pack_tile(tile[128 * r:128 * r + 128]) + ku.pack_gathered(np.ascontiguousarray(feats[128 * r:128 * r + 128]))
+        images += img + bytes(16384 - len(img))
+    idesc = capi.lib().b200spmm_kat_instr_desc(2 if tf32 else 0, 256, 256, 0, 1)
+    mma = capi.KatMma(a_off=0, a_lbo=16, a_sbo=256, a_swizzle=6, b_off=4096, b_lbo=1024 if tf32 else 2048,
+                      b_sbo=512 if tf32 else 1024, b_swizzle=1 if tf32 else 2, idesc=idesc, d_col=0, accumulate=0,
+                      kind=1 if tf32 else 0)
+    out = np.zeros((2, 128, 256), np.float32)
+    buf = np.frombuffer(images, np.uint8)
+    st = capi.lib().b200spmm_kat_umma_pair(buf.ctypes.data, 16384, (capi.KatMma * 1)(mma), 1, 256, out.ctypes.data, 0)
+    assert st == 0
+    want = tile.astype(np.float32) @ feats.astype(np.float32).T
+    assert np.array_equal(out.reshape(256, 256), want)  # small integers: exact
+
+
 def test_kat1_fp16_values():
     # src/test_fp16.cu:407-415 re-expressed for the transposed mapping: the 64x16 operand
     # A[i] = half(i+1) plays the feature side (M = 64), the all-ones operand the window side.

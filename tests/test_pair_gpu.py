@@ -1,0 +1,124 @@
+"""The CTA-pair path on the device: 256-row super-windows multiplied by clusters of two CTAs that share one
+MMA of 256 window rows x 256 features (tcgen05.mma.cta_group::2).  The merged format against a conversion
+at 256 rows (the reference's algorithm, src/utils/convert.h:146-225, at ROW_WINDOW = 256) and the kernel
+against the CPU oracle.  Small matrices are sent down this path with B200SPMM_WINDOW=256."""
+import numpy as np
+import pytest
+
+import hopper_spmm_b200 as hs
+import oracle
+import parity
+from cases import dense_b, random_csr
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture
+def pair(monkeypatch):
+    monkeypatch.setenv("B200SPMM_WINDOW", "256")
+
+
+@pytest.mark.parametrize("dt", [np.float16, np.float32])
+def test_merged_format_equals_a_conversion_at_256_rows(dt, pair):
+    rows, cols, rp, ci, v = random_csr(1100, 900, 0.02, 5, dt, empty_rows=[(0, 130), (256, 512), (900, 960)], dense_rows=[140, 700])
+    v = v.copy()
+    v[::9] = 0  # explicit zeros keep their column
+    plan = hs.SpmmPlan(hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v)))
+    try:
+        got = plan.tall_format(256)
+    finally:
+        plan.close()
+    cw = 16 if dt == np.float16 else 8
+    want = oracle.csr2btcf_nobitmap(rows, cols, rp, ci, v, 256, cw)
+    assert got is not None and got["row_window"] == 256
+    assert got["eff_row_windows"] == want.eff_row_windows and got["total_tiles"] == want.total_tiles
+    for k in ("rowOffset", "tcA2B", "rowIdx"):
+        assert np.array_equal(got[k], getattr(want, k)), k
+    bits = np.uint16 if dt == np.float16 else np.uint32
+    assert np.array_equal(got["data"].view(bits), np.asarray(want.data).view(bits))
+
+
+@pytest.mark.parametrize("dt", [np.float16, np.float32])
+@pytest.mark.parametrize("n", [136, 256, 320, 520])
+def test_ragged_matrix_every_slab_width(dt, n, pair):
+    import torch
+    rows, cols, rp, ci, v = random_csr(1100, 517, 0.03, 11, dt, empty_rows=[(0, 130), (256, 512), (1000, 1100)], dense_rows=[140])
+    B = dense_b(cols, n, 3, dt)
+    plan = hs.SpmmPlan(hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v)))
+    try:
+        dC = torch.full((rows, n), float("nan"), device="cuda")  # every row must be written
+        plan.spmm(torch.from_numpy(B).cuda(), dC)
+        info = plan.launch_info()
+        assert info.row_window == 256 and info.feature_slab == 256 and info.kernel_launches == 1
+        C_out = dC.cpu().numpy()
+        parity.check(C_out, rows, rp, ci, v, B)
+        assert np.all(C_out[0:130] == 0) and np.all(C_out[256:512] == 0) and np.all(C_out[1000:] == 0)
+        half = plan.spmm_host(B, c_half=True)
+        assert half.dtype == np.float16 and np.array_equal(half, C_out.astype(np.float16))
+    finally:
+        plan.close()
+
+
+@pytest.mark.parametrize("dt", [np.float16, np.float32])
+def test_same_bits_as_the_128_row_kernel(dt, monkeypatch):
+    # both kernels add a row's products in ascending column order, one tile of CW columns per MMA: merging
+    # two 128-row windows moves columns between tiles, so results agree to rounding, and exactly where both
+    # window heights give a row the same tiles - a matrix whose windows hold every column
+    import torch
+    rows, cols = 1024, 640
+    rows_, cols_, rp, ci, v = random_csr(rows, cols, 0.05, 31, dt, dense_rows=list(range(3, rows, 128)))
+    B = torch.from_numpy(dense_b(cols, 512, 4, dt)).cuda()
+    out = {}
+    for win in ("128", "256"):
+        monkeypatch.setenv("B200SPMM_WINDOW", win)
+        plan = hs.SpmmPlan(hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v)))
+        try:
+            out[win] = plan.spmm(B).cpu().numpy()
+            assert plan.launch_info().row_window == int(win)
+        finally:
+            plan.close()
+    assert np.array_equal(out["128"], out["256"])
+    parity.check(out["256"], rows, rp, ci, v, B.cpu().numpy())
+
+
+@pytest.mark.parametrize("dt", [np.float16, np.float32])
+def test_more_items_than_pairs_and_strided_operands(dt, pair):
+    # 40 super-windows x 4 slabs = 160 work items on at most 74 pairs: the run-time hand-out is used (the
+    # even CTA writes the item into the odd CTA's list); B and C are views with larger leading dimensions
+    import torch
+    rows, cols, rp, ci, v = random_csr(10240, 300, 0.04, 17, dt, empty_rows=[(2560, 2830)])
+    n = 1024
+    Bfull = torch.from_numpy(dense_b(cols, n + 64, 8, dt)).cuda()
+    Cfull = torch.zeros((rows, n + 128), device="cuda")
+    Bv, Cv = Bfull[:, 32:32 + n], Cfull[:, 64:64 + n]
+    plan = hs.SpmmPlan(hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v)))
+    try:
+        for _ in range(2):  # the hand-out counters must be back at zero for the second launch
+            Cv.fill_(float("nan"))
+            plan.spmm(Bv, Cv)
+            assert plan.launch_info().row_window == 256 and plan.launch_info().n_slabs == 4
+            parity.check(Cv.cpu().numpy(), rows, rp, ci, v, Bv.cpu().numpy())
+        assert float(Cfull[:, :64].abs().sum()) == 0 and float(Cfull[:, 64 + n:].abs().sum()) == 0
+    finally:
+        plan.close()
+
+
+@pytest.mark.parametrize("dt", [np.float16, np.float32])
+def test_dense_windows_take_packed_rows_of_b(dt, pair):
+    # every super-window holds a full row: all tiles but the ragged last one name an aligned group of rows
+    # of B and are fed from the per-launch images of B (128-feature blocks, one per CTA of the pair)
+    import torch
+    n = 328
+    rows, cols = 1300, 1000 + (8 if dt == np.float32 else 16) // 2
+    rows_, cols_, rp, ci, v = random_csr(rows, cols, 0.01, 23, dt, empty_rows=[(256, 512)], dense_rows=[5, 130, 600, 800, 1030, 1290])
+    Bfull = torch.from_numpy(dense_b(cols, n + 72, 9, dt)).cuda()
+    Bv = Bfull[:, 8:8 + n]
+    plan = hs.SpmmPlan(hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v)))
+    try:
+        dC = torch.full((rows, n), float("nan"), device="cuda")
+        plan.spmm(Bv, dC)
+        info = plan.launch_info()
+        assert info.row_window == 256 and info.kernel_launches == 2
+        parity.check(dC.cpu().numpy(), rows, rp, ci, v, Bv.cpu().numpy())
+    finally:
+        plan.close()

@@ -41,7 +41,8 @@ def _noalloc(info, d_ro, d_a2b, d_data, d_ridx, dB, dC, n_ctas, torch):
                                           d_ridx.data_ptr(), dB.data_ptr(), dB.stride(0), dB.shape[1], dC.data_ptr(),
                                           dC.stride(0), capi.C_F32, 0, n_ctas, torch.cuda.current_stream().cuda_stream)
     capi.check(st, "b200spmm_spmm_noalloc")
-    torch.cuda.synchronize()
+    # the kernel's own verdict (a bounded wait that gave up would show here), read back without allocating
+    capi.check(capi.lib().b200spmm_spmm_noalloc_status(0, torch.cuda.current_stream().cuda_stream), "b200spmm_spmm_noalloc_status")
 
 
 @pytest.mark.parametrize("dt", [np.float16, np.float32])
