@@ -116,33 +116,71 @@ int ensure_comms(b200spmm_sharded *s) {
 }
 
 // Every device holds all of `full[d]` except that only its own byte range [cut[d], cut[d+1]) is valid;
-// on return (stream order) every device holds every range.  One grouped exchange: all transfers in
-// flight together, the ranges may differ in length.
+// on return (stream order) every device holds every range.  The ranges may differ in length - the rows are
+// cut for equal work, so the device with the lightest rows holds several times the average - and a direct
+// exchange is as slow as that device's outgoing link (eight GPUs: 31.6 ms for 8.6 GB).  So it runs in two
+// steps: (1) one grouped send/receive moves every byte that lies outside its holder's EVEN part (part q =
+// bytes [q total / N, (q + 1) total / N), rounded to 512) to the device whose even part it falls into - each
+// such byte crosses one link once; (2) the library's in-place all-gather of the even parts, which loads all
+// links alike.  The few bytes past N whole parts go to everybody in step 1.  Where the busiest device would send
+// hardly less that way than by sending its range to everybody (two devices), step 1 alone does it all.
 int exchange_ranges(b200spmm_sharded *s, void *const *full, const std::vector<uint64_t> &cut) {
     if (s->n_dev == 1) return B200SPMM_OK;
     int st = ensure_comms(s);
     if (st != B200SPMM_OK) return st;
     const Nccl &n = nccl();
+    const int N = s->n_dev;
+    const uint64_t total = cut[N];
     bool equal = true;
-    for (int d = 0; d < s->n_dev; ++d) equal = equal && (cut[d + 1] - cut[d] == cut[1] - cut[0]);
-    B200_NCCL_TRY(n.GroupStart());
-    for (int d = 0; d < s->n_dev; ++d) {
-        char *base = static_cast<char *>(full[d]);
-        if (equal) {  // equal parts: the library's all-gather, in place
-            ncclResult_t r = n.AllGather(base + cut[d], base, cut[1] - cut[0], ncclChar, s->comms[d], s->streams[d]);
-            if (r != ncclSuccess) { n.GroupEnd(); set_last_error_static(n.GetErrorString(r)); return B200SPMM_ERR_CUDA; }
-            continue;
+    for (int d = 0; d < N; ++d) equal = equal && (cut[d + 1] - cut[d] == cut[1] - cut[0]);
+    uint64_t part = equal ? cut[1] - cut[0] : total / (uint64_t)N / 512u * 512u;
+    if (!equal && part) {  // does the two-step exchange save the busiest device at least 15 % of its sends?
+        uint64_t longest = 0, outside = 0;
+        for (int d = 0; d < N; ++d) {
+            const uint64_t len = cut[d + 1] - cut[d];
+            const uint64_t lo = std::max(cut[d], part * (uint64_t)d), hi = std::min(cut[d + 1], part * (uint64_t)(d + 1));
+            longest = std::max(longest, len);
+            outside = std::max(outside, len - (hi > lo ? hi - lo : 0));
         }
-        for (int step = 1; step < s->n_dev; ++step) {  // a different peer for every device at every step
-            const int to = (d + step) % s->n_dev, from = (d - step + s->n_dev) % s->n_dev;
-            ncclResult_t r = ncclSuccess;
-            if (cut[d + 1] > cut[d]) r = n.Send(base + cut[d], cut[d + 1] - cut[d], ncclChar, to, s->comms[d], s->streams[d]);
-            if (r == ncclSuccess && cut[from + 1] > cut[from])
-                r = n.Recv(base + cut[from], cut[from + 1] - cut[from], ncclChar, from, s->comms[d], s->streams[d]);
-            if (r != ncclSuccess) { n.GroupEnd(); set_last_error_static(n.GetErrorString(r)); return B200SPMM_ERR_CUDA; }
-        }
+        if ((double)(outside + part * (uint64_t)(N - 1)) * 1.15 >= (double)longest * (double)(N - 1)) part = 0;
     }
-    B200_NCCL_TRY(n.GroupEnd());
+    auto fail = [&](ncclResult_t r) {
+        n.GroupEnd();
+        set_last_error_static(n.GetErrorString(r));
+        return B200SPMM_ERR_CUDA;
+    };
+    if (!equal) {
+        const uint64_t whole = part * (uint64_t)N;  // bytes the all-gather covers; [whole, total) is the tail
+        B200_NCCL_TRY(n.GroupStart());
+        for (int d = 0; d < N; ++d) {
+            char *base = static_cast<char *>(full[d]);
+            for (int step = 1; step < N; ++step) {  // a different peer for every device at every step
+                const int to = (d + step) % N, from = (d - step + N) % N;
+                // what this device holds of `to`'s even part, then what it holds of the tail
+                const uint64_t s_lo = std::max(cut[d], part * (uint64_t)to), s_hi = std::min(cut[d + 1], part * (uint64_t)(to + 1));
+                const uint64_t st_lo = std::max(cut[d], whole), st_hi = cut[d + 1];
+                // what `from` holds of this device's even part, then of the tail (same order as its sends)
+                const uint64_t r_lo = std::max(cut[from], part * (uint64_t)d), r_hi = std::min(cut[from + 1], part * (uint64_t)(d + 1));
+                const uint64_t rt_lo = std::max(cut[from], whole), rt_hi = cut[from + 1];
+                ncclResult_t r = ncclSuccess;
+                if (s_hi > s_lo) r = n.Send(base + s_lo, s_hi - s_lo, ncclChar, to, s->comms[d], s->streams[d]);
+                if (r == ncclSuccess && st_hi > st_lo) r = n.Send(base + st_lo, st_hi - st_lo, ncclChar, to, s->comms[d], s->streams[d]);
+                if (r == ncclSuccess && r_hi > r_lo) r = n.Recv(base + r_lo, r_hi - r_lo, ncclChar, from, s->comms[d], s->streams[d]);
+                if (r == ncclSuccess && rt_hi > rt_lo) r = n.Recv(base + rt_lo, rt_hi - rt_lo, ncclChar, from, s->comms[d], s->streams[d]);
+                if (r != ncclSuccess) return fail(r);
+            }
+        }
+        B200_NCCL_TRY(n.GroupEnd());
+    }
+    if (part) {
+        B200_NCCL_TRY(n.GroupStart());
+        for (int d = 0; d < N; ++d) {  // the library's all-gather, in place
+            char *base = static_cast<char *>(full[d]);
+            ncclResult_t r = n.AllGather(base + part * (uint64_t)d, base, part, ncclChar, s->comms[d], s->streams[d]);
+            if (r != ncclSuccess) return fail(r);
+        }
+        B200_NCCL_TRY(n.GroupEnd());
+    }
     return B200SPMM_OK;
 }
 

@@ -31,28 +31,57 @@ def slice_csr(row_ptr, col_idx, values, r0: int, r1: int):
 
 def _exchange_row_slices(full, cuts, group=None):
     """Rank p holds rows [cuts[p], cuts[p+1]) of `full`; on return every rank holds all of it.
-    One grouped exchange: every rank sends its slice to every other rank and receives theirs, all
-    transfers in flight together (NCCL runs the group as one kernel over all NVLink peers: 4.3 GB
-    replicated in 6.1 ms on eight B200s and 3.3 ms on two, against 7.1 and 6.2 ms for a loop of
-    broadcasts).  The slices may differ in length, which is why this is not a plain all-gather."""
+    The slices may differ in length - rows are cut for equal work, so the rank with the lightest rows
+    holds several times the average - and a direct exchange is as slow as that rank's outgoing link
+    (eight B200s: 31.6 ms for 8.6 GB of C).  So it runs in two steps: (1) one grouped send/receive moves
+    every row that lies outside its holder's EVEN part (part q = rows [q K, (q + 1) K), K = rows // world)
+    to the rank whose even part it falls into - such a row crosses one link once; (2) the library's
+    in-place all-gather of the even parts, which loads all links alike.  The rows past world * K go to
+    everybody in step 1.  Where the busiest rank would send hardly less that way than by sending its
+    slice to everybody (two ranks; nearly equal slices with a remainder), step 1 alone does it all."""
     import torch.distributed as dist
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
-    mine = full[int(cuts[rank]):int(cuts[rank + 1])]
+    if world < 2:
+        return
+    cuts = [int(c) for c in cuts]
+    total = cuts[-1]
+    part = total // world if full.is_contiguous() else 0   # without whole parts: step 1 alone, everything to everybody
+    equal = all(cuts[p + 1] - cuts[p] == part for p in range(world))   # then the all-gather alone does it
+    if part and not equal and not two_step_pays(cuts, part):
+        part = 0
+    whole = part * world
     ops = []
+
+    def piece(lo, hi, op, peer):
+        if hi > lo:
+            ops.append(dist.P2POp(op, full[lo:hi], dist.get_global_rank(group, peer) if group is not None else peer, group))
+
     for step in range(1, world):
         # a different peer for every rank at every step, so no rank is everybody's first target
         to, frm = (rank + step) % world, (rank - step) % world
-        theirs = full[int(cuts[frm]):int(cuts[frm + 1])]
-        g_to = dist.get_global_rank(group, to) if group is not None else to
-        g_frm = dist.get_global_rank(group, frm) if group is not None else frm
-        if mine.numel():
-            ops.append(dist.P2POp(dist.isend, mine, g_to, group))
-        if theirs.numel():
-            ops.append(dist.P2POp(dist.irecv, theirs, g_frm, group))
+        # what this rank holds of `to`'s even part, then of the tail; what `frm` holds of this rank's
+        # even part, then of the tail - sends and receives of a pair in the same order
+        piece(max(cuts[rank], part * to), min(cuts[rank + 1], part * (to + 1)), dist.isend, to)
+        piece(max(cuts[rank], whole), cuts[rank + 1], dist.isend, to)
+        piece(max(cuts[frm], part * rank), min(cuts[frm + 1], part * (rank + 1)), dist.irecv, frm)
+        piece(max(cuts[frm], whole), cuts[frm + 1], dist.irecv, frm)
     if ops:
         for w in dist.batch_isend_irecv(ops):
             w.wait()
+    if part:
+        dist.all_gather_into_tensor(full[:whole], full[part * rank:part * (rank + 1)], group=group)
+
+
+def two_step_pays(cuts, part) -> bool:
+    """Does the busiest rank send at least 15 % less with the two-step exchange of `_exchange_row_slices`
+    (its rows outside its even part once, then its even part to everybody) than with the direct one (its
+    slice to everybody)?  `cuts`: the world + 1 slice boundaries; `part`: rows of an even part."""
+    world = len(cuts) - 1
+    direct = max(cuts[p + 1] - cuts[p] for p in range(world)) * (world - 1)
+    outside = max((cuts[p + 1] - cuts[p]) - max(0, min(cuts[p + 1], part * (p + 1)) - max(cuts[p], part * p))
+                  for p in range(world))
+    return (outside + part * (world - 1)) * 1.15 < direct
 
 
 def allgather_rows(C_local, cuts, group=None):

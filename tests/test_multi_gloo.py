@@ -42,6 +42,21 @@ def _worker(rank, world, port, out_dir):
         full = sharded.allgather_rows(C_local, cuts)
         want = oracle.spmm_csr(csr.rows, rp, ci, v, B.numpy())
         assert np.array_equal(full.numpy(), want)  # same per-row order of additions: bit-identical
+        # the exchange itself on crafted cuts: equal slices, skewed slices (re-sharded to even parts first, then
+        # the library's all-gather: the two-step path), slices whose busiest rank gains nothing from that (direct
+        # sends), an empty slice, a remainder past the whole even parts
+        cases = {2: [[0, 500, 1000], [0, 100, 1000], [0, 0, 7], [0, 999, 1001]],
+                 3: [[0, 333, 666, 999], [0, 50, 120, 1000], [0, 400, 400, 1001], [0, 1, 2, 5]]}[world]
+        took_two_steps = []
+        for cc in cases:
+            rows_all = torch.arange(cc[-1] * 4, dtype=torch.float32).reshape(cc[-1], 4)
+            buf = torch.full_like(rows_all, float("nan"))
+            buf[cc[rank]:cc[rank + 1]] = rows_all[cc[rank]:cc[rank + 1]]
+            sharded._exchange_row_slices(buf, cc)
+            assert torch.equal(buf, rows_all), cc
+            took_two_steps.append(cc[-1] // world > 0 and sharded.two_step_pays(cc, cc[-1] // world))
+        assert any(took_two_steps) or world == 2
+        assert not all(took_two_steps)
         # the replicated operand: every rank brings 1/N of it in, the rest arrives from the other ranks
         B_dev = torch.full_like(B, float("nan"))
         moved = sharded.upload_replicated(B, B_dev)
