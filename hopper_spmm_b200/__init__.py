@@ -5,9 +5,9 @@ The computing code is CUDA/C++ in ``csrc/`` behind the C ABI of ``include/b200_s
 benchmark inputs.
 """
 from .spmm import (BTCF_MTX_NO_BITMAP, CSR2BTCFNOBITMAP, CSR_MTX, DENSE_MTX, DeviceBtcf, IDX_MAX, PERF_RESULT, ROW_WINDOW, RUNS,
-                   WARMUP_RUNS, ShardedSpmm, SpmmPlan, fp16_spmm, rewindow, shard_rows, tf32_spmm)
+                   WARMUP_RUNS, ShardedSpmm, SpmmPlan, fp16_spmm, rewindow, shard_rows, tf32_spmm, transpose_tiles)
 
 from .formats import BTCF2GBTCF, BTCF_MTX, CSR2BTCF, GBTCF_MTX, load_matrix, validateBTCF2GBTCFConversion
 
 __all__ = ["BTCF2GBTCF", "BTCF_MTX", "CSR2BTCF", "GBTCF_MTX", "load_matrix", "validateBTCF2GBTCFConversion", "BTCF_MTX_NO_BITMAP", "CSR2BTCFNOBITMAP", "CSR_MTX", "DENSE_MTX", "DeviceBtcf", "IDX_MAX", "PERF_RESULT", "ROW_WINDOW",
-           "RUNS", "WARMUP_RUNS", "ShardedSpmm", "SpmmPlan", "fp16_spmm", "rewindow", "shard_rows", "tf32_spmm"]
+           "RUNS", "WARMUP_RUNS", "ShardedSpmm", "SpmmPlan", "fp16_spmm", "rewindow", "shard_rows", "tf32_spmm", "transpose_tiles"]

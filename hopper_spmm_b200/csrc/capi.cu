@@ -66,6 +66,9 @@ struct b200spmm_plan {
         std::vector<uint64_t> band_row;
     } sched;
     cudaStream_t copy_stream = nullptr;       // host-buffer call: C goes out on this one
+    cudaStream_t upload_stream = nullptr;     // ... and the second half of B's features comes in on this one
+    cudaEvent_t half_up[2] = {nullptr, nullptr};
+    bool host_split = true;                   // B200SPMM_HOST_SPLIT=0 (read when the plan is made) turns the halves off
     std::vector<cudaEvent_t> band_done;
     const Sched *launch_sched = nullptr;  // the one the next launch uses
     CompressedTiles comp;                 // the tiles as bitmap + stored values (empty: dense tiles only)
@@ -525,6 +528,7 @@ int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, const uint32_t *h
     // few per cent fill but costs the producer warps more instructions per tile than they can
     // spare today, so dense tiles are the default.
     p->gather_cpasync = env_is("B200SPMM_GATHER", "cpasync");
+    p->host_split = !env_is("B200SPMM_HOST_SPLIT", "0");
     if (info.total_tiles && env_is("B200SPMM_TILES", "bitmap")) {
         int st = compress_tiles_device(p->d_data, info.total_tiles, info.dtype, &p->comp);
         if (st != B200SPMM_OK) return st;
@@ -643,6 +647,14 @@ int b200spmm_csr2btcf_nobitmap(uint64_t rows, uint64_t cols, uint64_t nnz, const
     return B200SPMM_OK;
 }
 
+int b200spmm_btcf_transpose_tiles(b200spmm_btcf_t *f) {
+    if (!f) return B200SPMM_ERR_INVALID_ARG;
+    transpose_tiles(&f->f);
+    return B200SPMM_OK;
+}
+
+int b200spmm_btcf_tiles_col_major(const b200spmm_btcf_t *f) { return f && f->f.col_major_tiles ? 1 : 0; }
+
 int b200spmm_btcf_rewindow(const b200spmm_btcf_info_t *info, const uint32_t *rowOffset, const uint32_t *tcA2B,
                            const void *data, const uint32_t *rowIdx, int row_window, int n_threads,
                            b200spmm_btcf_t **out) {
@@ -756,6 +768,9 @@ void b200spmm_plan_destroy(b200spmm_plan_t *p) {
     if (p->image_is_copy) cudaFree(p->d_tiles_image);
     for (cudaEvent_t e : p->band_done) cudaEventDestroy(e);
     if (p->copy_stream) cudaStreamDestroy(p->copy_stream);
+    if (p->upload_stream) cudaStreamDestroy(p->upload_stream);
+    for (cudaEvent_t e : p->half_up)
+        if (e) cudaEventDestroy(e);
     cudaFree(p->d_partial);
     cudaFree(p->d_status);
     cudaFree(p->d_B);
@@ -766,6 +781,10 @@ void b200spmm_plan_destroy(b200spmm_plan_t *p) {
 int b200spmm_plan_create(const b200spmm_btcf_t *h, int device, int n_ctas, b200spmm_plan_t **out) {
     if (!h || !out) return B200SPMM_ERR_INVALID_ARG;
     *out = nullptr;
+    if (h->f.col_major_tiles) {  // the kernels read row-major tiles (the reference's default build)
+        set_last_error_static("tiles are stored column-major: b200spmm_btcf_transpose_tiles brings them back");
+        return B200SPMM_ERR_UNSUPPORTED;
+    }
     int n_dev = 0;
     if (cudaGetDeviceCount(&n_dev) != cudaSuccess || device < 0 || device >= n_dev) {
         cudaGetLastError();
@@ -1047,10 +1066,10 @@ int b200spmm_spmm_host(b200spmm_plan_t *p, const void *h_B, int64_t n, void *h_C
         B200_CUDA_TRY(cudaMalloc(&p->d_C, c_bytes));
         p->d_C_bytes = c_bytes;
     }
-    B200_CUDA_TRY(cudaMemcpyAsync(p->d_B, h_B, b_bytes, cudaMemcpyHostToDevice, nullptr));
     const b200spmm_plan::Sched &sc = p->sched;
     const size_t bands = sc.band_chunk.size() > 1 && !use_tall(p, n) ? sc.band_chunk.size() - 1 : 1;
     if (bands == 1 || p->info.eff_row_windows == 0) {
+        B200_CUDA_TRY(cudaMemcpyAsync(p->d_B, h_B, b_bytes, cudaMemcpyHostToDevice, nullptr));
         int st = b200spmm_spmm(p, p->d_B, n, n, p->d_C, n, c_dtype, nullptr);
         if (st != B200SPMM_OK) return st;
         B200_CUDA_TRY(cudaMemcpyAsync(h_C, p->d_C, c_bytes, cudaMemcpyDeviceToHost, nullptr));
@@ -1058,23 +1077,56 @@ int b200spmm_spmm_host(b200spmm_plan_t *p, const void *h_B, int64_t n, void *h_C
     }
     // Large matrix: band after band on the compute stream; as soon as a band is done its rows of C
     // leave on a second stream while the next band is computed.
+    //
+    // Every row of C needs all rows of B, so the two copies of a step cannot overlap - except by
+    // features: with the features cut in two halves, the first half of C goes out while the second
+    // half of B comes in, and the host link carries both directions at once for the middle third of
+    // the step.  Each half is a product of its own (B and C as views with the full leading dimension).
+    const size_t esz = (size_t)p->info.elt_size, csz = c_dtype == B200SPMM_C_F32 ? 4 : 2;
+    const int64_t n_first = n / 2;
+    const bool halves = p->host_split && n % 16 == 0 && (size_t)n_first * esz >= 128;
+    const int n_parts = halves ? 2 : 1;
     if (!p->copy_stream) B200_CUDA_TRY(cudaStreamCreateWithFlags(&p->copy_stream, cudaStreamNonBlocking));
-    while (p->band_done.size() < bands) {
+    if (halves && !p->upload_stream) {
+        B200_CUDA_TRY(cudaStreamCreateWithFlags(&p->upload_stream, cudaStreamNonBlocking));
+        for (cudaEvent_t &e : p->half_up) B200_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    while (p->band_done.size() < bands * (size_t)n_parts) {
         cudaEvent_t e;
         B200_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         p->band_done.push_back(e);
     }
-    const size_t row_bytes = (size_t)n * (c_dtype == B200SPMM_C_F32 ? 4 : 2);
+    const size_t b_pitch = (size_t)n * esz, c_pitch = (size_t)n * csz;
+    if (!halves) {
+        B200_CUDA_TRY(cudaMemcpyAsync(p->d_B, h_B, b_bytes, cudaMemcpyHostToDevice, nullptr));
+    } else {  // first half on the compute stream, the second one behind it on a stream of its own
+        B200_CUDA_TRY(cudaMemcpy2DAsync(p->d_B, b_pitch, h_B, b_pitch, (size_t)n_first * esz, (size_t)p->info.cols,
+                                        cudaMemcpyHostToDevice, nullptr));
+        B200_CUDA_TRY(cudaEventRecord(p->half_up[0], nullptr));
+        B200_CUDA_TRY(cudaStreamWaitEvent(p->upload_stream, p->half_up[0], 0));
+        B200_CUDA_TRY(cudaMemcpy2DAsync(static_cast<char *>(p->d_B) + (size_t)n_first * esz, b_pitch,
+                                        static_cast<const char *>(h_B) + (size_t)n_first * esz, b_pitch,
+                                        (size_t)(n - n_first) * esz, (size_t)p->info.cols, cudaMemcpyHostToDevice, p->upload_stream));
+        B200_CUDA_TRY(cudaEventRecord(p->half_up[1], p->upload_stream));
+    }
     int64_t launches = 0;
-    for (size_t k = 0; k < bands; ++k) {
-        int st = spmm_launch(p, p->d_B, n, n, p->d_C, n, c_dtype, nullptr, (int)k);
-        if (st != B200SPMM_OK) return st;
-        launches += p->last.kernel_launches;
-        B200_CUDA_TRY(cudaEventRecord(p->band_done[k], nullptr));
-        B200_CUDA_TRY(cudaStreamWaitEvent(p->copy_stream, p->band_done[k], 0));
-        const uint64_t r0 = sc.band_row[k], r1 = sc.band_row[k + 1];
-        B200_CUDA_TRY(cudaMemcpyAsync(static_cast<char *>(h_C) + r0 * row_bytes, static_cast<char *>(p->d_C) + r0 * row_bytes,
-                                      (r1 - r0) * row_bytes, cudaMemcpyDeviceToHost, p->copy_stream));
+    for (int part = 0; part < n_parts; ++part) {
+        const int64_t f0 = part == 0 ? 0 : n_first, nf = halves ? (part == 0 ? n_first : n - n_first) : n;
+        if (part == 1) B200_CUDA_TRY(cudaStreamWaitEvent(nullptr, p->half_up[1], 0));
+        const char *b_part = static_cast<const char *>(p->d_B) + (size_t)f0 * esz;
+        char *c_part = static_cast<char *>(p->d_C) + (size_t)f0 * csz;
+        for (size_t k = 0; k < bands; ++k) {
+            int st = spmm_launch(p, b_part, n, nf, c_part, n, c_dtype, nullptr, (int)k);
+            if (st != B200SPMM_OK) return st;
+            launches += p->last.kernel_launches;
+            cudaEvent_t done = p->band_done[(size_t)part * bands + k];
+            B200_CUDA_TRY(cudaEventRecord(done, nullptr));
+            B200_CUDA_TRY(cudaStreamWaitEvent(p->copy_stream, done, 0));
+            const uint64_t r0 = sc.band_row[k], r1 = sc.band_row[k + 1];
+            if (r1 == r0) continue;
+            B200_CUDA_TRY(cudaMemcpy2DAsync(static_cast<char *>(h_C) + r0 * c_pitch + (size_t)f0 * csz, c_pitch, c_part + r0 * c_pitch,
+                                            c_pitch, (size_t)nf * csz, r1 - r0, cudaMemcpyDeviceToHost, p->copy_stream));
+        }
     }
     p->last.kernel_launches = launches;
     B200_CUDA_TRY(cudaStreamSynchronize(p->copy_stream));

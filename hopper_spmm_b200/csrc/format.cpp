@@ -312,6 +312,21 @@ void build_cta_schedule(const uint32_t *rowOffset, uint64_t eff, int n_ctas, std
     (*cta_window)[n_ctas] = (uint32_t)eff;
 }
 
+void transpose_tiles(Btcf *f) {
+    const size_t rw = (size_t)f->row_window, cw = (size_t)f->col_window, esz = (size_t)f->elt_size;
+    const size_t tile_bytes = rw * cw * esz;
+    // rows x row_len elements in, row_len x rows out: row-major (rw x cw) <-> column-major (cw x rw)
+    const size_t in_rows = f->col_major_tiles ? cw : rw, in_len = f->col_major_tiles ? rw : cw;
+    std::vector<uint8_t> tmp(tile_bytes);
+    for (uint64_t t = 0; t < f->total_tiles; ++t) {
+        uint8_t *tile = f->data.data() + t * tile_bytes;
+        std::memcpy(tmp.data(), tile, tile_bytes);
+        for (size_t r = 0; r < in_rows; ++r)
+            for (size_t c = 0; c < in_len; ++c) std::memcpy(tile + (c * in_rows + r) * esz, tmp.data() + (r * in_len + c) * esz, esz);
+    }
+    f->col_major_tiles = !f->col_major_tiles;
+}
+
 void build_tile_schedule(const uint32_t *rowOffset, uint64_t eff, int n_ctas, bool allow_split, TileSchedule *out) {
     TileSchedule &sc = *out;
     const uint64_t tiles = eff ? rowOffset[eff] : 0;

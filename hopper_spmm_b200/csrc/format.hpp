@@ -26,7 +26,12 @@ struct Btcf {
     std::vector<uint32_t> tcA2B;      // [tiles*CW], padded with kIdxMax
     std::vector<uint8_t> data;        // [tiles*RW*CW*elt_size]
     std::vector<uint32_t> rowIdx;     // [eff], first row of each non-empty window
+    bool col_major_tiles = false;     // tiles stored column by column (the reference's SPARSE_A_TRANSPOSE build)
 };
+
+// Rewrites every tile from row-major to column-major storage or back (src/utils/convert.h:207-213:
+// offset = local_col * ROW_WINDOW + local_row under SPARSE_A_TRANSPOSE) and flips the flag.
+void transpose_tiles(Btcf *f);
 
 // Returns a B200SPMM_* status.
 int validate_csr(uint64_t rows, uint64_t cols, uint64_t nnz, const uint32_t *row_ptr, const uint32_t *col_idx);

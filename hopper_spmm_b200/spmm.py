@@ -74,6 +74,7 @@ class BTCF_MTX_NO_BITMAP:
         self.row_window, self.col_window = ROW_WINDOW, 0
         self.rowOffset = self.tcA2B = self.data = self.rowIdx = None
         self.dtype = None
+        self.col_major_tiles = False
 
     def _adopt(self, handle):
         lib = capi.lib()
@@ -108,6 +109,15 @@ class BTCF_MTX_NO_BITMAP:
             except Exception:  # interpreter shutdown
                 pass
             self._h = None
+
+
+def transpose_tiles(btcf: BTCF_MTX_NO_BITMAP) -> BTCF_MTX_NO_BITMAP:
+    """Rewrites the tiles of ``btcf`` in place from row-major to column-major storage or back: what the
+    reference's SPARSE_A_TRANSPOSE build stores (src/utils/convert.h:207-213).  ``btcf.col_major_tiles`` says
+    which it holds; the kernels (and SpmmPlan) take row-major tiles only."""
+    capi.check(capi.lib().b200spmm_btcf_transpose_tiles(btcf._h), "b200spmm_btcf_transpose_tiles")
+    btcf.col_major_tiles = bool(capi.lib().b200spmm_btcf_tiles_col_major(btcf._h))
+    return btcf
 
 
 def CSR2BTCFNOBITMAP(csr: CSR_MTX, btcf: BTCF_MTX_NO_BITMAP | None = None, row_window: int = ROW_WINDOW,

@@ -101,6 +101,17 @@ int b200spmm_btcf_rewindow(const b200spmm_btcf_info_t *info, const uint32_t *row
                            const void *data, const uint32_t *rowIdx, int row_window, int n_threads,
                            b200spmm_btcf_t **out);
 
+/*
+ * The reference's SPARSE_A_TRANSPOSE build stores every tile column by column (src/utils/convert.h:207-213:
+ * offset = local_col * ROW_WINDOW + local_row).  b200spmm_btcf_transpose_tiles rewrites the tiles of `f` in
+ * place from row-major to column-major or back; b200spmm_btcf_tiles_col_major says which it holds (1 / 0).
+ * Everything else in the format is the same in both builds.  The kernels read row-major tiles, so
+ * b200spmm_plan_create refuses a column-major format with B200SPMM_ERR_UNSUPPORTED (the reference's own
+ * kernel never reads the transposed tiles either: its tensor map is the row-major one, src/fp16.cu:177-219).
+ */
+int b200spmm_btcf_transpose_tiles(b200spmm_btcf_t *f);
+int b200spmm_btcf_tiles_col_major(const b200spmm_btcf_t *f);
+
 /* The reference's structs are freed by going out of scope (std::vector members). */
 void b200spmm_btcf_destroy(b200spmm_btcf_t *f);
 

@@ -292,3 +292,27 @@ def test_rewindow_to_taller_windows_equals_a_direct_conversion(dt, rw_out):
     tall = hs.rewindow(rows, cols, len(ci), f16.rowOffset, f16.tcA2B, f16.data, f16.rowIdx, row_window_in=16, row_window=rw_out)
     want = oracle.csr2btcf_nobitmap(rows, cols, rp, ci, v, rw_out, cw)
     assert same_format(tall, want) and tall.row_window == rw_out
+
+
+@pytest.mark.parametrize("dt,rw", [(np.float16, 8), (np.float16, 16), (np.float32, 8), (np.float32, 16)])
+def test_column_major_tiles_of_the_transposed_build(dt, rw):
+    # SPARSE_A_TRANSPOSE (src/utils/convert.h:207-213): the same lists and offsets, every tile stored column
+    # by column.  The library reaches it by rewriting a converted format in place; doing so twice gives the
+    # row-major format back, and a plan refuses column-major tiles whatever the device.
+    from cases import random_csr
+    import oracle
+    rows, cols, rp, ci, v = random_csr(203, 300, 0.04, 3, dt, empty_rows=[(16, 40)], dense_rows=[77])
+    cw = 16 if dt == np.float16 else 8
+    f = hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v), row_window=rw)
+    row_major = np.array(f.data).copy()
+    bits = np.uint16 if dt == np.float16 else np.uint32
+    want = oracle.csr2btcf_nobitmap(rows, cols, rp, ci, v, rw, cw, col_major_tiles=True)
+    hs.transpose_tiles(f)
+    assert f.col_major_tiles
+    assert np.array_equal(np.asarray(f.data).view(bits), np.asarray(want.data).view(bits))
+    for k in ("rowOffset", "tcA2B", "rowIdx"):
+        assert np.array_equal(getattr(f, k), getattr(want, k)), k
+    p = C.c_void_p()
+    assert capi.lib().b200spmm_plan_create(f._h, 0, 0, C.byref(p)) == capi.ERR_UNSUPPORTED
+    hs.transpose_tiles(f)
+    assert not f.col_major_tiles and np.array_equal(np.asarray(f.data).view(bits), row_major.view(bits))

@@ -233,7 +233,7 @@ def test_benchmark_configurations(name, k):
     print(name, stats)
 
 
-def test_rmat_rows_sum_to_one_at_scale():
+def test_rmat_rows_sum_to_one_at_scale(monkeypatch):
     # size-independent property: with values 1/deg(row) and B = ones, every non-empty row of C is 1
     import torch
     csr, _ = synth.make_config("rmat24_sharded_fp16", 0, "cuda", 4)  # 2^20 nodes, ~30M entries
@@ -254,7 +254,18 @@ def test_rmat_rows_sum_to_one_at_scale():
         got_c = plan.spmm_host(Bn.cpu().numpy(), c_half=c_half)
         assert plan.launch_info().kernel_launches > 2, "expected one launch per band"
         assert np.array_equal(got_c.view(np.uint16 if c_half else np.uint32), want_c.view(np.uint16 if c_half else np.uint32))
+    # That call also cuts the features in two halves (the first half of C leaves while the second half of B
+    # arrives): twice the launches of the call with the halves switched off, the same bits.
+    split_launches = plan.launch_info().kernel_launches
     plan.close()
+    monkeypatch.setenv("B200SPMM_HOST_SPLIT", "0")
+    plan = hs.SpmmPlan(f)
+    try:
+        got_c = plan.spmm_host(Bn.cpu().numpy(), c_half=True)
+        assert plan.launch_info().kernel_launches * 2 == split_launches
+        assert np.array_equal(got_c.view(np.uint16), want_c.view(np.uint16))
+    finally:
+        plan.close()
 
 
 def test_bitmap_format_feeds_the_spmm_after_expansion():
