@@ -72,6 +72,9 @@ struct b200spmm_plan {
     std::vector<cudaEvent_t> band_done;
     const Sched *launch_sched = nullptr;  // the one the next launch uses
     CompressedTiles comp;                 // the tiles as bitmap + stored values (empty: dense tiles only)
+    // fp16 tiles as records of 32 (position, value) words (SpmmParams::tile_entries), or null: B200SPMM_TILES=entries
+    uint32_t *d_tile_entries = nullptr;
+    uint64_t entry_dense_tiles = 0;       // tiles with more than 32 entries, which stay dense
     // The same matrix in 128-row super-windows, built when merging eight windows shortens the tile
     // stream enough for the wide-MMA kernel (spmm_tall_kernel.cuh) to win; empty otherwise.
     TallFormat tall;
@@ -122,14 +125,58 @@ __global__ void swizzle_tiles_kernel(const uint4 *__restrict__ src, uint4 *__res
     }
 }
 
+// One warp per fp16 tile of the reference's layout (16 rows x 16 columns, row-major): the tile's record of 32
+// words.  Lane l looks at row l / 2, columns 8 (l % 2) .. +7; a stored entry is any value whose bits are not
+// zero; its word is (byte offset in the tile's shared-memory image << 16) | bits, where the image swaps the
+// two 16-byte halves of a row when row / 4 is odd (the 32-byte swizzle).
+__global__ void __launch_bounds__(256)
+tile_entries_kernel(const uint16_t *__restrict__ data, uint64_t tiles, uint32_t *__restrict__ records,
+                    unsigned long long *__restrict__ n_dense) {
+    const uint32_t lane = threadIdx.x & 31u;
+    for (uint64_t t = (uint64_t)blockIdx.x * 8u + (threadIdx.x >> 5); t < tiles; t += (uint64_t)gridDim.x * 8u) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(data + t * 256u + lane * 8u);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t mask = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mask |= (((w[k >> 1] >> ((k & 1) * 16)) & 0xFFFFu) != 0u) ? (1u << k) : 0u;
+        const uint32_t mine = (uint32_t)__popc(mask);
+        uint32_t before = mine;  // inclusive warp scan
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xffffffffu, before, d);
+            if ((int)lane >= d) before += up;
+        }
+        const uint32_t total = __shfl_sync(0xffffffffu, before, 31);
+        before -= mine;
+        uint32_t *rec = records + (t << 5);
+        if (total > 32u) {
+            rec[lane] = b200spmm::kDenseTile;
+            if (lane == 0) atomicAdd(n_dense, 1ull);
+            continue;
+        }
+        rec[lane] = b200spmm::kNoEntry;
+        __syncwarp();
+        const uint32_t row = lane >> 1, half = lane & 1u;
+        const uint32_t base = row * 32u + ((half ^ ((row >> 2) & 1u)) << 4);
+        uint32_t k_out = before;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (mask & (1u << k)) {
+                const uint32_t bits = (w[k >> 1] >> ((k & 1) * 16)) & 0xFFFFu;
+                rec[k_out++] = ((base + (uint32_t)k * 2u) << 16) | bits;
+            }
+        }
+    }
+}
+
 }  // namespace tileimage
 
 namespace {
 
-template <bool kTf32, int kNs, bool kTma, bool kBitmap>
+template <bool kTf32, int kNs, bool kTma, int kTiles>
 int launch_one(b200spmm_plan *p, const SpmmParams &prm, const CUtensorMap &tmap_b, cudaStream_t stream) {
-    using Cfg = SpmmCfg<kTf32, kNs, kTma, kBitmap>;
-    auto kernel = spmm_sm100_kernel<kTf32, kNs, kTma, kBitmap>;
+    using Cfg = SpmmCfg<kTf32, kNs, kTma, kTiles>;
+    auto kernel = spmm_sm100_kernel<kTf32, kNs, kTma, kTiles>;
     static thread_local int configured_device = -1;
     if (configured_device != p->device) {
         B200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::kSmemBytes));
@@ -147,7 +194,7 @@ int launch_one(b200spmm_plan *p, const SpmmParams &prm, const CUtensorMap &tmap_
     p->last.smem_bytes = (int64_t)Cfg::kSmemBytes;
     p->last.kernel_launches = 1;
     p->last.tma_gather = kTma ? 1 : 0;
-    p->last.bitmap_tiles = kBitmap ? 1 : 0;
+    p->last.bitmap_tiles = kTiles;
     p->last.row_window = kRowWindow;
     return B200SPMM_OK;
 }
@@ -161,13 +208,13 @@ constexpr uint32_t kRowBands = 8;  // bands of the host-buffer call (large matri
 inline uint32_t slab_for(uint32_t n) { return std::min(128u, (n + 63u) / 64u * 64u); }
 constexpr int kCtasPerSm = 2;  // every kernel variant in use is sized for two resident CTAs per SM
 
-template <bool kTf32, bool kTma, bool kBitmap>
+template <bool kTf32, bool kTma, int kTiles>
 int launch_slab(b200spmm_plan *p, SpmmParams &prm, const CUtensorMap &tmap_b, cudaStream_t stream) {
     const uint32_t ns = slab_for(prm.n);
     prm.n_slabs = (prm.n + ns - 1) / ns;
     switch (ns) {
-        case 64: return launch_one<kTf32, 64, kTma, kBitmap>(p, prm, tmap_b, stream);
-        default: return launch_one<kTf32, 128, kTma, kBitmap>(p, prm, tmap_b, stream);
+        case 64: return launch_one<kTf32, 64, kTma, kTiles>(p, prm, tmap_b, stream);
+        default: return launch_one<kTf32, 128, kTma, kTiles>(p, prm, tmap_b, stream);
     }
 }
 
@@ -210,7 +257,7 @@ int b_tensor_map(b200spmm_plan *p, const void *B, int64_t ldb, uint32_t n, uint3
 template <bool kTf32>
 int launch_dtype(b200spmm_plan *p, SpmmParams &prm, cudaStream_t stream) {
     constexpr uint32_t esz = kTf32 ? 4 : 2, box = 128 / esz;
-    if (p->gather_cpasync || prm.n < box) return launch_slab<kTf32, false, false>(p, prm, p->tmap_b, stream);
+    if (p->gather_cpasync || prm.n < box) return launch_slab<kTf32, false, 0>(p, prm, p->tmap_b, stream);
     {
         int st = b_tensor_map(p, prm.B, prm.ldb, prm.n, prm.cols, kTf32);
         if (st != B200SPMM_OK) return st;
@@ -220,9 +267,15 @@ int launch_dtype(b200spmm_plan *p, SpmmParams &prm, cudaStream_t stream) {
         prm.tcBit = p->comp.tcBit;
         prm.nnzOffset = p->comp.nnzOffset;
         prm.values = p->comp.values;
-        return launch_slab<kTf32, true, true>(p, prm, tmap_b, stream);
+        return launch_slab<kTf32, true, 1>(p, prm, tmap_b, stream);
     }
-    return launch_slab<kTf32, true, false>(p, prm, tmap_b, stream);
+    if constexpr (!kTf32) {
+        if (p->d_tile_entries && prm.tiles_image) {  // stream the entry lists; tiles with many entries come from the image
+            prm.tile_entries = p->d_tile_entries;
+            return launch_slab<false, true, 2>(p, prm, tmap_b, stream);
+        }
+    }
+    return launch_slab<kTf32, true, 0>(p, prm, tmap_b, stream);
 }
 
 // Tensor map over `data` seen as rows of 32 bytes: one tile is 16 consecutive rows, one box is
@@ -533,6 +586,23 @@ int plan_finish(b200spmm_plan *p, const uint32_t *h_rowOffset, const uint32_t *h
         int st = compress_tiles_device(p->d_data, info.total_tiles, info.dtype, &p->comp);
         if (st != B200SPMM_OK) return st;
     }
+    // B200SPMM_TILES=entries (fp16): the kernels stream the tiles as records of 32 (position, value) words - a
+    // quarter of the dense bytes - which a producer warp expands with two stores per lane; tiles with more than
+    // 32 entries still come from the dense image.  Same C bit for bit.
+    if (info.total_tiles && info.dtype == B200SPMM_F16 && env_is("B200SPMM_TILES", "entries")) {
+        B200_CUDA_TRY(cudaMalloc(&p->d_tile_entries, info.total_tiles * 128));
+        unsigned long long *d_count = nullptr;
+        B200_CUDA_TRY(cudaMalloc(&d_count, 8));
+        B200_CUDA_TRY(cudaMemset(d_count, 0, 8));
+        const int grid = (int)std::min<uint64_t>((info.total_tiles + 7) / 8, (uint64_t)p->n_sms * 32);
+        tileimage::tile_entries_kernel<<<grid, 256>>>(static_cast<const uint16_t *>(p->d_data), info.total_tiles, p->d_tile_entries, d_count);
+        cudaError_t e = cudaGetLastError();
+        unsigned long long n_dense = 0;
+        if (e == cudaSuccess) e = cudaMemcpy(&n_dense, d_count, 8, cudaMemcpyDeviceToHost);
+        cudaFree(d_count);
+        B200_CUDA_TRY(e);
+        p->entry_dense_tiles = n_dense;
+    }
     if (n_ctas <= 0 && !p->comp.tcBit) {  // an explicit CTA count or compressed tiles ask for the 16-row kernel
         int st = plan_build_tall(p, h_rowOffset, h_rowIdx);
         if (st != B200SPMM_OK) return st;
@@ -762,6 +832,7 @@ void b200spmm_plan_destroy(b200spmm_plan_t *p) {
         cudaFree(ps.d_piece_slots);
     }
     free_compressed_tiles(&p->comp);
+    cudaFree(p->d_tile_entries);
     free_tall(&p->tall);
     free_tall(&p->pair);
     cudaFree(p->d_b_packed);

@@ -152,6 +152,9 @@ B200_DEVICE void tma_gather4_2d(uint32_t dst, const void *tmap, int32_t x, int32
 B200_DEVICE void st_shared_v4(uint32_t addr, uint4 v) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
+B200_DEVICE void st_shared_u16(uint32_t addr, uint16_t v) {
+    asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(v) : "memory");
+}
 
 // ------------------------------------------------------------------ cp.async (16-byte gathers)
 

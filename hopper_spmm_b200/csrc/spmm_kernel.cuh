@@ -106,6 +106,11 @@ struct SpmmParams {
     const uint64_t *tcBit;       // [tiles * 16*CW/64] one bit per tile slot, row-major, low bit first
     const uint32_t *nnzOffset;   // [tiles+1] first stored value of each tile
     const void *values;          // stored values, tile after tile, row-major inside a tile
+    // entry-list kernels only (fp16): per tile a record of 32 words, one per lane of a producer warp -
+    // (byte offset inside the tile's shared-memory image << 16) | value bits for a stored entry, kNoEntry for an
+    // unused word, kDenseTile in all 32 words of a tile with more than 32 entries (that tile comes from
+    // tiles_image by a bulk copy).  The expansion is a zero fill and one 2-byte store per lane.
+    const uint32_t *tile_entries;
     const void *B;               // [cols, n] row-major
     void *C;                     // [rows, n] row-major
     int64_t ldb, ldc;            // elements
@@ -126,11 +131,16 @@ struct SpmmParams {
 // kTma selects how the rows of B reach shared memory: true = TMA tile::gather4 (four rows per
 // instruction, issued by a few lanes, completion counted in bytes on the stage's mbarrier);
 // false = 16-byte cp.async copies by all lanes of the producer warps.
-// kBitmap: the sparse tiles come compressed (bitmap + stored values) and the producer warps expand
-// them into the ring, instead of TMA copying 512 dense bytes per tile.
-template <bool kTf32, int kNs, bool kTma = true, bool kBitmap = false>
+// kTiles: 0 = dense tiles (512 bytes each, by TMA / bulk copy); 1 = the tiles come compressed as bitmap +
+// stored values (the reference's bitmap format) and the producer warps expand them into the ring; 2 = the
+// tiles come as records of 32 (position, value) words (SpmmParams::tile_entries), a quarter of the dense
+// bytes, which a producer warp expands with two stores per lane.
+constexpr uint32_t kNoEntry = 0xFFFF0000u, kDenseTile = 0xFFFFFFFEu;
+template <bool kTf32, int kNs, bool kTma = true, int kTiles = 0>
 struct SpmmCfg {
-    static_assert(kTma || !kBitmap, "compressed tiles go with the TMA gather");
+    static constexpr bool kBitmap = kTiles == 1, kEntries = kTiles == 2;
+    static_assert(kTma || kTiles == 0, "compressed tiles go with the TMA gather");
+    static_assert(!kEntries || !kTf32, "entry lists hold 16-bit values");
     static_assert(kNs == 64 || kNs == 128 || kNs == 192 || kNs == 256, "feature slab");  // in use: 64 and 128
     // One thread issues a CTA's MMAs, and with 16-row windows every MMA is small: the issuing
     // thread, not the tensor core, sets the pace.  Up to 128 features a CTA is small enough for
@@ -184,11 +194,12 @@ struct SpmmCfg {
         1024 + (size_t)kStages * kStageBytes + kIdxBytes + kBarrierBytes + kWinBytes + kChunkBytes;
 };
 
-template <bool kTf32, int kNs, bool kTma, bool kBitmap>
-__global__ void __launch_bounds__((SpmmCfg<kTf32, kNs, kTma, kBitmap>::kThreads), (SpmmCfg<kTf32, kNs, kTma, kBitmap>::kCtasPerSm))
+template <bool kTf32, int kNs, bool kTma, int kTiles>
+__global__ void __launch_bounds__((SpmmCfg<kTf32, kNs, kTma, kTiles>::kThreads), (SpmmCfg<kTf32, kNs, kTma, kTiles>::kCtasPerSm))
 spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const SpmmParams p) {
-    using Cfg = SpmmCfg<kTf32, kNs, kTma, kBitmap>;
+    using Cfg = SpmmCfg<kTf32, kNs, kTma, kTiles>;
+    constexpr bool kBitmap = Cfg::kBitmap, kEntries = Cfg::kEntries;
     constexpr int kStages = Cfg::kStages;
     constexpr int kTps = Cfg::kTilesPerStage;
     constexpr int kProducerGroups = Cfg::kProducerGroups;
@@ -281,7 +292,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         chunk_list[0] = p.chunk_begin + blockIdx.x < p.chunk_end ? p.chunk_begin + blockIdx.x : kNoChunk;
         *chunk_avail = 1;
         ptx::fence_mbar_init();
-        if (!kBitmap) ptx::prefetch_tensormap(&tmap_a);
+        if (kTiles == 0) ptx::prefetch_tensormap(&tmap_a);
         if (kTma) ptx::prefetch_tensormap(&tmap_b);
     }
     if (warp == kMmaWarp) {
@@ -636,6 +647,23 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // where the lane's piece goes: K-major rows of 32 bytes, 16-byte halves swapped in rows 4-7 and 12-15
         const uint32_t piece_off = ((uint32_t)lane >> 1) * 32u + ((((uint32_t)lane & 1u) ^ (((uint32_t)lane >> 3) & 1u)) << 4);
         prefetch_values();
+        // Entry lists: lane l holds word l of the record of each of the warp's two tiles of the NEXT iteration
+        // (loaded right after the current tiles were expanded and fenced, like the stored values above).
+        uint32_t my_ent[kTpw] = {};
+        Cursor ec = cur;
+        auto prefetch_entries = [&]() {
+            if (!kEntries) return;
+            const uint32_t tpos0 = ec.sp * kTps + pw * kTpw;
+            const uint32_t here = (!ec.done && tpos0 < ec.n_tiles) ? min(kTpw, ec.n_tiles - tpos0) : 0u;
+#pragma unroll
+            for (uint32_t j = 0; j < kTpw; ++j)
+                my_ent[j] = (j < here && !(B200_DEBUG_BITS(p) & 8u)) ? __ldg(p.tile_entries + ((uint64_t)(ec.tile_begin + tpos0 + j) << 5) + lane) : kNoEntry;
+            if (!ec.done) {
+                ec.sp += kProducerGroups;
+                normalise(ec);
+            }
+        };
+        prefetch_entries();
 
         const uint32_t n_bytes = p.n * Cfg::kEsz;
         uint32_t issued = 0;  // cp.async path: stages whose copies were issued and not yet reported
@@ -657,7 +685,7 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     ok = ptx::mbar_wait(empty_bar(s), (use & 1u) ^ 1u, abort_flag, limit) ? 1u : 0u;
                     B200_PROF_ADD(prof_wait_empty);
                 }
-                if (ok && !kBitmap) {
+                if (ok && kTiles == 0) {
                     const bool a_tiles = pw == 0 && !(B200_DEBUG_BITS(p) & 4u);
                     // the stage's eight A tiles (tiles past the chunk's end are fetched too, as long as the
                     // array holds them: they are never multiplied)
@@ -714,6 +742,39 @@ spmm_sm100_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                                         (int32_t)(slab * kNs + op_x),
                                         (int32_t)min(rows4.x, p.cols), (int32_t)min(rows4.y, p.cols),
                                         (int32_t)min(rows4.z, p.cols), (int32_t)min(rows4.w, p.cols), full_bar(s));
+                }
+                if (kEntries) {  // after the gathers were issued: the expansion runs while they are in flight (their bytes may
+                                 // be counted before this warp announces them: the phase cannot end before its arrival)
+                    // expand this warp's tiles: zeros, then every lane drops its entry at its place; a tile with more
+                    // than 32 entries comes whole from the tile image instead (async proxy: no zero fill for it)
+                    uint32_t n_dense = 0;
+                    if (here && !(B200_DEBUG_BITS(p) & 4u)) {
+#pragma unroll
+                        for (uint32_t j = 0; j < kTpw; ++j)
+                            if (j < here && my_ent[j] != kDenseTile)
+                                ptx::st_shared_v4(atile_addr + (first_slot + j) * kATileBytes + (uint32_t)lane * 16u, make_uint4(0, 0, 0, 0));
+                        __syncwarp();
+#pragma unroll
+                        for (uint32_t j = 0; j < kTpw; ++j) {
+                            if (j < here) {
+                                const uint32_t e = my_ent[j];
+                                if (e == kDenseTile) ++n_dense;
+                                else if ((e >> 16) != 0xFFFFu)
+                                    ptx::st_shared_u16(atile_addr + (first_slot + j) * kATileBytes + (e >> 16), (uint16_t)e);
+                            }
+                        }
+                        ptx::fence_proxy_async_smem();
+                    }
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::mbar_arrive_expect_tx(full_bar(s), gather_here * Cfg::kGatherBytes + n_dense * kATileBytes);
+#pragma unroll
+                        for (uint32_t j = 0; j < kTpw; ++j)
+                            if (j < here && my_ent[j] == kDenseTile && !(B200_DEBUG_BITS(p) & 4u))
+                                ptx::bulk_load(atile_addr + (first_slot + j) * kATileBytes,
+                                               p.tiles_image + (uint64_t)(tile_begin + tpos0 + j) * kATileBytes, kATileBytes, full_bar(s));
+                    }
+                    prefetch_entries();
                 }
                 fetch_list();
                 ptx::cp_async_commit();

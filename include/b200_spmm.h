@@ -442,7 +442,8 @@ typedef struct {
     int64_t smem_bytes;
     int64_t kernel_launches; /* launches issued by that call */
     int32_t tma_gather;      /* 1: rows of B fetched by TMA tile::gather4, 0: by cp.async copies */
-    int32_t bitmap_tiles;    /* 1: tiles streamed as bitmap + stored values and expanded in the kernel, 0: dense tiles */
+    int32_t bitmap_tiles;    /* 0: dense tiles; 1: tiles streamed as bitmap + stored values and expanded in the kernel;
+                                2: tiles streamed as records of 32 (position, value) words (B200SPMM_TILES=entries) */
     int32_t row_window;      /* rows per window the launched kernel consumed: 16, or 128 (super-windows) */
 } b200spmm_launch_info_t;
 int b200spmm_plan_launch_info(const b200spmm_plan_t *p, b200spmm_launch_info_t *info);

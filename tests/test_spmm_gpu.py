@@ -155,7 +155,8 @@ def test_more_ctas_than_windows_and_one_cta():
 def test_compressed_tiles_give_the_same_bits_as_dense_tiles(dt, n, monkeypatch):
     # bitmap + stored values expanded by the producer warps (the shape of the reference's BTCF_MTX,
     # src/utils/class.h:55-67) against the dense 512-byte tiles; explicit zeros, -0.0, a full tile
-    rows, cols, rp, ci, v = random_csr(331, 4000, 0.01, 33, dt, empty_rows=[(32, 80)], dense_rows=[5, 300])
+    # ... and a window whose tiles are all full, rows with 2-3 entries per tile on average
+    rows, cols, rp, ci, v = random_csr(331, 4000, 0.01, 33, dt, empty_rows=[(32, 80)], dense_rows=[5, 300] + list(range(160, 176)))
     v = v.copy()
     v[::7] = 0
     v[3::11] = -0.0
@@ -169,6 +170,12 @@ def test_compressed_tiles_give_the_same_bits_as_dense_tiles(dt, n, monkeypatch):
     assert info_d.bitmap_tiles == 0 and info_b.bitmap_tiles == 1
     assert np.array_equal(dense.view(np.uint32), packed.view(np.uint32))
     parity.check(packed, rows, rp, ci, v, B)
+    # the tiles as records of 32 (position, value) words, expanded by a zero fill and one store per lane; tiles
+    # with more than 32 entries still arrive dense (fp16 matrices only: a tf32 plan keeps its dense tiles)
+    monkeypatch.setenv("B200SPMM_TILES", "entries")
+    listed, info_e = run_host(rows, cols, rp, ci, v, B, n_ctas=296)
+    assert info_e.bitmap_tiles == (2 if dt == np.float16 else 0)
+    assert np.array_equal(dense.view(np.uint32), listed.view(np.uint32))
 
 
 def test_fp16_output():
