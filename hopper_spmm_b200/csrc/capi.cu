@@ -446,8 +446,8 @@ int launch_tall(b200spmm_plan *p, const void *d_B, int64_t ldb, int64_t n, void 
     prm.wait_limit_ns = p->wait_limit_ns;
 #ifdef B200SPMM_PROFILE
     if (const char *dbg = std::getenv("B200SPMM_DEBUG")) prm.debug = (uint32_t)std::atoi(dbg);  // results invalid
-    if (!g_prof) cudaMalloc(&g_prof, 1024 * 24 * 8);
-    cudaMemsetAsync(g_prof, 0, 1024 * 24 * 8, stream);
+    if (!g_prof) cudaMalloc(&g_prof, 1024 * 32 * 8);
+    cudaMemsetAsync(g_prof, 0, 1024 * 32 * 8, stream);
     prm.prof = g_prof;
 #endif
     if (pair) return tf32 ? launch_pair_one<true>(p, prm, stream) : launch_pair_one<false>(p, prm, stream);
@@ -677,7 +677,7 @@ using namespace noalloc;
 
 #ifdef B200SPMM_PROFILE
 extern "C" int b200spmm_debug_read_profile(unsigned long long *out, int n_ctas) {
-    return cudaMemcpy(out, g_prof, (size_t)n_ctas * 24 * 8, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -5;
+    return cudaMemcpy(out, g_prof, (size_t)n_ctas * 32 * 8, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -5;
 }
 #endif
 
@@ -1066,8 +1066,8 @@ int spmm_launch(b200spmm_plan_t *p, const void *d_B, int64_t ldb, int64_t n, voi
     prm.status = p->d_status;
     prm.wait_limit_ns = p->wait_limit_ns;
 #ifdef B200SPMM_PROFILE
-    if (!g_prof) cudaMalloc(&g_prof, 1024 * 24 * 8);
-    cudaMemsetAsync(g_prof, 0, 1024 * 24 * 8, stream);
+    if (!g_prof) cudaMalloc(&g_prof, 1024 * 32 * 8);
+    cudaMemsetAsync(g_prof, 0, 1024 * 32 * 8, stream);
     prm.prof = g_prof;
     if (const char *dbg = std::getenv("B200SPMM_DEBUG")) prm.debug = (uint32_t)std::atoi(dbg);  // results invalid
 #endif

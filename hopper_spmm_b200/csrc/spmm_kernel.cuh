@@ -56,7 +56,7 @@
 #define B200_PROF_DECL(name) long long name = 0
 #define B200_PROF_T0() const long long prof_t0__ = clock64()
 #define B200_PROF_ADD(name) name += clock64() - prof_t0__
-#define B200_PROF_STORE(slot, value) p.prof[(size_t)blockIdx.x * 24 + (slot)] = (unsigned long long)(value)
+#define B200_PROF_STORE(slot, value) p.prof[(size_t)blockIdx.x * 32 + (slot)] = (unsigned long long)(value)
 #define B200_DEBUG_BITS(p) ((p).debug)
 #else
 #define B200_PROF_DECL(name)
@@ -124,7 +124,7 @@ struct SpmmParams {
     // measurement builds only: bit 0 skips the B gathers, bit 1 the MMAs, bit 2 the A tiles, bit 3 the
     // loads of a compressed tile's stored values (results are then invalid)
     uint32_t debug;
-    unsigned long long *prof;    // [gridDim.x][24] cycle counters
+    unsigned long long *prof;    // [gridDim.x][32] cycle counters
 #endif
 };
 

@@ -63,7 +63,7 @@ struct TallParams {
     unsigned long long wait_limit_ns;
 #ifdef B200SPMM_PROFILE
     uint32_t debug;  // measurement builds only: bit 0 skips the B gathers, bit 1 the MMAs, bit 2 the A tiles
-    unsigned long long *prof;  // [gridDim.x][24] cycle counters
+    unsigned long long *prof;  // [gridDim.x][32] cycle counters
 #endif
 };
 
