@@ -391,7 +391,7 @@ bool use_pair(const b200spmm_plan *p, int64_t n) {
 // 128-byte box wide), and - unless forced - only when there are enough (window, slab) items to
 // occupy every SM.
 bool use_tall(const b200spmm_plan *p, int64_t n) {
-    if (!p->tall.tiles || p->gather_cpasync || p->starve_gathers) return false;
+    if (!p->tall.tiles || p->gather_cpasync) return false;
     if (n * p->info.elt_size < 128) return false;
     if (p->tall_forced) return true;
     const int64_t slab = n <= 128 ? 128 : 256;
@@ -444,6 +444,7 @@ int launch_tall(b200spmm_plan *p, const void *d_B, int64_t ldb, int64_t n, void 
     prm.c_is_half = c_dtype == B200SPMM_C_F16;
     prm.status = p->d_status;
     prm.wait_limit_ns = p->wait_limit_ns;
+    prm.starve_bytes = p->starve_gathers ? 16u : 0u;
 #ifdef B200SPMM_PROFILE
     if (const char *dbg = std::getenv("B200SPMM_DEBUG")) prm.debug = (uint32_t)std::atoi(dbg);  // results invalid
     if (!g_prof) cudaMalloc(&g_prof, 1024 * 32 * 8);

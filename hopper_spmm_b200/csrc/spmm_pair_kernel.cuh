@@ -329,7 +329,7 @@ spmm_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_consta
                     const uint32_t gather_bytes = (B200_DEBUG_BITS(p) & 1u) ? 0u : (uint32_t)Cfg::kGatherBytes;
                     const uint32_t tile_bytes = (B200_DEBUG_BITS(p) & 4u) ? 0u : (uint32_t)kTallTileBytes;
                     B200_PROF_T0();
-                    ptx::mbar_arrive_expect_tx(full_bar(s), here * (gather_bytes + tile_bytes));
+                    ptx::mbar_arrive_expect_tx(full_bar(s), here * (gather_bytes + tile_bytes) + p.starve_bytes);
                     // this CTA's halves of the stage's tiles are neighbours in memory and in the ring: one copy
                     if (tile_bytes)
                         ptx::bulk_load(atile_addr + s * kTps * kTallTileBytes,

@@ -61,6 +61,8 @@ struct TallParams {
     uint32_t c_is_half;
     uint32_t *status;
     unsigned long long wait_limit_ns;
+    uint32_t starve_bytes;      // known-answer launches only: bytes every stage expects on top of what its loads deliver,
+                                // so that no stage ever fills and the bounded waits run out (0 in a product)
 #ifdef B200SPMM_PROFILE
     uint32_t debug;  // measurement builds only: bit 0 skips the B gathers, bit 1 the MMAs, bit 2 the A tiles
     unsigned long long *prof;  // [gridDim.x][32] cycle counters
@@ -354,7 +356,7 @@ spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_consta
                 if (ok) {
                     const uint32_t gather_bytes = (B200_DEBUG_BITS(p) & 1u) ? 0u : (uint32_t)Cfg::kGatherBytes;
                     const uint32_t tile_bytes = (B200_DEBUG_BITS(p) & 4u) ? 0u : (uint32_t)kTallTileBytes;
-                    ptx::mbar_arrive_expect_tx(full_bar(s), here * (gather_bytes + tile_bytes));
+                    ptx::mbar_arrive_expect_tx(full_bar(s), here * (gather_bytes + tile_bytes) + p.starve_bytes);
                     // the stage's tiles of A are neighbours in memory and in the ring: one copy
                     if (tile_bytes)
                         ptx::bulk_load(atile_addr + s * kTps * kTallTileBytes,

@@ -65,7 +65,9 @@ unsigned long long b200spmm_kat_wait_limit(unsigned long long limit_ns);
  * tensor memory is released - and b200spmm_plan_sync must then report B200SPMM_ERR_DEVICE_TIMEOUT
  * and leave the plan ready for a normal launch.  C receives nothing meaningful.  This is the bounded
  * replacement of the reference's endless waits (src/ptx/barrier.h:29-41, 72-86) under test; fp32 C,
- * n at least one 128-byte box wide.  The plan type is declared in b200_spmm.h.
+ * n at least one 128-byte box wide.  A plan that would run one of its super-window kernels for this n runs that
+ * one, every stage expecting sixteen bytes more than its loads deliver, and must unwind the same way (both
+ * CTAs of a pair included).  The plan type is declared in b200_spmm.h.
  */
 struct b200spmm_plan;
 int b200spmm_kat_spmm_starved(struct b200spmm_plan *plan, const void *d_B, int64_t ldb, int64_t n, void *d_C,

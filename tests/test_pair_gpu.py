@@ -122,3 +122,33 @@ def test_dense_windows_take_packed_rows_of_b(dt, pair):
         parity.check(dC.cpu().numpy(), rows, rp, ci, v, Bv.cpu().numpy())
     finally:
         plan.close()
+
+
+@pytest.mark.parametrize("dt", [np.float16, np.float32])
+def test_starved_pipeline_times_out_and_the_plan_recovers(dt, pair):
+    # A failure made on the host: every stage expects sixteen bytes more than its loads deliver, so no stage
+    # ever fills.  With waits limited to 5 ms every role of the kernel has to leave its loop by itself, tensor
+    # memory is released, the status says so, and the next launch of the same plan is a normal, correct product.
+    import time
+    import torch
+    from hopper_spmm_b200 import _capi as capi
+    rows, cols, rp, ci, v = random_csr(1100, 517, 0.03, 11, dt, empty_rows=[(256, 512)], dense_rows=[140])
+    n = 320
+    B = torch.from_numpy(dense_b(cols, n, 3, dt)).cuda()
+    plan = hs.SpmmPlan(hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v)))
+    try:
+        dC = torch.zeros((rows, n), device="cuda")
+        s = torch.cuda.current_stream().cuda_stream
+        lib = capi.lib()
+        assert lib.b200spmm_kat_spmm_starved(plan._p, B.data_ptr(), n, n, dC.data_ptr(), n, 5_000_000, s) == 0
+        assert plan.launch_info().row_window == 256
+        t0 = time.perf_counter()
+        assert lib.b200spmm_plan_sync(plan._p, s) == capi.ERR_DEVICE_TIMEOUT
+        assert time.perf_counter() - t0 < 5.0
+        for _ in range(2):  # tensor memory was released and the hand-out counters are back at zero
+            dC = torch.full((rows, n), float("nan"), device="cuda")
+            plan.spmm(B, dC)
+            assert plan.launch_info().row_window == 256
+            parity.check(dC.cpu().numpy(), rows, rp, ci, v, B.cpu().numpy())
+    finally:
+        plan.close()
