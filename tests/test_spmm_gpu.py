@@ -327,3 +327,29 @@ def test_command_line_run_on_a_matrix_market_file(kind, tmp_path):
     assert out.returncode == 0, out.stdout + out.stderr
     assert "nonzeros: %d" % len(ci) in out.stdout and "SPMM mean time" in out.stdout and "(ok," in out.stdout
     assert ("8-row format:" in out.stdout) == kind.endswith("rw8") and "tiles (16x" in out.stdout
+
+
+@pytest.mark.parametrize("window", ["16", "128", "256"])
+def test_tf32_product_against_the_oracle_on_truncated_inputs(window, monkeypatch):
+    # The 5e-3 bound of the tf32 configuration has to absorb the rounding of the inputs to tf32.  Against an
+    # oracle that sees the inputs as the tensor core does (low 13 mantissa bits dropped; the reference's
+    # in-shared-memory conversion is a no-op, src/ptx/ptx_utils.h:32-36) only the order of the fp32 additions
+    # differs: the result must agree to 1e-5 of the magnitude sum, for all three kernels.
+    import torch
+    import oracle
+    monkeypatch.setenv("B200SPMM_WINDOW", window)
+    rows, cols, rp, ci, v = random_csr(1100, 900, 0.03, 19, np.float32, empty_rows=[(256, 512)], dense_rows=[140, 700])
+    B = dense_b(cols, 320, 5, np.float32)
+    plan = hs.SpmmPlan(hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v)))
+    try:
+        got = plan.spmm(torch.from_numpy(B).cuda()).cpu().numpy()
+        assert plan.launch_info().row_window == int(window)
+    finally:
+        plan.close()
+    seen = oracle.spmm_csr(rows, rp, ci, v, B, tf32_mode=1)
+    mag = oracle.spmm_csr(rows, rp, ci, np.abs(v), np.abs(B))
+    live = mag > 0
+    tight = float((np.abs(got - seen)[live] / mag[live]).max())
+    loose = float((np.abs(got - oracle.spmm_csr(rows, rp, ci, v, B))[live] / mag[live]).max())
+    print(f"window {window}: error relative to the magnitude sum {tight:.2e} against truncated inputs, {loose:.2e} against fp32 inputs")
+    assert tight < 1e-5 < loose < 5e-3
