@@ -412,8 +412,10 @@ int launch_tall(b200spmm_plan *p, const void *d_B, int64_t ldb, int64_t n, void 
     prm.data = static_cast<const uint8_t *>(fmt.d_data);
     if (p->tall_pack_b) {
         const uint32_t cw = (uint32_t)p->info.col_window, esz = (uint32_t)p->info.elt_size;
-        // the pair kernel's CTAs fetch 128-feature halves of a 256-feature slab
-        const uint32_t slab = (n <= 128 || pair) ? 128u : 256u, n_slabs = (uint32_t)((n + slab - 1) / slab);
+        // the pair kernel's CTAs fetch 128-feature halves of a 256-feature slab: both halves of the last slab must
+        // exist in the packed copy (as zeros past n), so an even number of 128-feature blocks
+        const uint32_t slab = (n <= 128 || pair) ? 128u : 256u;
+        const uint32_t n_slabs = pair ? 2u * (uint32_t)((n + 255) / 256) : (uint32_t)((n + slab - 1) / slab);
         const uint32_t groups = (uint32_t)((p->info.cols + cw - 1) / cw);
         const size_t need = (size_t)n_slabs * groups * 32u * slab;
         if (need > p->b_packed_bytes) {

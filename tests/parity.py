@@ -29,7 +29,8 @@ def check(got, rows, rp, ci, v, B, tf32_mode=1, threads=0):
     assert scaled <= tol, f"error relative to the magnitude sum {scaled:.3e} > {tol}"
     tight = ref if B.dtype == np.float16 else oracle.spmm_csr(rows, rp, ci, v, B, n_threads=threads, tf32_mode=tf32_mode)
     bad, max_rel, max_abs = oracle.compare(got, tight, tol)
-    assert bad <= 1e-3 * got.size, f"{bad} of {got.size} elements fail the reference's rule (max rel {max_rel:.3e})"
+    # (a result of fewer than a thousand elements may hold one such element)
+    assert bad <= max(1.0, 1e-3 * got.size), f"{bad} of {got.size} elements fail the reference's rule (max rel {max_rel:.3e})"
     return {"scaled_err": scaled, "rule_failures": bad, "max_rel": max_rel, "max_abs": max_abs}
 
 
