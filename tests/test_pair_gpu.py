@@ -152,3 +152,45 @@ def test_starved_pipeline_times_out_and_the_plan_recovers(dt, pair):
             parity.check(dC.cpu().numpy(), rows, rp, ci, v, B.cpu().numpy())
     finally:
         plan.close()
+
+
+@pytest.mark.parametrize("window", ["128", "256"])
+def test_random_shapes_against_the_oracle(window, monkeypatch):
+    # twenty seeded shapes per kernel: ragged row and column counts, empty stretches, full rows, feature counts
+    # that leave the last slab (and, for the pair kernel, the odd CTA's half of it) partly or wholly empty, both
+    # element types, fp32 and fp16 C.  Every row must be written, two launches must give the same bits, fp16 C
+    # is the rounded fp32 C.
+    import torch
+    monkeypatch.setenv("B200SPMM_WINDOW", window)
+    rng = np.random.default_rng(int(window))
+    ran = set()
+    for case in range(20):
+        dt = [np.float16, np.float32][rng.integers(2)]
+        rows, cols = int(rng.integers(1, 6000)), int(rng.integers(1, 1200))
+        dens = float(10 ** rng.uniform(-3, -0.7))
+        n = int(rng.choice([64, 128, 136, 192, 256, 264, 320, 520, 776]))
+        dense_rows = sorted(set(int(x) for x in rng.integers(0, rows, int(rng.integers(0, 4)))))
+        empties = []
+        if rows > 600 and rng.random() < 0.6:
+            a = int(rng.integers(0, rows - 32))
+            empties = [(a, min(rows, a + int(rng.integers(1, 900))))]
+        seed = int(rng.integers(1 << 30))
+        c_half = bool(rng.integers(2))
+        rows_, cols_, rp, ci, v = random_csr(rows, cols, dens, seed, dt, empty_rows=empties, dense_rows=dense_rows)
+        B = torch.from_numpy(dense_b(cols, n, seed + 1, dt)).cuda()
+        tag = f"case {case}: {dt.__name__} rows={rows} cols={cols} dens={dens:.4g} n={n} dense={dense_rows} empty={empties} c_half={c_half}"
+        plan = hs.SpmmPlan(hs.CSR2BTCFNOBITMAP(hs.CSR_MTX(rows, cols, rp, ci, v)))
+        try:
+            dC = torch.full((rows, n), float("nan"), device="cuda", dtype=torch.float16 if c_half else torch.float32)
+            plan.spmm(B, dC, c_half=c_half)
+            ran.add(plan.launch_info().row_window)
+            out = dC.float().cpu().numpy()
+            assert np.isfinite(out).all(), tag
+            out32 = plan.spmm(B).cpu().numpy()
+            assert np.array_equal(plan.spmm(B).cpu().numpy().view(np.uint32), out32.view(np.uint32)), tag
+            if c_half:
+                assert np.array_equal(out.astype(np.float16).view(np.uint16), out32.astype(np.float16).view(np.uint16)), tag
+            parity.check(out32, rows, rp, ci, v, B.cpu().numpy())
+        finally:
+            plan.close()
+    assert int(window) in ran
