@@ -104,6 +104,7 @@ SIGNATURES = {
     "b200spmm_spmm_noalloc": (C.c_int, [C.POINTER(BtcfInfo), vp, vp, vp, vp, vp, i64, i64, vp, i64, C.c_int, C.c_int,
                                         C.c_int, vp]),
     "b200spmm_spmm_noalloc_status": (C.c_int, [C.c_int, vp]),
+    "b200spmm_allgather_plan": (C.c_int, [vp, C.c_int, vp, vp]),
     "b200spmm_btcf_transpose_tiles": (C.c_int, [vp]),
     "b200spmm_btcf_tiles_col_major": (C.c_int, [vp]),
     "b200spmm_plan_tall_info": (C.c_int, [vp, C.POINTER(BtcfInfo)]),

@@ -778,6 +778,22 @@ int b200spmm_shard_rows_weighted(uint64_t rows, const uint32_t *row_ptr, int row
     return shard_rows(rows, row_ptr, row_window, parts, row_charge, row_begin);
 }
 
+int b200spmm_allgather_plan(const uint64_t *cut, int n_parts, uint64_t *even_part, uint64_t *pieces) {
+    if (!cut || !even_part || n_parts < 1 || (n_parts > 1 && !pieces)) return B200SPMM_ERR_INVALID_ARG;
+    for (int d = 0; d < n_parts; ++d)
+        if (cut[d + 1] < cut[d]) return B200SPMM_ERR_INVALID_ARG;
+    *even_part = exchange_even_part(cut, n_parts);
+    for (int d = 0; d < n_parts; ++d)
+        for (int step = 1; step < n_parts; ++step) {
+            uint64_t *out = pieces + ((size_t)d * (size_t)(n_parts - 1) + (size_t)(step - 1)) * 10;
+            int to = 0, from = 0;
+            exchange_pieces(cut, n_parts, *even_part, d, step, &to, &from, out + 2);
+            out[0] = (uint64_t)to;
+            out[1] = (uint64_t)from;
+        }
+    return B200SPMM_OK;
+}
+
 int b200spmm_build_schedule(const uint32_t *rowOffset, uint64_t eff_row_windows, int n_ctas, uint32_t *cta_window) {
     if (!rowOffset || !cta_window || n_ctas < 1) return B200SPMM_ERR_INVALID_ARG;
     std::vector<uint32_t> cuts;

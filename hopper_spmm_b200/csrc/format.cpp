@@ -421,4 +421,38 @@ void build_row_bands(const TileSchedule &sc, const uint32_t *rowIdx, uint64_t ro
     b.split.push_back((uint32_t)sc.splits.size());
 }
 
+uint64_t exchange_even_part(const uint64_t *cut, int n) {
+    const uint64_t total = cut[n];
+    bool equal = true;
+    for (int d = 0; d < n; ++d) equal = equal && (cut[d + 1] - cut[d] == cut[1] - cut[0]);
+    if (equal) return cut[1] - cut[0];
+    const uint64_t part = total / (uint64_t)n / 512u * 512u;
+    if (!part) return 0;
+    // does the two-step exchange save the busiest device at least 15 % of its sends?
+    uint64_t longest = 0, outside = 0;
+    for (int d = 0; d < n; ++d) {
+        const uint64_t len = cut[d + 1] - cut[d];
+        const uint64_t lo = std::max(cut[d], part * (uint64_t)d), hi = std::min(cut[d + 1], part * (uint64_t)(d + 1));
+        longest = std::max(longest, len);
+        outside = std::max(outside, len - (hi > lo ? hi - lo : 0));
+    }
+    if ((double)(outside + part * (uint64_t)(n - 1)) * 1.15 >= (double)longest * (double)(n - 1)) return 0;
+    return part;
+}
+
+void exchange_pieces(const uint64_t *cut, int n, uint64_t part, int d, int step, int *to_out, int *from_out, uint64_t out[8]) {
+    const int to = (d + step) % n, from = (d - step + n) % n;  // a different peer for every device at every step
+    const uint64_t whole = part * (uint64_t)n;                 // bytes the all-gather covers; [whole, total) is the tail
+    *to_out = to;
+    *from_out = from;
+    out[0] = std::max(cut[d], part * (uint64_t)to);
+    out[1] = std::min(cut[d + 1], part * (uint64_t)(to + 1));
+    out[2] = std::max(cut[d], whole);
+    out[3] = cut[d + 1];
+    out[4] = std::max(cut[from], part * (uint64_t)d);
+    out[5] = std::min(cut[from + 1], part * (uint64_t)(d + 1));
+    out[6] = std::max(cut[from], whole);
+    out[7] = cut[from + 1];
+}
+
 }  // namespace b200spmm

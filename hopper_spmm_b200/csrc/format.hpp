@@ -90,4 +90,14 @@ struct RowBands {
 };
 void build_row_bands(const TileSchedule &sc, const uint32_t *rowIdx, uint64_t rows, uint32_t want, RowBands *out);
 
+// The all-gather of N byte ranges [cut[d], cut[d+1]) of unequal length (see exchange_ranges in sharded.cu).
+// exchange_even_part: bytes of an even part when the exchange runs in two steps (misplaced bytes to the holder of
+// their even part, then an all-gather of the even parts), the common length when all ranges are equal (the
+// all-gather alone), or 0: every range goes to everybody directly.
+uint64_t exchange_even_part(const uint64_t *cut, int n);
+// Step 1 of device d with its step-th peer pair: it sends to `to` what it holds of to's even part (out[0..1]) and
+// of the tail past n whole parts (out[2..3]), and receives from `from` what that one holds of d's even part
+// (out[4..5]) and of the tail (out[6..7]); a pair lo >= hi is empty.
+void exchange_pieces(const uint64_t *cut, int n, uint64_t part, int d, int step, int *to, int *from, uint64_t out[8]);
+
 }  // namespace b200spmm

@@ -130,43 +130,28 @@ int exchange_ranges(b200spmm_sharded *s, void *const *full, const std::vector<ui
     if (st != B200SPMM_OK) return st;
     const Nccl &n = nccl();
     const int N = s->n_dev;
-    const uint64_t total = cut[N];
     bool equal = true;
     for (int d = 0; d < N; ++d) equal = equal && (cut[d + 1] - cut[d] == cut[1] - cut[0]);
-    uint64_t part = equal ? cut[1] - cut[0] : total / (uint64_t)N / 512u * 512u;
-    if (!equal && part) {  // does the two-step exchange save the busiest device at least 15 % of its sends?
-        uint64_t longest = 0, outside = 0;
-        for (int d = 0; d < N; ++d) {
-            const uint64_t len = cut[d + 1] - cut[d];
-            const uint64_t lo = std::max(cut[d], part * (uint64_t)d), hi = std::min(cut[d + 1], part * (uint64_t)(d + 1));
-            longest = std::max(longest, len);
-            outside = std::max(outside, len - (hi > lo ? hi - lo : 0));
-        }
-        if ((double)(outside + part * (uint64_t)(N - 1)) * 1.15 >= (double)longest * (double)(N - 1)) part = 0;
-    }
+    const uint64_t part = exchange_even_part(cut.data(), N);
     auto fail = [&](ncclResult_t r) {
         n.GroupEnd();
         set_last_error_static(n.GetErrorString(r));
         return B200SPMM_ERR_CUDA;
     };
     if (!equal) {
-        const uint64_t whole = part * (uint64_t)N;  // bytes the all-gather covers; [whole, total) is the tail
         B200_NCCL_TRY(n.GroupStart());
         for (int d = 0; d < N; ++d) {
             char *base = static_cast<char *>(full[d]);
-            for (int step = 1; step < N; ++step) {  // a different peer for every device at every step
-                const int to = (d + step) % N, from = (d - step + N) % N;
-                // what this device holds of `to`'s even part, then what it holds of the tail
-                const uint64_t s_lo = std::max(cut[d], part * (uint64_t)to), s_hi = std::min(cut[d + 1], part * (uint64_t)(to + 1));
-                const uint64_t st_lo = std::max(cut[d], whole), st_hi = cut[d + 1];
-                // what `from` holds of this device's even part, then of the tail (same order as its sends)
-                const uint64_t r_lo = std::max(cut[from], part * (uint64_t)d), r_hi = std::min(cut[from + 1], part * (uint64_t)(d + 1));
-                const uint64_t rt_lo = std::max(cut[from], whole), rt_hi = cut[from + 1];
+            for (int step = 1; step < N; ++step) {
+                int to = 0, from = 0;
+                uint64_t pc[8];
+                exchange_pieces(cut.data(), N, part, d, step, &to, &from, pc);
                 ncclResult_t r = ncclSuccess;
-                if (s_hi > s_lo) r = n.Send(base + s_lo, s_hi - s_lo, ncclChar, to, s->comms[d], s->streams[d]);
-                if (r == ncclSuccess && st_hi > st_lo) r = n.Send(base + st_lo, st_hi - st_lo, ncclChar, to, s->comms[d], s->streams[d]);
-                if (r == ncclSuccess && r_hi > r_lo) r = n.Recv(base + r_lo, r_hi - r_lo, ncclChar, from, s->comms[d], s->streams[d]);
-                if (r == ncclSuccess && rt_hi > rt_lo) r = n.Recv(base + rt_lo, rt_hi - rt_lo, ncclChar, from, s->comms[d], s->streams[d]);
+                // sends and receives of a pair of devices in the same order: even part, then tail
+                if (pc[1] > pc[0]) r = n.Send(base + pc[0], pc[1] - pc[0], ncclChar, to, s->comms[d], s->streams[d]);
+                if (r == ncclSuccess && pc[3] > pc[2]) r = n.Send(base + pc[2], pc[3] - pc[2], ncclChar, to, s->comms[d], s->streams[d]);
+                if (r == ncclSuccess && pc[5] > pc[4]) r = n.Recv(base + pc[4], pc[5] - pc[4], ncclChar, from, s->comms[d], s->streams[d]);
+                if (r == ncclSuccess && pc[7] > pc[6]) r = n.Recv(base + pc[6], pc[7] - pc[6], ncclChar, from, s->comms[d], s->streams[d]);
                 if (r != ncclSuccess) return fail(r);
             }
         }

@@ -173,7 +173,12 @@ int b200spmm_shard_rows_weighted(uint64_t rows, const uint32_t *row_ptr, int row
  *                               devices[p] that already holds shard p's rows in place (let
  *                               b200spmm_spmm_sharded write them there: d_C[p] = d_C_full[p] +
  *                               row_begin[p] * ldc); on return, in stream order, every device holds
- *                               all rows.  One grouped NCCL exchange; the ranges may differ in length.
+ *                               all rows.  The ranges may differ in length: bytes outside their holder's
+ *                               even share first move to the device whose even share they fall into (one
+ *                               grouped send/receive), then NCCL's in-place all-gather of the even shares
+ *                               loads all links alike; where that saves the busiest device less than 15 %
+ *                               of its sends, every range goes to everybody directly.
+ *                               b200spmm_allgather_plan (below) gives the plan for given ranges.
  *   b200spmm_sharded_stream     the cudaStream_t shard p's work is queued on (a non-blocking stream of the
  *                               handle's own: whatever produces d_B / d_C on other streams has to be
  *                               complete, or ordered before this stream, when the calls above are made).
@@ -192,6 +197,17 @@ int b200spmm_spmm_sharded(b200spmm_sharded_t *s, const void *const *d_B, int64_t
 int b200spmm_sharded_sync(b200spmm_sharded_t *s);
 int b200spmm_spmm_sharded_host(b200spmm_sharded_t *s, const void *h_B, int64_t n, void *h_C, int c_dtype);
 int b200spmm_allgather_c(b200spmm_sharded_t *s, void *const *d_C_full, int64_t n, int c_dtype);
+/*
+ * The plan b200spmm_allgather_c follows for byte ranges [cut[p], cut[p+1]), p < n_parts (host arithmetic only;
+ * for callers who run the exchange over a transport of their own, and for tests).  *even_part: bytes of an even
+ * share when the exchange runs in two steps, the common length when all ranges are equal (the all-gather
+ * alone), 0 when every range goes to everybody.  pieces[(p * (n_parts - 1) + step - 1) * 10 ..]: for device p and
+ * step = 1 .. n_parts - 1 the ten numbers {to, from, send lo, send hi, send-tail lo, send-tail hi, receive lo,
+ * receive hi, receive-tail lo, receive-tail hi}: p sends to `to` what it holds of to's even share and of the tail
+ * past n_parts whole shares, and receives the same from `from`; a pair lo >= hi is empty.  After these, the
+ * all-gather of [q * even_part, (q + 1) * even_part) from every q completes the job.
+ */
+int b200spmm_allgather_plan(const uint64_t *cut, int n_parts, uint64_t *even_part, uint64_t *pieces);
 void b200spmm_sharded_destroy(b200spmm_sharded_t *s);
 
 /*

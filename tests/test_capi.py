@@ -3,6 +3,8 @@ import ctypes as C
 import os
 import re
 
+import numpy as np
+
 import pytest
 
 from hopper_spmm_b200 import _capi as capi
@@ -86,3 +88,57 @@ def test_sharded_operator_argument_checks_need_no_device():
     import torch
     if not torch.cuda.is_available():
         assert lib.b200spmm_sharded_create(*args, one, 1, 6, C.byref(out)) == capi.ERR_NO_DEVICE
+
+
+def test_allgather_plan_moves_every_byte_to_every_device():
+    # The plan of the C library's all-gather of unequal ranges, simulated on intervals: after the sends of step 1
+    # (only bytes the sender holds may be sent; a receive must match the peer's send) and the all-gather of the
+    # even shares (every device must hold its own share by then), every device holds every byte.  Crafted and
+    # seeded random ranges, byte counts around the 512-byte rounding of the shares.
+    rng = np.random.default_rng(5)
+    cases = [[0, 10, 20], [0, 0, 7], [0, 4096, 4096 * 8], [0, 100, 300, 5000, 100000], [0, 512 * 3, 512 * 3, 512 * 9 + 5],
+             [0, 1 << 20, 3 << 20, 9 << 20, 10 << 20, 11 << 20, 20 << 20, 21 << 20, 64 << 20]]
+    for _ in range(60):
+        n = int(rng.integers(2, 9))
+        total = int(rng.integers(1, 1 << int(rng.integers(4, 24))))
+        cases.append([0] + sorted(int(x) for x in rng.integers(0, total + 1, n - 1)) + [total])
+    two_step = 0
+    for cut in cases:
+        n = len(cut) - 1
+        c = np.asarray(cut, np.uint64)
+        part = C.c_uint64()
+        pieces = np.zeros((n, n - 1, 10), np.uint64)
+        assert capi.lib().b200spmm_allgather_plan(c.ctypes.data, n, C.byref(part), pieces.ctypes.data) == capi.OK
+        part = int(part.value)
+        total = cut[-1]
+        have = [np.zeros(total, bool) for _ in range(n)]
+        for d in range(n):
+            have[d][cut[d]:cut[d + 1]] = True
+        sends = {}
+        for d in range(n):
+            for k in range(n - 1):
+                to, frm, s_lo, s_hi, t_lo, t_hi = (int(x) for x in pieces[d, k, :6])
+                assert to == (d + k + 1) % n and frm == (d - k - 1) % n
+                for lo, hi in ((s_lo, s_hi), (t_lo, t_hi)):
+                    if hi > lo:
+                        assert cut[d] <= lo and hi <= cut[d + 1], "a device sends only what it holds"
+                sends[(d, to)] = ((s_lo, s_hi), (t_lo, t_hi))
+        for d in range(n):
+            for k in range(n - 1):
+                frm = int(pieces[d, k, 1])
+                got = tuple((int(pieces[d, k, 6 + 2 * i]), int(pieces[d, k, 7 + 2 * i])) for i in range(2))
+                want = sends[(frm, d)]
+                for (lo, hi), (wlo, whi) in zip(got, want):
+                    assert (hi > lo) == (whi > wlo) and (hi <= lo or (lo, hi) == (wlo, whi)), "a receive matches the peer's send"
+                    if hi > lo:
+                        have[d][lo:hi] = True
+        if part:
+            two_step += 1
+            assert part * n <= total
+            for q in range(n):
+                assert have[q][part * q:part * (q + 1)].all(), "every device holds its even share before the all-gather"
+            for d in range(n):
+                have[d][:part * n] = True
+        for d in range(n):
+            assert have[d].all(), (cut, part)
+    assert 0 < two_step < len(cases)

@@ -47,6 +47,11 @@ def _worker(rank, world, port, out_dir):
         # sends), an empty slice, a remainder past the whole even parts
         cases = {2: [[0, 500, 1000], [0, 100, 1000], [0, 0, 7], [0, 999, 1001]],
                  3: [[0, 333, 666, 999], [0, 50, 120, 1000], [0, 400, 400, 1001], [0, 1, 2, 5]]}[world]
+        rng = np.random.default_rng(world)  # ... and twenty seeded random cut sets, the same on every rank
+        for _ in range(20):
+            total = int(rng.integers(1, 3000))
+            inner = np.sort(rng.integers(0, total + 1, world - 1)) if rng.random() < 0.7 else np.sort(rng.choice([0, total], world - 1))
+            cases.append([0] + [int(x) for x in inner] + [total])
         took_two_steps = []
         for cc in cases:
             rows_all = torch.arange(cc[-1] * 4, dtype=torch.float32).reshape(cc[-1], 4)
