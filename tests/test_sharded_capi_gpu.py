@@ -69,3 +69,40 @@ def test_shards_on_several_devices_give_the_one_device_result(n_dev):
             assert np.array_equal(Cs[d].cpu().numpy().view(np.uint32), got.view(np.uint32)), d
     finally:
         sh.close()
+
+
+@pytest.mark.parametrize("n_dev", [4, 8])
+def test_allgather_of_skewed_ranges_runs_in_two_steps(n_dev):
+    # Rows whose weight decays fast: the shards are cut for equal work, so the last one holds most of the rows and
+    # the all-gather of C must take its two-step form (misplaced bytes to the holder of their even share, then the
+    # in-place all-gather of the even shares).  Every device must end up with the whole product.
+    if _n_devices() < n_dev:
+        pytest.skip(f"needs {n_dev} devices")
+    import ctypes as C
+    import torch
+    from hopper_spmm_b200 import _capi as capi
+    rows, cols, n = 40000, 2000, 256
+    rng = np.random.default_rng(0)
+    deg = np.maximum(1, (1500 * np.exp(-np.arange(rows) / 1200.0)).astype(np.int64))
+    rp = np.concatenate([[0], np.cumsum(deg)]).astype(np.uint32)
+    ci = np.concatenate([np.sort(rng.choice(cols, d, replace=False)) for d in deg]).astype(np.uint32)
+    v = rng.uniform(-1, 1, ci.size).astype(np.float32).astype(np.float16)
+    B = dense_b(cols, n, 1)
+    sh = hs.ShardedSpmm(hs.CSR_MTX(rows, cols, rp, ci, v), list(range(n_dev)), row_charge=0)
+    try:
+        cut = np.asarray(sh.row_begin, np.uint64) * np.uint64(n * 4)
+        part = C.c_uint64()
+        pieces = np.zeros((n_dev, n_dev - 1, 10), np.uint64)
+        assert capi.lib().b200spmm_allgather_plan(cut.ctypes.data, n_dev, C.byref(part), pieces.ctypes.data) == capi.OK
+        assert part.value > 0, f"expected the two-step exchange for row ranges {list(sh.row_begin)}"
+        Bs = [torch.from_numpy(B).to(f"cuda:{d}") for d in range(n_dev)]
+        Cs = [torch.full((rows, n), float("nan"), device=f"cuda:{d}") for d in range(n_dev)]
+        for d in range(n_dev):
+            torch.cuda.synchronize(d)
+        sh.spmm_allgather(Bs, Cs)
+        first = Cs[0].cpu().numpy()
+        parity.check(first, rows, rp, ci, v, B)
+        for d in range(1, n_dev):
+            assert np.array_equal(Cs[d].cpu().numpy().view(np.uint32), first.view(np.uint32)), d
+    finally:
+        sh.close()
