@@ -27,6 +27,7 @@ oracle/, is what can run on the host cores).
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import subprocess
@@ -277,6 +278,11 @@ def graph_replay_ms(plan, B, C_dev, steps):
         return None
 
 
+def capi_mod():
+    from hopper_spmm_b200 import _capi
+    return _capi
+
+
 def run_other_workload(name, dev, steps, warmup, hbm_gbs, f16_tflops, tf32_tflops, peak_kind, flush_buf):
     """One of the smaller configurations at full size on one GPU: time (L2 flushed between the timed
     launches), roofline, CPU baseline, and the timed result checked whole against the CPU oracle."""
@@ -328,6 +334,18 @@ def run_other_workload(name, dev, steps, warmup, hbm_gbs, f16_tflops, tf32_tflop
                       "stages": info.stages, "launches_per_step": int(info.kernel_launches),
                       "row_window": int(getattr(info, "row_window", 16) or 16)},
            "graph_replay_ms": graph_replay_ms(plan, B, C_dev, steps) if ms_hot < 0.2 else None}
+    # executed MMA work: every tile of the kernel that ran is a dense (window rows x CW) block times all features
+    win = rec["kernel"]["row_window"]
+    if win == 16:
+        ex_tiles = int(btcf.total_tiles)
+    else:
+        lib = capi_mod().lib()
+        tinfo = capi_mod().BtcfInfo()
+        getattr(lib, "b200spmm_plan_tall_info" if win == 128 else "b200spmm_plan_pair_info")(plan._p, ctypes.byref(tinfo))
+        ex_tiles = int(tinfo.total_tiles)
+    slab = int(info.feature_slab)
+    rec["executed_mma_gflop"] = 2.0 * ex_tiles * win * btcf.col_window * (int(info.n_slabs) * slab) / 1e9
+    rec["executed_mma_tflops"] = rec["executed_mma_gflop"] / ms
     rp, ci, v = csr.numpy()
     B_host = B.cpu().numpy()
     got = C_dev.cpu().numpy()
