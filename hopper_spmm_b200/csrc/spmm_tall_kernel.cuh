@@ -69,6 +69,51 @@ struct TallParams {
 #endif
 };
 
+// A thread's 32 consecutive features (fp32 bits, feat0 ..) of row `row` -> C, as 16-byte vectors: 8 features per
+// store for fp16 C, 4 for fp32 C (n is a multiple of 8).  Rows past the end and features past n are dropped.
+B200_DEVICE void tall_store_row32(const TallParams &p, uint32_t row, uint32_t feat0, const uint32_t (&r)[32]) {
+    if (row >= p.rows || feat0 >= p.n) return;
+    if (p.c_is_half) {
+        __half *dst = static_cast<__half *>(p.C) + (int64_t)row * p.ldc + feat0;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            if (feat0 + v * 8 < p.n) {
+                uint4 pk;
+                __half2 h0 = __floats2half2_rn(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                __half2 h1 = __floats2half2_rn(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                __half2 h2 = __floats2half2_rn(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                __half2 h3 = __floats2half2_rn(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                pk.x = *reinterpret_cast<uint32_t *>(&h0);
+                pk.y = *reinterpret_cast<uint32_t *>(&h1);
+                pk.z = *reinterpret_cast<uint32_t *>(&h2);
+                pk.w = *reinterpret_cast<uint32_t *>(&h3);
+                *reinterpret_cast<uint4 *>(dst + v * 8) = pk;
+            }
+        }
+    } else {
+        float *dst = static_cast<float *>(p.C) + (int64_t)row * p.ldc + feat0;
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+            if (feat0 + v * 4 < p.n)
+                *reinterpret_cast<uint4 *>(dst + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+    }
+}
+
+// Zeros into rows [lo, hi) of C, features [f0, f0 + feats): warp `who` of `of` takes every of-th row.
+B200_DEVICE void tall_clear_rows(const TallParams &p, uint32_t lo, uint32_t hi, uint32_t who, uint32_t of, uint32_t f0,
+                                 uint32_t feats, int lane) {
+    const uint32_t vec_per_row = feats / 4;
+    for (uint32_t rr = lo + who; rr < hi; rr += of) {
+        for (uint32_t v4 = lane; v4 < vec_per_row; v4 += 32) {
+            const uint32_t feat = f0 + v4 * 4;
+            if (p.c_is_half)
+                *reinterpret_cast<uint2 *>(static_cast<__half *>(p.C) + (int64_t)rr * p.ldc + feat) = make_uint2(0, 0);
+            else
+                *reinterpret_cast<float4 *>(static_cast<float *>(p.C) + (int64_t)rr * p.ldc + feat) = make_float4(0, 0, 0, 0);
+        }
+    }
+}
+
 template <bool kTf32, int kNs>
 struct TallCfg {
     static_assert(kNs == 128 || kNs == 256, "feature slab");
@@ -215,32 +260,7 @@ spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_consta
                     if (lane == 0) ptx::mbar_arrive(acc_empty_bar(a));
                 }
                 const uint32_t feat0 = f_slab + col0;  // this thread: features feat0 .. feat0 + 31 of its row
-                if (row < p.rows && feat0 < p.n) {
-                    if (p.c_is_half) {
-                        __half *dst = static_cast<__half *>(p.C) + (int64_t)row * p.ldc + feat0;
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {  // 8 features = 16 bytes per store (n is a multiple of 8)
-                            if (feat0 + v * 8 < p.n) {
-                                uint4 pk;
-                                __half2 h0 = __floats2half2_rn(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-                                __half2 h1 = __floats2half2_rn(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-                                __half2 h2 = __floats2half2_rn(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-                                __half2 h3 = __floats2half2_rn(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-                                pk.x = *reinterpret_cast<uint32_t *>(&h0);
-                                pk.y = *reinterpret_cast<uint32_t *>(&h1);
-                                pk.z = *reinterpret_cast<uint32_t *>(&h2);
-                                pk.w = *reinterpret_cast<uint32_t *>(&h3);
-                                *reinterpret_cast<uint4 *>(dst + v * 8) = pk;
-                            }
-                        }
-                    } else {
-                        float *dst = static_cast<float *>(p.C) + (int64_t)row * p.ldc + feat0;
-#pragma unroll
-                        for (int v = 0; v < 8; ++v)  // 4 features = 16 bytes per store
-                            if (feat0 + v * 4 < p.n)
-                                *reinterpret_cast<uint4 *>(dst + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
-                    }
-                }
+                tall_store_row32(p, row, feat0, r);
             }
             // Rows of super-windows without entries are absent from the format: clear the gap after this
             // window (and the rows before the very first one), this slab's features.  Warp w takes every
@@ -248,20 +268,8 @@ spmm_tall_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_consta
             const bool lead = w == 0 && row0 > 0;
             if (gap_hi > row0 + kTallRows || lead) {
                 const uint32_t slab_feats = min((uint32_t)kNs, p.n - f_slab);
-                const uint32_t vec_per_row = slab_feats / 4;
-                for (int pass = 0; pass < 2; ++pass) {
-                    const uint32_t lo = pass == 0 ? row0 + kTallRows : 0u;
-                    const uint32_t hi = pass == 0 ? min(gap_hi, p.rows) : (lead ? row0 : 0u);
-                    for (uint32_t rr = lo + (uint32_t)warp; rr < hi; rr += Cfg::kEpilogueWarps) {
-                        for (uint32_t v4 = lane; v4 < vec_per_row; v4 += 32) {
-                            const uint32_t feat = f_slab + v4 * 4;
-                            if (p.c_is_half)
-                                *reinterpret_cast<uint2 *>(static_cast<__half *>(p.C) + (int64_t)rr * p.ldc + feat) = make_uint2(0, 0);
-                            else
-                                *reinterpret_cast<float4 *>(static_cast<float *>(p.C) + (int64_t)rr * p.ldc + feat) = make_float4(0, 0, 0, 0);
-                        }
-                    }
-                }
+                tall_clear_rows(p, row0 + kTallRows, min(gap_hi, p.rows), (uint32_t)warp, Cfg::kEpilogueWarps, f_slab, slab_feats, lane);
+                if (lead) tall_clear_rows(p, 0u, row0, (uint32_t)warp, Cfg::kEpilogueWarps, f_slab, slab_feats, lane);
             }
         }
     } else if (warp >= Cfg::kFirstProducerWarp) {
